@@ -1,0 +1,182 @@
+// Shared device helpers for the dgnn_b200 kernels (sm_100a).
+//
+// Scheduling model used by every per-row (or per-column) operator in this
+// library: rows whose degree is at most SEG edges are handled by one warp each
+// (k_rows).  Longer rows are cut at the global edge positions that are
+// multiples of SEG; every (chunk, row) piece is handled by one warp (k_chunks)
+// that writes a partial state to a workspace slot, and one warp per long row
+// (k_merge) folds the partials in edge order.  A chunk of SEG edges can meet at
+// most two long rows -- one that began before the chunk (slot 0) and one that
+// begins inside it (slot 1) -- so the workspace needs 2 * ceil(nnz / SEG)
+// slots and no atomics, and the result does not depend on scheduling.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/dgnn_b200.h"
+
+typedef long long i64;
+
+#define DGNN_FULL 0xffffffffu
+constexpr int DGNN_SEG = 1024;         // edges per chunk for long-row splitting
+constexpr int DGNN_WARPS = 8;          // warps per CTA in the row kernels
+constexpr int DGNN_THREADS = DGNN_WARPS * 32;
+constexpr float DGNN_NEG_INIT = -1e38f;  // initial running maximum (matches the reference)
+
+// index-pointer arrays come as int32 or int64; the width is uniform per launch
+__device__ __forceinline__ i64 ldp(const void* p, int bits, i64 i) {
+  return bits == 64 ? __ldg(reinterpret_cast<const i64*>(p) + i)
+                    : (i64)__ldg(reinterpret_cast<const int*>(p) + i);
+}
+
+// row r with indptr[r] <= pos < indptr[r+1]; requires 0 <= pos < indptr[n_rows]
+__device__ __forceinline__ i64 find_row(const void* indptr, int bits, i64 n_rows, i64 pos) {
+  i64 lo = 0, hi = n_rows;
+  while (hi - lo > 1) {
+    i64 mid = (lo + hi) >> 1;
+    if (ldp(indptr, bits, mid) <= pos) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float4 ld4(const float4* p) { return __ldg(p); }
+__device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ void fma4(float4& acc, float w, const float4& x) {
+  acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
+  acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+}
+__device__ __forceinline__ void scale4(float4& a, float s) { a.x *= s; a.y *= s; a.z *= s; a.w *= s; }
+__device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+__device__ __forceinline__ float dot4(const float4& a, const float4& b) {
+  return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
+}
+__device__ __forceinline__ float leaky(float x, float slope) { return x > 0.f ? x : x * slope; }
+
+// Feature rows are H*F floats viewed as HF4 = H*F/4 float4 vectors.  Lane l owns
+// vectors q = l + 32*v (v < VPL); vector q belongs to head q >> f4_shift where
+// 2^f4_shift = F/4 vectors per head.
+template <int VPL>
+struct LaneMap {
+  int q[VPL];
+  int hd[VPL];
+  bool act[VPL];
+  bool lead[VPL];  // first vector of its head: writes the per-head scalars
+  __device__ __forceinline__ void init(int lane, int hf4, int f4_shift) {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      q[v] = lane + 32 * v;
+      act[v] = q[v] < hf4;
+      hd[v] = act[v] ? (q[v] >> f4_shift) : 0;
+      lead[v] = act[v] && ((q[v] & ((1 << f4_shift) - 1)) == 0);
+    }
+  }
+};
+
+// Sum p[v] over all vectors of the same head; every lane of the head ends with
+// the total.  All 32 lanes must call it.
+template <int VPL>
+__device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
+  const int span = f4_shift < 5 ? (1 << f4_shift) : 32;
+  for (int o = 1; o < span; o <<= 1) {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) p[v] += __shfl_xor_sync(DGNN_FULL, p[v], o);
+  }
+  if (f4_shift > 5) {
+    const int g = 1 << (f4_shift - 5);  // vector slots per head
+#pragma unroll
+    for (int s = 1; s < VPL; s <<= 1) {
+      if (s < g) {
+        float t[VPL];
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) t[v] = p[v] + p[v ^ s];
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) p[v] = t[v];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// the three scheduling kernels, generic over an operator object
+// Op must provide: n_rows, nnz, indptr, idx_bits, struct State,
+//   init(State&, row, lane), range(State&, row, e0, e1, lane),
+//   finalize(State&, row, lane), store_partial(State&, slot, lane),
+//   merge_partial(State&, slot, lane)
+// ---------------------------------------------------------------------------
+template <class Op>
+__global__ void __launch_bounds__(DGNN_THREADS) k_rows(const Op op) {
+  const int lane = threadIdx.x & 31;
+  const i64 r = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  if (r >= op.n_rows) return;
+  const i64 lb = ldp(op.indptr, op.idx_bits, r);
+  const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
+  if (hb - lb > DGNN_SEG) return;  // long row: chunk + merge kernels own it
+  typename Op::State st;
+  op.init(st, r, lane);
+  op.range(st, r, lb, hb, lane);
+  op.finalize(st, r, lane);
+}
+
+template <class Op>
+__global__ void __launch_bounds__(DGNN_THREADS) k_chunks(const Op op) {
+  const int lane = threadIdx.x & 31;
+  const i64 w = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  const i64 j = w >> 1;
+  const int slot = (int)(w & 1);
+  const i64 cs = j * DGNN_SEG;
+  if (cs >= op.nnz) return;
+  const i64 ce = (cs + DGNN_SEG < op.nnz) ? cs + DGNN_SEG : op.nnz;
+  const i64 r = find_row(op.indptr, op.idx_bits, op.n_rows, slot ? ce - 1 : cs);
+  const i64 lb = ldp(op.indptr, op.idx_bits, r);
+  const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
+  if (hb - lb <= DGNN_SEG) return;
+  if (slot == 0 ? (lb >= cs) : (lb < cs)) return;
+  typename Op::State st;
+  op.init(st, r, lane);
+  op.range(st, r, lb > cs ? lb : cs, hb < ce ? hb : ce, lane);
+  op.store_partial(st, 2 * j + slot, lane);
+}
+
+template <class Op>
+__global__ void __launch_bounds__(DGNN_THREADS) k_merge(const Op op) {
+  const int lane = threadIdx.x & 31;
+  const i64 j = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  const i64 cs = j * DGNN_SEG;
+  if (cs >= op.nnz) return;
+  const i64 ce = (cs + DGNN_SEG < op.nnz) ? cs + DGNN_SEG : op.nnz;
+  const i64 r = find_row(op.indptr, op.idx_bits, op.n_rows, ce - 1);
+  const i64 lb = ldp(op.indptr, op.idx_bits, r);
+  const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
+  if (hb - lb <= DGNN_SEG || lb < cs) return;  // the long row that begins in this chunk
+  typename Op::State st;
+  op.init(st, r, lane);
+  op.merge_partial(st, 2 * j + 1, lane);
+  for (i64 jj = j + 1; jj * DGNN_SEG < hb; ++jj) op.merge_partial(st, 2 * jj, lane);
+  op.finalize(st, r, lane);
+}
+
+static inline unsigned dgnn_grid(i64 items, int per_block) {
+  i64 g = (items + per_block - 1) / per_block;
+  return (unsigned)(g < 1 ? 1 : g);
+}
+static inline i64 dgnn_num_chunks(i64 nnz) { return (nnz + DGNN_SEG - 1) / DGNN_SEG; }
+
+// launch the row / chunk / merge trio for one operator
+template <class Op>
+static inline int dgnn_launch_trio(const Op& op, bool has_partials, cudaStream_t s) {
+  if (op.n_rows <= 0) return DGNN_OK;
+  k_rows<Op><<<dgnn_grid(op.n_rows, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
+  if (op.nnz > DGNN_SEG) {
+    const i64 nc = dgnn_num_chunks(op.nnz);
+    k_chunks<Op><<<dgnn_grid(2 * nc, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
+    if (has_partials) k_merge<Op><<<dgnn_grid(nc, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+static inline int ilog2_exact(int x) {  // -1 unless x is a power of two
+  if (x <= 0 || (x & (x - 1))) return -1;
+  int s = 0;
+  while ((1 << s) < x) ++s;
+  return s;
+}

@@ -1,0 +1,333 @@
+// CSR -> CSC conversion and COO -> CSR for sm_100a, bit-exact and deterministic.
+//
+// csr2csc is a stable least-significant-digit radix sort of the CSR entries by
+// column id (8-bit digits over ceil(log2(n_cols)) bits), carrying the CSR
+// position (-> permute) and the row id (-> row_ind) as payload.  Each pass is
+// histogram per tile -> exclusive scan over (digit, tile) -> stable scatter;
+// ranks inside a tile come from warp match_any votes taken in index order, so
+// entries of one column keep their CSR order exactly as the reference's
+// cuSPARSE conversion (and scipy's tocsc) produce.  col_ptr is the exclusive
+// scan of the column histogram.  Only integer atomics (commutative) are used.
+#include "common.cuh"
+
+namespace {
+
+constexpr int RS_THREADS = 256;
+constexpr int RS_IPT = 16;                       // items per thread
+constexpr int RS_TILE = RS_THREADS * RS_IPT;     // 4096 items per tile
+constexpr int RS_WARPS = RS_THREADS / 32;
+constexpr int RS_WARP_ITEMS = 32 * RS_IPT;       // consecutive items owned by one warp
+constexpr int RADIX = 256;
+
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_IPT = 8;
+constexpr int SCAN_TILE = SCAN_THREADS * SCAN_IPT;  // 2048
+
+inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
+inline i64 cdiv(i64 a, i64 b) { return (a + b - 1) / b; }
+
+// ---- exclusive scan of unsigned ints (three-phase, recursive on the host) ----
+__device__ __forceinline__ unsigned block_exclusive_scan(unsigned v, unsigned* total, unsigned* sm /*[32]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned inc = v;
+  for (int o = 1; o < 32; o <<= 1) {
+    unsigned t = __shfl_up_sync(DGNN_FULL, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) sm[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned w = lane < (int)(blockDim.x >> 5) ? sm[lane] : 0u;
+    unsigned winc = w;
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned t = __shfl_up_sync(DGNN_FULL, winc, o);
+      if (lane >= o) winc += t;
+    }
+    sm[lane] = winc - w;  // exclusive warp offsets
+    if (lane == 31) *total = winc;
+  }
+  __syncthreads();
+  const unsigned r = sm[warp] + inc - v;
+  __syncthreads();
+  return r;
+}
+
+// data[i] <- exclusive scan inside its tile; sums[tile] <- tile total
+__global__ void __launch_bounds__(SCAN_THREADS)
+k_scan_tiles(unsigned* data, i64 n, unsigned* sums) {
+  __shared__ unsigned sm[32];
+  __shared__ unsigned total;
+  const i64 base = (i64)blockIdx.x * SCAN_TILE + (i64)threadIdx.x * SCAN_IPT;
+  unsigned v[SCAN_IPT];
+  unsigned s = 0;
+#pragma unroll
+  for (int i = 0; i < SCAN_IPT; ++i) {
+    v[i] = (base + i < n) ? data[base + i] : 0u;
+    s += v[i];
+  }
+  unsigned off = block_exclusive_scan(s, &total, sm);
+#pragma unroll
+  for (int i = 0; i < SCAN_IPT; ++i) {
+    if (base + i < n) data[base + i] = off;
+    off += v[i];
+  }
+  if (threadIdx.x == 0 && sums) sums[blockIdx.x] = total;
+}
+
+__global__ void k_scan_add(unsigned* data, i64 n, const unsigned* sums) {
+  const i64 i = (i64)blockIdx.x * SCAN_TILE + threadIdx.x;
+  const unsigned add = sums[blockIdx.x];
+#pragma unroll
+  for (int j = 0; j < SCAN_IPT; ++j) {
+    const i64 p = i + (i64)j * SCAN_THREADS;
+    if (p < n) data[p] += add;
+  }
+}
+
+// number of scratch uints the recursive scan of n items needs
+inline i64 scan_scratch_items(i64 n) {
+  i64 total = 0;
+  while (n > SCAN_TILE) {
+    n = cdiv(n, SCAN_TILE);
+    total += up256((size_t)n * 4) / 4;
+  }
+  return total + 64;
+}
+
+// in-place exclusive scan of data[0..n); scratch as sized above
+int exclusive_scan(unsigned* data, i64 n, unsigned* scratch, cudaStream_t s) {
+  if (n <= 0) return DGNN_OK;
+  const i64 tiles = cdiv(n, SCAN_TILE);
+  if (tiles == 1) {
+    k_scan_tiles<<<1, SCAN_THREADS, 0, s>>>(data, n, nullptr);
+    return DGNN_OK;
+  }
+  unsigned* sums = scratch;
+  unsigned* next = scratch + up256((size_t)tiles * 4) / 4;
+  k_scan_tiles<<<(unsigned)tiles, SCAN_THREADS, 0, s>>>(data, n, sums);
+  int rc = exclusive_scan(sums, tiles, next, s);
+  if (rc) return rc;
+  k_scan_add<<<(unsigned)tiles, SCAN_THREADS, 0, s>>>(data, n, sums);
+  return DGNN_OK;
+}
+
+// ---- column histogram -> col_ptr ------------------------------------------
+__global__ void k_col_hist(i64 nnz, const int* col_ind, unsigned* hist) {
+  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < nnz) atomicAdd(hist + __ldg(col_ind + t), 1u);
+}
+__global__ void k_write_ptr(i64 n_plus_1, const unsigned* scanned, void* out, int bits) {
+  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_plus_1) return;
+  if (bits == 64) reinterpret_cast<i64*>(out)[t] = (i64)scanned[t];
+  else reinterpret_cast<int*>(out)[t] = (int)scanned[t];
+}
+
+// ---- radix passes -----------------------------------------------------------
+// tile_hist layout: [digit][tile]
+__global__ void __launch_bounds__(RS_THREADS)
+k_radix_hist(const unsigned* keys, i64 n, int shift, unsigned* tile_hist, i64 ntiles) {
+  __shared__ unsigned h[RADIX];
+  h[threadIdx.x] = 0;
+  __syncthreads();
+  const i64 base = (i64)blockIdx.x * RS_TILE;
+#pragma unroll
+  for (int i = 0; i < RS_IPT; ++i) {
+    const i64 idx = base + (i64)i * RS_THREADS + threadIdx.x;
+    if (idx < n) atomicAdd(&h[(__ldg(keys + idx) >> shift) & (RADIX - 1)], 1u);
+  }
+  __syncthreads();
+  tile_hist[(i64)threadIdx.x * ntiles + blockIdx.x] = h[threadIdx.x];
+}
+
+// FIRST: keys are the CSR column ids, payload (position,row) is generated here.
+// LAST: keys are not written.
+template <bool FIRST, bool LAST>
+__global__ void __launch_bounds__(RS_THREADS)
+k_radix_scatter(const unsigned* keys_in, const int* pos_in, const int* row_in, unsigned* keys_out,
+                int* pos_out, int* row_out, i64 n, int shift, const unsigned* tile_off, i64 ntiles,
+                const void* row_ptr, int idx_bits, i64 n_rows) {
+  __shared__ unsigned cnt[RS_WARPS][RADIX];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < RS_WARPS * RADIX; i += RS_THREADS) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+  const i64 wbase = (i64)blockIdx.x * RS_TILE + (i64)warp * RS_WARP_ITEMS;
+  unsigned key[RS_IPT];
+  unsigned rank[RS_IPT];
+#pragma unroll
+  for (int t = 0; t < RS_IPT; ++t) {
+    const i64 idx = wbase + t * 32 + lane;
+    const bool valid = idx < n;
+    key[t] = valid ? __ldg(keys_in + idx) : 0u;
+    const unsigned d = (key[t] >> shift) & (RADIX - 1);
+    const unsigned peers = __match_any_sync(DGNN_FULL, valid ? d : (unsigned)RADIX);
+    const int leader = __ffs(peers) - 1;
+    unsigned base = 0;
+    if (lane == leader && valid) {
+      base = cnt[warp][d];
+      cnt[warp][d] = base + __popc(peers);
+    }
+    base = __shfl_sync(DGNN_FULL, base, leader);
+    rank[t] = base + __popc(peers & ((1u << lane) - 1u));
+    __syncwarp();
+  }
+  __syncthreads();
+  {  // per digit: exclusive prefix over the warps of this tile + global tile offset
+    const int d = threadIdx.x;
+    unsigned run = tile_off[(i64)d * ntiles + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < RS_WARPS; ++w) {
+      const unsigned c = cnt[w][d];
+      cnt[w][d] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  // row of the first / last entry this warp owns (FIRST pass only)
+  i64 r_lo = 0, r_hi = 0;
+  if (FIRST && wbase < n) {
+    const i64 last = (wbase + RS_WARP_ITEMS <= n ? wbase + RS_WARP_ITEMS : n) - 1;
+    r_lo = find_row(row_ptr, idx_bits, n_rows, wbase);
+    r_hi = find_row(row_ptr, idx_bits, n_rows, last);
+  }
+#pragma unroll
+  for (int t = 0; t < RS_IPT; ++t) {
+    const i64 idx = wbase + t * 32 + lane;
+    if (idx >= n) continue;
+    const unsigned d = (key[t] >> shift) & (RADIX - 1);
+    const i64 dst = (i64)cnt[warp][d] + rank[t];
+    int pos, row;
+    if (FIRST) {
+      pos = (int)idx;
+      i64 lo = r_lo, hi = r_hi + 1;  // row_ptr[lo] <= idx < row_ptr[hi]
+      while (hi - lo > 1) {
+        const i64 mid = (lo + hi) >> 1;
+        if (ldp(row_ptr, idx_bits, mid) <= idx) lo = mid; else hi = mid;
+      }
+      row = (int)lo;
+    } else {
+      pos = __ldg(pos_in + idx);
+      row = __ldg(row_in + idx);
+    }
+    if (!LAST) keys_out[dst] = key[t];
+    pos_out[dst] = pos;
+    row_out[dst] = row;
+  }
+}
+
+__global__ void k_coo2csr(i64 nnz, i64 m, const int* row_ind, void* row_ptr, int bits) {
+  const i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > m) return;
+  i64 lo = 0, hi = nnz;  // first position whose row id is >= i
+  while (lo < hi) {
+    const i64 mid = (lo + hi) >> 1;
+    if ((i64)__ldg(row_ind + mid) < i) lo = mid + 1; else hi = mid;
+  }
+  if (bits == 64) reinterpret_cast<i64*>(row_ptr)[i] = lo;
+  else reinterpret_cast<int*>(row_ptr)[i] = (int)lo;
+}
+
+struct C2CLayout {
+  size_t col_hist, tile_hist, scan_scratch, keys[2], pos[2], row[2], total;
+  i64 ntiles;
+  int passes;
+};
+inline C2CLayout c2c_layout(i64 n_cols, i64 nnz) {
+  C2CLayout L;
+  int bits = 1;
+  while (((i64)1 << bits) < n_cols) ++bits;
+  L.passes = (bits + 7) / 8;
+  L.ntiles = cdiv(nnz > 0 ? nnz : 1, RS_TILE);
+  const i64 hist_items = (i64)RADIX * L.ntiles;
+  const i64 scan_items = hist_items > n_cols + 1 ? hist_items : n_cols + 1;
+  size_t off = 0;
+  L.col_hist = off;     off += up256((size_t)(n_cols + 1) * 4);
+  L.tile_hist = off;    off += up256((size_t)hist_items * 4);
+  L.scan_scratch = off; off += up256((size_t)scan_scratch_items(scan_items) * 4);
+  for (int i = 0; i < 2; ++i) {
+    const bool need = L.passes > i + 1;  // passes-1 intermediate buffers, at most 2 alive
+    L.keys[i] = off; off += need ? up256((size_t)nnz * 4) : 0;
+    L.pos[i] = off;  off += need ? up256((size_t)nnz * 4) : 0;
+    L.row[i] = off;  off += need ? up256((size_t)nnz * 4) : 0;
+  }
+  L.total = off + 256;
+  return L;
+}
+
+}  // namespace
+
+// implementation shared with the allocation-free entry point
+int dgnn_csr2csc_impl(i64 n_rows, i64 n_cols, i64 nnz, const void* row_ptr, int idx_bits,
+                      const int32_t* col_ind, void* col_ptr, int32_t* row_ind, int32_t* permute,
+                      char* wsb, cudaStream_t s) {
+  const C2CLayout L = c2c_layout(n_cols, nnz);
+  unsigned* col_hist = reinterpret_cast<unsigned*>(wsb + L.col_hist);
+  unsigned* tile_hist = reinterpret_cast<unsigned*>(wsb + L.tile_hist);
+  unsigned* scratch = reinterpret_cast<unsigned*>(wsb + L.scan_scratch);
+  cudaError_t e = cudaMemsetAsync(col_hist, 0, (size_t)(n_cols + 1) * 4, s);
+  if (e != cudaSuccess) return (int)e;
+  if (nnz > 0) k_col_hist<<<dgnn_grid(nnz, 256), 256, 0, s>>>(nnz, col_ind, col_hist);
+  int rc = exclusive_scan(col_hist, n_cols + 1, scratch, s);
+  if (rc) return rc;
+  k_write_ptr<<<dgnn_grid(n_cols + 1, 256), 256, 0, s>>>(n_cols + 1, col_hist, col_ptr, idx_bits);
+  if (nnz > 0) {
+    const unsigned* kin = reinterpret_cast<const unsigned*>(col_ind);
+    const int* pin = nullptr;
+    const int* rin = nullptr;
+    const unsigned grid = (unsigned)L.ntiles;
+    for (int p = 0; p < L.passes; ++p) {
+      const bool first = p == 0, last = p == L.passes - 1;
+      const int shift = 8 * p;
+      unsigned* kout = last ? nullptr : reinterpret_cast<unsigned*>(wsb + L.keys[p & 1]);
+      int* pout = last ? permute : reinterpret_cast<int*>(wsb + L.pos[p & 1]);
+      int* rout = last ? row_ind : reinterpret_cast<int*>(wsb + L.row[p & 1]);
+      k_radix_hist<<<grid, RS_THREADS, 0, s>>>(kin, nnz, shift, tile_hist, L.ntiles);
+      rc = exclusive_scan(tile_hist, (i64)RADIX * L.ntiles, scratch, s);
+      if (rc) return rc;
+#define RS_ARGS kin, pin, rin, kout, pout, rout, nnz, shift, tile_hist, L.ntiles, row_ptr, idx_bits, n_rows
+      if (first && last) k_radix_scatter<true, true><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
+      else if (first) k_radix_scatter<true, false><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
+      else if (last) k_radix_scatter<false, true><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
+      else k_radix_scatter<false, false><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
+#undef RS_ARGS
+      kin = kout; pin = pout; rin = rout;
+    }
+  }
+  e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+size_t dgnn_csr2csc_scratch_bytes(i64 n_cols, i64 nnz) { return c2c_layout(n_cols, nnz).total; }
+
+extern "C" {
+
+size_t dgnn_csr2csc_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz) {
+  (void)n_rows;
+  if (n_cols < 0 || nnz < 0) return 256;
+  return c2c_layout(n_cols, nnz).total;
+}
+
+int dgnn_csr2csc(int64_t n_rows, int64_t n_cols, int64_t nnz, const void* row_ptr, int idx_bits,
+                 const int32_t* col_ind, void* col_ptr, int32_t* row_ind, int32_t* permute,
+                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (n_rows < 0 || n_cols < 0 || nnz < 0) return DGNN_ERR_SHAPE;
+  if (idx_bits != 32 && idx_bits != 64) return DGNN_ERR_IDX_BITS;
+  if (nnz > 0x7fffffffLL || n_rows > 0x7fffffffLL || n_cols > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;
+  if (!row_ptr || !col_ptr || (nnz > 0 && (!col_ind || !row_ind || !permute))) return DGNN_ERR_NULL;
+  if (!workspace || workspace_bytes < c2c_layout(n_cols, nnz).total) return DGNN_ERR_WORKSPACE;
+  char* wsb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  return dgnn_csr2csc_impl(n_rows, n_cols, nnz, row_ptr, idx_bits, col_ind, col_ptr, row_ind, permute, wsb,
+                           reinterpret_cast<cudaStream_t>(stream));
+}
+
+int dgnn_coo2csr(int64_t nnz, int64_t m, const int32_t* row_ind, void* row_ptr, int idx_bits, void* stream) {
+  if (nnz < 0 || m < 0) return DGNN_ERR_SHAPE;
+  if (idx_bits != 32 && idx_bits != 64) return DGNN_ERR_IDX_BITS;
+  if (idx_bits == 32 && nnz > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;
+  if (!row_ptr || (nnz > 0 && !row_ind)) return DGNN_ERR_NULL;
+  k_coo2csr<<<dgnn_grid(m + 1, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(nnz, m, row_ind, row_ptr, idx_bits);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+}  // extern "C"

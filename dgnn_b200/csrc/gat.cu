@@ -1,0 +1,688 @@
+// Fused GAT forward / backward for sm_100a.
+//
+// Forward: one sweep over each destination row.  A warp owns the row's H*F
+// output floats as float4 vectors (lane l holds vectors l, l+32, ...), reads 32
+// column ids at a time with one coalesced load, then gathers the source rows
+// four edges at a time (each gather is a contiguous H*F*4-byte row, 16 B per
+// lane) while an online softmax keeps (max, sum, weighted accumulator) per head
+// in registers -- column ids and attention terms are read once, features once.
+// Rows longer than DGNN_SEG edges are split (see common.cuh); no atomics.
+//
+// Backward: S[r,h] = <grad_out[r,h,:], out[r,h,:]> replaces the reference's
+// per-row edge sweep, so one pass over the CSC form yields grad_feat,
+// grad_attn_col and the per-edge term d_e (scattered to CSR order), and a
+// streaming row reduction of d_e yields grad_attn_row.  Two feature gathers in
+// total for forward+backward instead of three, and no float atomics.
+#include "common.cuh"
+
+namespace {
+
+template <int VPL> struct Unroll { static constexpr int U = VPL <= 2 ? 4 : 2; };
+
+// ------------------------------------------------------------------ forward
+template <int VPL, bool MASK>
+struct GatFwdOp {
+  i64 n_rows, nnz;
+  const void* indptr;
+  int idx_bits;
+  int H, hf4, f4_shift;
+  const int* col_ind;
+  const float* attn_row;
+  const float* attn_col;
+  const float4* in_feat;
+  const float* mask;
+  float slope, drop_p, inv_keep;
+  float4* out;
+  float* edge_max;
+  float* edge_sum;
+  float* ws;
+  i64 slot_stride;  // floats per partial slot
+
+  struct State {
+    LaneMap<VPL> lm;
+    float ar[VPL], m[VPL], z[VPL];
+    float4 acc[VPL];
+  };
+
+  __device__ __forceinline__ void init(State& st, i64 r, int lane) const {
+    st.lm.init(lane, hf4, f4_shift);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      st.ar[v] = st.lm.act[v] ? __ldg(attn_row + r * H + st.lm.hd[v]) : 0.f;
+      st.m[v] = DGNN_NEG_INIT;
+      st.z[v] = 0.f;
+      st.acc[v] = zero4();
+    }
+  }
+
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+    constexpr int U = Unroll<VPL>::U;
+    for (i64 base = e0; base < e1; base += 32) {
+      const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
+      const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
+      for (int k = 0; k < cnt; k += U) {
+        int c[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) c[u] = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
+        float s[U][VPL];
+        float4 x[U][VPL];
+        bool keep[U][VPL];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) {
+            const bool ok = (k + u < cnt) && st.lm.act[v];
+            s[u][v] = ok ? __ldg(attn_col + (i64)c[u] * H + st.lm.hd[v]) : 0.f;
+            x[u][v] = ok ? ld4(in_feat + (i64)c[u] * hf4 + st.lm.q[v]) : zero4();
+            keep[u][v] = true;
+            if (MASK) keep[u][v] = ok ? (__ldg(mask + (base + k + u) * H + st.lm.hd[v]) > drop_p) : false;
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          if (!st.lm.act[v]) continue;
+          float l[U];
+          float bm = st.m[v];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            l[u] = (k + u < cnt) ? leaky(st.ar[v] + s[u][v], slope) : DGNN_NEG_INIT;
+            bm = fmaxf(bm, l[u]);
+          }
+          if (bm > st.m[v]) {
+            const float sc = expf(st.m[v] - bm);
+            st.z[v] *= sc;
+            scale4(st.acc[v], sc);
+            st.m[v] = bm;
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (k + u < cnt) {
+              const float p = expf(l[u] - st.m[v]);
+              st.z[v] += p;
+              if (keep[u][v]) fma4(st.acc[v], p, x[u][v]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  __device__ __forceinline__ void finalize(State& st, i64 r, int) const {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (!st.lm.act[v]) continue;
+      const float sc = st.z[v] > 0.f ? inv_keep / st.z[v] : 0.f;
+      float4 a = st.acc[v];
+      scale4(a, sc);
+      out[r * hf4 + st.lm.q[v]] = a;
+      if (st.lm.lead[v] && edge_max) {
+        edge_max[r * H + st.lm.hd[v]] = st.m[v];
+        edge_sum[r * H + st.lm.hd[v]] = st.z[v];
+      }
+    }
+  }
+
+  __device__ __forceinline__ void store_partial(State& st, i64 slot, int) const {
+    float* p = ws + slot * slot_stride;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (!st.lm.act[v]) continue;
+      reinterpret_cast<float4*>(p)[st.lm.q[v]] = st.acc[v];
+      if (st.lm.lead[v]) {
+        p[hf4 * 4 + st.lm.hd[v]] = st.m[v];
+        p[hf4 * 4 + H + st.lm.hd[v]] = st.z[v];
+      }
+    }
+  }
+
+  __device__ __forceinline__ void merge_partial(State& st, i64 slot, int) const {
+    const float* p = ws + slot * slot_stride;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (!st.lm.act[v]) continue;
+      const float4 ai = reinterpret_cast<const float4*>(p)[st.lm.q[v]];
+      const float mi = p[hf4 * 4 + st.lm.hd[v]];
+      const float zi = p[hf4 * 4 + H + st.lm.hd[v]];
+      const float mn = fmaxf(st.m[v], mi);
+      const float s1 = expf(st.m[v] - mn), s2 = expf(mi - mn);
+      st.z[v] = st.z[v] * s1 + zi * s2;
+      scale4(st.acc[v], s1);
+      fma4(st.acc[v], s2, ai);
+      st.m[v] = mn;
+    }
+  }
+};
+
+// any H, F: one warp per (row, head), lanes over features (slow path)
+__global__ void __launch_bounds__(DGNN_THREADS)
+k_gat_fwd_generic(i64 n_rows, int H, int F, const void* indptr, int idx_bits, const int* col_ind,
+                  const float* attn_row, const float* attn_col, const float* in_feat,
+                  const float* mask, float slope, float drop_p, float inv_keep,
+                  float* out, float* edge_max, float* edge_sum) {
+  const int lane = threadIdx.x & 31;
+  const i64 w = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  if (w >= n_rows * H) return;
+  const i64 r = w / H;
+  const int h = (int)(w % H);
+  const i64 lb = ldp(indptr, idx_bits, r), hb = ldp(indptr, idx_bits, r + 1);
+  const float ar = __ldg(attn_row + r * H + h);
+  float m = DGNN_NEG_INIT;
+  for (i64 e = lb + lane; e < hb; e += 32)
+    m = fmaxf(m, leaky(ar + __ldg(attn_col + (i64)col_ind[e] * H + h), slope));
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(DGNN_FULL, m, o));
+  float z = 0.f;
+  for (i64 e = lb + lane; e < hb; e += 32)
+    z += expf(leaky(ar + __ldg(attn_col + (i64)col_ind[e] * H + h), slope) - m);
+  for (int o = 16; o; o >>= 1) z += __shfl_xor_sync(DGNN_FULL, z, o);
+  if (lane == 0 && edge_max) { edge_max[r * H + h] = m; edge_sum[r * H + h] = z; }
+  const float sc = z > 0.f ? inv_keep / z : 0.f;
+  for (int fb = lane; fb < F; fb += 32) {
+    float acc = 0.f;
+    for (i64 e = lb; e < hb; ++e) {
+      const i64 c = col_ind[e];
+      if (mask && !(__ldg(mask + e * H + h) > drop_p)) continue;
+      const float p = expf(leaky(ar + __ldg(attn_col + c * H + h), slope) - m);
+      acc = fmaf(p, __ldg(in_feat + (c * H + h) * F + fb), acc);
+    }
+    out[(r * H + h) * F + fb] = acc * sc;
+  }
+}
+
+// ------------------------------------------------------------------ rowstat
+template <int VPL>
+__global__ void __launch_bounds__(DGNN_THREADS)
+k_gat_rowstat(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, const float* edge_max,
+              const float* edge_sum, const float4* out, const float4* grad, float4* pack) {
+  const int lane = threadIdx.x & 31;
+  const i64 r = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  LaneMap<VPL> lm;
+  lm.init(lane, hf4, f4_shift);
+  float s[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v)
+    s[v] = lm.act[v] ? dot4(ld4(grad + r * hf4 + lm.q[v]), ld4(out + r * hf4 + lm.q[v])) : 0.f;
+  head_reduce<VPL>(s, f4_shift);
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    if (lm.lead[v]) {
+      const i64 i = r * H + lm.hd[v];
+      pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), __ldg(edge_sum + i), s[v]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(DGNN_THREADS)
+k_gat_rowstat_generic(i64 n_rows, int H, int F, const float* attn_row, const float* edge_max,
+                      const float* edge_sum, const float* out, const float* grad, float4* pack) {
+  const int lane = threadIdx.x & 31;
+  const i64 w = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  if (w >= n_rows * H) return;
+  float s = 0.f;
+  for (int f = lane; f < F; f += 32) s = fmaf(__ldg(grad + w * F + f), __ldg(out + w * F + f), s);
+  for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(DGNN_FULL, s, o);
+  if (lane == 0) pack[w] = make_float4(attn_row[w], edge_max[w], edge_sum[w], s);
+}
+
+// ------------------------------------------------------------ backward cols
+template <int VPL, bool MASK>
+struct GatBwdOp {
+  i64 n_rows, nnz;      // "rows" of the CSC form = source columns
+  const void* indptr;   // col_ptr
+  int idx_bits;
+  int H, hf4, f4_shift;
+  const int* row_ind;
+  const int* permute;
+  const float4* pack;
+  const float* mask;
+  const float4* in_feat;
+  const float* attn_col;
+  const float4* grad_out;
+  float slope, drop_p, inv_keep;
+  float4* grad_feat;
+  float* grad_attn_col;
+  float* grad_edge;  // [nnz,H] in CSR order
+  float* ws;
+  i64 slot_stride;
+
+  struct State {
+    LaneMap<VPL> lm;
+    float4 x[VPL], acc[VPL];
+    float ac[VPL], gc[VPL];
+  };
+
+  __device__ __forceinline__ void init(State& st, i64 c, int lane) const {
+    st.lm.init(lane, hf4, f4_shift);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      st.x[v] = st.lm.act[v] ? ld4(in_feat + c * hf4 + st.lm.q[v]) : zero4();
+      st.ac[v] = st.lm.act[v] ? __ldg(attn_col + c * H + st.lm.hd[v]) : 0.f;
+      st.acc[v] = zero4();
+      st.gc[v] = 0.f;
+    }
+  }
+
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+    constexpr int U = Unroll<VPL>::U;
+    for (i64 base = e0; base < e1; base += 32) {
+      const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
+      const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
+      const int my_p = lane < cnt ? __ldg(permute + base + lane) : 0;
+      for (int k = 0; k < cnt; k += U) {
+        int r[U], pp[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          r[u] = __shfl_sync(DGNN_FULL, my_r, (k + u) & 31);
+          pp[u] = __shfl_sync(DGNN_FULL, my_p, (k + u) & 31);
+        }
+        float4 pk[U][VPL], g4[U][VPL];
+        bool keep[U][VPL];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) {
+            const bool ok = (k + u < cnt) && st.lm.act[v];
+            pk[u][v] = ok ? ld4(pack + (i64)r[u] * H + st.lm.hd[v]) : make_float4(0.f, 0.f, 1.f, 0.f);
+            g4[u][v] = ok ? ld4(grad_out + (i64)r[u] * hf4 + st.lm.q[v]) : zero4();
+            keep[u][v] = ok;
+            if (MASK) keep[u][v] = ok ? (__ldg(mask + (i64)pp[u] * H + st.lm.hd[v]) > drop_p) : false;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float d[VPL];
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) d[v] = dot4(g4[u][v], st.x[v]);
+          head_reduce<VPL>(d, f4_shift);  // uniform: executed by all lanes, also past cnt
+          if (k + u < cnt) {
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+              if (!st.lm.act[v]) continue;
+              const float l = leaky(pk[u][v].x + st.ac[v], slope);
+              const float alpha = expf(l - pk[u][v].y) / pk[u][v].z;
+              const float kp = keep[u][v] ? inv_keep : 0.f;
+              float de = alpha * (d[v] * kp - pk[u][v].w);
+              if (l < 0.f) de *= slope;
+              st.gc[v] += de;
+              fma4(st.acc[v], alpha * kp, g4[u][v]);
+              if (st.lm.lead[v]) grad_edge[(i64)pp[u] * H + st.lm.hd[v]] = de;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  __device__ __forceinline__ void finalize(State& st, i64 c, int) const {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (!st.lm.act[v]) continue;
+      grad_feat[c * hf4 + st.lm.q[v]] = st.acc[v];
+      if (st.lm.lead[v]) grad_attn_col[c * H + st.lm.hd[v]] = st.gc[v];
+    }
+  }
+
+  __device__ __forceinline__ void store_partial(State& st, i64 slot, int) const {
+    float* p = ws + slot * slot_stride;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (!st.lm.act[v]) continue;
+      reinterpret_cast<float4*>(p)[st.lm.q[v]] = st.acc[v];
+      if (st.lm.lead[v]) p[hf4 * 4 + st.lm.hd[v]] = st.gc[v];
+    }
+  }
+
+  __device__ __forceinline__ void merge_partial(State& st, i64 slot, int) const {
+    const float* p = ws + slot * slot_stride;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (!st.lm.act[v]) continue;
+      add4(st.acc[v], reinterpret_cast<const float4*>(p)[st.lm.q[v]]);
+      st.gc[v] += p[hf4 * 4 + st.lm.hd[v]];
+    }
+  }
+};
+
+// any H, F: one warp per (column, head)
+__global__ void __launch_bounds__(DGNN_THREADS)
+k_gat_bwd_cols_generic(i64 n_cols, int H, int F, const void* col_ptr, int idx_bits, const int* row_ind,
+                       const int* permute, const float4* pack, const float* mask, const float* in_feat,
+                       const float* attn_col, const float* grad_out, float slope, float drop_p,
+                       float inv_keep, float* grad_feat, float* grad_attn_col, float* grad_edge) {
+  const int lane = threadIdx.x & 31;
+  const i64 w = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  if (w >= n_cols * H) return;
+  const i64 c = w / H;
+  const int h = (int)(w % H);
+  const i64 lb = ldp(col_ptr, idx_bits, c), hb = ldp(col_ptr, idx_bits, c + 1);
+  const float ac = __ldg(attn_col + c * H + h);
+  float gc = 0.f;
+  for (i64 e = lb; e < hb; ++e) {
+    const i64 r = row_ind[e];
+    const i64 pp = permute[e];
+    const float4 pk = pack[r * H + h];
+    float d = 0.f;
+    for (int f = lane; f < F; f += 32)
+      d = fmaf(__ldg(grad_out + (r * H + h) * F + f), __ldg(in_feat + (c * H + h) * F + f), d);
+    for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(DGNN_FULL, d, o);
+    const float l = leaky(pk.x + ac, slope);
+    const float alpha = expf(l - pk.y) / pk.z;
+    const float kp = (!mask || __ldg(mask + pp * H + h) > drop_p) ? inv_keep : 0.f;
+    float de = alpha * (d * kp - pk.w);
+    if (l < 0.f) de *= slope;
+    gc += de;
+    if (lane == 0) grad_edge[pp * H + h] = de;
+  }
+  if (lane == 0) grad_attn_col[c * H + h] = gc;
+  for (int fb = lane; fb < F; fb += 32) {
+    float acc = 0.f;
+    for (i64 e = lb; e < hb; ++e) {
+      const i64 r = row_ind[e];
+      const float4 pk = pack[r * H + h];
+      const float kp = (!mask || __ldg(mask + (i64)permute[e] * H + h) > drop_p) ? inv_keep : 0.f;
+      const float alpha = expf(leaky(pk.x + ac, slope) - pk.y) / pk.z;
+      acc = fmaf(alpha * kp, __ldg(grad_out + (r * H + h) * F + fb), acc);
+    }
+    grad_feat[(c * H + h) * F + fb] = acc;
+  }
+}
+
+// ------------------------------------------- row reduction of d_e (CSR order)
+// one thread per (row, head); long rows go through chunk partials like the
+// feature kernels so that every sum has a fixed order
+__global__ void k_rowred_rows(i64 n_rows, int H, const void* indptr, int idx_bits,
+                              const float* grad_edge, float* grad_attn_row) {
+  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_rows * H) return;
+  const i64 r = t / H;
+  const int h = (int)(t % H);
+  const i64 lb = ldp(indptr, idx_bits, r), hb = ldp(indptr, idx_bits, r + 1);
+  if (hb - lb > DGNN_SEG) return;
+  float s = 0.f;
+  for (i64 e = lb; e < hb; ++e) s += __ldg(grad_edge + e * H + h);
+  grad_attn_row[t] = s;
+}
+
+__global__ void k_rowred_chunks(i64 n_rows, i64 nnz, int H, const void* indptr, int idx_bits,
+                                const float* grad_edge, float* part) {
+  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  const i64 w = t / H;
+  const int h = (int)(t % H);
+  const i64 j = w >> 1;
+  const int slot = (int)(w & 1);
+  const i64 cs = j * DGNN_SEG;
+  if (cs >= nnz) return;
+  const i64 ce = (cs + DGNN_SEG < nnz) ? cs + DGNN_SEG : nnz;
+  const i64 r = find_row(indptr, idx_bits, n_rows, slot ? ce - 1 : cs);
+  const i64 lb = ldp(indptr, idx_bits, r), hb = ldp(indptr, idx_bits, r + 1);
+  if (hb - lb <= DGNN_SEG) return;
+  if (slot == 0 ? (lb >= cs) : (lb < cs)) return;
+  const i64 e0 = lb > cs ? lb : cs, e1 = hb < ce ? hb : ce;
+  float s = 0.f;
+  for (i64 e = e0; e < e1; ++e) s += __ldg(grad_edge + e * H + h);
+  part[(2 * j + slot) * H + h] = s;
+}
+
+__global__ void k_rowred_merge(i64 n_rows, i64 nnz, int H, const void* indptr, int idx_bits,
+                               const float* part, float* grad_attn_row) {
+  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  const i64 j = t / H;
+  const int h = (int)(t % H);
+  const i64 cs = j * DGNN_SEG;
+  if (cs >= nnz) return;
+  const i64 ce = (cs + DGNN_SEG < nnz) ? cs + DGNN_SEG : nnz;
+  const i64 r = find_row(indptr, idx_bits, n_rows, ce - 1);
+  const i64 lb = ldp(indptr, idx_bits, r), hb = ldp(indptr, idx_bits, r + 1);
+  if (hb - lb <= DGNN_SEG || lb < cs) return;
+  float s = part[(2 * j + 1) * H + h];
+  for (i64 jj = j + 1; jj * DGNN_SEG < hb; ++jj) s += part[(2 * jj) * H + h];
+  grad_attn_row[r * H + h] = s;
+}
+
+// ---------------------------------------------------------------- host side
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
+inline i64 up4(i64 x) { return (x + 3) & ~i64(3); }
+
+struct FastShape {
+  bool ok;
+  int hf4, f4_shift, vpl;
+};
+inline FastShape fast_shape(int h, int f) {
+  FastShape s{false, 0, 0, 0};
+  if (f % 4) return s;
+  const int sh = ilog2_exact(f / 4);
+  if (sh < 0) return s;
+  const i64 hf4 = (i64)h * (f / 4);
+  if (hf4 > 256) return s;
+  s.ok = true;
+  s.hf4 = (int)hf4;
+  s.f4_shift = sh;
+  s.vpl = hf4 <= 32 ? 1 : hf4 <= 64 ? 2 : hf4 <= 128 ? 4 : 8;
+  return s;
+}
+
+inline i64 fwd_slot_stride(int h, int f) { return (i64)h * f + up4(2 * (i64)h); }
+inline i64 bwd_slot_stride(int h, int f) { return (i64)h * f + up4((i64)h); }
+
+template <int VPL, bool MASK>
+int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
+               const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
+               float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
+               void* ws, cudaStream_t s) {
+  GatFwdOp<VPL, MASK> op;
+  op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
+  op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
+  op.col_ind = col_ind; op.attn_row = attn_row; op.attn_col = attn_col;
+  op.in_feat = reinterpret_cast<const float4*>(in_feat); op.mask = mask;
+  op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
+  op.out = reinterpret_cast<float4*>(out); op.edge_max = edge_max; op.edge_sum = edge_sum;
+  op.ws = reinterpret_cast<float*>(ws); op.slot_stride = fwd_slot_stride(h, f);
+  return dgnn_launch_trio(op, true, s);
+}
+
+template <int VPL, bool MASK>
+int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const void* col_ptr, int idx_bits,
+               const int* row_ind, const int* permute, const float* pack, const float* mask,
+               const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
+               float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, cudaStream_t s) {
+  GatBwdOp<VPL, MASK> op;
+  op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
+  op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
+  op.row_ind = row_ind; op.permute = permute; op.pack = reinterpret_cast<const float4*>(pack);
+  op.mask = mask; op.in_feat = reinterpret_cast<const float4*>(in_feat); op.attn_col = attn_col;
+  op.grad_out = reinterpret_cast<const float4*>(grad_out);
+  op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
+  op.grad_feat = reinterpret_cast<float4*>(grad_feat); op.grad_attn_col = grad_attn_col;
+  op.grad_edge = grad_edge; op.ws = ws; op.slot_stride = bwd_slot_stride(h, f);
+  return dgnn_launch_trio(op, true, s);
+}
+
+#define DGNN_DISPATCH_VPL(vpl, MASKED, CALL)                         \
+  switch (vpl) {                                                     \
+    case 1: return MASKED ? CALL(1, true) : CALL(1, false);          \
+    case 2: return MASKED ? CALL(2, true) : CALL(2, false);          \
+    case 4: return MASKED ? CALL(4, true) : CALL(4, false);          \
+    default: return MASKED ? CALL(8, true) : CALL(8, false);         \
+  }
+
+struct BwdLayout {
+  size_t grad_edge, col_part, row_part, pack, total;
+};
+inline BwdLayout bwd_layout(i64 n_rows, i64 nnz, int h, int f) {
+  BwdLayout L;
+  const i64 nc = dgnn_num_chunks(nnz);
+  size_t off = 0;
+  L.grad_edge = off; off += up256((size_t)nnz * h * sizeof(float));
+  L.col_part = off;  off += up256((size_t)(2 * nc) * bwd_slot_stride(h, f) * sizeof(float));
+  L.row_part = off;  off += up256((size_t)(2 * nc) * h * sizeof(float));
+  L.pack = off;      off += up256((size_t)n_rows * h * 4 * sizeof(float));
+  L.total = off + 256;
+  return L;
+}
+
+int check_common(i64 n, i64 nnz, int h, int f, int idx_bits) {
+  if (n < 0 || nnz < 0 || h <= 0 || f <= 0) return DGNN_ERR_SHAPE;
+  if (idx_bits != 32 && idx_bits != 64) return DGNN_ERR_IDX_BITS;
+  if (idx_bits == 32 && nnz > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;
+  if (n > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;  // node ids are int32
+  return DGNN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t dgnn_gat_forward_workspace_bytes(int64_t n_rows, int64_t nnz, int h, int f) {
+  (void)n_rows;
+  if (nnz <= DGNN_SEG || h <= 0 || f <= 0) return 256;
+  return up256((size_t)(2 * dgnn_num_chunks(nnz)) * fwd_slot_stride(h, f) * sizeof(float)) + 256;
+}
+
+int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
+                     const int32_t* col_ind, const float* attn_row, const float* attn_col,
+                     const float* in_feat, float negative_slope, float attn_drop, const float* edge_mask,
+                     float* out, float* edge_max, float* edge_sum, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  int st = check_common(n_rows, nnz, h, f, idx_bits);
+  if (st) return st;
+  if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
+  if (n_rows == 0) return DGNN_OK;
+  if (!row_ptr || !attn_row || !out || (nnz > 0 && (!col_ind || !attn_col || !in_feat))) return DGNN_ERR_NULL;
+  if ((edge_max == nullptr) != (edge_sum == nullptr)) return DGNN_ERR_NULL;
+  if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
+  const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const FastShape fs = fast_shape(h, f);
+  if (fs.ok && aligned16(in_feat) && aligned16(out)) {
+    if (nnz > DGNN_SEG) {
+      if (!workspace || workspace_bytes < dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f))
+        return DGNN_ERR_WORKSPACE;
+      if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
+    }
+#define CALL_FWD(V, M)                                                                               \
+  launch_fwd<V, M>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
+                   negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, s)
+    DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, CALL_FWD)
+#undef CALL_FWD
+  }
+  k_gat_fwd_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
+      n_rows, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, mask, negative_slope,
+      attn_drop, (float)(1.0 / (1.0 - (double)attn_drop)), out, edge_max, edge_sum);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+int dgnn_gat_rowstat(int64_t n_rows, int h, int f, const float* attn_row, const float* edge_max,
+                     const float* edge_sum, const float* out, const float* grad_out, float* pack,
+                     void* stream) {
+  if (n_rows < 0 || h <= 0 || f <= 0) return DGNN_ERR_SHAPE;
+  if (n_rows == 0) return DGNN_OK;
+  if (!attn_row || !edge_max || !edge_sum || !out || !grad_out || !pack) return DGNN_ERR_NULL;
+  if (!aligned16(pack)) return DGNN_ERR_ALIGN;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const FastShape fs = fast_shape(h, f);
+  float4* pk = reinterpret_cast<float4*>(pack);
+  if (fs.ok && aligned16(out) && aligned16(grad_out)) {
+    const float4* o4 = reinterpret_cast<const float4*>(out);
+    const float4* g4 = reinterpret_cast<const float4*>(grad_out);
+    const unsigned grid = dgnn_grid(n_rows, DGNN_WARPS);
+    switch (fs.vpl) {
+      case 1: k_gat_rowstat<1><<<grid, DGNN_THREADS, 0, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, pk); break;
+      case 2: k_gat_rowstat<2><<<grid, DGNN_THREADS, 0, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, pk); break;
+      case 4: k_gat_rowstat<4><<<grid, DGNN_THREADS, 0, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, pk); break;
+      default: k_gat_rowstat<8><<<grid, DGNN_THREADS, 0, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, pk); break;
+    }
+  } else {
+    k_gat_rowstat_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
+        n_rows, h, f, attn_row, edge_max, edge_sum, out, grad_out, pk);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+size_t dgnn_gat_backward_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f) {
+  (void)n_cols;
+  if (n_rows < 0 || nnz < 0 || h <= 0 || f <= 0) return 256;
+  return bwd_layout(n_rows, nnz, h, f).total;
+}
+
+int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f, const void* row_ptr,
+                           const void* col_ptr, int idx_bits, const int32_t* row_ind,
+                           const int32_t* permute, const float* pack, const float* edge_mask,
+                           const float* in_feat, const float* attn_col, const float* grad_out,
+                           float negative_slope, float attn_drop, float* grad_feat, float* grad_attn_row,
+                           float* grad_attn_col, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = check_common(n_rows, nnz, h, f, idx_bits);
+  if (st) return st;
+  st = check_common(n_cols, nnz, h, f, idx_bits);
+  if (st) return st;
+  if (nnz > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;  // permute is int32
+  if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
+  if (!row_ptr || !col_ptr) return DGNN_ERR_NULL;
+  if (n_cols > 0 && (!in_feat || !attn_col || !grad_feat || !grad_attn_col)) return DGNN_ERR_NULL;
+  if (n_rows > 0 && (!pack || !grad_out || !grad_attn_row)) return DGNN_ERR_NULL;
+  if (nnz > 0 && (!row_ind || !permute)) return DGNN_ERR_NULL;
+  if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
+  const BwdLayout L = bwd_layout(n_rows, nnz, h, f);
+  if (!workspace || workspace_bytes < L.total) return DGNN_ERR_WORKSPACE;
+  if (!aligned16(pack)) return DGNN_ERR_ALIGN;
+  char* wsb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  float* grad_edge = reinterpret_cast<float*>(wsb + L.grad_edge);
+  float* col_part = reinterpret_cast<float*>(wsb + L.col_part);
+  float* row_part = reinterpret_cast<float*>(wsb + L.row_part);
+  const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const FastShape fs = fast_shape(h, f);
+  if (n_cols > 0) {
+    if (fs.ok && aligned16(in_feat) && aligned16(grad_out) && aligned16(grad_feat)) {
+      int rc;
+#define CALL_BWD(V, M)                                                                                  \
+  launch_bwd<V, M>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
+                   attn_col, grad_out, negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, \
+                   col_part, s)
+      auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, CALL_BWD) };
+#undef CALL_BWD
+      rc = run();
+      if (rc) return rc;
+    } else {
+      k_gat_bwd_cols_generic<<<dgnn_grid(n_cols * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
+          n_cols, h, f, col_ptr, idx_bits, row_ind, permute, reinterpret_cast<const float4*>(pack), mask,
+          in_feat, attn_col, grad_out, negative_slope, attn_drop,
+          (float)(1.0 / (1.0 - (double)attn_drop)), grad_feat, grad_attn_col, grad_edge);
+    }
+  }
+  if (n_rows > 0) {
+    const int tb = 256;
+    k_rowred_rows<<<dgnn_grid(n_rows * h, tb), tb, 0, s>>>(n_rows, h, row_ptr, idx_bits, grad_edge, grad_attn_row);
+    if (nnz > DGNN_SEG) {
+      const i64 nc = dgnn_num_chunks(nnz);
+      k_rowred_chunks<<<dgnn_grid(2 * nc * h, tb), tb, 0, s>>>(n_rows, nnz, h, row_ptr, idx_bits, grad_edge, row_part);
+      k_rowred_merge<<<dgnn_grid(nc * h, tb), tb, 0, s>>>(n_rows, nnz, h, row_ptr, idx_bits, row_part, grad_attn_row);
+    }
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+int dgnn_gat_backward(int64_t n, int64_t nnz, int h, int f, const void* row_ptr, const void* col_ptr,
+                      int idx_bits, const int32_t* row_ind, const int32_t* permute, const float* edge_max,
+                      const float* edge_sum, const float* edge_mask, const float* in_feat, const float* out,
+                      const float* attn_row, const float* attn_col, const float* grad_out,
+                      float negative_slope, float attn_drop, float* grad_feat, float* grad_attn_row,
+                      float* grad_attn_col, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = check_common(n, nnz, h, f, idx_bits);
+  if (st) return st;
+  if (n == 0) return DGNN_OK;
+  const BwdLayout L = bwd_layout(n, nnz, h, f);
+  if (!workspace || workspace_bytes < L.total) return DGNN_ERR_WORKSPACE;
+  char* wsb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  float* pack = reinterpret_cast<float*>(wsb + L.pack);
+  st = dgnn_gat_rowstat(n, h, f, attn_row, edge_max, edge_sum, out, grad_out, pack, stream);
+  if (st) return st;
+  return dgnn_gat_backward_cols(n, n, nnz, h, f, row_ptr, col_ptr, idx_bits, row_ind, permute, pack, edge_mask,
+                                in_feat, attn_col, grad_out, negative_slope, attn_drop, grad_feat,
+                                grad_attn_row, grad_attn_col, workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,307 @@
+"""Tensor-level wrappers over the C ABI: validate, allocate outputs, launch.
+
+Each function enqueues kernels on the current stream of the inputs' device and
+returns torch tensors; nothing synchronises.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _C
+from ._C import _cuda_f32, _cuda_i32, _cuda_ptr, _p, _same_bits, _stream, _workspace, check, lib
+
+
+def _dims3(t, name):
+    if t.dim() != 3:
+        raise RuntimeError(f"dgnn_b200: {name} must be [N,H,F], got shape {tuple(t.shape)}")
+    return t.shape
+
+
+# ------------------------------------------------------------------- GAT
+def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop=0.0,
+                edge_mask=None, save_stats=True):
+    """Fused GAT forward.  Returns (out, edge_max, edge_sum); the statistics are
+    None when save_stats is False (inference)."""
+    attn_row = _cuda_f32(attn_row, "attn_row")
+    attn_col = _cuda_f32(attn_col, "attn_col")
+    in_feat = _cuda_f32(in_feat, "in_feat")
+    col_ind = _cuda_i32(col_ind, "col_ind")
+    row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
+    _, h, f = _dims3(in_feat, "in_feat")
+    n_rows = row_ptr.numel() - 1
+    nnz = col_ind.numel()
+    if attn_row.shape != (n_rows, h):
+        raise RuntimeError(f"dgnn_b200: attn_row must be [{n_rows},{h}], got {tuple(attn_row.shape)}")
+    if attn_col.dim() != 2 or attn_col.shape[1] != h or attn_col.shape[0] != in_feat.shape[0]:
+        raise RuntimeError("dgnn_b200: attn_col must be [n_src,H] with n_src = in_feat.shape[0]")
+    if attn_drop > 0.0:
+        if edge_mask is None:
+            raise RuntimeError("dgnn_b200: attn_drop > 0 needs an edge_mask")
+        edge_mask = _cuda_f32(edge_mask, "edge_mask")
+        if edge_mask.shape != (nnz, h):
+            raise RuntimeError(f"dgnn_b200: edge_mask must be [{nnz},{h}]")
+    else:
+        edge_mask = None
+    dev = in_feat.device
+    with torch.cuda.device(dev):
+        out = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
+        edge_max = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if save_stats else None
+        edge_sum = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if save_stats else None
+        ws_bytes = lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f)
+        ws = _workspace(ws_bytes, dev)
+        check(lib().dgnn_gat_forward(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
+                                     _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
+                                     _p(edge_mask), _p(out), _p(edge_max), _p(edge_sum), _p(ws), ws.numel(),
+                                     _stream(dev)), "gat_forward")
+    return out, edge_max, edge_sum
+
+
+def gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out):
+    """pack[r,h] = (attn_row, edge_max, edge_sum, <grad_out[r,h], out[r,h]>) as [N,H,4]."""
+    out = _cuda_f32(out, "out")
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    n, h, f = _dims3(out, "out")
+    dev = out.device
+    with torch.cuda.device(dev):
+        pack = torch.empty((n, h, 4), dtype=torch.float32, device=dev)
+        check(lib().dgnn_gat_rowstat(n, h, f, _p(_cuda_f32(attn_row, "attn_row")), _p(_cuda_f32(edge_max, "edge_max")),
+                                     _p(_cuda_f32(edge_sum, "edge_sum")), _p(out), _p(grad_out), _p(pack),
+                                     _stream(dev)), "gat_rowstat")
+    return pack
+
+
+def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_feat, attn_col, grad_out,
+                      negative_slope, attn_drop=0.0):
+    """Column pass of the backward on an [n_rows x n_cols] block (see the header).
+    Returns (grad_feat [n_cols,H,F], grad_attn_row [n_rows,H], grad_attn_col [n_cols,H])."""
+    in_feat = _cuda_f32(in_feat, "in_feat")
+    attn_col = _cuda_f32(attn_col, "attn_col")
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    pack = _cuda_f32(pack, "pack")
+    row_ind = _cuda_i32(row_ind, "row_ind")
+    permute = _cuda_i32(permute, "permute")
+    row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
+    col_ptr, cbits = _cuda_ptr(col_ptr, "col_ptr")
+    if cbits != bits:
+        col_ptr = _same_bits(bits, col_ptr, "col_ptr")
+    n_cols, h, f = _dims3(in_feat, "in_feat")
+    n_rows = row_ptr.numel() - 1
+    nnz = row_ind.numel()
+    if col_ptr.numel() - 1 != n_cols:
+        raise RuntimeError("dgnn_b200: col_ptr length must be in_feat.shape[0] + 1")
+    if grad_out.shape != (n_rows, h, f) or pack.shape != (n_rows, h, 4):
+        raise RuntimeError("dgnn_b200: grad_out / pack must have one row per CSR row")
+    if attn_drop > 0.0:
+        edge_mask = _cuda_f32(edge_mask, "edge_mask")
+    else:
+        edge_mask = None
+    dev = in_feat.device
+    with torch.cuda.device(dev):
+        grad_feat = torch.empty((n_cols, h, f), dtype=torch.float32, device=dev)
+        grad_attn_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+        grad_attn_col = torch.empty((n_cols, h), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gat_backward_workspace_bytes(n_rows, n_cols, nnz, h, f), dev)
+        check(lib().dgnn_gat_backward_cols(n_rows, n_cols, nnz, h, f, _p(row_ptr), _p(col_ptr), bits, _p(row_ind),
+                                           _p(permute), _p(pack), _p(edge_mask), _p(in_feat), _p(attn_col),
+                                           _p(grad_out), float(negative_slope), float(attn_drop), _p(grad_feat),
+                                           _p(grad_attn_row), _p(grad_attn_col), _p(ws), ws.numel(), _stream(dev)),
+              "gat_backward_cols")
+    return grad_feat, grad_attn_row, grad_attn_col
+
+
+def gat_backward(negative_slope, attn_drop, row_ptr, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask,
+                 in_feat, out, attn_row, attn_col, grad_out):
+    """Whole backward on a square graph.  Returns (grad_feat, grad_attn_row, grad_attn_col)."""
+    in_feat = _cuda_f32(in_feat, "in_feat")
+    out = _cuda_f32(out, "out")
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    attn_row = _cuda_f32(attn_row, "attn_row")
+    attn_col = _cuda_f32(attn_col, "attn_col")
+    edge_max = _cuda_f32(edge_max, "edge_max")
+    edge_sum = _cuda_f32(edge_sum, "edge_sum")
+    row_ind = _cuda_i32(row_ind, "row_ind")
+    permute = _cuda_i32(permute, "permute")
+    row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
+    col_ptr, cbits = _cuda_ptr(col_ptr, "col_ptr")
+    if cbits != bits:
+        col_ptr = _same_bits(bits, col_ptr, "col_ptr")
+    n, h, f = _dims3(in_feat, "in_feat")
+    nnz = row_ind.numel()
+    if row_ptr.numel() - 1 != n or col_ptr.numel() - 1 != n:
+        raise RuntimeError("dgnn_b200: gat_backward needs a square graph (row_ptr, col_ptr of length N+1)")
+    if grad_out.shape != (n, h, f) or out.shape != (n, h, f):
+        raise RuntimeError("dgnn_b200: grad_out / out must be [N,H,F]")
+    if attn_drop > 0.0:
+        edge_mask = _cuda_f32(edge_mask, "edge_mask")
+    else:
+        edge_mask = None
+    dev = in_feat.device
+    with torch.cuda.device(dev):
+        grad_feat = torch.empty((n, h, f), dtype=torch.float32, device=dev)
+        grad_attn_row = torch.empty((n, h), dtype=torch.float32, device=dev)
+        grad_attn_col = torch.empty((n, h), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gat_backward_workspace_bytes(n, n, nnz, h, f), dev)
+        check(lib().dgnn_gat_backward(n, nnz, h, f, _p(row_ptr), _p(col_ptr), bits, _p(row_ind), _p(permute),
+                                      _p(edge_max), _p(edge_sum), _p(edge_mask), _p(in_feat), _p(out),
+                                      _p(attn_row), _p(attn_col), _p(grad_out), float(negative_slope),
+                                      float(attn_drop), _p(grad_feat), _p(grad_attn_row), _p(grad_attn_col),
+                                      _p(ws), ws.numel(), _stream(dev)), "gat_backward")
+    return grad_feat, grad_attn_row, grad_attn_col
+
+
+def uniform_fill(shape, seed, offset, device):
+    """Uniform (0,1] floats from the library's Philox stream."""
+    dev = torch.device(device)
+    with torch.cuda.device(dev):
+        out = torch.empty(shape, dtype=torch.float32, device=dev)
+        check(lib().dgnn_uniform_fill(int(seed) & (2**64 - 1), int(offset), out.numel(), _p(out), _stream(dev)),
+              "uniform_fill")
+    return out
+
+
+# ------------------------------------------------------- SDDMM / transpose
+def mhsddmm(row_ptr, col_ind, a, b):
+    """out[e,h] = <a[row_e,h,:], b[col_e,h,:]>, [E,H]."""
+    a = _cuda_f32(a, "grad")
+    b = _cuda_f32(b, "feature")
+    col_ind = _cuda_i32(col_ind, "colind")
+    row_ptr, bits = _cuda_ptr(row_ptr, "rowptr")
+    _, h, f = _dims3(b, "feature")
+    n_rows = row_ptr.numel() - 1
+    if a.shape[0] != n_rows or a.shape[1:] != b.shape[1:]:
+        raise RuntimeError("dgnn_b200: mhsddmm operands must be [V,H,F] with V = len(rowptr) - 1 rows in `grad`")
+    nnz = col_ind.numel()
+    dev = b.device
+    with torch.cuda.device(dev):
+        out = torch.empty((nnz, h), dtype=torch.float32, device=dev)
+        check(lib().dgnn_mhsddmm(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(a), _p(b), _p(out),
+                                 _stream(dev)), "mhsddmm")
+    return out
+
+
+def mhtranspose(permute, attention):
+    """out[i,:] = attention[permute[i],:]."""
+    permute = _cuda_i32(permute, "permute")
+    attention = _cuda_f32(attention, "attention")
+    if attention.dim() != 2:
+        raise RuntimeError("dgnn_b200: mhtranspose input must be [E,H]")
+    nnz, h = permute.numel(), attention.shape[1]
+    dev = attention.device
+    with torch.cuda.device(dev):
+        out = torch.empty((nnz, h), dtype=torch.float32, device=dev)
+        check(lib().dgnn_mhtranspose(nnz, h, _p(permute), _p(attention), _p(out), _stream(dev)), "mhtranspose")
+    return out
+
+
+# --------------------------------------------------------------------- GMM
+def gmm_forward(row_ptr, col_ind, node_feat, pseudo, mu, inv_sigma):
+    node_feat = _cuda_f32(node_feat, "node_feat")
+    pseudo = _cuda_f32(pseudo, "pseudo")
+    mu = _cuda_f32(mu, "mu")
+    inv_sigma = _cuda_f32(inv_sigma, "sigma")
+    col_ind = _cuda_i32(col_ind, "colind")
+    row_ptr, bits = _cuda_ptr(row_ptr, "rowptr")
+    _, k, f = _dims3(node_feat, "node_feat")
+    n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
+    dim = mu.shape[1]
+    if mu.shape != (k, dim) or inv_sigma.shape != (k, dim) or pseudo.shape != (nnz, dim):
+        raise RuntimeError("dgnn_b200: gmmconv needs mu, sigma [K,dim] and pseudo [E,dim]")
+    dev = node_feat.device
+    with torch.cuda.device(dev):
+        out = torch.empty((n_rows, k, f), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gmm_forward_workspace_bytes(n_rows, nnz, k, f), dev)
+        check(lib().dgnn_gmm_forward(n_rows, nnz, k, dim, f, _p(row_ptr), bits, _p(col_ind), _p(node_feat),
+                                     _p(pseudo), _p(mu), _p(inv_sigma), _p(out), _p(ws), ws.numel(),
+                                     _stream(dev)), "gmm_forward")
+    return out
+
+
+def gaussian(pseudo, mu, inv_sigma):
+    pseudo = _cuda_f32(pseudo, "pseudo")
+    mu = _cuda_f32(mu, "mu")
+    inv_sigma = _cuda_f32(inv_sigma, "sigma")
+    nnz, dim = pseudo.shape
+    k = mu.shape[0]
+    dev = pseudo.device
+    with torch.cuda.device(dev):
+        out = torch.empty((nnz, k), dtype=torch.float32, device=dev)
+        check(lib().dgnn_gaussian(nnz, k, dim, _p(pseudo), _p(mu), _p(inv_sigma), _p(out), _stream(dev)), "gaussian")
+    return out
+
+
+def gaussian_bp(pseudo, mu, inv_sigma, grad_gauss):
+    pseudo = _cuda_f32(pseudo, "pseudo")
+    mu = _cuda_f32(mu, "mu")
+    inv_sigma = _cuda_f32(inv_sigma, "sigma")
+    grad_gauss = _cuda_f32(grad_gauss, "grad_gauss")
+    nnz, dim = pseudo.shape
+    k = mu.shape[0]
+    if grad_gauss.shape != (nnz, k):
+        raise RuntimeError("dgnn_b200: GaussianBp needs grad [E,K]")
+    dev = pseudo.device
+    with torch.cuda.device(dev):
+        pseudo_out = torch.empty((nnz, dim), dtype=torch.float32, device=dev)
+        mu_out = torch.empty((k, dim), dtype=torch.float32, device=dev)
+        sigma_out = torch.empty((k, dim), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gaussian_bp_workspace_bytes(nnz, k, dim), dev)
+        check(lib().dgnn_gaussian_bp(nnz, k, dim, _p(pseudo), _p(mu), _p(inv_sigma), _p(grad_gauss), _p(pseudo_out),
+                                     _p(mu_out), _p(sigma_out), _p(ws), ws.numel(), _stream(dev)), "gaussian_bp")
+    return pseudo_out, mu_out, sigma_out
+
+
+# ---------------------------------------------------------------- EdgeConv
+def edgeconv_forward(k, src_ind, h_src, h_dst):
+    """Returns (out [M,F] fp32, max_idx [M,F] int32)."""
+    h_src = _cuda_f32(h_src, "h_src")
+    h_dst = _cuda_f32(h_dst, "h_dst")
+    src_ind = _cuda_i32(src_ind, "src_ind")
+    m, f = h_src.shape
+    if h_dst.shape != (m, f) or src_ind.numel() != m * int(k):
+        raise RuntimeError("dgnn_b200: edgeconv needs h_src, h_dst [M,F] and src_ind [M*k]")
+    dev = h_src.device
+    with torch.cuda.device(dev):
+        out = torch.empty((m, f), dtype=torch.float32, device=dev)
+        max_idx = torch.empty((m, f), dtype=torch.int32, device=dev)
+        check(lib().dgnn_edgeconv_forward(m, f, int(k), _p(src_ind), _p(h_src), _p(h_dst), _p(out), _p(max_idx),
+                                          _stream(dev)), "edgeconv_forward")
+    return out, max_idx
+
+
+def edgeconv_backward(grad_out, max_idx):
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    max_idx = _cuda_i32(max_idx, "max_idx")
+    m, f = grad_out.shape
+    dev = grad_out.device
+    with torch.cuda.device(dev):
+        grad_src = torch.empty((m, f), dtype=torch.float32, device=dev)
+        check(lib().dgnn_edgeconv_backward(m, f, _p(max_idx), _p(grad_out), _p(grad_src), _stream(dev)),
+              "edgeconv_backward")
+    return grad_src
+
+
+# -------------------------------------------------------------- conversion
+def csr2csc(row_ptr, col_ind, n_cols=None):
+    """Returns (col_ptr [same width as row_ptr], row_ind int32, permute int32)."""
+    col_ind = _cuda_i32(col_ind, "colind")
+    row_ptr, bits = _cuda_ptr(row_ptr, "rowptr")
+    n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
+    n_cols = n_rows if n_cols is None else int(n_cols)
+    dev = col_ind.device
+    with torch.cuda.device(dev):
+        col_ptr = torch.empty(n_cols + 1, dtype=row_ptr.dtype, device=dev)
+        row_ind = torch.empty(nnz, dtype=torch.int32, device=dev)
+        permute = torch.empty(nnz, dtype=torch.int32, device=dev)
+        ws = _workspace(lib().dgnn_csr2csc_workspace_bytes(n_rows, n_cols, nnz), dev)
+        check(lib().dgnn_csr2csc(n_rows, n_cols, nnz, _p(row_ptr), bits, _p(col_ind), _p(col_ptr), _p(row_ind),
+                                 _p(permute), _p(ws), ws.numel(), _stream(dev)), "csr2csc")
+    return col_ptr, row_ind, permute
+
+
+def coo2csr(row_ind, m, dtype=torch.int32):
+    row_ind = _cuda_i32(row_ind, "cooRowInd")
+    dev = row_ind.device
+    bits = 32 if dtype == torch.int32 else 64
+    with torch.cuda.device(dev):
+        row_ptr = torch.empty(int(m) + 1, dtype=dtype, device=dev)
+        check(lib().dgnn_coo2csr(row_ind.numel(), int(m), _p(row_ind), _p(row_ptr), bits, _stream(dev)), "coo2csr")
+    return row_ptr

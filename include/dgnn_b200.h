@@ -1,0 +1,184 @@
+/* dgnn_b200 -- C ABI of the B200 (sm_100a) fused GNN-layer kernels.
+ *
+ * Drop-in boundary for the six torch extension modules of dgSPARSE/dgNN
+ * (fused_gatconv, fused_gmmconv, fused_edgeconv, mhsddmm, mhtranspose,
+ * format_conversion).  Each entry point below names the reference binding it
+ * replaces (path within the dgNN project : line).
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer on the current CUDA device; inputs are
+ *    borrowed, outputs and workspaces are caller-allocated; the library never
+ *    allocates or frees device memory and keeps no state between calls;
+ *  - floating data is fp32, row-major, contiguous; node / edge ids are int32;
+ *    index-pointer arrays (row_ptr, col_ptr) are int32 or int64, chosen by
+ *    `idx_bits` (32 or 64); permutations are int32 (nnz < 2^31);
+ *  - CSR rows are destination nodes, columns are source nodes;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream); calls
+ *    only enqueue work and do not synchronise;
+ *  - return value: 0 = ok, < 0 = argument error (dgnn_status), > 0 = cudaError_t
+ *    reported by the launch.  dgnn_status_string() explains either.
+ *  - a NULL or too small workspace where one is required gives
+ *    DGNN_ERR_WORKSPACE; sizes come from the *_workspace_bytes() queries.
+ */
+#ifndef DGNN_B200_H
+#define DGNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum dgnn_status {
+  DGNN_OK = 0,
+  DGNN_ERR_NULL = -1,        /* required pointer is NULL */
+  DGNN_ERR_SHAPE = -2,       /* negative or inconsistent size */
+  DGNN_ERR_IDX_BITS = -3,    /* idx_bits is not 32 or 64 */
+  DGNN_ERR_ALIGN = -4,       /* pointer not aligned for vector access */
+  DGNN_ERR_OVERFLOW = -5,    /* size does not fit the index type */
+  DGNN_ERR_WORKSPACE = -6,   /* workspace missing or too small */
+  DGNN_ERR_VALUE = -7        /* scalar argument out of range */
+} dgnn_status;
+
+int dgnn_version(void);
+const char* dgnn_status_string(int status);
+/* edges per chunk used when rows longer than this are split across warps */
+int64_t dgnn_seg_chunk(void);
+
+/* ---- GAT -----------------------------------------------------------------
+ * dgnn_gat_forward replaces fused_gatconv.gat_forward and .gat_inference
+ * (dgNN/src/fused_gatconv/fused_gatconv.cpp:11-32, 38-60; kernels
+ * fused_gatconv_kernel.cu:24-118, 391-478).
+ *   e = LeakyReLU(attn_row[r,h] + attn_col[c,h]); alpha = softmax over row r;
+ *   out[r,h,:] = sum_e keep_e * alpha_e / (1 - attn_drop) * in_feat[c_e,h,:]
+ *   keep_e = edge_mask[e,h] > attn_drop  (edge_mask NULL: every edge kept;
+ *   required non-NULL when attn_drop > 0).
+ * edge_max / edge_sum [n_rows,h] receive the row maximum and sum of exp saved
+ * for the backward pass; pass both NULL for inference.  An empty row gives
+ * out = 0, edge_max = -1e38, edge_sum = 0.  attn_col / in_feat are indexed by
+ * column id, so they may hold more rows than n_rows (row-block sharding).
+ */
+size_t dgnn_gat_forward_workspace_bytes(int64_t n_rows, int64_t nnz, int h, int f);
+int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f,
+                     const void* row_ptr, int idx_bits, const int32_t* col_ind,
+                     const float* attn_row, const float* attn_col, const float* in_feat,
+                     float negative_slope, float attn_drop, const float* edge_mask,
+                     float* out, float* edge_max, float* edge_sum,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Row statistics for the backward pass: pack[r,h] = (attn_row, edge_max,
+ * edge_sum, S) with S[r,h] = <grad_out[r,h,:], out[r,h,:]>, which equals the
+ * reference's per-row sum of alpha*g (fused_gatconv_kernel.cu:903-929) without
+ * an edge pass.  pack is [n_rows,h,4] fp32, 16-byte aligned. */
+int dgnn_gat_rowstat(int64_t n_rows, int h, int f,
+                     const float* attn_row, const float* edge_max, const float* edge_sum,
+                     const float* out, const float* grad_out, float* pack, void* stream);
+
+/* Column pass of the backward over the CSC form of an [n_rows x n_cols] block:
+ *   grad_feat[c,h,:]   = sum_{e in col c} keep*alpha/(1-p) * grad_out[row_e,h,:]
+ *   g_e                = keep/(1-p) * <grad_out[row_e,h,:], in_feat[c,h,:]>
+ *   d_e                = alpha_e * (g_e - S_row) * (slope if leaky<0 else 1)
+ *   grad_attn_col[c,h] = sum_{e in col c} d_e
+ *   grad_attn_row[r,h] = sum_{e in row r} d_e      (via grad_edge, CSR order)
+ * replaces mhspmm_backward_kernel + mhsddmm + fused_backward_kernel
+ * (fused_gatconv_kernel.cu:712-763, 814-890, 892-968); no float atomics.
+ * in_feat / attn_col / grad_feat / grad_attn_col have n_cols rows; pack and
+ * grad_out have n_rows rows; permute[j] is the CSR position of CSC entry j and
+ * row_ptr is the CSR index pointer of the same block. */
+size_t dgnn_gat_backward_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f);
+int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f,
+                           const void* row_ptr, const void* col_ptr, int idx_bits,
+                           const int32_t* row_ind, const int32_t* permute,
+                           const float* pack, const float* edge_mask,
+                           const float* in_feat, const float* attn_col, const float* grad_out,
+                           float negative_slope, float attn_drop,
+                           float* grad_feat, float* grad_attn_row, float* grad_attn_col,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* Whole backward on a square graph: replaces fused_gatconv.gat_backward
+ * (fused_gatconv.cpp:104-166).  `out` is the forward result (the reference
+ * recomputes the row sums from edges instead). */
+int dgnn_gat_backward(int64_t n, int64_t nnz, int h, int f,
+                      const void* row_ptr, const void* col_ptr, int idx_bits,
+                      const int32_t* row_ind, const int32_t* permute,
+                      const float* edge_max, const float* edge_sum, const float* edge_mask,
+                      const float* in_feat, const float* out,
+                      const float* attn_row, const float* attn_col, const float* grad_out,
+                      float negative_slope, float attn_drop,
+                      float* grad_feat, float* grad_attn_row, float* grad_attn_col,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Uniform floats in (0,1] from a counter-based Philox4x32-10 stream; stands in
+ * for the cuRAND fill of edge_mask (fused_gatconv_kernel.cu:333-341). */
+int dgnn_uniform_fill(uint64_t seed, uint64_t offset, int64_t n, float* out, void* stream);
+
+/* ---- multi-head SDDMM / transpose -----------------------------------------
+ * out[e,h] = <a[row_e,h,:], b[col_e,h,:]>; replaces mhsddmm.mhsddmm
+ * (dgNN/src/sddmm/mhsddmm.cc:11-28, mhsddmm_kernel.cu:5-99). */
+int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f,
+                 const void* row_ptr, int idx_bits, const int32_t* col_ind,
+                 const float* a, const float* b, float* out, void* stream);
+/* out[i,:] = in[permute[i],:] for [nnz,h] fp32; replaces mhtranspose.mhtranspose
+ * (dgNN/src/csr2csc/mhtranspose.cc:10-18, mhtranspose_kernel.cu:6-47). */
+int dgnn_mhtranspose(int64_t nnz, int h, const int32_t* permute,
+                     const float* in, float* out, void* stream);
+
+/* ---- MoNet / GMM ----------------------------------------------------------
+ * w[e,k] = exp(-0.5 sum_d ((pseudo[e,d]-mu[k,d]) inv_sigma[k,d])^2);
+ * out[r,k,:] = sum_{e in row r} w[e,k] node_feat[col_e,k,:]; replaces
+ * fused_gmmconv.gmmconv (fused_gmmconv.cpp:37-47, fused_gmmconv_kernel.cu:24-55). */
+size_t dgnn_gmm_forward_workspace_bytes(int64_t n_rows, int64_t nnz, int kernels, int f);
+int dgnn_gmm_forward(int64_t n_rows, int64_t nnz, int kernels, int dim, int f,
+                     const void* row_ptr, int idx_bits, const int32_t* col_ind,
+                     const float* node_feat, const float* pseudo,
+                     const float* mu, const float* inv_sigma, float* out,
+                     void* workspace, size_t workspace_bytes, void* stream);
+/* replaces fused_gmmconv.Gaussian (fused_gmmconv.cpp:29-35, kernel :11-22) */
+int dgnn_gaussian(int64_t nnz, int kernels, int dim, const float* pseudo,
+                  const float* mu, const float* inv_sigma, float* gauss, void* stream);
+/* Gradients of the Gaussian weights w.r.t. pseudo [nnz,dim], mu and inv_sigma
+ * [kernels,dim] given grad_gauss [nnz,kernels]; stands where
+ * fused_gmmconv.GaussianBp stands (fused_gmmconv.cpp:49-57), computing the
+ * derivative of the forward formula (the reference kernel :57-87 does not).
+ * Deterministic two-stage reduction through the workspace. */
+size_t dgnn_gaussian_bp_workspace_bytes(int64_t nnz, int kernels, int dim);
+int dgnn_gaussian_bp(int64_t nnz, int kernels, int dim, const float* pseudo,
+                     const float* mu, const float* inv_sigma, const float* grad_gauss,
+                     float* pseudo_out, float* mu_out, float* sigma_out,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- EdgeConv -------------------------------------------------------------
+ * out[i,f] = max_j (h_dst[i,f] + h_src[src_ind[i*k+j],f]); max_idx[i,f] = that
+ * source id (smallest j on ties); replaces fused_edgeconv.edgeconv_forward
+ * (fused_edgeconv.cpp:11-27, fused_edgeconv_kernel.cu:7-74).  max_idx is int32
+ * (the reference stores the id in a float tensor). */
+int dgnn_edgeconv_forward(int64_t m, int f, int k, const int32_t* src_ind,
+                          const float* h_src, const float* h_dst,
+                          float* out, int32_t* max_idx, void* stream);
+/* grad_src = 0; grad_src[max_idx[i,f],f] += grad_out[i,f]; replaces
+ * fused_edgeconv.edgeconv_backward (fused_edgeconv.cpp:32-45, kernel :76-100);
+ * the zero fill is ordered before the scatter. */
+int dgnn_edgeconv_backward(int64_t m, int f, const int32_t* max_idx,
+                           const float* grad_out, float* grad_src, void* stream);
+
+/* ---- format conversion ----------------------------------------------------
+ * Stable counting sort of CSR entries by column: col_ptr [n_cols+1] (width
+ * idx_bits), row_ind [nnz], permute [nnz] = CSR position of each CSC entry;
+ * entries of a column keep CSR order.  Replaces format_conversion.csr2csc
+ * (dgNN/src/convert/convert.cpp:16-28, convert_kernel.cu:6-42: cuSPARSE
+ * csr2cscEx2 with the position carried as an fp32 value). */
+size_t dgnn_csr2csc_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz);
+int dgnn_csr2csc(int64_t n_rows, int64_t n_cols, int64_t nnz,
+                 const void* row_ptr, int idx_bits, const int32_t* col_ind,
+                 void* col_ptr, int32_t* row_ind, int32_t* permute,
+                 void* workspace, size_t workspace_bytes, void* stream);
+/* row_ptr[i] = number of entries with row id < i, for sorted COO row ids;
+ * replaces format_conversion.coo2csr (convert.cpp:32-35, convert_kernel.cu:44-59) */
+int dgnn_coo2csr(int64_t nnz, int64_t m, const int32_t* row_ind,
+                 void* row_ptr, int idx_bits, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DGNN_B200_H */

@@ -1,0 +1,159 @@
+"""GPU parity of the fused GAT kernels against the CPU oracle (through the C ABI)."""
+import pytest
+import torch
+
+from dgnn_b200 import kernels, synth
+from dgnn_b200.ext import fused_gatconv
+from dgnn_b200.operators import GATConvFuse, GATConvFuse_inference
+from helpers import assert_close, assert_equal, gat_inputs, scipy_csc
+from oracle import dgnn_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+SEG = 1024  # long-row split threshold of the library (dgnn_seg_chunk)
+
+
+def _case(n, avg, seed, long_rows=(), ptr64=False):
+    import numpy as np
+    rp, ci = synth.random_graph(n, avg, seed, long_rows=long_rows, ptr_dtype=np.int64 if ptr64 else np.int32)
+    return rp, ci
+
+
+GRAPHS = {
+    "tiny": dict(n=40, avg=3, seed=1, long_rows=[(0, 1), (5, 33), (9, 65)]),
+    "medium": dict(n=700, avg=9, seed=2, long_rows=[(3, 100), (400, 257)]),
+    "long_rows": dict(n=900, avg=6, seed=3, long_rows=[(7, SEG + 1), (8, 3 * SEG + 17), (500, 2 * SEG), (899, SEG + 300)]),
+}
+SHAPES = [(1, 4), (1, 64), (3, 16), (4, 64), (8, 32), (2, 256), (16, 64), (3, 5), (2, 12), (1, 1), (4, 33)]
+
+
+def _fwd_bwd_check(cuda, rp, ci, h, f, seed, slope=0.2, p=0.0):
+    n = rp.numel() - 1
+    ar, ac, x, g = gat_inputs(rp, n, h, f, seed)
+    mask = None
+    if p > 0:
+        mask = torch.rand(ci.numel(), h, generator=torch.Generator().manual_seed(seed + 1))
+    o_ref, m_ref, z_ref = orc.gat_forward(ar, ac, rp, ci, slope, x, p, mask)
+    gf_ref, gr_ref, gc_ref = orc.gat_backward(slope, p, rp, ci, m_ref, z_ref, mask, x, ar, ac, g)
+    d = lambda t: None if t is None else t.to(cuda)
+    out, emax, esum = kernels.gat_forward(d(ar), d(ac), d(rp), d(ci), slope, d(x), p, d(mask))
+    assert_close(out, o_ref, "out")
+    assert_equal(emax, m_ref, "edge_max")          # a max is exact
+    assert_close(esum, z_ref, "edge_sum")
+    cp, ri, pm = scipy_csc(rp, ci)
+    gf, gr, gc = kernels.gat_backward(slope, p, d(rp), d(cp.to(rp.dtype)), d(ri.int()), d(pm.int()), emax, esum,
+                                      d(mask), d(x), out, d(ar), d(ac), d(g))
+    assert_close(gf, gf_ref, "grad_feat")
+    assert_close(gr, gr_ref, "grad_attn_row", atol=2e-5)
+    assert_close(gc, gc_ref, "grad_attn_col", atol=2e-5)
+    # inference path: same output, no statistics
+    out2, a, b = kernels.gat_forward(d(ar), d(ac), d(rp), d(ci), slope, d(x), p, d(mask), save_stats=False)
+    assert a is None and b is None
+    assert_equal(out2, out, "inference out")
+
+
+@pytest.mark.parametrize("h,f", SHAPES)
+@pytest.mark.parametrize("graph", ["tiny", "medium"])
+def test_gat_parity_shapes(cuda, graph, h, f):
+    rp, ci = _case(**GRAPHS[graph])
+    _fwd_bwd_check(cuda, rp, ci, h, f, seed=11)
+
+
+@pytest.mark.parametrize("h,f", [(8, 32), (4, 64), (1, 16), (3, 7), (16, 64)])
+@pytest.mark.parametrize("ptr64", [False, True])
+def test_gat_parity_long_rows(cuda, h, f, ptr64):
+    rp, ci = _case(ptr64=ptr64, **GRAPHS["long_rows"])
+    _fwd_bwd_check(cuda, rp, ci, h, f, seed=12)
+
+
+@pytest.mark.parametrize("h,f", [(4, 64), (3, 5)])
+@pytest.mark.parametrize("graph", ["medium", "long_rows"])
+def test_gat_parity_dropout_mask(cuda, graph, h, f):
+    rp, ci = _case(**GRAPHS[graph])
+    _fwd_bwd_check(cuda, rp, ci, h, f, seed=13, p=0.4)
+
+
+def test_gat_degenerate_graphs(cuda):
+    # no edges at all, and a graph whose rows are all empty but one
+    for rp, ci in [(torch.zeros(6, dtype=torch.int32), torch.zeros(0, dtype=torch.int32)),
+                   (torch.tensor([0, 0, 0, 3, 3], dtype=torch.int32), torch.tensor([1, 1, 3], dtype=torch.int32))]:
+        _fwd_bwd_check(cuda, rp, ci, 2, 8, seed=3)
+
+
+def test_gat_negative_and_extreme_scores(cuda):
+    rp, ci = _case(**GRAPHS["medium"])
+    n = rp.numel() - 1
+    ar, ac, x, g = gat_inputs(rp, n, 4, 16, 21, scale=30.0)   # softmax saturates: exp arguments down to -100s
+    o_ref, m_ref, z_ref = orc.gat_forward(ar, ac, rp, ci, 0.2, x)
+    out, emax, esum = kernels.gat_forward(ar.to(cuda), ac.to(cuda), rp.to(cuda), ci.to(cuda), 0.2, x.to(cuda))
+    assert_close(out, o_ref, "out"); assert_equal(emax, m_ref, "edge_max"); assert_close(esum, z_ref, "edge_sum")
+
+
+def test_c1_config_layer_parity(cuda):
+    """Config 1: 2708 nodes, 10556 directed edges + self-loops, 1433 -> 4 heads x 64, through the layer API."""
+    from dgnn_b200.layers import GATConv
+    rp, ci = synth.powerlaw_graph()
+    n, nnz = rp.numel() - 1, ci.numel()
+    assert n == 2708 and nnz == 10556 + 2708
+    g = torch.Generator().manual_seed(1)
+    feat = (torch.rand(n, 1433, generator=g) < 0.013).float()
+    layer = GATConv(1433, 64, 4)
+    with torch.no_grad():
+        layer.W.copy_(synth.xavier_uniform((1433, 256), 1433, 256, g))
+        layer.attn_l.copy_(synth.xavier_uniform((1, 4, 64), 64, 64, g))
+        layer.attn_r.copy_(synth.xavier_uniform((1, 4, 64), 64, 64, g))
+    cot = torch.randn(n, 4, 64, generator=g)
+    # CPU oracle of the whole layer, autograd backward
+    W, al, ar_ = [p.detach().clone().requires_grad_() for p in (layer.W, layer.attn_l, layer.attn_r)]
+    ref = orc.gat_layer_forward(rp, ci, feat, W, al, ar_, 0.2, 4, 64)
+    (ref * cot).sum().backward()
+    cp, ri, pm = scipy_csc(rp, ci)
+    layer = layer.to(cuda).train()
+    out = layer(rp.to(cuda), ci.to(cuda), cp.int().to(cuda), ri.int().to(cuda), pm.int().to(cuda), feat.to(cuda))
+    (out * cot.to(cuda)).sum().backward()
+    assert_close(out, ref, "layer out")
+    assert_close(layer.W.grad, W.grad, "dW", atol=5e-5)
+    assert_close(layer.attn_l.grad, al.grad, "d attn_l", atol=5e-5)
+    assert_close(layer.attn_r.grad, ar_.grad, "d attn_r", atol=5e-5)
+    layer.eval()
+    with torch.no_grad():
+        out_eval = layer(rp.to(cuda), ci.to(cuda), cp.int().to(cuda), ri.int().to(cuda), pm.int().to(cuda), feat.to(cuda))
+    assert_close(out_eval, ref, "eval out")
+
+
+def test_ext_module_surface(cuda):
+    """fused_gatconv.* keeps the reference's argument lists and return lists."""
+    rp, ci = _case(**GRAPHS["medium"])
+    n, h, f = rp.numel() - 1, 4, 32
+    ar, ac, x, g = [t.to(cuda) for t in gat_inputs(rp, n, h, f, 2)]
+    cp, ri, pm = [t.int().to(cuda) for t in scipy_csc(rp, ci)]
+    rp, ci = rp.to(cuda), ci.to(cuda)
+    out, emax, esum, mask = fused_gatconv.gat_forward(ar, ac, rp, ci, 0.2, x, 0.0)
+    assert mask.shape == (ci.numel(), h)
+    gf, gr, gc = fused_gatconv.gat_backward(0.2, 0.0, rp, ci, cp, ri, pm, emax, esum, mask, x, ar, ac, g)  # no out_feat given
+    gf2, gr2, gc2 = fused_gatconv.gat_backward(0.2, 0.0, rp, ci, cp, ri, pm, emax, esum, mask, x, ar, ac, g, out)
+    assert_equal(gf, gf2, "grad_feat"); assert_equal(gr, gr2, "grad_row"); assert_equal(gc, gc2, "grad_col")
+    assert_equal(fused_gatconv.gat_inference(ar, ac, rp, ci, 0.2, x), out, "inference")
+    tb = fused_gatconv.gat_forward_tb(ar, ac, rp, ci, 0.2, x, None)
+    assert len(tb) == 3 and torch.equal(tb[0], out)
+    # dropout through the operator: statistical check of the keep rate and scaling
+    torch.manual_seed(0)
+    out_d, _, _, mask_d = fused_gatconv.gat_forward(ar, ac, rp, ci, 0.2, x, 0.5)
+    keep = (mask_d > 0.5).float().mean().item()
+    assert 0.45 < keep < 0.55
+    o_ref, _, _ = orc.gat_forward(ar.cpu(), ac.cpu(), rp.cpu(), ci.cpu(), 0.2, x.cpu(), 0.5, mask_d.cpu())
+    assert_close(out_d, o_ref, "dropout forward with the drawn mask")
+
+
+def test_deterministic_repeat(cuda):
+    rp, ci = _case(**GRAPHS["long_rows"])
+    n, h, f = rp.numel() - 1, 8, 32
+    ar, ac, x, g = [t.to(cuda) for t in gat_inputs(rp, n, h, f, 4)]
+    cp, ri, pm = [t.int().to(cuda) for t in scipy_csc(rp, ci)]
+    rp, ci = rp.to(cuda), ci.to(cuda)
+    runs = []
+    for _ in range(2):
+        out, emax, esum = kernels.gat_forward(ar, ac, rp, ci, 0.2, x)
+        runs.append((out,) + kernels.gat_backward(0.2, 0.0, rp, cp, ri, pm, emax, esum, None, x, out, ar, ac, g))
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)   # no float atomics anywhere: bit-identical

@@ -1,0 +1,169 @@
+"""GPU parity of SDDMM, transpose, GMM, EdgeConv and the conversions against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from dgnn_b200 import kernels, synth
+from dgnn_b200.ext import format_conversion, fused_edgeconv
+from dgnn_b200.operators import EdgeConvFuse, GmmConvFuse
+from helpers import assert_close, assert_equal, scipy_csc
+from oracle import dgnn_oracle as orc
+
+pytestmark = pytest.mark.gpu
+SEG = 1024
+
+
+def _graph(kind, ptr64=False):
+    dt = np.int64 if ptr64 else np.int32
+    if kind == "tiny":
+        return synth.random_graph(40, 3, 1, long_rows=[(0, 1), (5, 33), (9, 65)], ptr_dtype=dt)
+    if kind == "medium":
+        return synth.random_graph(700, 9, 2, long_rows=[(3, 100), (400, 257)], ptr_dtype=dt)
+    return synth.random_graph(900, 6, 3, long_rows=[(7, SEG + 1), (8, 3 * SEG + 17), (500, 2 * SEG)], ptr_dtype=dt)
+
+
+@pytest.mark.parametrize("h,f", [(1, 64), (3, 16), (4, 64), (8, 32), (16, 64), (2, 256), (3, 5), (1, 1), (2, 33)])
+@pytest.mark.parametrize("kind", ["tiny", "medium", "long"])
+def test_mhsddmm(cuda, kind, h, f):
+    rp, ci = _graph(kind)
+    n = rp.numel() - 1
+    g = torch.Generator().manual_seed(3)
+    a, b = torch.randn(n, h, f, generator=g), torch.randn(n, h, f, generator=g)
+    out = kernels.mhsddmm(rp.to(cuda), ci.to(cuda), a.to(cuda), b.to(cuda))
+    assert_close(out, orc.mhsddmm(rp, ci, a, b), "mhsddmm")
+
+
+@pytest.mark.parametrize("h", [1, 2, 3, 4, 8, 16])
+def test_mhtranspose_bit_exact(cuda, h):
+    g = torch.Generator().manual_seed(5)
+    nnz = 10007
+    perm = torch.randperm(nnz, generator=g).int()
+    x = torch.randn(nnz, h, generator=g)
+    assert_equal(kernels.mhtranspose(perm.to(cuda), x.to(cuda)), orc.mhtranspose(perm, x), "mhtranspose")
+    assert kernels.mhtranspose(perm[:0].to(cuda), x[:0].to(cuda)).shape == (0, h)
+
+
+@pytest.mark.parametrize("kind,ptr64", [("tiny", False), ("medium", False), ("long", False), ("long", True)])
+def test_csr2csc_bit_exact(cuda, kind, ptr64):
+    rp, ci = _graph(kind, ptr64)
+    cp, ri, pm = kernels.csr2csc(rp.to(cuda), ci.to(cuda))
+    scp, sri, spm = scipy_csc(rp, ci)
+    assert cp.dtype == rp.dtype
+    assert_equal(cp, scp, "col_ptr"); assert_equal(ri, sri, "row_ind"); assert_equal(pm, spm, "permute")
+    ocp, ori, opm = orc.csr2csc(rp, ci)
+    assert_equal(cp, ocp, "col_ptr vs oracle"); assert_equal(ri, ori, "row_ind vs oracle"); assert_equal(pm, opm, "permute vs oracle")
+
+
+@pytest.mark.parametrize("n,nnz", [(1, 5), (300, 5000), (70000, 300000), (2**17 + 3, 1 << 20)])
+def test_csr2csc_sizes_and_passes(cuda, n, nnz):
+    """1, 2 and 3 radix passes (n_cols <= 2^8, 2^16, 2^24), several tiles, duplicates."""
+    g = torch.Generator().manual_seed(n)
+    dst = torch.randint(0, n, (nnz,), generator=g)
+    src = torch.randint(0, n, (nnz,), generator=g)
+    src[: nnz // 8] = src[0]                       # a hub column
+    rp, ci = synth.csr_from_edges(dst.numpy(), src.numpy(), n)
+    cp, ri, pm = kernels.csr2csc(rp.to(cuda), ci.to(cuda))
+    ocp, ori, opm = orc.csr2csc(rp, ci)
+    assert_equal(cp, ocp, "col_ptr"); assert_equal(ri, ori, "row_ind"); assert_equal(pm, opm, "permute")
+
+
+def test_csr2csc_rectangular_and_empty(cuda):
+    rp = torch.tensor([0, 2, 2, 5], dtype=torch.int32)
+    ci = torch.tensor([6, 1, 0, 6, 6], dtype=torch.int32)
+    cp, ri, pm = kernels.csr2csc(rp.to(cuda), ci.to(cuda), n_cols=7)
+    ocp, ori, opm = orc.csr2csc(rp, ci, 7)
+    assert_equal(cp, ocp, "col_ptr"); assert_equal(ri, ori, "row_ind"); assert_equal(pm, opm, "permute")
+    cp, ri, pm = kernels.csr2csc(torch.zeros(4, dtype=torch.int32, device=cuda), torch.zeros(0, dtype=torch.int32, device=cuda))
+    assert cp.tolist() == [0, 0, 0, 0] and ri.numel() == 0
+
+
+def test_format_conversion_module(cuda):
+    rp, ci = _graph("medium")
+    vals = torch.arange(ci.numel(), dtype=torch.float32)
+    colptr, rowind, cscval = format_conversion.csr2csc(rp.to(cuda), ci.to(cuda), vals.to(cuda))
+    scp, sri, spm = scipy_csc(rp, ci)
+    assert_equal(colptr, scp, "colptr"); assert_equal(rowind, sri, "rowind"); assert_equal(cscval.long(), spm, "values = positions")
+    rows = orc.edge_rows(rp).int()
+    assert_equal(format_conversion.coo2csr(rows.to(cuda), rp.numel() - 1), rp, "coo2csr")
+    assert_equal(kernels.coo2csr(rows.to(cuda), rp.numel() - 1, torch.int64), rp, "coo2csr int64")
+    assert kernels.coo2csr(rows[:0].to(cuda), 3).tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("k,f,dim", [(3, 16, 2), (1, 64, 1), (2, 5, 3), (4, 32, 2)])
+@pytest.mark.parametrize("kind", ["tiny", "medium", "long"])
+def test_gmm_forward_backward(cuda, kind, k, f, dim):
+    rp, ci = _graph(kind)
+    n, nnz = rp.numel() - 1, ci.numel()
+    g = torch.Generator().manual_seed(8)
+    feat = torch.randn(n, k, f, generator=g)
+    pseudo = torch.rand(nnz, dim, generator=g)
+    mu = torch.rand(k, dim, generator=g)
+    sig = torch.rand(k, dim, generator=g) + 0.5
+    go = torch.randn(n, k, f, generator=g)
+    # oracle: autograd through the CPU forward (fp64 for the reference gradients)
+    f64 = [t.double().requires_grad_() for t in (feat, pseudo, mu, sig)]
+    ref = orc.gmm_forward(rp, ci, *f64)
+    ref.backward(go.double())
+    cp, ri, pm = scipy_csc(rp, ci)
+    dev = [t.to(cuda).requires_grad_() for t in (feat, pseudo, mu, sig)]
+    out = GmmConvFuse(rp.to(cuda), ci.to(cuda), cp.int().to(cuda), ri.int().to(cuda), pm.int().to(cuda), *dev)
+    out.backward(go.to(cuda))
+    assert_close(out, ref.float(), "gmm out", rtol=1e-4, atol=1e-5)
+    assert_close(kernels.gaussian(dev[1].detach(), dev[2].detach(), dev[3].detach()),
+                 orc.gaussian(pseudo, mu, sig), "gaussian")
+    scale = max(1.0, float(f64[2].grad.abs().max()))
+    assert_close(dev[0].grad, f64[0].grad.float(), "node_feat grad")
+    assert_close(dev[1].grad, f64[1].grad.float(), "pseudo grad", atol=1e-4)
+    assert_close(dev[2].grad, f64[2].grad.float(), "mu grad", rtol=1e-4, atol=1e-4 * scale)
+    assert_close(dev[3].grad, f64[3].grad.float(), "sigma grad", rtol=1e-4, atol=1e-4 * scale)
+
+
+@pytest.mark.parametrize("m,k,f", [(500, 20, 64), (300, 7, 128), (100, 40, 3), (64, 1, 6), (33, 5, 256)])
+def test_edgeconv(cuda, m, k, f):
+    g = torch.Generator().manual_seed(m)
+    src = torch.randint(0, m, (m * k,), generator=g, dtype=torch.int32)
+    hs, hd, go = (torch.randn(m, f, generator=g) for _ in range(3))
+    o_ref, i_ref = orc.edgeconv_forward(k, src, hs, hd)
+    out, idx = kernels.edgeconv_forward(k, src.to(cuda), hs.to(cuda), hd.to(cuda))
+    assert_equal(out, o_ref, "edgeconv out (a max of identical sums: bit-exact)")
+    assert_equal(idx, i_ref, "max_idx")
+    out_f, idx_f = fused_edgeconv.edgeconv_forward(k, src.to(cuda), hs.to(cuda), hd.to(cuda))
+    assert idx_f.dtype == torch.float32 and torch.equal(idx_f.int(), idx)
+    assert_close(kernels.edgeconv_backward(go.to(cuda), idx), orc.edgeconv_backward(go, i_ref), "grad_src")
+    # autograd surface
+    a = hs.to(cuda).requires_grad_(); b = hd.to(cuda).requires_grad_()
+    EdgeConvFuse(k, src.to(cuda), a, b).backward(go.to(cuda))
+    assert_close(a.grad, orc.edgeconv_backward(go, i_ref), "h_src grad"); assert_equal(b.grad, go, "h_dst grad")
+
+
+def test_edgeconv_ties_pick_first_neighbour(cuda):
+    hs = torch.zeros(4, 8); hd = torch.zeros(4, 8)
+    src = torch.tensor([3, 1, 2, 0, 1, 1, 2, 3], dtype=torch.int32)
+    _, idx = kernels.edgeconv_forward(2, src.to(cuda), hs.to(cuda), hd.to(cuda))
+    assert idx[:, 0].tolist() == [3, 2, 1, 2]
+
+
+def test_c3_config_edgeconv_stack(cuda):
+    """Config 3 at reduced batch: kNN k=20 on unit-sphere clouds, widths 3-64-64-128, through the layer API."""
+    from dgnn_b200.layers import EdgeConv
+    x = synth.unit_sphere_clouds(4, 512, seed=3)
+    src = synth.knn_src_ind(x, 20)
+    feat = x.reshape(-1, 3)
+    torch.manual_seed(3)
+    layers = [EdgeConv(3, 64), EdgeConv(64, 64), EdgeConv(64, 128)]
+    h_ref = feat
+    for l in layers:   # CPU reference of the same stack
+        hs = l.theta(h_ref); hd = l.phi(h_ref) - hs
+        h_ref = orc.edgeconv_forward(20, src, hs, hd)[0]
+    h = feat.to(cuda)
+    for l in layers:
+        h = l.to(cuda)(20, src.to(cuda), h)
+    assert_close(h, h_ref, "3-layer EdgeConv stack", rtol=1e-4, atol=1e-4)
+
+
+def test_uniform_fill_statistics(cuda):
+    u = kernels.uniform_fill((1 << 20,), seed=7, offset=0, device=cuda)
+    assert float(u.min()) > 0.0 and float(u.max()) <= 1.0
+    assert abs(float(u.mean()) - 0.5) < 2e-3 and abs(float(u.var()) - 1 / 12) < 2e-3
+    assert torch.equal(u, kernels.uniform_fill((1 << 20,), seed=7, offset=0, device=cuda))
+    assert not torch.equal(u, kernels.uniform_fill((1 << 20,), seed=8, offset=0, device=cuda))
