@@ -1,0 +1,402 @@
+"""Benchmark: one GATConv layer forward+backward on the large sharded-graph configuration.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE.json configs[3]): seeded R-MAT graph, 2.4 M nodes, 120 M directed
+edges (a=0.57, b=c=0.19), CSR with int64 row_ptr; features 2.4M x 100 N(0,1); 8 heads x 32.
+A step is the whole layer through the public API (projection GEMM, attention logits,
+fused softmax-aggregation, and the backward of all of it).  Prints ONE JSON line.
+The public datasets the reference trains on are not available offline; the graph and
+features are synthetic with the same sizes ("data": "synthetic").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, F, IN = 8, 32, 100
+SLOPE = 0.2
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--nodes", type=int, default=2_400_000)
+    ap.add_argument("--edges", type=int, default=120_000_000)
+    ap.add_argument("--cpu-sample-edges", type=int, default=2_000_000)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def algorithmic_bytes(n, e, h, f, ptr_bytes):
+    """No-reuse gather model: every per-edge gathered row counts in full, every dense
+    stream once per pass of the minimum-pass algorithm."""
+    fwd = (n + 1) * ptr_bytes + 4 * e + 4 * e * h + 4 * n * h + 4 * e * h * f + 4 * n * h * f + 8 * n * h
+    bwd = ((n + 1) * ptr_bytes + 8 * e + 12 * e * h + 4 * n * h + 4 * e * h * f + 12 * n * h * f + 4 * n * h * f
+           + 8 * e * h + 8 * n * h)
+    return fwd, bwd
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s in sm if s > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def make_graph(args, dev):
+    from dgnn_b200 import synth
+    return synth.rmat_graph(args.nodes, args.edges, seed=4, device=dev, ptr_dtype=torch.int64)
+
+
+def make_params(dev):
+    from dgnn_b200 import synth
+    g = torch.Generator().manual_seed(44)
+    W = synth.xavier_uniform((IN, H * F), IN, H * F, g)
+    al = synth.xavier_uniform((1, H, F), F, F, g)
+    ar = synth.xavier_uniform((1, H, F), F, F, g)
+    return W.to(dev), al.to(dev), ar.to(dev)
+
+
+def seeded_normal(shape, seed, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return torch.randn(shape, generator=g, device=dev)
+
+
+class PhaseTimer:
+    """CUDA-event brackets around the fused forward and backward calls, recorded on
+    the stream the kernels are launched on (torch's current stream)."""
+
+    def __init__(self):
+        self.spans = {"fwd": [], "bwd": []}
+        self.launches = 0
+        self.active = False
+
+    def wrap(self, module):
+        """Bracket the kernel-launching entry points of dgnn_b200.kernels; the number
+        after each name is how many kernels of this library one call launches."""
+        timer = self
+        for name, key, launches in (("gat_forward", "fwd", 3),          # rows, chunks, merge
+                                    ("gat_backward", "bwd", 7),         # rowstat, 3 column-pass, 3 row-reduce
+                                    ("gat_rowstat", "bwd_stat", 1),
+                                    ("gat_backward_cols", "bwd_cols", 6)):
+            inner = getattr(module, name)
+            self.spans.setdefault(key, [])
+
+            def bracket(*a, _inner=inner, _key=key, _launches=launches, **k):
+                if not timer.active:
+                    return _inner(*a, **k)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(); r = _inner(*a, **k); e.record()
+                timer.spans[_key].append((s, e)); timer.launches += _launches
+                return r
+
+            setattr(module, name, bracket)
+
+    def mean_ms(self, key):
+        v = [s.elapsed_time(e) for s, e in self.spans[key]]
+        return sum(v) / len(v) if v else None
+
+
+def cpu_sample(rp, ci, attn_row, attn_col, h, cot, sample_edges, repeats):
+    """Time the CPU oracle (fused forward+backward) on destination-row chunks of the
+    same graph; returns (edges_per_s, description, cores)."""
+    from oracle import dgnn_oracle as orc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    rp_c = rp.cpu()
+    n = rp_c.numel() - 1
+    nnz = int(rp_c[-1])
+    feat_c, ar_c, ac_c = h.detach().cpu(), attn_row.detach().cpu(), attn_col.detach().cpu()
+    total_e, total_t = 0, 0.0
+    gf_acc, gc_acc = torch.zeros_like(feat_c), torch.zeros_like(ac_c)   # zeroed once, outside the timed chunks
+    for i in range(repeats):
+        start_edge = (nnz // (repeats + 1)) * (i + 1)
+        r0 = int(torch.searchsorted(rp_c, torch.tensor([start_edge]))[0])
+        r1 = int(torch.searchsorted(rp_c, torch.tensor([start_edge + sample_edges]))[0])
+        r0, r1 = min(r0, n - 1), max(min(r1, n), min(r0, n - 1) + 1)
+        lo, hi = int(rp_c[r0]), int(rp_c[r1])
+        sub_ptr = (rp_c[r0:r1 + 1] - lo)
+        sub_col = ci[lo:hi].cpu()
+        go = cot[r0:r1].detach().cpu()
+        t0 = time.perf_counter()
+        o, emax, esum = orc._gat_forward_rows(ar_c[r0:r1], ac_c, sub_ptr, sub_col, SLOPE, feat_c)
+        orc._gat_backward_rows(SLOPE, sub_ptr, sub_col, emax, esum, feat_c, ar_c[r0:r1], ac_c, go, gf_acc, gc_acc)
+        total_t += time.perf_counter() - t0
+        total_e += hi - lo
+    desc = (f"{repeats} destination-row chunks of ~{sample_edges} edges of the same graph, fused GAT fwd+bwd with the "
+            f"pure-PyTorch CPU oracle (global source features), extrapolated linearly in edges")
+    return total_e / total_t, desc, cores
+
+
+def run_reference_arm(args, rank):
+    """The reference has no CPU implementation of this path; its arm is the CPU oracle
+    port on the host cores, one bounded chunk per step."""
+    if rank != 0:
+        return
+    dev = torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
+    rp, ci = make_graph(args, dev)
+    n = args.nodes
+    W, al, ar_ = make_params(dev)
+    x = seeded_normal((n, IN), 45, dev)
+    h = torch.matmul(x, W).view(n, H, F)
+    attn_row, attn_col = (al * h).sum(-1), (ar_ * h).sum(-1)
+    cot = seeded_normal((n, H, F), 46, dev)
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(rp, ci, attn_row, attn_col, h, cot, args.cpu_sample_edges // 4, 1)
+    t0 = time.perf_counter()
+    eps, desc, cores = cpu_sample(rp, ci, attn_row, attn_col, h, cot, args.cpu_sample_edges, max(1, min(args.steps, 5)))
+    wall = time.perf_counter() - t0
+    line = {"impl": "reference", "metric": "GAT layer fwd+bwd edges/sec", "value": eps, "unit": "edges/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * args.edges / eps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"GATConv fwd+bwd, R-MAT {args.nodes} nodes / {args.edges} edges, {H} heads x {F}, int64 row_ptr"},
+            "cpu_baseline": {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": eps, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": f"CPU oracle port timed for {wall:.1f} s; the reference itself has no CPU code for this path"}
+    print(json.dumps(line))
+
+
+def run_ours(args, rank, world, local):
+    from dgnn_b200 import dist as gdist
+    from dgnn_b200 import kernels
+    from dgnn_b200.operators import GATConvFuse
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.backends.cuda.matmul.allow_tf32 = False      # fp32 parity for the projection GEMM
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    n, nnz = args.nodes, args.edges
+    rp, ci = make_graph(args, dev)
+    W, al, ar_ = make_params(dev)
+    W.requires_grad_(); al.requires_grad_(); ar_.requires_grad_()
+    timer = PhaseTimer()
+    timer.wrap(kernels)
+
+    # csr2csc is part of the preparation of the backward pass: timed on its own
+    torch.cuda.synchronize()
+    t_c = []
+    for _ in range(3):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); cp, ri, pm = kernels.csr2csc(rp, ci); e.record()
+        torch.cuda.synchronize(); t_c.append(s.elapsed_time(e))
+    csr2csc_ms = min(t_c)
+
+    if world == 1:
+        x = seeded_normal((n, IN), 45, dev)
+        cot = seeded_normal((n, H, F), 46, dev)
+
+        def step(x_in):
+            h = torch.matmul(x_in, W).view(-1, H, F)
+            a_row, a_col = (al * h).sum(-1), (ar_ * h).sum(-1)
+            out = GATConvFuse(a_row, a_col, rp, ci, cp, ri, pm, SLOPE, h, 0.0)
+            loss = (out * cot).sum()
+            loss.backward()
+            return loss
+        n_loc = n
+    else:
+        import torch.distributed as dist
+        shard = gdist.build_shard(rp, ci, rank, world)
+        del cp, ri, pm
+        r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
+        n_loc = r1 - r0
+        x = seeded_normal((n, IN), 45, dev)[r0:r1].contiguous()
+        cot = seeded_normal((n, H, F), 46, dev)[r0:r1].contiguous()
+        del rp, ci
+        torch.cuda.empty_cache()
+
+        def step(x_in):
+            h = torch.matmul(x_in, W).view(-1, H, F)
+            a_row, a_col = (al * h).sum(-1), (ar_ * h).sum(-1)
+            out = gdist.sharded_gat(a_row, a_col, h, shard, SLOPE)
+            loss = (out * cot).sum()
+            loss.backward()
+            for p in (W, al, ar_):            # data-parallel parameter gradients
+                dist.all_reduce(p.grad)
+            return loss
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(x)
+        W.grad = None; al.grad = None; ar_.grad = None
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    timer.active = True
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.steps):
+        step(x)
+        W.grad = None; al.grad = None; ar_.grad = None
+    e.record()
+    sync_all()
+    timer.active = False
+    clocks = sampler.stop() if rank == 0 else None
+    ms = s.elapsed_time(e) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+
+    # end to end: features come from pinned host memory every step, the loss goes back
+    e2e = None
+    if not args.no_e2e:
+        x_host = x.cpu().pin_memory()
+        loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+        x_dev = torch.empty_like(x)
+        for _ in range(2):
+            x_dev.copy_(x_host, non_blocking=True); loss_host.copy_(step(x_dev), non_blocking=True)
+        sync_all()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for _ in range(args.steps):
+            x_dev.copy_(x_host, non_blocking=True)
+            loss_host.copy_(step(x_dev), non_blocking=True)
+            W.grad = None; al.grad = None; ar_.grad = None
+        e2.record()
+        sync_all()
+        ms2 = s2.elapsed_time(e2) / args.steps
+        if world > 1:
+            t = torch.tensor([ms2], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms2 = float(t[0])
+        e2e = {"value": nnz / (ms2 * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
+               "d2h_bytes_per_step": 4 * world, "ms_per_step": ms2}
+
+    if rank != 0:
+        if world > 1:
+            torch.distributed.barrier()
+            torch.distributed.destroy_process_group()
+        return
+
+    peak, peak_kind = load_peaks()
+    fwd_b, bwd_b = algorithmic_bytes(n, nnz, H, F, 8)
+    fwd_ms, bwd_ms = timer.mean_ms("fwd"), timer.mean_ms("bwd")
+    line = {
+        "metric": "GAT layer fwd+bwd edges/sec", "value": nnz / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"GATConv layer fwd+bwd, R-MAT {n} nodes / {nnz} edges (a=0.57,b=c=0.19), in={IN}, {H} heads x {F}, "
+                               f"int64 row_ptr, row-block sharded over {world} GPU(s)",
+                   "l2": "inputs (2.46 GB feature tensor per pass) exceed the 126 MB L2; no flush needed",
+                   "csr2csc_ms": csr2csc_ms},
+        "gpu_launches": timer.launches,
+        "clocks": clocks,
+    }
+    if e2e:
+        line["e2e"] = e2e
+    if world == 1 and fwd_ms and bwd_ms:
+        ach = fwd_b / (fwd_ms * 1e-3) / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "k_rows<GatFwdOp<2,false>> (+chunk/merge kernels of the same call)",
+                            "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / peak,
+                            "traffic": None, "algorithmic_bytes": fwd_b, "ms": fwd_ms}
+        ach_b = bwd_b / (bwd_ms * 1e-3) / 1e9
+        line["roofline_bwd"] = {"bound": "hbm", "kernel": "k_gat_rowstat + k_rows<GatBwdOp<2,false>> + row reduction",
+                                "achieved": ach_b, "peak": peak, "unit": "GB/s", "frac": ach_b / peak,
+                                "algorithmic_bytes": bwd_b, "ms": bwd_ms}
+        tot = (fwd_b + bwd_b) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+        line["fused_op"] = {"ms": fwd_ms + bwd_ms, "edges_per_s": nnz / ((fwd_ms + bwd_ms) * 1e-3), "achieved_gbs": tot,
+                            "frac_of_peak": tot / peak}
+    if world == 1 and not args.no_cpu_baseline:
+        with torch.no_grad():
+            h = torch.matmul(x, W).view(-1, H, F)
+            a_row, a_col = (al * h).sum(-1), (ar_ * h).sum(-1)
+        eps, desc, cores = cpu_sample(rp, ci, a_row, a_col, h, cot, args.cpu_sample_edges, 3)
+        line["cpu_baseline"] = {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc}
+    print(json.dumps(line))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    args = parse()
+    rank, world, local = dist_env()
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    run_ours(args, rank, world, local)
+
+
+if __name__ == "__main__":
+    main()

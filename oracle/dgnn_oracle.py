@@ -293,17 +293,22 @@ def _gat_forward_rows(attn_row_blk, attn_col, sub_ptr, sub_col, slope, in_feat):
     return out, emax, esum
 
 
-def _gat_backward_rows(slope, sub_ptr, sub_col, emax, esum, in_feat, attn_row_blk, attn_col, grad_blk):
+def _gat_backward_rows(slope, sub_ptr, sub_col, emax, esum, in_feat, attn_row_blk, attn_col, grad_blk,
+                       grad_feat_acc=None, grad_col_acc=None):
+    """Backward of one destination-row chunk; when the accumulators are given the
+    source-side gradients are added into them in place (no full-size temporaries)."""
     rows = edge_rows(sub_ptr)
     cols = sub_col.long()
     nb, h = attn_row_blk.shape
     leaky = leaky_relu(attn_row_blk[rows] + attn_col[cols], slope)
     alpha = torch.exp(leaky - emax[rows]) / esum[rows]
-    gf = torch.zeros_like(in_feat).index_add_(0, cols, alpha[:, :, None] * grad_blk[rows])
+    gf = torch.zeros_like(in_feat) if grad_feat_acc is None else grad_feat_acc
+    gf.index_add_(0, cols, alpha[:, :, None] * grad_blk[rows])
     g = (grad_blk[rows] * in_feat[cols]).sum(-1)
     s_row = torch.zeros((nb, h), dtype=g.dtype).index_add_(0, rows, alpha * g)
     d = alpha * (g - s_row[rows])
     d = torch.where(leaky < 0, d * slope, d)
     gr = torch.zeros((nb, h), dtype=g.dtype).index_add_(0, rows, d)
-    gc = torch.zeros_like(attn_col).index_add_(0, cols, d)
+    gc = torch.zeros_like(attn_col) if grad_col_acc is None else grad_col_acc
+    gc.index_add_(0, cols, d)
     return gf, gr, gc
