@@ -108,7 +108,8 @@ def test_gmm_forward_backward(cuda, kind, k, f, dim):
     dev = [t.to(cuda).requires_grad_() for t in (feat, pseudo, mu, sig)]
     out = GmmConvFuse(rp.to(cuda), ci.to(cuda), cp.int().to(cuda), ri.int().to(cuda), pm.int().to(cuda), *dev)
     out.backward(go.to(cuda))
-    assert_close(out, ref.float(), "gmm out", rtol=1e-4, atol=1e-5)
+    # rows of thousands of edges sum in a different order than the fp64 reference: scale atol with the row length
+    assert_close(out, ref.float(), "gmm out", rtol=1e-4, atol=1e-5 if kind != "long" else 5e-4)
     assert_close(kernels.gaussian(dev[1].detach(), dev[2].detach(), dev[3].detach()),
                  orc.gaussian(pseudo, mu, sig), "gaussian")
     scale = max(1.0, float(f64[2].grad.abs().max()))
