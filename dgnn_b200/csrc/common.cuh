@@ -20,6 +20,9 @@ typedef long long i64;
 constexpr int DGNN_SEG = 1024;         // edges per chunk for long-row splitting
 constexpr int DGNN_WARPS = 8;          // warps per CTA in the row kernels
 constexpr int DGNN_THREADS = DGNN_WARPS * 32;
+constexpr int DGNN_ROW_WARPS = 4;      // warps per CTA in the strided short-row kernel
+constexpr int DGNN_ROW_THREADS = DGNN_ROW_WARPS * 32;
+constexpr int DGNN_ROW_WAVES = 8;      // CTAs launched per SM-resident CTA slot (pool oversubscription)
 constexpr float DGNN_NEG_INIT = -1e38f;  // initial running maximum (matches the reference)
 
 // index-pointer arrays come as int32 or int64; the width is uniform per launch
@@ -50,6 +53,9 @@ __device__ __forceinline__ float dot4(const float4& a, const float4& b) {
   return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
 }
 __device__ __forceinline__ float leaky(float x, float slope) { return x > 0.f ? x : x * slope; }
+// exp through the hardware ex2 unit: relative error ~2^-22 plus |x| * 2^-24 from the
+// log2(e) scaling, far inside the fp32 tolerance of the operators (1e-4 relative)
+__device__ __forceinline__ float fast_exp(float x) { return __expf(x); }
 
 // Feature rows are H*F floats viewed as HF4 = H*F/4 float4 vectors.  Lane l owns
 // vectors q = l + 32*v (v < VPL); vector q belongs to head q >> f4_shift where
@@ -102,18 +108,22 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 //   finalize(State&, row, lane), store_partial(State&, slot, lane),
 //   merge_partial(State&, slot, lane)
 // ---------------------------------------------------------------------------
+// Short rows: a fixed pool of warps strides over the rows (row = warp id, + pool
+// size, ...), so every warp sees a similar mix of degrees and no CTA waits on one
+// heavy row while its other warps sit idle.
 template <class Op>
-__global__ void __launch_bounds__(DGNN_THREADS) k_rows(const Op op) {
+__global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op) {
   const int lane = threadIdx.x & 31;
-  const i64 r = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
-  if (r >= op.n_rows) return;
-  const i64 lb = ldp(op.indptr, op.idx_bits, r);
-  const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
-  if (hb - lb > DGNN_SEG) return;  // long row: chunk + merge kernels own it
-  typename Op::State st;
-  op.init(st, r, lane);
-  op.range(st, r, lb, hb, lane);
-  op.finalize(st, r, lane);
+  const i64 stride = (i64)gridDim.x * DGNN_ROW_WARPS;
+  for (i64 r = (i64)blockIdx.x * DGNN_ROW_WARPS + (threadIdx.x >> 5); r < op.n_rows; r += stride) {
+    const i64 lb = ldp(op.indptr, op.idx_bits, r);
+    const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
+    if (hb - lb > DGNN_SEG) continue;  // long row: chunk + merge kernels own it
+    typename Op::State st;
+    op.init(st, r, lane);
+    op.range(st, r, lb, hb, lane);
+    op.finalize(st, r, lane);
+  }
 }
 
 template <class Op>
@@ -164,7 +174,14 @@ static inline i64 dgnn_num_chunks(i64 nnz) { return (nnz + DGNN_SEG - 1) / DGNN_
 template <class Op>
 static inline int dgnn_launch_trio(const Op& op, bool has_partials, cudaStream_t s) {
   if (op.n_rows <= 0) return DGNN_OK;
-  k_rows<Op><<<dgnn_grid(op.n_rows, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
+  {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const i64 pool = (i64)sms * Op::MIN_BLOCKS * DGNN_ROW_WAVES;
+    const i64 need = (op.n_rows + DGNN_ROW_WARPS - 1) / DGNN_ROW_WARPS;
+    k_rows<Op><<<(unsigned)(need < pool ? need : pool), DGNN_ROW_THREADS, 0, s>>>(op);
+  }
   if (op.nnz > DGNN_SEG) {
     const i64 nc = dgnn_num_chunks(op.nnz);
     k_chunks<Op><<<dgnn_grid(2 * nc, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);

@@ -20,8 +20,9 @@ namespace {
 template <int VPL> struct Unroll { static constexpr int U = VPL <= 2 ? 4 : 2; };
 
 // ------------------------------------------------------------------ forward
-template <int VPL, bool MASK>
+template <int VPL, bool MASK, bool FULL>
 struct GatFwdOp {
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
   i64 n_rows, nnz;
   const void* indptr;
   int idx_bits;
@@ -55,55 +56,60 @@ struct GatFwdOp {
     }
   }
 
+  // one batch of U edges starting at tile slot k; ALL = every slot of the batch holds an edge
+  template <bool ALL>
+  __device__ __forceinline__ void batch(State& st, int my_c, i64 ebase, int k, int cnt) const {
+    constexpr int U = Unroll<VPL>::U;
+    int c[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) c[u] = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
+    float s[U][VPL];
+    float4 x[U][VPL];
+    bool keep[U][VPL];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act[v]);
+        s[u][v] = ok ? __ldg(attn_col + (i64)c[u] * H + st.lm.hd[v]) : 0.f;
+        x[u][v] = ok ? ld4(in_feat + (i64)c[u] * hf4 + st.lm.q[v]) : zero4();
+        keep[u][v] = ok;
+        if (MASK) keep[u][v] = ok ? (__ldg(mask + (ebase + k + u) * H + st.lm.hd[v]) > drop_p) : false;
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (!FULL && !st.lm.act[v]) continue;
+      float l[U];
+      float bm = st.m[v];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        l[u] = (ALL || k + u < cnt) ? leaky(st.ar[v] + s[u][v], slope) : DGNN_NEG_INIT;
+        bm = fmaxf(bm, l[u]);
+      }
+      const float sc = fast_exp(st.m[v] - bm);  // 1 when the maximum did not move
+      st.z[v] *= sc;
+      scale4(st.acc[v], sc);
+      st.m[v] = bm;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (ALL || k + u < cnt) {
+          const float p = fast_exp(l[u] - bm);
+          st.z[v] += p;
+          if (!MASK || keep[u][v]) fma4(st.acc[v], p, x[u][v]);
+        }
+      }
+    }
+  }
+
   __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
     constexpr int U = Unroll<VPL>::U;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
-      for (int k = 0; k < cnt; k += U) {
-        int c[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) c[u] = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
-        float s[U][VPL];
-        float4 x[U][VPL];
-        bool keep[U][VPL];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-#pragma unroll
-          for (int v = 0; v < VPL; ++v) {
-            const bool ok = (k + u < cnt) && st.lm.act[v];
-            s[u][v] = ok ? __ldg(attn_col + (i64)c[u] * H + st.lm.hd[v]) : 0.f;
-            x[u][v] = ok ? ld4(in_feat + (i64)c[u] * hf4 + st.lm.q[v]) : zero4();
-            keep[u][v] = true;
-            if (MASK) keep[u][v] = ok ? (__ldg(mask + (base + k + u) * H + st.lm.hd[v]) > drop_p) : false;
-          }
-        }
-#pragma unroll
-        for (int v = 0; v < VPL; ++v) {
-          if (!st.lm.act[v]) continue;
-          float l[U];
-          float bm = st.m[v];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            l[u] = (k + u < cnt) ? leaky(st.ar[v] + s[u][v], slope) : DGNN_NEG_INIT;
-            bm = fmaxf(bm, l[u]);
-          }
-          if (bm > st.m[v]) {
-            const float sc = expf(st.m[v] - bm);
-            st.z[v] *= sc;
-            scale4(st.acc[v], sc);
-            st.m[v] = bm;
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            if (k + u < cnt) {
-              const float p = expf(l[u] - st.m[v]);
-              st.z[v] += p;
-              if (keep[u][v]) fma4(st.acc[v], p, x[u][v]);
-            }
-          }
-        }
-      }
+      int k = 0;
+      for (; k + U <= cnt; k += U) batch<true>(st, my_c, base, k, cnt);
+      if (k < cnt) batch<false>(st, my_c, base, k, cnt);
     }
   }
 
@@ -144,7 +150,7 @@ struct GatFwdOp {
       const float mi = p[hf4 * 4 + st.lm.hd[v]];
       const float zi = p[hf4 * 4 + H + st.lm.hd[v]];
       const float mn = fmaxf(st.m[v], mi);
-      const float s1 = expf(st.m[v] - mn), s2 = expf(mi - mn);
+      const float s1 = fast_exp(st.m[v] - mn), s2 = fast_exp(mi - mn);
       st.z[v] = st.z[v] * s1 + zi * s2;
       scale4(st.acc[v], s1);
       fma4(st.acc[v], s2, ai);
@@ -207,7 +213,7 @@ k_gat_rowstat(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, c
   for (int v = 0; v < VPL; ++v) {
     if (lm.lead[v]) {
       const i64 i = r * H + lm.hd[v];
-      pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), __ldg(edge_sum + i), s[v]);
+      pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), 1.f / __ldg(edge_sum + i), s[v]);
     }
   }
 }
@@ -221,12 +227,13 @@ k_gat_rowstat_generic(i64 n_rows, int H, int F, const float* attn_row, const flo
   float s = 0.f;
   for (int f = lane; f < F; f += 32) s = fmaf(__ldg(grad + w * F + f), __ldg(out + w * F + f), s);
   for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(DGNN_FULL, s, o);
-  if (lane == 0) pack[w] = make_float4(attn_row[w], edge_max[w], edge_sum[w], s);
+  if (lane == 0) pack[w] = make_float4(attn_row[w], edge_max[w], 1.f / edge_sum[w], s);
 }
 
 // ------------------------------------------------------------ backward cols
-template <int VPL, bool MASK>
+template <int VPL, bool MASK, bool FULL>
 struct GatBwdOp {
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? 4 : (VPL == 4 ? 3 : 2);
   i64 n_rows, nnz;      // "rows" of the CSC form = source columns
   const void* indptr;   // col_ptr
   int idx_bits;
@@ -262,54 +269,60 @@ struct GatBwdOp {
     }
   }
 
+  template <bool ALL>
+  __device__ __forceinline__ void batch(State& st, int my_r, int my_p, int k, int cnt) const {
+    constexpr int U = Unroll<VPL>::U;
+    int r[U], pp[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      r[u] = __shfl_sync(DGNN_FULL, my_r, (k + u) & 31);
+      pp[u] = __shfl_sync(DGNN_FULL, my_p, (k + u) & 31);
+    }
+    float4 pk[U][VPL], g4[U][VPL];
+    bool keep[U][VPL];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act[v]);
+        pk[u][v] = ok ? ld4(pack + (i64)r[u] * H + st.lm.hd[v]) : zero4();
+        g4[u][v] = ok ? ld4(grad_out + (i64)r[u] * hf4 + st.lm.q[v]) : zero4();
+        keep[u][v] = ok;
+        if (MASK) keep[u][v] = ok ? (__ldg(mask + (i64)pp[u] * H + st.lm.hd[v]) > drop_p) : false;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float d[VPL];
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) d[v] = dot4(g4[u][v], st.x[v]);
+      head_reduce<VPL>(d, f4_shift);  // executed by all lanes, also for slots past cnt
+      if (ALL || k + u < cnt) {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          if (!FULL && !st.lm.act[v]) continue;
+          const float l = leaky(pk[u][v].x + st.ac[v], slope);
+          const float alpha = fast_exp(l - pk[u][v].y) * pk[u][v].z;   // pack.z = 1 / edge_sum
+          const float kp = (!MASK || keep[u][v]) ? inv_keep : 0.f;
+          float de = alpha * (d[v] * kp - pk[u][v].w);
+          de = l < 0.f ? de * slope : de;
+          st.gc[v] += de;
+          fma4(st.acc[v], alpha * kp, g4[u][v]);
+          if (st.lm.lead[v]) grad_edge[(i64)pp[u] * H + st.lm.hd[v]] = de;
+        }
+      }
+    }
+  }
+
   __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
     constexpr int U = Unroll<VPL>::U;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
       const int my_p = lane < cnt ? __ldg(permute + base + lane) : 0;
-      for (int k = 0; k < cnt; k += U) {
-        int r[U], pp[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          r[u] = __shfl_sync(DGNN_FULL, my_r, (k + u) & 31);
-          pp[u] = __shfl_sync(DGNN_FULL, my_p, (k + u) & 31);
-        }
-        float4 pk[U][VPL], g4[U][VPL];
-        bool keep[U][VPL];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-#pragma unroll
-          for (int v = 0; v < VPL; ++v) {
-            const bool ok = (k + u < cnt) && st.lm.act[v];
-            pk[u][v] = ok ? ld4(pack + (i64)r[u] * H + st.lm.hd[v]) : make_float4(0.f, 0.f, 1.f, 0.f);
-            g4[u][v] = ok ? ld4(grad_out + (i64)r[u] * hf4 + st.lm.q[v]) : zero4();
-            keep[u][v] = ok;
-            if (MASK) keep[u][v] = ok ? (__ldg(mask + (i64)pp[u] * H + st.lm.hd[v]) > drop_p) : false;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          float d[VPL];
-#pragma unroll
-          for (int v = 0; v < VPL; ++v) d[v] = dot4(g4[u][v], st.x[v]);
-          head_reduce<VPL>(d, f4_shift);  // uniform: executed by all lanes, also past cnt
-          if (k + u < cnt) {
-#pragma unroll
-            for (int v = 0; v < VPL; ++v) {
-              if (!st.lm.act[v]) continue;
-              const float l = leaky(pk[u][v].x + st.ac[v], slope);
-              const float alpha = expf(l - pk[u][v].y) / pk[u][v].z;
-              const float kp = keep[u][v] ? inv_keep : 0.f;
-              float de = alpha * (d[v] * kp - pk[u][v].w);
-              if (l < 0.f) de *= slope;
-              st.gc[v] += de;
-              fma4(st.acc[v], alpha * kp, g4[u][v]);
-              if (st.lm.lead[v]) grad_edge[(i64)pp[u] * H + st.lm.hd[v]] = de;
-            }
-          }
-        }
-      }
+      int k = 0;
+      for (; k + U <= cnt; k += U) batch<true>(st, my_r, my_p, k, cnt);
+      if (k < cnt) batch<false>(st, my_r, my_p, k, cnt);
     }
   }
 
@@ -366,7 +379,7 @@ k_gat_bwd_cols_generic(i64 n_cols, int H, int F, const void* col_ptr, int idx_bi
       d = fmaf(__ldg(grad_out + (r * H + h) * F + f), __ldg(in_feat + (c * H + h) * F + f), d);
     for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(DGNN_FULL, d, o);
     const float l = leaky(pk.x + ac, slope);
-    const float alpha = expf(l - pk.y) / pk.z;
+    const float alpha = expf(l - pk.y) * pk.z;
     const float kp = (!mask || __ldg(mask + pp * H + h) > drop_p) ? inv_keep : 0.f;
     float de = alpha * (d * kp - pk.w);
     if (l < 0.f) de *= slope;
@@ -380,7 +393,7 @@ k_gat_bwd_cols_generic(i64 n_cols, int H, int F, const void* col_ptr, int idx_bi
       const i64 r = row_ind[e];
       const float4 pk = pack[r * H + h];
       const float kp = (!mask || __ldg(mask + (i64)permute[e] * H + h) > drop_p) ? inv_keep : 0.f;
-      const float alpha = expf(leaky(pk.x + ac, slope) - pk.y) / pk.z;
+      const float alpha = expf(leaky(pk.x + ac, slope) - pk.y) * pk.z;
       acc = fmaf(alpha * kp, __ldg(grad_out + (r * H + h) * F + fb), acc);
     }
     grad_feat[(c * H + h) * F + fb] = acc;
@@ -465,12 +478,12 @@ inline FastShape fast_shape(int h, int f) {
 inline i64 fwd_slot_stride(int h, int f) { return (i64)h * f + up4(2 * (i64)h); }
 inline i64 bwd_slot_stride(int h, int f) { return (i64)h * f + up4((i64)h); }
 
-template <int VPL, bool MASK>
+template <int VPL, bool MASK, bool FULL>
 int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
                const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
                float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
                void* ws, cudaStream_t s) {
-  GatFwdOp<VPL, MASK> op;
+  GatFwdOp<VPL, MASK, FULL> op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
   op.col_ind = col_ind; op.attn_row = attn_row; op.attn_col = attn_col;
@@ -481,12 +494,12 @@ int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const voi
   return dgnn_launch_trio(op, true, s);
 }
 
-template <int VPL, bool MASK>
+template <int VPL, bool MASK, bool FULL>
 int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const void* col_ptr, int idx_bits,
                const int* row_ind, const int* permute, const float* pack, const float* mask,
                const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
                float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, cudaStream_t s) {
-  GatBwdOp<VPL, MASK> op;
+  GatBwdOp<VPL, MASK, FULL> op;
   op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
   op.row_ind = row_ind; op.permute = permute; op.pack = reinterpret_cast<const float4*>(pack);
@@ -498,12 +511,16 @@ int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const voi
   return dgnn_launch_trio(op, true, s);
 }
 
-#define DGNN_DISPATCH_VPL(vpl, MASKED, CALL)                         \
-  switch (vpl) {                                                     \
-    case 1: return MASKED ? CALL(1, true) : CALL(1, false);          \
-    case 2: return MASKED ? CALL(2, true) : CALL(2, false);          \
-    case 4: return MASKED ? CALL(4, true) : CALL(4, false);          \
-    default: return MASKED ? CALL(8, true) : CALL(8, false);         \
+// FULL = the row is exactly 32*VPL float4 vectors wide: no lane is ever idle
+#define DGNN_DISPATCH_VM(V, MASKED, FULLW, CALL)                                       \
+  return MASKED ? (FULLW ? CALL(V, true, true) : CALL(V, true, false))                 \
+                : (FULLW ? CALL(V, false, true) : CALL(V, false, false));
+#define DGNN_DISPATCH_VPL(vpl, MASKED, FULLW, CALL)         \
+  switch (vpl) {                                            \
+    case 1: DGNN_DISPATCH_VM(1, MASKED, FULLW, CALL)        \
+    case 2: DGNN_DISPATCH_VM(2, MASKED, FULLW, CALL)        \
+    case 4: DGNN_DISPATCH_VM(4, MASKED, FULLW, CALL)        \
+    default: DGNN_DISPATCH_VM(8, MASKED, FULLW, CALL)       \
   }
 
 struct BwdLayout {
@@ -560,10 +577,10 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_
         return DGNN_ERR_WORKSPACE;
       if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
     }
-#define CALL_FWD(V, M)                                                                               \
-  launch_fwd<V, M>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
+#define CALL_FWD(V, M, FW)                                                                           \
+  launch_fwd<V, M, FW>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
                    negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, s)
-    DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, CALL_FWD)
+    DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, fs.hf4 == 32 * fs.vpl, CALL_FWD)
 #undef CALL_FWD
   }
   k_gat_fwd_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
@@ -637,11 +654,11 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
   if (n_cols > 0) {
     if (fs.ok && aligned16(in_feat) && aligned16(grad_out) && aligned16(grad_feat)) {
       int rc;
-#define CALL_BWD(V, M)                                                                                  \
-  launch_bwd<V, M>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
+#define CALL_BWD(V, M, FW)                                                                              \
+  launch_bwd<V, M, FW>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
                    attn_col, grad_out, negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, \
                    col_part, s)
-      auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, CALL_BWD) };
+      auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, fs.hf4 == 32 * fs.vpl, CALL_BWD) };
 #undef CALL_BWD
       rc = run();
       if (rc) return rc;

@@ -31,6 +31,7 @@ inline FastShape fast_shape(int h, int f) {
 // ------------------------------------------------------------------- SDDMM
 template <int VPL>
 struct SddmmOp {
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
   i64 n_rows, nnz;
   const void* indptr;
   int idx_bits;
@@ -131,6 +132,7 @@ __device__ __forceinline__ float gauss_w(const float* pseudo, const float* mu, c
 
 template <int VPL>
 struct GmmOp {
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
   i64 n_rows, nnz;
   const void* indptr;
   int idx_bits;

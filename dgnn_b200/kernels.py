@@ -57,7 +57,7 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
 
 
 def gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out):
-    """pack[r,h] = (attn_row, edge_max, edge_sum, <grad_out[r,h], out[r,h]>) as [N,H,4]."""
+    """pack[r,h] = (attn_row, edge_max, 1/edge_sum, <grad_out[r,h], out[r,h]>) as [N,H,4]."""
     out = _cuda_f32(out, "out")
     grad_out = _cuda_f32(grad_out, "grad_out")
     n, h, f = _dims3(out, "out")

@@ -68,7 +68,7 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f,
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* Row statistics for the backward pass: pack[r,h] = (attn_row, edge_max,
- * edge_sum, S) with S[r,h] = <grad_out[r,h,:], out[r,h,:]>, which equals the
+ * 1/edge_sum, S) with S[r,h] = <grad_out[r,h,:], out[r,h,:]>, which equals the
  * reference's per-row sum of alpha*g (fused_gatconv_kernel.cu:903-929) without
  * an edge pass.  pack is [n_rows,h,4] fp32, 16-byte aligned. */
 int dgnn_gat_rowstat(int64_t n_rows, int h, int f,

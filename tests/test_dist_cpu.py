@@ -24,7 +24,7 @@ class OracleBackend:
 
     @staticmethod
     def gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out):
-        return torch.stack([attn_row, edge_max, edge_sum, (grad_out * out).sum(-1)], dim=-1).contiguous()
+        return torch.stack([attn_row, edge_max, 1.0 / edge_sum.clamp(min=1e-30), (grad_out * out).sum(-1)], dim=-1).contiguous()
 
     @staticmethod
     def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_feat, attn_col, grad_out, slope):
@@ -35,7 +35,7 @@ class OracleBackend:
         rows_csr = torch.empty_like(cols)
         rows_csr[permute.long()] = row_ind.long()
         assert torch.equal(rows_csr, orc.edge_rows(row_ptr)), "permute / row_ptr inconsistent"
-        safe_sum = pack[..., 2].clamp(min=1e-30)
+        safe_sum = 1.0 / pack[..., 2].clamp(min=1e-30)
         return orc.gat_backward(slope, 0.0, row_ptr, col_ind, pack[..., 1], safe_sum, None, in_feat,
                                 pack[..., 0], attn_col, grad_out, s_row=pack[..., 3])
 
