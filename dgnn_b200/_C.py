@@ -52,6 +52,9 @@ SIGNATURES = {
     "dgnn_edgeconv_backward": (c_int, [c_i64, c_int, c_p, c_p, c_p, c_p]),
     "dgnn_csr2csc_workspace_bytes": (c_sz, [c_i64, c_i64, c_i64]),
     "dgnn_csr2csc": (c_int, [c_i64, c_i64, c_i64, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
+    "dgnn_csr2csc_static_max_nnz": (c_i64, []),
+    "dgnn_csr2csc_static_max_cols": (c_i64, []),
+    "dgnn_csr2csc_static": (c_int, [c_i64, c_i64, c_i64, c_p, c_int, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_coo2csr": (c_int, [c_i64, c_i64, c_p, c_p, c_int, c_p]),
 }
 

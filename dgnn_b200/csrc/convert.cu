@@ -9,6 +9,7 @@
 // cuSPARSE conversion (and scipy's tocsc) produce.  col_ptr is the exclusive
 // scan of the column histogram.  Only integer atomics (commutative) are used.
 #include "common.cuh"
+#include <mutex>
 
 namespace {
 
@@ -299,6 +300,39 @@ int dgnn_csr2csc_impl(i64 n_rows, i64 n_cols, i64 nnz, const void* row_ptr, int 
 
 size_t dgnn_csr2csc_scratch_bytes(i64 n_cols, i64 nnz) { return c2c_layout(n_cols, nnz).total; }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant: the scratch of the conversion lives in a fixed array
+// inside the library image instead of a caller-supplied workspace.
+// ---------------------------------------------------------------------------
+constexpr i64 STATIC_MAX_NNZ = 1 << 20;    // entries
+constexpr i64 STATIC_MAX_COLS = 1 << 20;   // columns
+constexpr size_t STATIC_SCRATCH_BYTES = size_t(32) << 20;  // 32 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_csr2csc_scratch[STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mu;
+char* g_static_ptr[MAX_DEVICES] = {nullptr};
+
+// The symbol name is only a host-side handle; the device address has to be asked
+// for, once per device, while that device is current.
+int static_scratch_for_current_device(char** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= MAX_DEVICES) return DGNN_ERR_VALUE;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_csr2csc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_ptr[dev] = static_cast<char*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return DGNN_OK;
+}
+}  // namespace
+
 extern "C" {
 
 size_t dgnn_csr2csc_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz) {
@@ -328,6 +362,26 @@ int dgnn_coo2csr(int64_t nnz, int64_t m, const int32_t* row_ind, void* row_ptr, 
   k_coo2csr<<<dgnn_grid(m + 1, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(nnz, m, row_ind, row_ptr, idx_bits);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+int64_t dgnn_csr2csc_static_max_nnz(void) { return STATIC_MAX_NNZ; }
+int64_t dgnn_csr2csc_static_max_cols(void) { return STATIC_MAX_COLS; }
+
+int dgnn_csr2csc_static(int64_t n_rows, int64_t n_cols, int64_t nnz, const void* row_ptr, int idx_bits,
+                        const int32_t* col_ind, void* col_ptr, int32_t* row_ind, int32_t* permute, void* stream) {
+  if (n_rows < 0 || n_cols < 0 || nnz < 0) return DGNN_ERR_SHAPE;
+  if (idx_bits != 32 && idx_bits != 64) return DGNN_ERR_IDX_BITS;
+  if (n_rows > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;
+  if (nnz > STATIC_MAX_NNZ || n_cols > STATIC_MAX_COLS) return DGNN_ERR_STATIC_LIMIT;
+  if (c2c_layout(n_cols, nnz).total > STATIC_SCRATCH_BYTES) return DGNN_ERR_STATIC_LIMIT;
+  if (!row_ptr || !col_ptr || (nnz > 0 && (!col_ind || !row_ind || !permute))) return DGNN_ERR_NULL;
+  char* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  // every region of the scratch that is read is written first by this call (the column
+  // histogram is cleared, the rest is overwritten), so stale contents of the previous call do no harm
+  return dgnn_csr2csc_impl(n_rows, n_cols, nnz, row_ptr, idx_bits, col_ind, col_ptr, row_ind, permute, scratch,
+                           reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -49,6 +49,7 @@ const char* dgnn_status_string(int status) {
     case DGNN_ERR_OVERFLOW: return "size does not fit the index type";
     case DGNN_ERR_WORKSPACE: return "workspace missing or too small";
     case DGNN_ERR_VALUE: return "scalar argument out of range";
+    case DGNN_ERR_STATIC_LIMIT: return "size exceeds the fixed scratch of the allocation-free entry point";
     default: break;
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));

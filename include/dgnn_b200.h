@@ -38,7 +38,8 @@ typedef enum dgnn_status {
   DGNN_ERR_ALIGN = -4,       /* pointer not aligned for vector access */
   DGNN_ERR_OVERFLOW = -5,    /* size does not fit the index type */
   DGNN_ERR_WORKSPACE = -6,   /* workspace missing or too small */
-  DGNN_ERR_VALUE = -7        /* scalar argument out of range */
+  DGNN_ERR_VALUE = -7,       /* scalar argument out of range */
+  DGNN_ERR_STATIC_LIMIT = -8 /* size beyond the fixed scratch of an allocation-free entry point */
 } dgnn_status;
 
 int dgnn_version(void);
@@ -173,6 +174,25 @@ int dgnn_csr2csc(int64_t n_rows, int64_t n_cols, int64_t nnz,
                  const void* row_ptr, int idx_bits, const int32_t* col_ind,
                  void* col_ptr, int32_t* row_ind, int32_t* permute,
                  void* workspace, size_t workspace_bytes, void* stream);
+/* Same conversion as dgnn_csr2csc for callers that cannot hand over a workspace
+ * because they are not allowed to allocate device memory at that point: code
+ * that runs after a host application has claimed the whole GPU for its own pool,
+ * plug-ins that are given buffers for inputs and outputs only, and services that
+ * forbid allocation after start-up so that memory use stays fixed.  It has no
+ * counterpart in the reference.  The scratch is a 32 MiB array inside the library
+ * image (every GPU that loads the library holds it until the process exits), so
+ * sizes are limited: nnz <= dgnn_csr2csc_static_max_nnz() (2^20) and n_cols <=
+ * dgnn_csr2csc_static_max_cols() (2^20); anything larger returns
+ * DGNN_ERR_STATIC_LIMIT.  The call neither allocates nor frees.  The first call
+ * on each device looks up the array's device address (cudaGetSymbolAddress) with
+ * that device current; make that first call before any stream capture begins.
+ * All calls on a device share the one array: calls that may overlap on the GPU
+ * (different streams, different threads) race and must be serialised by the caller. */
+int64_t dgnn_csr2csc_static_max_nnz(void);
+int64_t dgnn_csr2csc_static_max_cols(void);
+int dgnn_csr2csc_static(int64_t n_rows, int64_t n_cols, int64_t nnz,
+                        const void* row_ptr, int idx_bits, const int32_t* col_ind,
+                        void* col_ptr, int32_t* row_ind, int32_t* permute, void* stream);
 /* row_ptr[i] = number of entries with row id < i, for sorted COO row ids;
  * replaces format_conversion.coo2csr (convert.cpp:32-35, convert_kernel.cu:44-59) */
 int dgnn_coo2csr(int64_t nnz, int64_t m, const int32_t* row_ind,

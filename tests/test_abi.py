@@ -32,7 +32,7 @@ def test_version_and_status_strings():
     assert lib.dgnn_version() >= 100
     assert lib.dgnn_seg_chunk() >= 32
     assert lib.dgnn_status_string(0) == b"ok"
-    for code in range(-7, 0):
+    for code in range(-8, 0):
         assert lib.dgnn_status_string(code) not in (b"ok", b"unknown dgnn status")
 
 
