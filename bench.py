@@ -278,6 +278,17 @@ def run_ours(args, rank, world, local):
         cot = seeded_normal((n, H, F), 46, dev)[r0:r1].contiguous()
         del rp, ci
         torch.cuda.empty_cache()
+        inner_ag = gdist._all_gather_rows
+        timer.spans["all_gather"] = []
+
+        def timed_all_gather(*a, **k):
+            if not timer.active:
+                return inner_ag(*a, **k)
+            s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_.record(); r_ = inner_ag(*a, **k); e_.record()
+            timer.spans["all_gather"].append((s_, e_))
+            return r_
+        gdist._all_gather_rows = timed_all_gather
 
         def step(x_in):
             h = torch.matmul(x_in, W).view(-1, H, F)
@@ -343,6 +354,12 @@ def run_ours(args, rank, world, local):
         e2e = {"value": nnz / (ms2 * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
                "d2h_bytes_per_step": 4 * world, "ms_per_step": ms2}
 
+    phases = None
+    if world > 1:
+        mine = {k: (sum(a.elapsed_time(b) for a, b in v) / args.steps) for k, v in timer.spans.items() if v}
+        mine["n_loc"] = n_loc
+        phases = [None] * world
+        torch.distributed.all_gather_object(phases, mine)
     if rank != 0:
         if world > 1:
             torch.distributed.barrier()
@@ -365,6 +382,8 @@ def run_ours(args, rank, world, local):
     }
     if e2e:
         line["e2e"] = e2e
+    if phases:
+        line["phases_ms_per_step_by_rank"] = phases
     if world == 1 and fwd_ms and bwd_ms:
         ach = fwd_b / (fwd_ms * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "kernel": "k_rows<GatFwdOp<2,false>> (+chunk/merge kernels of the same call)",

@@ -40,7 +40,8 @@ SIGNATURES = {
     "dgnn_gat_backward": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p,
                                   c_p, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_uniform_fill": (c_int, [c_u64, c_u64, c_i64, c_p, c_p]),
-    "dgnn_mhsddmm": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_p]),
+    "dgnn_mhsddmm_workspace_bytes": (c_sz, []),
+    "dgnn_mhsddmm": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_mhtranspose": (c_int, [c_i64, c_int, c_p, c_p, c_p, c_p]),
     "dgnn_gmm_forward_workspace_bytes": (c_sz, [c_i64, c_i64, c_int, c_int]),
     "dgnn_gmm_forward": (c_int, [c_i64, c_i64, c_int, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_p,

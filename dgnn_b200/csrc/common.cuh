@@ -22,7 +22,7 @@ constexpr int DGNN_WARPS = 8;          // warps per CTA in the row kernels
 constexpr int DGNN_THREADS = DGNN_WARPS * 32;
 constexpr int DGNN_ROW_WARPS = 4;      // warps per CTA in the strided short-row kernel
 constexpr int DGNN_ROW_THREADS = DGNN_ROW_WARPS * 32;
-constexpr int DGNN_ROW_WAVES = 8;      // CTAs launched per SM-resident CTA slot (pool oversubscription)
+constexpr int DGNN_CHUNK_WARPS = 4;    // warps that share one (chunk, long row) piece
 constexpr float DGNN_NEG_INIT = -1e38f;  // initial running maximum (matches the reference)
 
 // index-pointer arrays come as int32 or int64; the width is uniform per launch
@@ -103,19 +103,23 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 
 // ---------------------------------------------------------------------------
 // the three scheduling kernels, generic over an operator object
-// Op must provide: n_rows, nnz, indptr, idx_bits, struct State,
+// Op must provide: n_rows, nnz, indptr, idx_bits, ws (float* partial slots),
+//   slot_stride (floats per slot), MIN_BLOCKS, HAS_PARTIALS, struct State,
 //   init(State&, row, lane), range(State&, row, e0, e1, lane),
-//   finalize(State&, row, lane), store_partial(State&, slot, lane),
-//   merge_partial(State&, slot, lane)
+//   finalize(State&, row, lane), store_partial(State&, float* p, lane),
+//   merge_partial(State&, const float* p, lane)
 // ---------------------------------------------------------------------------
-// Short rows: a fixed pool of warps strides over the rows (row = warp id, + pool
-// size, ...), so every warp sees a similar mix of degrees and no CTA waits on one
-// heavy row while its other warps sit idle.
+// Short rows: every warp of a fixed pool draws the next row from a counter.  Rows
+// come out in id order, so whatever skew the ids carry (R-MAT: low ids are the
+// heavy ones) is spread over all warps and the tail consists of single rows.
 template <class Op>
-__global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op) {
+__global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op, unsigned long long* next_row) {
   const int lane = threadIdx.x & 31;
-  const i64 stride = (i64)gridDim.x * DGNN_ROW_WARPS;
-  for (i64 r = (i64)blockIdx.x * DGNN_ROW_WARPS + (threadIdx.x >> 5); r < op.n_rows; r += stride) {
+  for (;;) {
+    unsigned long long t = 0;
+    if (lane == 0) t = atomicAdd(next_row, 1ULL);
+    const i64 r = (i64)__shfl_sync(DGNN_FULL, t, 0);
+    if (r >= op.n_rows) break;
     const i64 lb = ldp(op.indptr, op.idx_bits, r);
     const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
     if (hb - lb > DGNN_SEG) continue;  // long row: chunk + merge kernels own it
@@ -126,10 +130,16 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const
   }
 }
 
+// Long rows: one CTA of DGNN_CHUNK_WARPS warps per (chunk, slot).  The piece of the
+// row inside the chunk is cut into equal sub-ranges, one per warp; the warps'
+// states are folded in edge order through shared memory and warp 0 writes the
+// chunk's partial state.
 template <class Op>
-__global__ void __launch_bounds__(DGNN_THREADS) k_chunks(const Op op) {
-  const int lane = threadIdx.x & 31;
-  const i64 w = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+__global__ void __launch_bounds__(DGNN_CHUNK_WARPS * 32) k_chunks(const Op op) {
+  extern __shared__ float4 dgnn_smem4[];
+  float* smem = reinterpret_cast<float*>(dgnn_smem4);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const i64 w = blockIdx.x;
   const i64 j = w >> 1;
   const int slot = (int)(w & 1);
   const i64 cs = j * DGNN_SEG;
@@ -140,10 +150,21 @@ __global__ void __launch_bounds__(DGNN_THREADS) k_chunks(const Op op) {
   const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
   if (hb - lb <= DGNN_SEG) return;
   if (slot == 0 ? (lb >= cs) : (lb < cs)) return;
+  const i64 e0 = lb > cs ? lb : cs, e1 = hb < ce ? hb : ce;
+  const i64 per = (e1 - e0 + DGNN_CHUNK_WARPS - 1) / DGNN_CHUNK_WARPS;
+  const i64 w0 = e0 + per * warp;
+  const i64 w1 = (w0 + per < e1) ? w0 + per : e1;
   typename Op::State st;
   op.init(st, r, lane);
-  op.range(st, r, lb > cs ? lb : cs, hb < ce ? hb : ce, lane);
-  op.store_partial(st, 2 * j + slot, lane);
+  if (w0 < w1) op.range(st, r, w0, w1, lane);
+  if (!Op::HAS_PARTIALS) return;
+  if (warp > 0) op.store_partial(st, smem + (i64)(warp - 1) * op.slot_stride, lane);
+  __syncthreads();
+  if (warp == 0) {
+    for (int k = 1; k < DGNN_CHUNK_WARPS; ++k)
+      if (e0 + per * k < e1) op.merge_partial(st, smem + (i64)(k - 1) * op.slot_stride, lane);
+    op.store_partial(st, op.ws + (2 * j + slot) * op.slot_stride, lane);
+  }
 }
 
 template <class Op>
@@ -159,8 +180,8 @@ __global__ void __launch_bounds__(DGNN_THREADS) k_merge(const Op op) {
   if (hb - lb <= DGNN_SEG || lb < cs) return;  // the long row that begins in this chunk
   typename Op::State st;
   op.init(st, r, lane);
-  op.merge_partial(st, 2 * j + 1, lane);
-  for (i64 jj = j + 1; jj * DGNN_SEG < hb; ++jj) op.merge_partial(st, 2 * jj, lane);
+  op.merge_partial(st, op.ws + (2 * j + 1) * op.slot_stride, lane);
+  for (i64 jj = j + 1; jj * DGNN_SEG < hb; ++jj) op.merge_partial(st, op.ws + (2 * jj) * op.slot_stride, lane);
   op.finalize(st, r, lane);
 }
 
@@ -170,26 +191,33 @@ static inline unsigned dgnn_grid(i64 items, int per_block) {
 }
 static inline i64 dgnn_num_chunks(i64 nnz) { return (nnz + DGNN_SEG - 1) / DGNN_SEG; }
 
-// launch the row / chunk / merge trio for one operator
+// Launch the row / chunk / merge trio for one operator.  `counter` points at 8
+// zero-able bytes of workspace (the row counter of k_rows).
 template <class Op>
-static inline int dgnn_launch_trio(const Op& op, bool has_partials, cudaStream_t s) {
+static inline int dgnn_launch_trio(const Op& op, unsigned long long* counter, cudaStream_t s) {
   if (op.n_rows <= 0) return DGNN_OK;
+  cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned long long), s);
+  if (e != cudaSuccess) return (int)e;
   {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const i64 pool = (i64)sms * Op::MIN_BLOCKS * DGNN_ROW_WAVES;
+    const i64 pool = (i64)sms * Op::MIN_BLOCKS;     // resident CTAs: one wave, rows are drawn dynamically
     const i64 need = (op.n_rows + DGNN_ROW_WARPS - 1) / DGNN_ROW_WARPS;
-    k_rows<Op><<<(unsigned)(need < pool ? need : pool), DGNN_ROW_THREADS, 0, s>>>(op);
+    k_rows<Op><<<(unsigned)(need < pool ? need : pool), DGNN_ROW_THREADS, 0, s>>>(op, counter);
   }
   if (op.nnz > DGNN_SEG) {
     const i64 nc = dgnn_num_chunks(op.nnz);
-    k_chunks<Op><<<dgnn_grid(2 * nc, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
-    if (has_partials) k_merge<Op><<<dgnn_grid(nc, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
+    const size_t smem = Op::HAS_PARTIALS ? (size_t)(DGNN_CHUNK_WARPS - 1) * op.slot_stride * sizeof(float) : 0;
+    k_chunks<Op><<<(unsigned)(2 * nc), DGNN_CHUNK_WARPS * 32, smem, s>>>(op);
+    if (Op::HAS_PARTIALS) k_merge<Op><<<dgnn_grid(nc, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
   }
-  cudaError_t e = cudaGetLastError();
+  e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
+
+// workspaces start with this many bytes reserved for the row counter
+constexpr size_t DGNN_WS_HEADER = 256;
 
 static inline int ilog2_exact(int x) {  // -1 unless x is a power of two
   if (x <= 0 || (x & (x - 1))) return -1;

@@ -23,6 +23,7 @@ template <int VPL> struct Unroll { static constexpr int U = VPL <= 2 ? 4 : 2; };
 template <int VPL, bool MASK, bool FULL>
 struct GatFwdOp {
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
+  static constexpr bool HAS_PARTIALS = true;
   i64 n_rows, nnz;
   const void* indptr;
   int idx_bits;
@@ -128,8 +129,7 @@ struct GatFwdOp {
     }
   }
 
-  __device__ __forceinline__ void store_partial(State& st, i64 slot, int) const {
-    float* p = ws + slot * slot_stride;
+  __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
@@ -141,8 +141,7 @@ struct GatFwdOp {
     }
   }
 
-  __device__ __forceinline__ void merge_partial(State& st, i64 slot, int) const {
-    const float* p = ws + slot * slot_stride;
+  __device__ __forceinline__ void merge_partial(State& st, const float* p, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
@@ -234,6 +233,7 @@ k_gat_rowstat_generic(i64 n_rows, int H, int F, const float* attn_row, const flo
 template <int VPL, bool MASK, bool FULL>
 struct GatBwdOp {
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 4 : (VPL == 4 ? 3 : 2);
+  static constexpr bool HAS_PARTIALS = true;
   i64 n_rows, nnz;      // "rows" of the CSC form = source columns
   const void* indptr;   // col_ptr
   int idx_bits;
@@ -335,8 +335,7 @@ struct GatBwdOp {
     }
   }
 
-  __device__ __forceinline__ void store_partial(State& st, i64 slot, int) const {
-    float* p = ws + slot * slot_stride;
+  __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
@@ -345,8 +344,7 @@ struct GatBwdOp {
     }
   }
 
-  __device__ __forceinline__ void merge_partial(State& st, i64 slot, int) const {
-    const float* p = ws + slot * slot_stride;
+  __device__ __forceinline__ void merge_partial(State& st, const float* p, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
@@ -490,15 +488,16 @@ int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const voi
   op.in_feat = reinterpret_cast<const float4*>(in_feat); op.mask = mask;
   op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
   op.out = reinterpret_cast<float4*>(out); op.edge_max = edge_max; op.edge_sum = edge_sum;
-  op.ws = reinterpret_cast<float*>(ws); op.slot_stride = fwd_slot_stride(h, f);
-  return dgnn_launch_trio(op, true, s);
+  op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER); op.slot_stride = fwd_slot_stride(h, f);
+  return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
 template <int VPL, bool MASK, bool FULL>
 int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const void* col_ptr, int idx_bits,
                const int* row_ind, const int* permute, const float* pack, const float* mask,
                const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
-               float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, cudaStream_t s) {
+               float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, unsigned long long* counter,
+               cudaStream_t s) {
   GatBwdOp<VPL, MASK, FULL> op;
   op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -508,7 +507,7 @@ int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const voi
   op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
   op.grad_feat = reinterpret_cast<float4*>(grad_feat); op.grad_attn_col = grad_attn_col;
   op.grad_edge = grad_edge; op.ws = ws; op.slot_stride = bwd_slot_stride(h, f);
-  return dgnn_launch_trio(op, true, s);
+  return dgnn_launch_trio(op, counter, s);
 }
 
 // FULL = the row is exactly 32*VPL float4 vectors wide: no lane is ever idle
@@ -524,12 +523,13 @@ int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const voi
   }
 
 struct BwdLayout {
-  size_t grad_edge, col_part, row_part, pack, total;
+  size_t counter, grad_edge, col_part, row_part, pack, total;
 };
 inline BwdLayout bwd_layout(i64 n_rows, i64 nnz, int h, int f) {
   BwdLayout L;
   const i64 nc = dgnn_num_chunks(nnz);
   size_t off = 0;
+  L.counter = off;   off += DGNN_WS_HEADER;
   L.grad_edge = off; off += up256((size_t)nnz * h * sizeof(float));
   L.col_part = off;  off += up256((size_t)(2 * nc) * bwd_slot_stride(h, f) * sizeof(float));
   L.row_part = off;  off += up256((size_t)(2 * nc) * h * sizeof(float));
@@ -552,8 +552,8 @@ extern "C" {
 
 size_t dgnn_gat_forward_workspace_bytes(int64_t n_rows, int64_t nnz, int h, int f) {
   (void)n_rows;
-  if (nnz <= DGNN_SEG || h <= 0 || f <= 0) return 256;
-  return up256((size_t)(2 * dgnn_num_chunks(nnz)) * fwd_slot_stride(h, f) * sizeof(float)) + 256;
+  if (nnz <= DGNN_SEG || h <= 0 || f <= 0) return DGNN_WS_HEADER;
+  return DGNN_WS_HEADER + up256((size_t)(2 * dgnn_num_chunks(nnz)) * fwd_slot_stride(h, f) * sizeof(float));
 }
 
 int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
@@ -572,11 +572,9 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const FastShape fs = fast_shape(h, f);
   if (fs.ok && aligned16(in_feat) && aligned16(out)) {
-    if (nnz > DGNN_SEG) {
-      if (!workspace || workspace_bytes < dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f))
-        return DGNN_ERR_WORKSPACE;
-      if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
-    }
+    if (!workspace || workspace_bytes < dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f))
+      return DGNN_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
 #define CALL_FWD(V, M, FW)                                                                           \
   launch_fwd<V, M, FW>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
                    negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, s)
@@ -648,6 +646,7 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
   float* grad_edge = reinterpret_cast<float*>(wsb + L.grad_edge);
   float* col_part = reinterpret_cast<float*>(wsb + L.col_part);
   float* row_part = reinterpret_cast<float*>(wsb + L.row_part);
+  unsigned long long* counter = reinterpret_cast<unsigned long long*>(wsb + L.counter);
   const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const FastShape fs = fast_shape(h, f);
@@ -657,7 +656,7 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
 #define CALL_BWD(V, M, FW)                                                                              \
   launch_bwd<V, M, FW>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
                    attn_col, grad_out, negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, \
-                   col_part, s)
+                   col_part, counter, s)
       auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, fs.hf4 == 32 * fs.vpl, CALL_BWD) };
 #undef CALL_BWD
       rc = run();

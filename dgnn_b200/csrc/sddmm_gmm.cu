@@ -32,10 +32,13 @@ inline FastShape fast_shape(int h, int f) {
 template <int VPL>
 struct SddmmOp {
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
+  static constexpr bool HAS_PARTIALS = false;   // outputs are per edge: nothing to fold
   i64 n_rows, nnz;
   const void* indptr;
   int idx_bits;
   int H, hf4, f4_shift;
+  float* ws;
+  i64 slot_stride;
   const int* col_ind;
   const float4* a;
   const float4* b;
@@ -80,8 +83,8 @@ struct SddmmOp {
     }
   }
   __device__ __forceinline__ void finalize(State&, i64, int) const {}
-  __device__ __forceinline__ void store_partial(State&, i64, int) const {}
-  __device__ __forceinline__ void merge_partial(State&, i64, int) const {}
+  __device__ __forceinline__ void store_partial(State&, float*, int) const {}
+  __device__ __forceinline__ void merge_partial(State&, const float*, int) const {}
 };
 
 // any H, F: one warp per (edge-block of a row, head) -- simple and slow
@@ -133,6 +136,7 @@ __device__ __forceinline__ float gauss_w(const float* pseudo, const float* mu, c
 template <int VPL>
 struct GmmOp {
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
+  static constexpr bool HAS_PARTIALS = true;
   i64 n_rows, nnz;
   const void* indptr;
   int idx_bits;
@@ -185,14 +189,14 @@ struct GmmOp {
     for (int v = 0; v < VPL; ++v)
       if (st.lm.act[v]) out[r * hf4 + st.lm.q[v]] = st.acc[v];
   }
-  __device__ __forceinline__ void store_partial(State& st, i64 slot, int) const {
-    float4* p = reinterpret_cast<float4*>(ws + slot * slot_stride);
+  __device__ __forceinline__ void store_partial(State& st, float* pf, int) const {
+    float4* p = reinterpret_cast<float4*>(pf);
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
       if (st.lm.act[v]) p[st.lm.q[v]] = st.acc[v];
   }
-  __device__ __forceinline__ void merge_partial(State& st, i64 slot, int) const {
-    const float4* p = reinterpret_cast<const float4*>(ws + slot * slot_stride);
+  __device__ __forceinline__ void merge_partial(State& st, const float* pf, int) const {
+    const float4* p = reinterpret_cast<const float4*>(pf);
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
       if (st.lm.act[v]) add4(st.acc[v], p[st.lm.q[v]]);
@@ -287,12 +291,13 @@ inline i64 gbp_blocks(i64 nnz) { return (nnz + GBP_EDGES_PER_BLOCK - 1) / GBP_ED
 
 template <int VPL>
 int launch_sddmm(const FastShape& fs, i64 n_rows, i64 nnz, int h, const void* row_ptr, int idx_bits,
-                 const int* col_ind, const float* a, const float* b, float* out, cudaStream_t s) {
+                 const int* col_ind, const float* a, const float* b, float* out, void* ws, cudaStream_t s) {
   SddmmOp<VPL> op;
+  op.ws = nullptr; op.slot_stride = 0;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift; op.col_ind = col_ind;
   op.a = reinterpret_cast<const float4*>(a); op.b = reinterpret_cast<const float4*>(b); op.out = out;
-  return dgnn_launch_trio(op, false, s);
+  return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
 template <int VPL>
@@ -303,17 +308,21 @@ int launch_gmm(const FastShape& fs, i64 n_rows, i64 nnz, int K, int dim, int f, 
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = K; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift; op.dim = dim; op.col_ind = col_ind;
   op.feat = reinterpret_cast<const float4*>(feat); op.pseudo = pseudo; op.mu = mu; op.sig = sig;
-  op.out = reinterpret_cast<float4*>(out); op.ws = reinterpret_cast<float*>(ws);
+  op.out = reinterpret_cast<float4*>(out);
+  op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER);
   op.slot_stride = (i64)K * f;
-  return dgnn_launch_trio(op, true, s);
+  return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
 }  // namespace
 
 extern "C" {
 
+size_t dgnn_mhsddmm_workspace_bytes(void) { return DGNN_WS_HEADER; }
+
 int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
-                 const int32_t* col_ind, const float* a, const float* b, float* out, void* stream) {
+                 const int32_t* col_ind, const float* a, const float* b, float* out, void* workspace,
+                 size_t workspace_bytes, void* stream) {
   if (n_rows < 0 || nnz < 0 || h <= 0 || f <= 0) return DGNN_ERR_SHAPE;
   if (idx_bits != 32 && idx_bits != 64) return DGNN_ERR_IDX_BITS;
   if (idx_bits == 32 && nnz > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;
@@ -322,11 +331,12 @@ int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr,
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const FastShape fs = fast_shape(h, f);
   if (fs.ok && aligned16(a) && aligned16(b)) {
+    if (!workspace || workspace_bytes < DGNN_WS_HEADER) return DGNN_ERR_WORKSPACE;
     switch (fs.vpl) {
-      case 1: return launch_sddmm<1>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, s);
-      case 2: return launch_sddmm<2>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, s);
-      case 4: return launch_sddmm<4>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, s);
-      default: return launch_sddmm<8>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, s);
+      case 1: return launch_sddmm<1>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
+      case 2: return launch_sddmm<2>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
+      case 4: return launch_sddmm<4>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
+      default: return launch_sddmm<8>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
     }
   }
   k_sddmm_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(n_rows, h, f, row_ptr, idx_bits,
@@ -353,8 +363,8 @@ int dgnn_mhtranspose(int64_t nnz, int h, const int32_t* permute, const float* in
 
 size_t dgnn_gmm_forward_workspace_bytes(int64_t n_rows, int64_t nnz, int kernels, int f) {
   (void)n_rows;
-  if (nnz <= DGNN_SEG || kernels <= 0 || f <= 0) return 256;
-  return up256((size_t)(2 * dgnn_num_chunks(nnz)) * kernels * f * sizeof(float)) + 256;
+  if (nnz <= DGNN_SEG || kernels <= 0 || f <= 0) return DGNN_WS_HEADER;
+  return DGNN_WS_HEADER + up256((size_t)(2 * dgnn_num_chunks(nnz)) * kernels * f * sizeof(float));
 }
 
 int dgnn_gmm_forward(int64_t n_rows, int64_t nnz, int kernels, int dim, int f, const void* row_ptr,
@@ -369,11 +379,9 @@ int dgnn_gmm_forward(int64_t n_rows, int64_t nnz, int kernels, int dim, int f, c
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const FastShape fs = fast_shape(kernels, f);
   if (fs.ok && aligned16(node_feat) && aligned16(out)) {
-    if (nnz > DGNN_SEG) {
-      if (!workspace || workspace_bytes < dgnn_gmm_forward_workspace_bytes(n_rows, nnz, kernels, f))
-        return DGNN_ERR_WORKSPACE;
-      if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
-    }
+    if (!workspace || workspace_bytes < dgnn_gmm_forward_workspace_bytes(n_rows, nnz, kernels, f))
+      return DGNN_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
     switch (fs.vpl) {
       case 1: return launch_gmm<1>(fs, n_rows, nnz, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out, workspace, s);
       case 2: return launch_gmm<2>(fs, n_rows, nnz, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out, workspace, s);

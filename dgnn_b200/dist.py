@@ -1,7 +1,6 @@
 """Destination-row-block sharding of the fused GAT operator over torch.distributed.
 
-The reference is single-GPU.  Here rank g owns a contiguous block of nodes,
-chosen so that every block holds about the same number of in-edges:
+The reference is single-GPU.  Here rank g owns a contiguous block of nodes:
 
   forward   rank g aggregates its destination rows A[block_g, :] and needs
             attn_col and in_feat of every source node  -> two all-gathers;
@@ -11,10 +10,12 @@ chosen so that every block holds about the same number of in-edges:
             its own nodes with no reduction; grad_attn_row comes out as
             per-rank partial sums over all rows -> one all-reduce of [N,H].
 
-Blocks have different node counts, so node ids are remapped into a padded id
-space (rank g' owns ids g'*n_max .. g'*n_max + n_g' - 1) in which the
-all-gathers are plain equal-size `all_gather_into_tensor` calls.  Gathered
-tensors land in this GPU's own memory before any kernel reads them.
+Blocks are chosen by a cost prefix (in-edges for the forward, out-edges for the
+backward, a per-node term for the dense projection around the operator), so
+they hold different node counts; the all-gathers therefore move uneven row
+ranges straight into their place in one [N, ...] buffer (node ids stay global,
+nothing is padded).  Gathered tensors land in this GPU's own memory before any
+kernel reads them.
 """
 from __future__ import annotations
 
@@ -25,15 +26,27 @@ import torch.distributed as dist
 
 from . import kernels
 
+# relative cost of one in-edge (forward gather), one out-edge (backward gather) and
+# one node (projection GEMM + elementwise work of the layer), measured on a B200
+COST_IN_EDGE, COST_OUT_EDGE, COST_NODE = 1.0, 2.8, 40.0
 
-def balanced_node_blocks(row_ptr: torch.Tensor, world: int) -> list[int]:
-    """Boundaries b[0..world] of contiguous node blocks with about nnz/world
-    in-edges each (b[g] = first row whose edge offset reaches g*nnz/world)."""
+
+def balanced_node_blocks(row_ptr: torch.Tensor, world: int, col_ptr: torch.Tensor | None = None,
+                         node_cost: float = 0.0) -> list[int]:
+    """Boundaries b[0..world] of contiguous node blocks with about equal cost.
+    With only `row_ptr` the cost of a node is its in-degree (equal in-edge counts);
+    with `col_ptr` the out-degree and a per-node term are added with the weights above."""
     rp = row_ptr.long()
     n = rp.numel() - 1
-    nnz = int(rp[-1])
-    targets = torch.tensor([(nnz * g) // world for g in range(1, world)], dtype=torch.long, device=rp.device)
-    inner = torch.searchsorted(rp[:-1].contiguous(), targets, right=False).tolist() if world > 1 else []
+    if col_ptr is None:
+        prefix = rp.to(torch.float64)
+    else:
+        cp = col_ptr.long()
+        ids = torch.arange(n + 1, device=rp.device, dtype=torch.float64)
+        prefix = COST_IN_EDGE * rp.to(torch.float64) + COST_OUT_EDGE * cp.to(torch.float64) + node_cost * ids
+    total = float(prefix[-1])
+    targets = torch.tensor([total * g / world for g in range(1, world)], dtype=torch.float64, device=rp.device)
+    inner = torch.searchsorted(prefix[:-1].contiguous(), targets, right=False).tolist() if world > 1 else []
     bounds = [0] + [min(max(int(b), 0), n) for b in inner] + [n]
     for i in range(1, len(bounds)):          # keep the boundaries monotone
         bounds[i] = max(bounds[i], bounds[i - 1])
@@ -42,30 +55,20 @@ def balanced_node_blocks(row_ptr: torch.Tensor, world: int) -> list[int]:
 
 @dataclass
 class GatShard:
-    """Per-rank graph pieces, all in the padded id space."""
+    """Per-rank graph pieces; node ids are global."""
     rank: int
     world: int
     bounds: list          # node block boundaries, len world+1
-    n_max: int            # padded block size
+    n: int                # number of nodes of the whole graph
     n_loc: int
-    # forward: local destination rows x all (padded) source columns
+    # forward: local destination rows x all source columns
     fwd_row_ptr: torch.Tensor
     fwd_col_ind: torch.Tensor
-    # backward: all (padded) destination rows x local source columns
-    bwd_row_ptr: torch.Tensor   # CSR index pointer of the block, over padded rows
+    # backward: all destination rows x local source columns
+    bwd_row_ptr: torch.Tensor   # CSR index pointer of the block, over all rows
     bwd_col_ptr: torch.Tensor   # CSC index pointer, local columns
-    bwd_row_ind: torch.Tensor   # padded row id of each CSC entry
+    bwd_row_ind: torch.Tensor   # row id of each CSC entry
     bwd_permute: torch.Tensor   # CSR position (within the block) of each CSC entry
-
-    @property
-    def n_pad(self) -> int:
-        return self.world * self.n_max
-
-
-def _pad_ids(ids: torch.Tensor, bounds: list, n_max: int) -> torch.Tensor:
-    b = torch.tensor(bounds, dtype=torch.long, device=ids.device)
-    blk = torch.searchsorted(b[1:].contiguous(), ids.long(), right=True)
-    return (blk * n_max + (ids.long() - b[blk])).to(torch.int32)
 
 
 def build_shard(row_ptr, col_ind, rank, world, csr2csc=None, bounds=None) -> GatShard:
@@ -75,36 +78,42 @@ def build_shard(row_ptr, col_ind, rank, world, csr2csc=None, bounds=None) -> Gat
     csr2csc = csr2csc or kernels.csr2csc
     rp = row_ptr.long()
     n = rp.numel() - 1
-    bounds = bounds or balanced_node_blocks(rp, world)
-    n_max = max(max(bounds[g + 1] - bounds[g] for g in range(world)), 1)
-    r0, r1 = bounds[rank], bounds[rank + 1]
     ptr_dtype = row_ptr.dtype
-    # forward piece
-    lo, hi = int(rp[r0]), int(rp[r1])
-    fwd_row_ptr = (rp[r0:r1 + 1] - lo).to(ptr_dtype).contiguous()
-    fwd_col_ind = _pad_ids(col_ind[lo:hi], bounds, n_max)
-    # backward piece: columns r0..r1 of the global CSC
     col_ptr, row_ind, _ = csr2csc(row_ptr, col_ind)
     cp = col_ptr.long()
+    bounds = bounds or balanced_node_blocks(rp, world, cp, COST_NODE)
+    r0, r1 = bounds[rank], bounds[rank + 1]
+    # forward piece: rows r0..r1 of the CSR
+    lo, hi = int(rp[r0]), int(rp[r1])
+    fwd_row_ptr = (rp[r0:r1 + 1] - lo).to(ptr_dtype).contiguous()
+    fwd_col_ind = col_ind[lo:hi].to(torch.int32).contiguous()
+    # backward piece: columns r0..r1 of the CSC
     clo, chi = int(cp[r0]), int(cp[r1])
     bwd_col_ptr = (cp[r0:r1 + 1] - clo).to(ptr_dtype).contiguous()
-    bwd_row_ind = _pad_ids(row_ind[clo:chi], bounds, n_max)
-    # CSR of the block over padded rows = "CSC" of its transpose; perm[i] = CSC position of CSR entry i
-    n_pad = world * n_max
-    bwd_row_ptr, _, perm = csr2csc(bwd_col_ptr, bwd_row_ind, n_pad)
+    bwd_row_ind = row_ind[clo:chi].to(torch.int32).contiguous()
+    # CSR of the block = "CSC" of its transpose; perm[i] = CSC position of CSR entry i
+    bwd_row_ptr, _, perm = csr2csc(bwd_col_ptr, bwd_row_ind, n)
     permute = torch.empty_like(perm)
     permute[perm.long()] = torch.arange(perm.numel(), dtype=perm.dtype, device=perm.device)
-    return GatShard(rank, world, bounds, n_max, r1 - r0, fwd_row_ptr, fwd_col_ind.contiguous(),
-                    bwd_row_ptr.to(ptr_dtype).contiguous(), bwd_col_ptr, bwd_row_ind.contiguous(), permute.contiguous())
+    return GatShard(rank, world, bounds, n, r1 - r0, fwd_row_ptr, fwd_col_ind,
+                    bwd_row_ptr.to(ptr_dtype).contiguous(), bwd_col_ptr, bwd_row_ind, permute.to(torch.int32).contiguous())
 
 
-def _all_gather_padded(x_loc: torch.Tensor, n_max: int, group) -> torch.Tensor:
-    """[n_loc, ...] -> [world*n_max, ...]; rows past n_loc of each block are zero."""
+def _all_gather_rows(x_loc: torch.Tensor, bounds: list, group) -> torch.Tensor:
+    """[n_loc, ...] on every rank -> [N, ...]: rank g's rows land at bounds[g]:bounds[g+1]."""
     world = dist.get_world_size(group)
-    pad = x_loc.new_zeros((n_max,) + tuple(x_loc.shape[1:]))
-    pad[: x_loc.shape[0]] = x_loc
-    out = x_loc.new_empty((world * n_max,) + tuple(x_loc.shape[1:]))
-    dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
+    rank = dist.get_rank(group)
+    out = x_loc.new_empty((bounds[-1],) + tuple(x_loc.shape[1:]))
+    views = [out[bounds[g]: bounds[g + 1]] for g in range(world)]
+    x_loc = x_loc.contiguous()
+    if dist.get_backend(group) == "nccl":
+        # uneven row ranges: NCCL runs this as one group of broadcasts straight into the views
+        dist.all_gather(views, x_loc, group=group)
+    else:
+        views[rank].copy_(x_loc)
+        for g in range(world):
+            if views[g].numel():
+                dist.broadcast(views[g], src=dist.get_global_rank(group, g) if group is not None else g, group=group)
     return out
 
 
@@ -114,8 +123,8 @@ class ShardedGATFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, attn_row, attn_col, in_feat, shard, negative_slope, group, backend):
-        attn_col_all = _all_gather_padded(attn_col, shard.n_max, group)
-        feat_all = _all_gather_padded(in_feat, shard.n_max, group)
+        attn_col_all = _all_gather_rows(attn_col, shard.bounds, group)
+        feat_all = _all_gather_rows(in_feat, shard.bounds, group)
         out, edge_max, edge_sum = backend.gat_forward(attn_row, attn_col_all, shard.fwd_row_ptr, shard.fwd_col_ind,
                                                       negative_slope, feat_all)
         ctx.save_for_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum)
@@ -128,15 +137,14 @@ class ShardedGATFunction(torch.autograd.Function):
         shard, backend, group = ctx.shard, ctx.backend, ctx.group
         grad_out = grad_out.contiguous()
         pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)      # [n_loc,H,4]
-        pack_all = _all_gather_padded(pack, shard.n_max, group)
-        grad_all = _all_gather_padded(grad_out, shard.n_max, group)
+        pack_all = _all_gather_rows(pack, shard.bounds, group)
+        grad_all = _all_gather_rows(grad_out, shard.bounds, group)
         grad_feat, grad_row_part, grad_col = backend.gat_backward_cols(
             shard.bwd_row_ptr, shard.bwd_col_ptr, shard.bwd_row_ind, shard.bwd_permute, pack_all, None,
             in_feat, attn_col, grad_all, ctx.slope)
         dist.all_reduce(grad_row_part, group=group)
-        lo = shard.rank * shard.n_max
-        grad_row = grad_row_part[lo: lo + shard.n_loc].contiguous()
-        return grad_row, grad_col, grad_feat, None, None, None, None
+        r0, r1 = shard.bounds[shard.rank], shard.bounds[shard.rank + 1]
+        return grad_row_part[r0:r1].contiguous(), grad_col, grad_feat, None, None, None, None
 
 
 def sharded_gat(attn_row, attn_col, in_feat, shard, negative_slope=0.2, group=None, backend=kernels):

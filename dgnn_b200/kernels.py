@@ -174,8 +174,9 @@ def mhsddmm(row_ptr, col_ind, a, b):
     dev = b.device
     with torch.cuda.device(dev):
         out = torch.empty((nnz, h), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_mhsddmm_workspace_bytes(), dev)
         check(lib().dgnn_mhsddmm(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(a), _p(b), _p(out),
-                                 _stream(dev)), "mhsddmm")
+                                 _p(ws), ws.numel(), _stream(dev)), "mhsddmm")
     return out
 
 

@@ -117,9 +117,11 @@ int dgnn_uniform_fill(uint64_t seed, uint64_t offset, int64_t n, float* out, voi
 /* ---- multi-head SDDMM / transpose -----------------------------------------
  * out[e,h] = <a[row_e,h,:], b[col_e,h,:]>; replaces mhsddmm.mhsddmm
  * (dgNN/src/sddmm/mhsddmm.cc:11-28, mhsddmm_kernel.cu:5-99). */
+size_t dgnn_mhsddmm_workspace_bytes(void);
 int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f,
                  const void* row_ptr, int idx_bits, const int32_t* col_ind,
-                 const float* a, const float* b, float* out, void* stream);
+                 const float* a, const float* b, float* out,
+                 void* workspace, size_t workspace_bytes, void* stream);
 /* out[i,:] = in[permute[i],:] for [nnz,h] fp32; replaces mhtranspose.mhtranspose
  * (dgNN/src/csr2csc/mhtranspose.cc:10-18, mhtranspose_kernel.cu:6-47). */
 int dgnn_mhtranspose(int64_t nnz, int h, const int32_t* permute,

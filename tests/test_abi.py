@@ -55,13 +55,13 @@ def test_argument_errors_return_before_any_launch():
     assert lib.dgnn_csr2csc(3, 3, 0, null, 32, null, null, null, null, null, 0, null) == -1
     assert lib.dgnn_edgeconv_forward(3, 0, 2, null, null, null, null, null, null) == -2
     # 32-bit index pointers cannot address 2^31 edges
-    assert lib.dgnn_mhsddmm(4, 2**31, 1, 4, null, 32, null, null, null, null, null) == -5
+    assert lib.dgnn_mhsddmm(4, 2**31, 1, 4, null, 32, null, null, null, null, null, 0, null) == -5
 
 
 def test_workspace_queries():
     lib = _C.lib()
     seg = lib.dgnn_seg_chunk()
-    assert lib.dgnn_gat_forward_workspace_bytes(10, seg, 8, 32) == 256          # no row can be long
+    assert lib.dgnn_gat_forward_workspace_bytes(10, seg, 8, 32) == 256          # no row can be long: just the row counter
     big = lib.dgnn_gat_forward_workspace_bytes(10, 100 * seg, 8, 32)
     assert big >= 2 * 100 * (8 * 32 + 16) * 4
     assert lib.dgnn_csr2csc_workspace_bytes(1000, 1000, 50000) > 0

@@ -97,6 +97,8 @@ def test_balanced_blocks():
     rp, _ = synth.random_graph(1000, 8, seed=2, long_rows=[(10, 3000)])
     for world in (1, 2, 4, 8):
         b = gdist.balanced_node_blocks(rp, world)
+        b2 = gdist.balanced_node_blocks(rp, world, rp, 40.0)      # with out-degree and per-node terms
+        assert b2[0] == 0 and b2[-1] == 1000 and all(x <= y for x, y in zip(b2, b2[1:]))
         assert b[0] == 0 and b[-1] == 1000 and all(x <= y for x, y in zip(b, b[1:]))
         nnz = int(rp[-1])
         loads = [int(rp[b[g + 1]] - rp[b[g]]) for g in range(world)]
