@@ -229,7 +229,6 @@ def run_reference_arm(args, rank):
 def run_ours(args, rank, world, local):
     from dgnn_b200 import dist as gdist
     from dgnn_b200 import kernels
-    from dgnn_b200.operators import GATConvFuse
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
@@ -256,15 +255,21 @@ def run_ours(args, rank, world, local):
         torch.cuda.synchronize(); t_c.append(s.elapsed_time(e))
     csr2csc_ms = min(t_c)
 
+    bias = torch.zeros(H * F, device=dev, requires_grad=True)
+    params = [W, al, ar_, bias]
     if world == 1:
+        from dgnn_b200.layers import GATConv
         x = seeded_normal((n, IN), 45, dev)
         cot = seeded_normal((n, H, F), 46, dev)
+        layer = GATConv(IN, F, H, negative_slope=SLOPE).to(dev).train()     # the public layer, default options
+        with torch.no_grad():
+            layer.W.copy_(W); layer.attn_l.copy_(al); layer.attn_r.copy_(ar_)
+        params = list(layer.parameters())
+        W, al, ar_ = layer.W, layer.attn_l, layer.attn_r
 
         def step(x_in):
-            h = torch.matmul(x_in, W).view(-1, H, F)
-            a_row, a_col = (al * h).sum(-1), (ar_ * h).sum(-1)
-            out = GATConvFuse(a_row, a_col, rp, ci, cp, ri, pm, SLOPE, h, 0.0)
-            loss = (out * cot).sum()
+            out = layer(rp, ci, cp, ri, pm, x_in)
+            loss = torch.dot(out.view(-1), cot.view(-1))       # dense fp32 cotangent for the backward
             loss.backward()
             return loss
         n_loc = n
@@ -291,14 +296,18 @@ def run_ours(args, rank, world, local):
         gdist._all_gather_rows = timed_all_gather
 
         def step(x_in):
+            # the same layer on this rank's node block: projection, logits + sharded aggregation, bias
             h = torch.matmul(x_in, W).view(-1, H, F)
-            a_row, a_col = (al * h).sum(-1), (ar_ * h).sum(-1)
-            out = gdist.sharded_gat(a_row, a_col, h, shard, SLOPE)
-            loss = (out * cot).sum()
+            out = gdist.sharded_gat_layer(h, al, ar_, shard, SLOPE) + bias.view(-1, H, F)
+            loss = torch.dot(out.reshape(-1), cot.view(-1))
             loss.backward()
-            for p in (W, al, ar_):            # data-parallel parameter gradients
+            for p in params:            # data-parallel parameter gradients
                 dist.all_reduce(p.grad)
             return loss
+
+    def zero_grads():
+        for p in params:
+            p.grad = None
 
     def sync_all():
         torch.cuda.synchronize()
@@ -308,7 +317,7 @@ def run_ours(args, rank, world, local):
 
     for _ in range(max(args.warmup, 3)):
         step(x)
-        W.grad = None; al.grad = None; ar_.grad = None
+        zero_grads()
     sync_all()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -318,7 +327,7 @@ def run_ours(args, rank, world, local):
     s.record()
     for _ in range(args.steps):
         step(x)
-        W.grad = None; al.grad = None; ar_.grad = None
+        zero_grads()
     e.record()
     sync_all()
     timer.active = False
@@ -343,7 +352,7 @@ def run_ours(args, rank, world, local):
         for _ in range(args.steps):
             x_dev.copy_(x_host, non_blocking=True)
             loss_host.copy_(step(x_dev), non_blocking=True)
-            W.grad = None; al.grad = None; ar_.grad = None
+            zero_grads()
         e2.record()
         sync_all()
         ms2 = s2.elapsed_time(e2) / args.steps
@@ -399,7 +408,7 @@ def run_ours(args, rank, world, local):
     if world == 1 and not args.no_cpu_baseline:
         with torch.no_grad():
             h = torch.matmul(x, W).view(-1, H, F)
-            a_row, a_col = (al * h).sum(-1), (ar_ * h).sum(-1)
+            a_row, a_col = kernels.gat_logits_forward(h, al, ar_)
         eps, desc, cores = cpu_sample(rp, ci, a_row, a_col, h, cot, args.cpu_sample_edges, 3)
         line["cpu_baseline"] = {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc}
     print(json.dumps(line))

@@ -117,16 +117,32 @@ def _all_gather_rows(x_loc: torch.Tensor, bounds: list, group) -> torch.Tensor:
     return out
 
 
+def _sharded_forward(attn_row, attn_col, in_feat, shard, negative_slope, group, backend):
+    attn_col_all = _all_gather_rows(attn_col, shard.bounds, group)
+    feat_all = _all_gather_rows(in_feat, shard.bounds, group)
+    return backend.gat_forward(attn_row, attn_col_all, shard.fwd_row_ptr, shard.fwd_col_ind, negative_slope, feat_all)
+
+
+def _sharded_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum, grad_out, shard, negative_slope, group,
+                      backend):
+    pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)      # [n_loc,H,4]
+    pack_all = _all_gather_rows(pack, shard.bounds, group)
+    grad_all = _all_gather_rows(grad_out, shard.bounds, group)
+    grad_feat, grad_row_part, grad_col = backend.gat_backward_cols(
+        shard.bwd_row_ptr, shard.bwd_col_ptr, shard.bwd_row_ind, shard.bwd_permute, pack_all, None,
+        in_feat, attn_col, grad_all, negative_slope)
+    dist.all_reduce(grad_row_part, group=group)
+    r0, r1 = shard.bounds[shard.rank], shard.bounds[shard.rank + 1]
+    return grad_feat, grad_row_part[r0:r1].contiguous(), grad_col
+
+
 class ShardedGATFunction(torch.autograd.Function):
     """Fused GAT on this rank's node block.  Inputs and outputs are the local
     rows: attn_row, attn_col [n_loc,H], in_feat [n_loc,H,F] -> out [n_loc,H,F]."""
 
     @staticmethod
     def forward(ctx, attn_row, attn_col, in_feat, shard, negative_slope, group, backend):
-        attn_col_all = _all_gather_rows(attn_col, shard.bounds, group)
-        feat_all = _all_gather_rows(in_feat, shard.bounds, group)
-        out, edge_max, edge_sum = backend.gat_forward(attn_row, attn_col_all, shard.fwd_row_ptr, shard.fwd_col_ind,
-                                                      negative_slope, feat_all)
+        out, edge_max, edge_sum = _sharded_forward(attn_row, attn_col, in_feat, shard, negative_slope, group, backend)
         ctx.save_for_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum)
         ctx.shard, ctx.slope, ctx.group, ctx.backend = shard, negative_slope, group, backend
         return out
@@ -134,19 +150,39 @@ class ShardedGATFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         attn_row, attn_col, in_feat, out, edge_max, edge_sum = ctx.saved_tensors
-        shard, backend, group = ctx.shard, ctx.backend, ctx.group
-        grad_out = grad_out.contiguous()
-        pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)      # [n_loc,H,4]
-        pack_all = _all_gather_rows(pack, shard.bounds, group)
-        grad_all = _all_gather_rows(grad_out, shard.bounds, group)
-        grad_feat, grad_row_part, grad_col = backend.gat_backward_cols(
-            shard.bwd_row_ptr, shard.bwd_col_ptr, shard.bwd_row_ind, shard.bwd_permute, pack_all, None,
-            in_feat, attn_col, grad_all, ctx.slope)
-        dist.all_reduce(grad_row_part, group=group)
-        r0, r1 = shard.bounds[shard.rank], shard.bounds[shard.rank + 1]
-        return grad_row_part[r0:r1].contiguous(), grad_col, grad_feat, None, None, None, None
+        grad_feat, grad_row, grad_col = _sharded_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum,
+                                                         grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group,
+                                                         ctx.backend)
+        return grad_row, grad_col, grad_feat, None, None, None, None
+
+
+class ShardedGATLayerFunction(torch.autograd.Function):
+    """Attention logits + sharded aggregation as one autograd node (CUDA only):
+    h [n_loc,H,F], attn_l, attn_r [1,H,F] -> out [n_loc,H,F]."""
+
+    @staticmethod
+    def forward(ctx, h, attn_l, attn_r, shard, negative_slope, group):
+        h = h.contiguous()
+        attn_row, attn_col = kernels.gat_logits_forward(h, attn_l, attn_r)
+        out, edge_max, edge_sum = _sharded_forward(attn_row, attn_col, h, shard, negative_slope, group, kernels)
+        ctx.save_for_backward(attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r)
+        ctx.shard, ctx.slope, ctx.group = shard, negative_slope, group
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r = ctx.saved_tensors
+        grad_h, grad_row, grad_col = _sharded_backward(attn_row, attn_col, h, out, edge_max, edge_sum,
+                                                      grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group, kernels)
+        grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_row, grad_col, grad_h)
+        return grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None
 
 
 def sharded_gat(attn_row, attn_col, in_feat, shard, negative_slope=0.2, group=None, backend=kernels):
     """out_loc = fused GAT over the sharded graph; differentiable in the three tensors."""
     return ShardedGATFunction.apply(attn_row, attn_col, in_feat, shard, negative_slope, group, backend)
+
+
+def sharded_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None):
+    """Logits + sharded aggregation; differentiable in h and the attention vectors."""
+    return ShardedGATLayerFunction.apply(h, attn_l, attn_r, shard, negative_slope, group)

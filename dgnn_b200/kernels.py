@@ -149,6 +149,49 @@ def gat_backward(negative_slope, attn_drop, row_ptr, col_ptr, row_ind, permute, 
     return grad_feat, grad_attn_row, grad_attn_col
 
 
+def logits_supported(h, f):
+    """Shapes the fused attention-logit kernels handle (f = 4 * 2^k, h*f <= 1024)."""
+    f4 = f // 4
+    return f % 4 == 0 and f4 > 0 and (f4 & (f4 - 1)) == 0 and h * f <= 1024
+
+
+def gat_logits_forward(feat, attn_l, attn_r):
+    """attn_row, attn_col [N,H] from feat [N,H,F] and the attention vectors [.., H, F]."""
+    feat = _cuda_f32(feat, "feat")
+    n, h, f = _dims3(feat, "feat")
+    attn_l = _cuda_f32(attn_l, "attn_l").reshape(h, f)
+    attn_r = _cuda_f32(attn_r, "attn_r").reshape(h, f)
+    dev = feat.device
+    with torch.cuda.device(dev):
+        attn_row = torch.empty((n, h), dtype=torch.float32, device=dev)
+        attn_col = torch.empty((n, h), dtype=torch.float32, device=dev)
+        check(lib().dgnn_gat_logits_forward(n, h, f, _p(feat), _p(attn_l), _p(attn_r), _p(attn_row), _p(attn_col),
+                                            _stream(dev)), "gat_logits_forward")
+    return attn_row, attn_col
+
+
+def gat_logits_backward(feat, attn_l, attn_r, grad_row, grad_col, grad_feat):
+    """grad_feat += grad_row (x) attn_l + grad_col (x) attn_r (in place); returns (grad_l, grad_r) [H,F]."""
+    feat = _cuda_f32(feat, "feat")
+    n, h, f = _dims3(feat, "feat")
+    attn_l = _cuda_f32(attn_l, "attn_l").reshape(h, f)
+    attn_r = _cuda_f32(attn_r, "attn_r").reshape(h, f)
+    grad_row = _cuda_f32(grad_row, "grad_row")
+    grad_col = _cuda_f32(grad_col, "grad_col")
+    if not (grad_feat.is_cuda and grad_feat.is_contiguous() and grad_feat.dtype == torch.float32
+            and grad_feat.shape == feat.shape):
+        raise RuntimeError("dgnn_b200: grad_feat must be a contiguous float32 CUDA tensor shaped like feat")
+    dev = feat.device
+    with torch.cuda.device(dev):
+        grad_l = torch.empty((h, f), dtype=torch.float32, device=dev)
+        grad_r = torch.empty((h, f), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gat_logits_backward_workspace_bytes(h, f), dev)
+        check(lib().dgnn_gat_logits_backward(n, h, f, _p(feat), _p(attn_l), _p(attn_r), _p(grad_row), _p(grad_col),
+                                             _p(grad_feat), _p(grad_l), _p(grad_r), _p(ws), ws.numel(), _stream(dev)),
+              "gat_logits_backward")
+    return grad_l, grad_r
+
+
 def uniform_fill(shape, seed, offset, device):
     """Uniform (0,1] floats from the library's Philox stream."""
     dev = torch.device(device)

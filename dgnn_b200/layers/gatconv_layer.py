@@ -8,7 +8,8 @@ import math
 import torch
 from torch import nn
 
-from ..operators.fused_gatconv import GATConvFuse, GATConvFuse_inference
+from .. import kernels
+from ..operators.fused_gatconv import GATConvFuse, GATConvFuse_inference, GATLayerFuse
 
 
 class GATConv(nn.Module):
@@ -49,13 +50,22 @@ class GATConv(nn.Module):
         heads, width = self.num_heads, self.out_feats
         h = self.feat_drop(torch.matmul(feat, self.W).view(-1, heads, width))
         # destination (row) logits use attn_l, source (column) logits use attn_r
-        attn_row = (h * self.attn_l).sum(-1)
-        attn_col = (h * self.attn_r).sum(-1)
-        if self.training:
-            rst = GATConvFuse(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, permute,
-                              self.negative_slope, h, self.attn_drop)
+        fused_logits = h.is_cuda and kernels.logits_supported(heads, width)
+        if self.training and fused_logits:
+            # logits, aggregation and their backward as one autograd node (same math as the branch below)
+            rst = GATLayerFuse(h, self.attn_l, self.attn_r, row_ptr, col_ind, col_ptr, row_ind, permute,
+                               self.negative_slope, self.attn_drop)
         else:
-            rst = GATConvFuse_inference(attn_row, attn_col, row_ptr, col_ind, self.negative_slope, h)
+            if fused_logits and not torch.is_grad_enabled():
+                attn_row, attn_col = kernels.gat_logits_forward(h, self.attn_l, self.attn_r)
+            else:
+                attn_row = (h * self.attn_l).sum(-1)
+                attn_col = (h * self.attn_r).sum(-1)
+            if self.training:
+                rst = GATConvFuse(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, permute,
+                                  self.negative_slope, h, self.attn_drop)
+            else:
+                rst = GATConvFuse_inference(attn_row, attn_col, row_ptr, col_ind, self.negative_slope, h)
         if self.res_fc is not None:
             # as in the reference the residual branch is applied to the projected features
             rst = rst + self.res_fc(h).view(-1, heads, width)

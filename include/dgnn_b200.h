@@ -110,6 +110,22 @@ int dgnn_gat_backward(int64_t n, int64_t nnz, int h, int f,
                       float* grad_feat, float* grad_attn_row, float* grad_attn_col,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* Attention logits of the GAT layer around the operator (the reference computes them with
+ * tensor ops, dgNN/layers/gatconv_layer.py:74-75): attn_row[n,h] = <feat[n,h,:], attn_l[h,:]>,
+ * attn_col[n,h] = <feat[n,h,:], attn_r[h,:]> in one pass.  The backward adds
+ * grad_row (x) attn_l + grad_col (x) attn_r into grad_feat IN PLACE and writes the parameter
+ * gradients grad_l, grad_r [h,f] (fixed-order reduction).  Only shapes with f = 4*2^k and
+ * h*f <= 1024 are supported (DGNN_ERR_SHAPE otherwise: the caller uses tensor ops instead). */
+int dgnn_gat_logits_forward(int64_t n, int h, int f, const float* feat,
+                            const float* attn_l, const float* attn_r,
+                            float* attn_row, float* attn_col, void* stream);
+size_t dgnn_gat_logits_backward_workspace_bytes(int h, int f);
+int dgnn_gat_logits_backward(int64_t n, int h, int f, const float* feat,
+                             const float* attn_l, const float* attn_r,
+                             const float* grad_row, const float* grad_col,
+                             float* grad_feat, float* grad_l, float* grad_r,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Uniform floats in (0,1] from a counter-based Philox4x32-10 stream; stands in
  * for the cuRAND fill of edge_mask (fused_gatconv_kernel.cu:333-341). */
 int dgnn_uniform_fill(uint64_t seed, uint64_t offset, int64_t n, float* out, void* stream);

@@ -157,3 +157,50 @@ def test_deterministic_repeat(cuda):
         runs.append((out,) + kernels.gat_backward(0.2, 0.0, rp, cp, ri, pm, emax, esum, None, x, out, ar, ac, g))
     for a, b in zip(*runs):
         assert torch.equal(a, b)   # no float atomics anywhere: bit-identical
+
+
+@pytest.mark.parametrize("h,f", [(8, 32), (4, 64), (1, 16), (3, 16), (16, 64), (2, 4)])
+def test_logits_kernels_match_tensor_ops(cuda, h, f):
+    g = torch.Generator().manual_seed(h * 100 + f)
+    n = 3001
+    x = torch.randn(n, h, f, generator=g)
+    al, ar = torch.randn(1, h, f, generator=g), torch.randn(1, h, f, generator=g)
+    g_row, g_col = torch.randn(n, h, generator=g), torch.randn(n, h, generator=g)
+    g_feat = torch.randn(n, h, f, generator=g)
+    xd, ald, ard = x.double(), al.double(), ar.double()
+    a_row, a_col = kernels.gat_logits_forward(x.to(cuda), al.to(cuda), ar.to(cuda))
+    assert_close(a_row, (xd * ald).sum(-1).float(), "attn_row")
+    assert_close(a_col, (xd * ard).sum(-1).float(), "attn_col")
+    gf = g_feat.clone().to(cuda)
+    gl, gr = kernels.gat_logits_backward(x.to(cuda), al.to(cuda), ar.to(cuda), g_row.to(cuda), g_col.to(cuda), gf)
+    ref_feat = g_feat.double() + g_row.double()[:, :, None] * ald + g_col.double()[:, :, None] * ard
+    assert_close(gf, ref_feat.float(), "grad_feat accumulated in place")
+    assert_close(gl, (g_row.double()[:, :, None] * xd).sum(0).float(), "grad attn_l", atol=1e-3)
+    assert_close(gr, (g_col.double()[:, :, None] * xd).sum(0).float(), "grad attn_r", atol=1e-3)
+
+
+def test_layer_fused_path_equals_composed_path(cuda):
+    """GATConv's single-node training path (GATLayerFuse) against the reference composition
+    (tensor-op logits + GATConvFuse), outputs and every parameter gradient."""
+    from dgnn_b200.layers import GATConv
+    from dgnn_b200.operators import GATConvFuse
+    rp, ci = _case(**GRAPHS["long_rows"])
+    n = rp.numel() - 1
+    cp, ri, pm = [t.int().to(cuda) for t in scipy_csc(rp, ci)]
+    rp, ci = rp.to(cuda), ci.to(cuda)
+    torch.manual_seed(0)
+    layer = GATConv(256, 32, 8, residual=True).to(cuda).train()   # in_feats == heads*out_feats: identity residual
+    feat = torch.randn(n, 256, device=cuda)
+    cot = torch.randn(n, 8, 32, device=cuda)
+    out = layer(rp, ci, cp, ri, pm, feat)
+    out.backward(cot)
+    got = {k: p.grad.clone() for k, p in layer.named_parameters()}
+    layer.zero_grad()
+    h = torch.matmul(feat, layer.W).view(-1, 8, 32)
+    ref = GATConvFuse((h * layer.attn_l).sum(-1), (h * layer.attn_r).sum(-1), rp, ci, cp, ri, pm, 0.2, h, 0.0)
+    ref = ref + layer.res_fc(h).view(-1, 8, 32) + layer.bias.view(-1, 8, 32)
+    ref.backward(cot)
+    assert_close(out, ref, "layer output")
+    for k, p in layer.named_parameters():
+        scale = max(1.0, float(p.grad.abs().max()))
+        assert_close(got[k], p.grad, f"grad {k}", atol=1e-4 * scale)

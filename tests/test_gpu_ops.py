@@ -168,3 +168,32 @@ def test_uniform_fill_statistics(cuda):
     assert abs(float(u.mean()) - 0.5) < 2e-3 and abs(float(u.var()) - 1 / 12) < 2e-3
     assert torch.equal(u, kernels.uniform_fill((1 << 20,), seed=7, offset=0, device=cuda))
     assert not torch.equal(u, kernels.uniform_fill((1 << 20,), seed=8, offset=0, device=cuda))
+
+
+def test_c2_config_gmm_layer(cuda):
+    """Config 2: the 2708-node graph, pseudo = (deg_src^-1/2, deg_dst^-1/2), 3 kernels, 1433 -> 16, through the layer API."""
+    from dgnn_b200.layers import GMMConv
+    rp, ci = synth.powerlaw_graph()
+    n, nnz = rp.numel() - 1, ci.numel()
+    pseudo = synth.monet_pseudo(rp, ci)
+    g = torch.Generator().manual_seed(2)
+    feat = (torch.rand(n, 1433, generator=g) < 0.013).float()
+    torch.manual_seed(2)
+    layer = GMMConv(1433, 16, 2, 3)
+    with torch.no_grad():
+        layer.mu.copy_(torch.rand(3, 2, generator=g))
+    cot = torch.randn(n, 16, generator=g)
+    # CPU oracle of the layer, autograd backward in fp64
+    fc_w, mu, sig = [p.detach().double().clone().requires_grad_() for p in (layer.fc.weight, layer.mu, layer.inv_sigma)]
+    node_feat = (feat.double() @ fc_w.t()).view(-1, 3, 16)
+    ref = orc.gmm_forward(rp, ci, node_feat, pseudo.double(), mu, sig).sum(1)
+    (ref * cot.double()).sum().backward()
+    cp, ri, pm = scipy_csc(rp, ci)
+    layer = layer.to(cuda)
+    out = layer(rp.to(cuda), ci.to(cuda), cp.int().to(cuda), ri.int().to(cuda), pm.int().to(cuda), feat.to(cuda), pseudo.to(cuda))
+    (out * cot.to(cuda)).sum().backward()
+    assert_close(out, ref.float(), "GMM layer out", rtol=1e-3, atol=1e-5)      # tolerance of the reference's own GMM script
+    for got, want, name in ((layer.fc.weight.grad, fc_w.grad, "d fc"), (layer.mu.grad, mu.grad, "d mu"),
+                            (layer.inv_sigma.grad, sig.grad, "d inv_sigma")):
+        scale = max(1.0, float(want.abs().max()))
+        assert_close(got, want.float(), name, rtol=1e-3, atol=1e-4 * scale)
