@@ -77,28 +77,46 @@ struct LaneMap {
   }
 };
 
-// Sum p[v] over all vectors of the same head; every lane of the head ends with
-// the total.  All 32 lanes must call it.
-template <int VPL>
-__device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
-  const int span = f4_shift < 5 ? (1 << f4_shift) : 32;
-  for (int o = 1; o < span; o <<= 1) {
+// Sum p[u][v] over all vectors of the same head, for U independent edges at once;
+// every lane of the head ends with the total.  All 32 lanes must call it.  The
+// butterfly steps are compile-time offsets under a uniform predicate, and each step
+// is issued for all U*VPL values before the next one so the shuffles overlap.
+template <int U, int VPL>
+__device__ __forceinline__ void head_reduce(float (&p)[U][VPL], int f4_shift) {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) p[v] += __shfl_xor_sync(DGNN_FULL, p[v], o);
+  for (int s = 0; s < 5; ++s) {
+    if (s < f4_shift) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) p[u][v] += __shfl_xor_sync(DGNN_FULL, p[u][v], 1 << s);
+    }
   }
   if (f4_shift > 5) {
     const int g = 1 << (f4_shift - 5);  // vector slots per head
 #pragma unroll
     for (int s = 1; s < VPL; s <<= 1) {
       if (s < g) {
-        float t[VPL];
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) t[v] = p[v] + p[v ^ s];
+        for (int u = 0; u < U; ++u) {
+          float t[VPL];
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) p[v] = t[v];
+          for (int v = 0; v < VPL; ++v) t[v] = p[u][v] + p[u][v ^ s];
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) p[u][v] = t[v];
+        }
       }
     }
   }
+}
+template <int VPL>
+__device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
+  float q[1][VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) q[0][v] = p[v];
+  head_reduce<1, VPL>(q, f4_shift);
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) p[v] = q[0][v];
 }
 
 // ---------------------------------------------------------------------------

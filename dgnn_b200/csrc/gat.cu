@@ -291,12 +291,14 @@ struct GatBwdOp {
         if (MASK) keep[u][v] = ok ? (__ldg(mask + (i64)pp[u] * H + st.lm.hd[v]) > drop_p) : false;
       }
     }
+    float d[U][VPL];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) d[u][v] = dot4(g4[u][v], st.x[v]);
+    head_reduce<U, VPL>(d, f4_shift);  // executed by all lanes, also for slots past cnt
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      float d[VPL];
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) d[v] = dot4(g4[u][v], st.x[v]);
-      head_reduce<VPL>(d, f4_shift);  // executed by all lanes, also for slots past cnt
       if (ALL || k + u < cnt) {
 #pragma unroll
         for (int v = 0; v < VPL; ++v) {
@@ -304,7 +306,7 @@ struct GatBwdOp {
           const float l = leaky(pk[u][v].x + st.ac[v], slope);
           const float alpha = fast_exp(l - pk[u][v].y) * pk[u][v].z;   // pack.z = 1 / edge_sum
           const float kp = (!MASK || keep[u][v]) ? inv_keep : 0.f;
-          float de = alpha * (d[v] * kp - pk[u][v].w);
+          float de = alpha * (d[u][v] * kp - pk[u][v].w);
           de = l < 0.f ? de * slope : de;
           st.gc[v] += de;
           fma4(st.acc[v], alpha * kp, g4[u][v]);

@@ -67,16 +67,18 @@ struct SddmmOp {
           for (int v = 0; v < VPL; ++v)
             x[u][v] = (k + u < cnt && st.lm.act[v]) ? ld4(b + (i64)c * hf4 + st.lm.q[v]) : zero4();
         }
+        float d[U][VPL];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) d[u][v] = dot4(st.a[v], x[u][v]);
+        head_reduce<U, VPL>(d, f4_shift);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          float d[VPL];
-#pragma unroll
-          for (int v = 0; v < VPL; ++v) d[v] = dot4(st.a[v], x[u][v]);
-          head_reduce<VPL>(d, f4_shift);
           if (k + u < cnt) {
 #pragma unroll
             for (int v = 0; v < VPL; ++v)
-              if (st.lm.lead[v]) out[(base + k + u) * H + st.lm.hd[v]] = d[v];
+              if (st.lm.lead[v]) out[(base + k + u) * H + st.lm.hd[v]] = d[u][v];
           }
         }
       }
