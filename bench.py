@@ -45,6 +45,9 @@ def parse():
     ap.add_argument("--cpu-sample-edges", type=int, default=2_000_000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--trace", default="", help="write a torch.profiler summary of two steps (rank 0) to this file")
+    ap.add_argument("--stages", type=int, default=-1,
+                    help="gather pipeline stages of the sharded path (-1: 1 up to 2 GPUs, 2 beyond; 0: contiguous blocks)")
     return ap.parse_args()
 
 
@@ -151,7 +154,11 @@ class PhaseTimer:
         for name, key, launches in (("gat_forward", "fwd", 3),          # rows, chunks, merge
                                     ("gat_backward", "bwd", 7),         # rowstat, 3 column-pass, 3 row-reduce
                                     ("gat_rowstat", "bwd_stat", 1),
-                                    ("gat_backward_cols", "bwd_cols", 6)):
+                                    ("gat_backward_cols", "bwd_cols", 6),
+                                    ("gat_forward_staged", "fwd", 3),
+                                    ("gat_backward_cols_staged", "bwd_cols", 6),
+                                    ("gat_logits_forward", "logits_fwd", 1),
+                                    ("gat_logits_backward", "logits_bwd", 2)):
             inner = getattr(module, name)
             self.spans.setdefault(key, [])
 
@@ -244,6 +251,8 @@ def run_ours(args, rank, world, local):
         dist.init_process_group("nccl", device_id=dev)
 
     n, nnz = args.nodes, args.edges
+    if args.stages < 0:
+        args.stages = 1 if world <= 2 else 2
     rp, ci = make_graph(args, dev)
     W, al, ar_ = make_params(dev)
     W.requires_grad_(); al.requires_grad_(); ar_.requires_grad_()
@@ -279,12 +288,20 @@ def run_ours(args, rank, world, local):
         n_loc = n
     else:
         import torch.distributed as dist
-        shard = gdist.build_shard(rp, ci, rank, world)
         del cp, ri, pm
-        r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
-        n_loc = r1 - r0
-        x = seeded_normal((n, IN), 45, dev)[r0:r1].contiguous()
-        cot = seeded_normal((n, H, F), 46, dev)[r0:r1].contiguous()
+        if args.stages > 0:
+            shard = gdist.build_pipe_shard(rp, ci, rank, world, stages=args.stages, seed=7)
+            n_loc = int((shard.local_ids >= 0).sum())
+            x = gdist.scatter_rows(seeded_normal((n, IN), 45, dev), shard)
+            cot = gdist.scatter_rows(seeded_normal((n, H, F), 46, dev), shard)
+            agg = lambda h_: gdist.pipelined_gat_layer(h_, al, ar_, shard, SLOPE)
+        else:
+            shard = gdist.build_shard(rp, ci, rank, world)
+            r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
+            n_loc = r1 - r0
+            x = seeded_normal((n, IN), 45, dev)[r0:r1].contiguous()
+            cot = seeded_normal((n, H, F), 46, dev)[r0:r1].contiguous()
+            agg = lambda h_: gdist.sharded_gat_layer(h_, al, ar_, shard, SLOPE)
         del rp, ci
         torch.cuda.empty_cache()
         inner_ag = gdist._all_gather_rows
@@ -302,7 +319,7 @@ def run_ours(args, rank, world, local):
         def step(x_in):
             # the same layer on this rank's node block: projection, logits + sharded aggregation, bias
             h = torch.matmul(x_in, W).view(-1, H, F)
-            out = gdist.sharded_gat_layer(h, al, ar_, shard, SLOPE) + bias.view(-1, H, F)
+            out = agg(h) + bias.view(-1, H, F)
             loss = torch.dot(out.reshape(-1), cot.view(-1))
             loss.backward()
             for p in params:            # data-parallel parameter gradients
@@ -323,6 +340,17 @@ def run_ours(args, rank, world, local):
         step(x)
         zero_grads()
     sync_all()
+    if args.trace:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for _ in range(2):
+                step(x)
+                zero_grads()
+            sync_all()
+        if rank == 0:
+            with open(args.trace, "w") as fh:
+                fh.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70))
+            prof.export_chrome_trace(args.trace + ".json")
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -408,7 +436,7 @@ def run_ours(args, rank, world, local):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"GATConv layer fwd+bwd, R-MAT {n} nodes / {nnz} edges (a=0.57,b=c=0.19), in={IN}, {H} heads x {F}, "
-                               f"int64 row_ptr, row-block sharded over {world} GPU(s)",
+                               f"int64 row_ptr, row-block sharded over {world} GPU(s)" + (f", {args.stages}-stage gather pipeline" if world > 1 and args.stages > 0 else ""),
                    "l2": "inputs (2.46 GB feature tensor per pass) exceed the 126 MB L2; no flush needed",
                    "csr2csc_ms": csr2csc_ms},
         "gpu_launches": timer.launches,

@@ -33,6 +33,12 @@ SIGNATURES = {
     "dgnn_gat_forward_workspace_bytes": (c_sz, [c_i64, c_i64, c_int, c_int]),
     "dgnn_gat_forward": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
                                  c_p, c_p, c_p, c_p, c_sz, c_p]),
+    "dgnn_gat_forward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
+    "dgnn_gat_forward_staged": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
+                                        c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
+    "dgnn_gat_backward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
+    "dgnn_gat_backward_cols_staged": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p,
+                                              c_p, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
     "dgnn_gat_rowstat": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_gat_backward_workspace_bytes": (c_sz, [c_i64, c_i64, c_i64, c_int, c_int]),
     "dgnn_gat_backward_cols": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p,

@@ -123,7 +123,9 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 // the three scheduling kernels, generic over an operator object
 // Op must provide: n_rows, nnz, indptr, idx_bits, ws (float* partial slots),
 //   slot_stride (floats per slot), MIN_BLOCKS, HAS_PARTIALS, struct State,
-//   init(State&, row, lane), range(State&, row, e0, e1, lane),
+//   skip_empty (rows without edges need no work), init(State&, row, lane) = empty state,
+//   resume(State&, row, lane) = fold in a state carried from an earlier call (once per row),
+//   range(State&, row, e0, e1, lane),
 //   finalize(State&, row, lane), store_partial(State&, float* p, lane),
 //   merge_partial(State&, const float* p, lane)
 // ---------------------------------------------------------------------------
@@ -141,8 +143,10 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const
     const i64 lb = ldp(op.indptr, op.idx_bits, r);
     const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
     if (hb - lb > DGNN_SEG) continue;  // long row: chunk + merge kernels own it
+    if (op.skip_empty && hb == lb) continue;  // middle stage of a staged sweep: the carried state stays as it is
     typename Op::State st;
     op.init(st, r, lane);
+    op.resume(st, r, lane);
     op.range(st, r, lb, hb, lane);
     op.finalize(st, r, lane);
   }
@@ -198,6 +202,7 @@ __global__ void __launch_bounds__(DGNN_THREADS) k_merge(const Op op) {
   if (hb - lb <= DGNN_SEG || lb < cs) return;  // the long row that begins in this chunk
   typename Op::State st;
   op.init(st, r, lane);
+  op.resume(st, r, lane);
   op.merge_partial(st, op.ws + (2 * j + 1) * op.slot_stride, lane);
   for (i64 jj = j + 1; jj * DGNN_SEG < hb; ++jj) op.merge_partial(st, op.ws + (2 * jj) * op.slot_stride, lane);
   op.finalize(st, r, lane);

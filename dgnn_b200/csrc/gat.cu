@@ -39,6 +39,10 @@ struct GatFwdOp {
   float* edge_sum;
   float* ws;
   i64 slot_stride;  // floats per partial slot
+  // staged sweep over column blocks: the (max, sum, accumulator) state of every row is
+  // carried in `state` (one slot per row) between calls; first / last mark the ends
+  float* state;
+  int first, last, skip_empty;
 
   struct State {
     LaneMap<VPL> lm;
@@ -55,6 +59,9 @@ struct GatFwdOp {
       st.z[v] = 0.f;
       st.acc[v] = zero4();
     }
+  }
+  __device__ __forceinline__ void resume(State& st, i64 r, int lane) const {
+    if (!first) merge_partial(st, state + r * slot_stride, lane);
   }
 
   // one batch of U edges starting at tile slot k; ALL = every slot of the batch holds an edge
@@ -114,7 +121,8 @@ struct GatFwdOp {
     }
   }
 
-  __device__ __forceinline__ void finalize(State& st, i64 r, int) const {
+  __device__ __forceinline__ void finalize(State& st, i64 r, int lane) const {
+    if (!last) { store_partial(st, state + r * slot_stride, lane); return; }
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
@@ -251,6 +259,8 @@ struct GatBwdOp {
   float* grad_edge;  // [nnz,H] in CSR order
   float* ws;
   i64 slot_stride;
+  float* state;      // staged sweep over row blocks: (grad_feat, grad_attn_col) accumulators per column
+  int first, last, skip_empty;
 
   struct State {
     LaneMap<VPL> lm;
@@ -267,6 +277,9 @@ struct GatBwdOp {
       st.acc[v] = zero4();
       st.gc[v] = 0.f;
     }
+  }
+  __device__ __forceinline__ void resume(State& st, i64 c, int lane) const {
+    if (!first) merge_partial(st, state + c * slot_stride, lane);
   }
 
   template <bool ALL>
@@ -328,7 +341,8 @@ struct GatBwdOp {
     }
   }
 
-  __device__ __forceinline__ void finalize(State& st, i64 c, int) const {
+  __device__ __forceinline__ void finalize(State& st, i64 c, int lane) const {
+    if (!last) { store_partial(st, state + c * slot_stride, lane); return; }
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
@@ -482,7 +496,7 @@ template <int VPL, bool MASK, bool FULL>
 int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
                const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
                float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
-               void* ws, cudaStream_t s) {
+               void* ws, float* state, int first, int last, cudaStream_t s) {
   GatFwdOp<VPL, MASK, FULL> op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -491,6 +505,7 @@ int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const voi
   op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
   op.out = reinterpret_cast<float4*>(out); op.edge_max = edge_max; op.edge_sum = edge_sum;
   op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER); op.slot_stride = fwd_slot_stride(h, f);
+  op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last) ? 1 : 0;
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
@@ -499,7 +514,7 @@ int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const voi
                const int* row_ind, const int* permute, const float* pack, const float* mask,
                const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
                float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, unsigned long long* counter,
-               cudaStream_t s) {
+               float* state, int first, int last, cudaStream_t s) {
   GatBwdOp<VPL, MASK, FULL> op;
   op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -509,6 +524,7 @@ int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const voi
   op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
   op.grad_feat = reinterpret_cast<float4*>(grad_feat); op.grad_attn_col = grad_attn_col;
   op.grad_edge = grad_edge; op.ws = ws; op.slot_stride = bwd_slot_stride(h, f);
+  op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last) ? 1 : 0;
   return dgnn_launch_trio(op, counter, s);
 }
 
@@ -558,16 +574,37 @@ size_t dgnn_gat_forward_workspace_bytes(int64_t n_rows, int64_t nnz, int h, int 
   return DGNN_WS_HEADER + up256((size_t)(2 * dgnn_num_chunks(nnz)) * fwd_slot_stride(h, f) * sizeof(float));
 }
 
+size_t dgnn_gat_forward_state_bytes(int64_t n_rows, int h, int f) {
+  if (n_rows < 0 || h <= 0 || f <= 0) return 0;
+  return (size_t)n_rows * fwd_slot_stride(h, f) * sizeof(float);
+}
+size_t dgnn_gat_backward_state_bytes(int64_t n_cols, int h, int f) {
+  if (n_cols < 0 || h <= 0 || f <= 0) return 0;
+  return (size_t)n_cols * bwd_slot_stride(h, f) * sizeof(float);
+}
+
 int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
                      const int32_t* col_ind, const float* attn_row, const float* attn_col,
                      const float* in_feat, float negative_slope, float attn_drop, const float* edge_mask,
                      float* out, float* edge_max, float* edge_sum, void* workspace,
                      size_t workspace_bytes, void* stream) {
+  return dgnn_gat_forward_staged(n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,
+                                 negative_slope, attn_drop, edge_mask, out, edge_max, edge_sum, nullptr, 1, 1,
+                                 workspace, workspace_bytes, stream);
+}
+
+int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
+                            const int32_t* col_ind, const float* attn_row, const float* attn_col,
+                            const float* in_feat, float negative_slope, float attn_drop,
+                            const float* edge_mask, float* out, float* edge_max, float* edge_sum, float* state,
+                            int first, int last, void* workspace, size_t workspace_bytes, void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
+  const bool staged = !(first && last);
+  if (staged && (!state || !aligned16(state))) return state ? DGNN_ERR_ALIGN : DGNN_ERR_NULL;
   if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
   if (n_rows == 0) return DGNN_OK;
-  if (!row_ptr || !attn_row || !out || (nnz > 0 && (!col_ind || !attn_col || !in_feat))) return DGNN_ERR_NULL;
+  if (!row_ptr || !attn_row || (last && !out) || (nnz > 0 && (!col_ind || !attn_col || !in_feat))) return DGNN_ERR_NULL;
   if ((edge_max == nullptr) != (edge_sum == nullptr)) return DGNN_ERR_NULL;
   if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
   const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
@@ -579,10 +616,11 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_
     if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
 #define CALL_FWD(V, M, FW)                                                                           \
   launch_fwd<V, M, FW>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
-                   negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, s)
+                   negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, state, first, last, s)
     DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, fs.hf4 == 32 * fs.vpl, CALL_FWD)
 #undef CALL_FWD
   }
+  if (staged) return DGNN_ERR_SHAPE;   // the staged sweep exists only for the float4 layout
   k_gat_fwd_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
       n_rows, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, mask, negative_slope,
       attn_drop, (float)(1.0 / (1.0 - (double)attn_drop)), out, edge_max, edge_sum);
@@ -630,14 +668,28 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
                            const float* in_feat, const float* attn_col, const float* grad_out,
                            float negative_slope, float attn_drop, float* grad_feat, float* grad_attn_row,
                            float* grad_attn_col, void* workspace, size_t workspace_bytes, void* stream) {
+  return dgnn_gat_backward_cols_staged(n_rows, n_cols, nnz, h, f, row_ptr, col_ptr, idx_bits, row_ind, permute, pack,
+                                       edge_mask, in_feat, attn_col, grad_out, negative_slope, attn_drop, grad_feat,
+                                       grad_attn_row, grad_attn_col, nullptr, 1, 1, workspace, workspace_bytes, stream);
+}
+
+int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f, const void* row_ptr,
+                                  const void* col_ptr, int idx_bits, const int32_t* row_ind,
+                                  const int32_t* permute, const float* pack, const float* edge_mask,
+                                  const float* in_feat, const float* attn_col, const float* grad_out,
+                                  float negative_slope, float attn_drop, float* grad_feat, float* grad_attn_row,
+                                  float* grad_attn_col, float* state, int first, int last, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
+  const bool staged = !(first && last);
+  if (staged && (!state || !aligned16(state))) return state ? DGNN_ERR_ALIGN : DGNN_ERR_NULL;
   st = check_common(n_cols, nnz, h, f, idx_bits);
   if (st) return st;
   if (nnz > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;  // permute is int32
   if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
   if (!row_ptr || !col_ptr) return DGNN_ERR_NULL;
-  if (n_cols > 0 && (!in_feat || !attn_col || !grad_feat || !grad_attn_col)) return DGNN_ERR_NULL;
+  if (n_cols > 0 && (!in_feat || !attn_col || (last && (!grad_feat || !grad_attn_col)))) return DGNN_ERR_NULL;
   if (n_rows > 0 && (!pack || !grad_out || !grad_attn_row)) return DGNN_ERR_NULL;
   if (nnz > 0 && (!row_ind || !permute)) return DGNN_ERR_NULL;
   if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
@@ -658,12 +710,13 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
 #define CALL_BWD(V, M, FW)                                                                              \
   launch_bwd<V, M, FW>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
                    attn_col, grad_out, negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, \
-                   col_part, counter, s)
+                   col_part, counter, state, first, last, s)
       auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, fs.hf4 == 32 * fs.vpl, CALL_BWD) };
 #undef CALL_BWD
       rc = run();
       if (rc) return rc;
     } else {
+      if (staged) return DGNN_ERR_SHAPE;
       k_gat_bwd_cols_generic<<<dgnn_grid(n_cols * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
           n_cols, h, f, col_ptr, idx_bits, row_ind, permute, reinterpret_cast<const float4*>(pack), mask,
           in_feat, attn_col, grad_out, negative_slope, attn_drop,

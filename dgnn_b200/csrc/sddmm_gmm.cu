@@ -39,6 +39,7 @@ struct SddmmOp {
   int H, hf4, f4_shift;
   float* ws;
   i64 slot_stride;
+  int skip_empty;
   const int* col_ind;
   const float4* a;
   const float4* b;
@@ -84,6 +85,7 @@ struct SddmmOp {
       }
     }
   }
+  __device__ __forceinline__ void resume(State&, i64, int) const {}
   __device__ __forceinline__ void finalize(State&, i64, int) const {}
   __device__ __forceinline__ void store_partial(State&, float*, int) const {}
   __device__ __forceinline__ void merge_partial(State&, const float*, int) const {}
@@ -151,6 +153,7 @@ struct GmmOp {
   float4* out;
   float* ws;
   i64 slot_stride;
+  int skip_empty;
 
   struct State {
     LaneMap<VPL> lm;
@@ -186,6 +189,7 @@ struct GmmOp {
       }
     }
   }
+  __device__ __forceinline__ void resume(State&, i64, int) const {}
   __device__ __forceinline__ void finalize(State& st, i64 r, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
@@ -295,7 +299,7 @@ template <int VPL>
 int launch_sddmm(const FastShape& fs, i64 n_rows, i64 nnz, int h, const void* row_ptr, int idx_bits,
                  const int* col_ind, const float* a, const float* b, float* out, void* ws, cudaStream_t s) {
   SddmmOp<VPL> op;
-  op.ws = nullptr; op.slot_stride = 0;
+  op.ws = nullptr; op.slot_stride = 0; op.skip_empty = 1;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift; op.col_ind = col_ind;
   op.a = reinterpret_cast<const float4*>(a); op.b = reinterpret_cast<const float4*>(b); op.out = out;
@@ -312,7 +316,7 @@ int launch_gmm(const FastShape& fs, i64 n_rows, i64 nnz, int K, int dim, int f, 
   op.feat = reinterpret_cast<const float4*>(feat); op.pseudo = pseudo; op.mu = mu; op.sig = sig;
   op.out = reinterpret_cast<float4*>(out);
   op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER);
-  op.slot_stride = (i64)K * f;
+  op.slot_stride = (i64)K * f; op.skip_empty = 0;
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 

@@ -186,3 +186,204 @@ def sharded_gat(attn_row, attn_col, in_feat, shard, negative_slope=0.2, group=No
 def sharded_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None):
     """Logits + sharded aggregation; differentiable in h and the attention vectors."""
     return ShardedGATLayerFunction.apply(h, attn_l, attn_r, shard, negative_slope, group)
+
+
+# ---------------------------------------------------------------------------
+# Pipelined sharding: random node relabelling, equal blocks, staged all-gathers
+# ---------------------------------------------------------------------------
+@dataclass
+class PipeShard:
+    """Pieces of the graph for one rank of the pipelined sharded operator.
+
+    Nodes are relabelled by a seeded random permutation and dealt out in equal
+    blocks of `blk` nodes per rank (ids past the real node count are padding
+    without edges), so in-edges, out-edges and node counts are all balanced.
+    Every block is cut into `stages` slices; stage p all-gathers slice p of every
+    rank ([world*slice, ...] buffer, row g*slice + i = node i of rank g's slice p)
+    while the kernels work on the edges of stage p-1."""
+    rank: int
+    world: int
+    stages: int
+    n: int
+    blk: int
+    slice: int
+    local_ids: torch.Tensor       # original node id of every local row (-1 for padding)
+    fwd: list                     # per stage: (row_ptr [blk+1], col_ind -> buffer row)
+    bwd: list                     # per stage: (row_ptr [world*slice+1], col_ptr [blk+1], row_ind -> buffer row, permute)
+
+
+def _expand_segments(ptr, ids):
+    """Positions and local segment index of all entries of the segments `ids` of a CSR/CSC pointer."""
+    valid = ids >= 0
+    safe = ids.clamp(min=0)
+    start = ptr[safe]
+    deg = torch.where(valid, ptr[safe + 1] - start, torch.zeros_like(start))
+    seg = torch.repeat_interleave(torch.arange(ids.numel(), device=ids.device), deg)
+    excl = torch.cumsum(deg, 0) - deg
+    pos = start[seg] + (torch.arange(int(deg.sum()), device=ids.device) - excl[seg])
+    return pos, seg
+
+
+def build_pipe_shard(row_ptr, col_ind, rank, world, stages=4, seed=0, csr2csc=None) -> PipeShard:
+    """Every rank calls this with the same global CSR (rows = destinations) and seed."""
+    csr2csc = csr2csc or kernels.csr2csc
+    dev = col_ind.device
+    rp = row_ptr.long()
+    n = rp.numel() - 1
+    blk = -(-n // (world * stages)) * stages
+    sl = blk // stages
+    n_pad = world * blk
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    order = torch.full((n_pad,), -1, dtype=torch.long)
+    order[:n] = torch.randperm(n, generator=g)
+    order = order[torch.randperm(n_pad, generator=g)].to(dev)        # padding spread over all blocks
+    inv = torch.empty(n, dtype=torch.long, device=dev)
+    real = order >= 0
+    inv[order[real]] = torch.arange(n_pad, device=dev)[real]
+    local_ids = order[rank * blk: (rank + 1) * blk].contiguous()
+
+    def buffer_row(new_id):
+        """(stage, row inside the stage's gathered buffer) of a relabelled node id."""
+        owner, rem = new_id // blk, new_id % blk
+        return rem // sl, owner * sl + rem % sl
+
+    # forward: local destination rows, all sources, split by the stage of the source
+    pos, row = _expand_segments(rp, local_ids)
+    stage, buf = buffer_row(inv[col_ind[pos].long()])
+    fwd = []
+    for p in range(stages):
+        m = stage == p
+        ptr = torch.zeros(blk + 1, dtype=torch.long, device=dev)
+        torch.cumsum(torch.bincount(row[m], minlength=blk), 0, out=ptr[1:])
+        fwd.append((ptr.to(torch.int32), buf[m].to(torch.int32).contiguous()))
+    del pos, row, stage, buf
+    # backward: local source columns, all destinations, split by the stage of the destination
+    col_ptr, row_ind, _ = csr2csc(row_ptr, col_ind)
+    pos, col = _expand_segments(col_ptr.long(), local_ids)
+    stage, buf = buffer_row(inv[row_ind[pos].long()])
+    bwd = []
+    for p in range(stages):
+        m = stage == p
+        cptr = torch.zeros(blk + 1, dtype=torch.long, device=dev)
+        torch.cumsum(torch.bincount(col[m], minlength=blk), 0, out=cptr[1:])
+        cptr = cptr.to(torch.int32)
+        rind = buf[m].to(torch.int32).contiguous()
+        # CSR of the sub-matrix = "CSC" of its transpose; perm[i] = CSC position of CSR entry i
+        rptr, _, perm = csr2csc(cptr, rind, world * sl)
+        permute = torch.empty_like(perm)
+        permute[perm.long()] = torch.arange(perm.numel(), dtype=perm.dtype, device=perm.device)
+        bwd.append((rptr.to(torch.int32).contiguous(), cptr, rind, permute.to(torch.int32).contiguous()))
+    return PipeShard(rank, world, stages, n, blk, sl, local_ids, fwd, bwd)
+
+
+def _gather_slices(x_loc, shard, group):
+    """Start the all-gathers of the `stages` slices of x_loc [blk, ...]; returns (buffers, works)."""
+    bufs, works = [], []
+    for p in range(shard.stages):
+        part = x_loc[p * shard.slice: (p + 1) * shard.slice]
+        buf = x_loc.new_empty((shard.world * shard.slice,) + tuple(x_loc.shape[1:]))
+        works.append(dist.all_gather_into_tensor(buf, part.contiguous(), group=group, async_op=True))
+        bufs.append(buf)
+    return bufs, works
+
+
+def _pipe_forward(attn_row, attn_col, h, shard, slope, group, backend):
+    col_bufs, col_works = _gather_slices(attn_col, shard, group)
+    feat_bufs, feat_works = _gather_slices(h, shard, group)
+    state = backend.gat_forward_state(shard.blk, h.shape[1], h.shape[2], h.device)
+    res = None
+    for p in range(shard.stages):
+        col_works[p].wait()
+        feat_works[p].wait()
+        ptr, col = shard.fwd[p]
+        res = backend.gat_forward_staged(attn_row, col_bufs[p], ptr, col, slope, feat_bufs[p], state,
+                                         p == 0, p == shard.stages - 1)
+    return res
+
+
+def _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum, grad_out, shard, slope, group, backend):
+    pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)
+    pack_bufs, pack_works = _gather_slices(pack, shard, group)
+    grad_bufs, grad_works = _gather_slices(grad_out, shard, group)
+    state = backend.gat_backward_state(shard.blk, h.shape[1], h.shape[2], h.device)
+    parts = []
+    grad_feat = grad_col = None
+    for p in range(shard.stages):
+        pack_works[p].wait()
+        grad_works[p].wait()
+        rptr, cptr, rind, perm = shard.bwd[p]
+        part, grad_feat, grad_col = backend.gat_backward_cols_staged(
+            rptr, cptr, rind, perm, pack_bufs[p], h, attn_col, grad_bufs[p], slope, state, p == 0,
+            p == shard.stages - 1)
+        parts.append(part)                                     # [world*slice, H]: partial sums for the rows of stage p
+    hh = h.shape[1]
+    # [stages, world, slice, H] -> sum over ranks, keep the rows this rank owns
+    allp = torch.stack(parts, 0).view(shard.stages, shard.world, shard.slice, hh)
+    if dist.get_backend(group) == "nccl":
+        send = allp.permute(1, 0, 2, 3).contiguous()           # [world, stages, slice, H]
+        mine = send.new_empty((shard.stages, shard.slice, hh))
+        dist.reduce_scatter_tensor(mine, send, group=group)
+    else:
+        allp = allp.contiguous()
+        dist.all_reduce(allp, group=group)
+        mine = allp[:, shard.rank]
+    return grad_feat, mine.reshape(shard.blk, hh).contiguous(), grad_col
+
+
+class PipelinedGATFunction(torch.autograd.Function):
+    """Fused GAT on this rank's block of the relabelled graph, with the gathers of the
+    source features (forward) and of grad_out (backward) overlapped with the kernels.
+    attn_row, attn_col [blk,H], in_feat [blk,H,F] (rows in PipeShard.local_ids order)."""
+
+    @staticmethod
+    def forward(ctx, attn_row, attn_col, in_feat, shard, negative_slope, group, backend):
+        out, edge_max, edge_sum = _pipe_forward(attn_row.contiguous(), attn_col.contiguous(), in_feat.contiguous(),
+                                                shard, negative_slope, group, backend)
+        ctx.save_for_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum)
+        ctx.shard, ctx.slope, ctx.group, ctx.backend = shard, negative_slope, group, backend
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        attn_row, attn_col, in_feat, out, edge_max, edge_sum = ctx.saved_tensors
+        grad_feat, grad_row, grad_col = _pipe_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum,
+                                                      grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group,
+                                                      ctx.backend)
+        return grad_row, grad_col, grad_feat, None, None, None, None
+
+
+class PipelinedGATLayerFunction(torch.autograd.Function):
+    """Attention logits + pipelined aggregation as one autograd node (CUDA only)."""
+
+    @staticmethod
+    def forward(ctx, h, attn_l, attn_r, shard, negative_slope, group):
+        h = h.contiguous()
+        attn_row, attn_col = kernels.gat_logits_forward(h, attn_l, attn_r)
+        out, edge_max, edge_sum = _pipe_forward(attn_row, attn_col, h, shard, negative_slope, group, kernels)
+        ctx.save_for_backward(attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r)
+        ctx.shard, ctx.slope, ctx.group = shard, negative_slope, group
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r = ctx.saved_tensors
+        grad_h, grad_row, grad_col = _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum,
+                                                   grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group, kernels)
+        grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_row, grad_col, grad_h)
+        return grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None
+
+
+def pipelined_gat(attn_row, attn_col, in_feat, shard, negative_slope=0.2, group=None, backend=kernels):
+    return PipelinedGATFunction.apply(attn_row, attn_col, in_feat, shard, negative_slope, group, backend)
+
+
+def pipelined_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None):
+    return PipelinedGATLayerFunction.apply(h, attn_l, attn_r, shard, negative_slope, group)
+
+
+def scatter_rows(x_global, shard):
+    """Rows of a global [N, ...] tensor in this rank's local order (padding rows are zero)."""
+    out = x_global.new_zeros((shard.blk,) + tuple(x_global.shape[1:]))
+    real = shard.local_ids >= 0
+    out[real] = x_global[shard.local_ids[real]]
+    return out

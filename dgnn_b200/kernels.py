@@ -349,3 +349,75 @@ def coo2csr(row_ind, m, dtype=torch.int32):
         row_ptr = torch.empty(int(m) + 1, dtype=dtype, device=dev)
         check(lib().dgnn_coo2csr(row_ind.numel(), int(m), _p(row_ind), _p(row_ptr), bits, _stream(dev)), "coo2csr")
     return row_ptr
+
+
+# ------------------------------------------------ staged (block-by-block) GAT
+def gat_forward_state(n_rows, h, f, device):
+    """Per-row softmax state carried between the calls of a staged forward."""
+    nbytes = lib().dgnn_gat_forward_state_bytes(int(n_rows), int(h), int(f))
+    return torch.empty(max(nbytes // 4, 4), dtype=torch.float32, device=device)
+
+
+def gat_backward_state(n_cols, h, f, device):
+    nbytes = lib().dgnn_gat_backward_state_bytes(int(n_cols), int(h), int(f))
+    return torch.empty(max(nbytes // 4, 4), dtype=torch.float32, device=device)
+
+
+def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope, feat_blk, state, first, last):
+    """One stage of the forward over the edges whose source lies in one column block.
+    Returns (out, edge_max, edge_sum) from the last stage, None before."""
+    attn_row = _cuda_f32(attn_row, "attn_row")
+    attn_col_blk = _cuda_f32(attn_col_blk, "attn_col")
+    feat_blk = _cuda_f32(feat_blk, "in_feat")
+    col_ind = _cuda_i32(col_ind, "col_ind")
+    row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
+    _, h, f = _dims3(feat_blk, "in_feat")
+    n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
+    dev = feat_blk.device
+    with torch.cuda.device(dev):
+        out = emax = esum = None
+        if last:
+            out = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
+            emax = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+            esum = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f), dev)
+        check(lib().dgnn_gat_forward_staged(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
+                                            _p(attn_col_blk), _p(feat_blk), float(negative_slope), 0.0, None,
+                                            _p(out), _p(emax), _p(esum), _p(state), int(bool(first)), int(bool(last)),
+                                            _p(ws), ws.numel(), _stream(dev)), "gat_forward_staged")
+    return (out, emax, esum) if last else None
+
+
+def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_feat, attn_col, grad_blk,
+                             negative_slope, state, first, last):
+    """One stage of the backward column pass over the edges whose destination lies in one
+    row block.  Returns (grad_attn_row of the block's rows, grad_feat or None, grad_attn_col or None)."""
+    in_feat = _cuda_f32(in_feat, "in_feat")
+    attn_col = _cuda_f32(attn_col, "attn_col")
+    grad_blk = _cuda_f32(grad_blk, "grad_out")
+    pack_blk = _cuda_f32(pack_blk, "pack")
+    row_ind = _cuda_i32(row_ind, "row_ind")
+    permute = _cuda_i32(permute, "permute")
+    row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
+    col_ptr, cbits = _cuda_ptr(col_ptr, "col_ptr")
+    if cbits != bits:
+        col_ptr = _same_bits(bits, col_ptr, "col_ptr")
+    n_cols, h, f = _dims3(in_feat, "in_feat")
+    n_rows, nnz = row_ptr.numel() - 1, row_ind.numel()
+    if grad_blk.shape != (n_rows, h, f) or pack_blk.shape != (n_rows, h, 4) or col_ptr.numel() - 1 != n_cols:
+        raise RuntimeError("dgnn_b200: staged backward: block shapes do not match the sub-matrix")
+    dev = in_feat.device
+    with torch.cuda.device(dev):
+        grad_feat = grad_col = None
+        if last:
+            grad_feat = torch.empty((n_cols, h, f), dtype=torch.float32, device=dev)
+            grad_col = torch.empty((n_cols, h), dtype=torch.float32, device=dev)
+        grad_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gat_backward_workspace_bytes(n_rows, n_cols, nnz, h, f), dev)
+        check(lib().dgnn_gat_backward_cols_staged(n_rows, n_cols, nnz, h, f, _p(row_ptr), _p(col_ptr), bits,
+                                                  _p(row_ind), _p(permute), _p(pack_blk), None, _p(in_feat),
+                                                  _p(attn_col), _p(grad_blk), float(negative_slope), 0.0,
+                                                  _p(grad_feat), _p(grad_row), _p(grad_col), _p(state),
+                                                  int(bool(first)), int(bool(last)), _p(ws), ws.numel(), _stream(dev)),
+              "gat_backward_cols_staged")
+    return grad_row, grad_feat, grad_col

@@ -68,6 +68,22 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f,
                      float* out, float* edge_max, float* edge_sum,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* Staged forward for sharded graphs whose source features arrive block by block: the
+ * columns are split into blocks, each call sweeps the edges of one block (row_ptr /
+ * col_ind of that sub-matrix, attn_col / in_feat of that block) and the per-row softmax
+ * state (max, sum, accumulator; dgnn_gat_forward_state_bytes) is carried in `state`.
+ * first != 0 starts from an empty state, last != 0 normalises and writes out / edge_max /
+ * edge_sum (they may be NULL otherwise).  first = last = 1 is dgnn_gat_forward.  No
+ * counterpart in the reference, which is single-GPU. */
+size_t dgnn_gat_forward_state_bytes(int64_t n_rows, int h, int f);
+int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f,
+                            const void* row_ptr, int idx_bits, const int32_t* col_ind,
+                            const float* attn_row, const float* attn_col, const float* in_feat,
+                            float negative_slope, float attn_drop, const float* edge_mask,
+                            float* out, float* edge_max, float* edge_sum,
+                            float* state, int first, int last,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
 /* Row statistics for the backward pass: pack[r,h] = (attn_row, edge_max,
  * 1/edge_sum, S) with S[r,h] = <grad_out[r,h,:], out[r,h,:]>, which equals the
  * reference's per-row sum of alpha*g (fused_gatconv_kernel.cu:903-929) without
@@ -96,6 +112,22 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
                            float negative_slope, float attn_drop,
                            float* grad_feat, float* grad_attn_row, float* grad_attn_col,
                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* Staged column pass: the destination rows are split into blocks, each call sweeps the
+ * edges of one row block (its CSC / CSR arrays, pack and grad_out of that block) and the
+ * per-column accumulators (dgnn_gat_backward_state_bytes) are carried in `state`;
+ * grad_feat / grad_attn_col are written by the last call, grad_attn_row (of the block's
+ * rows) by every call.  first = last = 1 is dgnn_gat_backward_cols. */
+size_t dgnn_gat_backward_state_bytes(int64_t n_cols, int h, int f);
+int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f,
+                                  const void* row_ptr, const void* col_ptr, int idx_bits,
+                                  const int32_t* row_ind, const int32_t* permute,
+                                  const float* pack, const float* edge_mask,
+                                  const float* in_feat, const float* attn_col, const float* grad_out,
+                                  float negative_slope, float attn_drop,
+                                  float* grad_feat, float* grad_attn_row, float* grad_attn_col,
+                                  float* state, int first, int last,
+                                  void* workspace, size_t workspace_bytes, void* stream);
 
 /* Whole backward on a square graph: replaces fused_gatconv.gat_backward
  * (fused_gatconv.cpp:104-166).  `out` is the forward result (the reference

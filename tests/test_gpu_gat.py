@@ -204,3 +204,45 @@ def test_layer_fused_path_equals_composed_path(cuda):
     for k, p in layer.named_parameters():
         scale = max(1.0, float(p.grad.abs().max()))
         assert_close(got[k], p.grad, f"grad {k}", atol=1e-4 * scale)
+
+
+@pytest.mark.parametrize("stages", [1, 2, 5])
+def test_staged_sweeps_equal_single_sweep(cuda, stages):
+    """The state-carrying staged forward / backward column pass (used by the pipelined multi-GPU
+    path) over `stages` column / row blocks gives the same results as one sweep."""
+    from dgnn_b200 import dist as gdist
+    rp, ci = _case(**GRAPHS["long_rows"])
+    n, h, f = rp.numel() - 1, 8, 32
+    ar, ac, x, g = [t.to(cuda) for t in gat_inputs(rp, n, h, f, 17)]
+    rp, ci = rp.to(cuda), ci.to(cuda)
+    cp, ri, pm = kernels.csr2csc(rp, ci)
+    out, emax, esum = kernels.gat_forward(ar, ac, rp, ci, 0.2, x)
+    gf, gr, gc = kernels.gat_backward(0.2, 0.0, rp, cp, ri, pm, emax, esum, None, x, out, ar, ac, g)
+
+    shard = gdist.build_pipe_shard(rp, ci, 0, 1, stages=stages, seed=1)     # one rank: the buffers are slices of the local arrays
+    real = shard.local_ids >= 0
+    idx = shard.local_ids[real]
+    ar_l, ac_l, x_l, g_l = [gdist.scatter_rows(t, shard) for t in (ar, ac, x, g)]
+    sl = shard.slice
+    state = kernels.gat_forward_state(shard.blk, h, f, cuda)
+    res = None
+    for p in range(stages):
+        ptr, col = shard.fwd[p]
+        res = kernels.gat_forward_staged(ar_l, ac_l[p * sl:(p + 1) * sl], ptr, col, 0.2, x_l[p * sl:(p + 1) * sl],
+                                         state, p == 0, p == stages - 1)
+    out_s, emax_s, esum_s = res
+    assert_close(out_s[real], out[idx], "staged out")
+    assert_equal(emax_s[real], emax[idx], "staged edge_max")
+    assert_close(esum_s[real], esum[idx], "staged edge_sum")
+    pack = kernels.gat_rowstat(ar_l, emax_s, esum_s, out_s, g_l)
+    bstate = kernels.gat_backward_state(shard.blk, h, f, cuda)
+    parts = []
+    for p in range(stages):
+        rptr, cptr, rind, perm = shard.bwd[p]
+        part, gf_s, gc_s = kernels.gat_backward_cols_staged(rptr, cptr, rind, perm, pack[p * sl:(p + 1) * sl], x_l, ac_l,
+                                                            g_l[p * sl:(p + 1) * sl], 0.2, bstate, p == 0, p == stages - 1)
+        parts.append(part)
+    gr_s = torch.cat(parts, 0)
+    assert_close(gf_s[real], gf[idx], "staged grad_feat")
+    assert_close(gc_s[real], gc[idx], "staged grad_attn_col", atol=2e-5)
+    assert_close(gr_s[real], gr[idx], "staged grad_attn_row", atol=2e-5)
