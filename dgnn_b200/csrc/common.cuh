@@ -57,22 +57,33 @@ __device__ __forceinline__ float leaky(float x, float slope) { return x > 0.f ? 
 // log2(e) scaling, far inside the fp32 tolerance of the operators (1e-4 relative)
 __device__ __forceinline__ float fast_exp(float x) { return __expf(x); }
 
-// Feature rows are H*F floats viewed as HF4 = H*F/4 float4 vectors.  Lane l owns
-// vectors q = l + 32*v (v < VPL); vector q belongs to head q >> f4_shift where
-// 2^f4_shift = F/4 vectors per head.
-template <int VPL>
+// Feature rows are H*F floats viewed as HF4 = H*F/4 float4 vectors.  With LPR = 32
+// lane l owns vectors q = l + 32*v (v < VPL); vector q belongs to head q >> f4_shift
+// where 2^f4_shift = F/4 vectors per head.  Narrow rows (HF4 <= 16, VPL = 1) use
+// LPR = 16 or 8 lanes per row: the warp is cut into 32/LPR sub-groups that work on
+// different edges of the same row at the same time (sub-group sg takes every
+// (32/LPR)-th edge) and fold their states at the end of the row, so no lane idles.
+template <int VPL, int LPR = 32>
 struct LaneMap {
+  static_assert(LPR == 32 || VPL == 1, "sub-groups only for rows of at most 32 vectors");
+  static constexpr int EPW = 32 / LPR;  // edges a warp works on per step
+  int sg;          // sub-group of this lane
   int q[VPL];
   int hd[VPL];
   bool act[VPL];
-  bool lead[VPL];  // first vector of its head: writes the per-head scalars
+  bool lead[VPL];   // first vector of its head (in its sub-group)
+  bool wr[VPL];     // this lane writes the row's vector q (sub-group 0 only)
+  bool wlead[VPL];  // this lane writes the per-head scalars of the row
   __device__ __forceinline__ void init(int lane, int hf4, int f4_shift) {
+    sg = lane / LPR;
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      q[v] = lane + 32 * v;
+      q[v] = (lane % LPR) + LPR * v;
       act[v] = q[v] < hf4;
       hd[v] = act[v] ? (q[v] >> f4_shift) : 0;
       lead[v] = act[v] && ((q[v] & ((1 << f4_shift) - 1)) == 0);
+      wr[v] = act[v] && sg == 0;
+      wlead[v] = lead[v] && sg == 0;
     }
   }
 };
@@ -125,7 +136,7 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 //   slot_stride (floats per slot), MIN_BLOCKS, HAS_PARTIALS, struct State,
 //   skip_empty (rows without edges need no work), init(State&, row, lane) = empty state,
 //   resume(State&, row, lane) = fold in a state carried from an earlier call (once per row),
-//   range(State&, row, e0, e1, lane),
+//   range(State&, row, e0, e1, lane), combine(State&, lane) = fold the sub-groups' states after range,
 //   finalize(State&, row, lane), store_partial(State&, float* p, lane),
 //   merge_partial(State&, const float* p, lane)
 // ---------------------------------------------------------------------------
@@ -148,6 +159,7 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const
     op.init(st, r, lane);
     op.resume(st, r, lane);
     op.range(st, r, lb, hb, lane);
+    op.combine(st, lane);
     op.finalize(st, r, lane);
   }
 }
@@ -180,6 +192,7 @@ __global__ void __launch_bounds__(DGNN_CHUNK_WARPS * 32) k_chunks(const Op op) {
   op.init(st, r, lane);
   if (w0 < w1) op.range(st, r, w0, w1, lane);
   if (!Op::HAS_PARTIALS) return;
+  op.combine(st, lane);
   if (warp > 0) op.store_partial(st, smem + (i64)(warp - 1) * op.slot_stride, lane);
   __syncthreads();
   if (warp == 0) {

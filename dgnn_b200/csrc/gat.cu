@@ -20,8 +20,9 @@ namespace {
 template <int VPL> struct Unroll { static constexpr int U = VPL <= 2 ? 4 : 2; };
 
 // ------------------------------------------------------------------ forward
-template <int VPL, bool MASK, bool FULL>
+template <int VPL, bool MASK, bool FULL, int LPR>
 struct GatFwdOp {
+  static constexpr int EPW = 32 / LPR;
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
   static constexpr bool HAS_PARTIALS = true;
   i64 n_rows, nnz;
@@ -45,7 +46,7 @@ struct GatFwdOp {
   int first, last, skip_empty;
 
   struct State {
-    LaneMap<VPL> lm;
+    LaneMap<VPL, LPR> lm;
     float ar[VPL], m[VPL], z[VPL];
     float4 acc[VPL];
   };
@@ -61,16 +62,45 @@ struct GatFwdOp {
     }
   }
   __device__ __forceinline__ void resume(State& st, i64 r, int lane) const {
-    if (!first) merge_partial(st, state + r * slot_stride, lane);
+    if (!first && st.lm.sg == 0) merge_partial(st, state + r * slot_stride, lane);
+  }
+  // fold the (max, sum, accumulator) of the sub-groups; afterwards every sub-group holds the row's state
+  __device__ __forceinline__ void combine(State& st, int) const {
+#pragma unroll
+    for (int off = LPR; off < 32; off <<= 1) {
+      const float mo = __shfl_xor_sync(DGNN_FULL, st.m[0], off);
+      const float zo = __shfl_xor_sync(DGNN_FULL, st.z[0], off);
+      float4 ao;
+      ao.x = __shfl_xor_sync(DGNN_FULL, st.acc[0].x, off);
+      ao.y = __shfl_xor_sync(DGNN_FULL, st.acc[0].y, off);
+      ao.z = __shfl_xor_sync(DGNN_FULL, st.acc[0].z, off);
+      ao.w = __shfl_xor_sync(DGNN_FULL, st.acc[0].w, off);
+      const float mn = fmaxf(st.m[0], mo);
+      const float s1 = fast_exp(st.m[0] - mn), s2 = fast_exp(mo - mn);
+      // both partners must compute the same sum: add in a fixed (lower sub-group first) order
+      const bool low = (st.lm.sg & (off / LPR)) == 0;
+      const float za = low ? st.z[0] * s1 : zo * s2, zb = low ? zo * s2 : st.z[0] * s1;
+      st.z[0] = za + zb;
+      float4 a = st.acc[0], b = ao;
+      scale4(a, s1);
+      scale4(b, s2);
+      if (!low) { const float4 t = a; a = b; b = t; }
+      add4(a, b);
+      st.acc[0] = a;
+      st.m[0] = mn;
+    }
   }
 
-  // one batch of U edges starting at tile slot k; ALL = every slot of the batch holds an edge
+  // one batch of U edges per sub-group starting at tile slot k; ALL = every slot of the batch holds an edge
   template <bool ALL>
   __device__ __forceinline__ void batch(State& st, int my_c, i64 ebase, int k, int cnt) const {
     constexpr int U = Unroll<VPL>::U;
-    int c[U];
+    int c[U], slot[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) c[u] = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
+    for (int u = 0; u < U; ++u) {
+      slot[u] = k + u * EPW + st.lm.sg;      // tile slot of this sub-group's u-th edge
+      c[u] = __shfl_sync(DGNN_FULL, my_c, slot[u] & 31);
+    }
     float s[U][VPL];
     float4 x[U][VPL];
     bool keep[U][VPL];
@@ -78,11 +108,11 @@ struct GatFwdOp {
     for (int u = 0; u < U; ++u) {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
-        const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act[v]);
+        const bool ok = (ALL || slot[u] < cnt) && (FULL || st.lm.act[v]);
         s[u][v] = ok ? __ldg(attn_col + (i64)c[u] * H + st.lm.hd[v]) : 0.f;
         x[u][v] = ok ? ld4(in_feat + (i64)c[u] * hf4 + st.lm.q[v]) : zero4();
         keep[u][v] = ok;
-        if (MASK) keep[u][v] = ok ? (__ldg(mask + (ebase + k + u) * H + st.lm.hd[v]) > drop_p) : false;
+        if (MASK) keep[u][v] = ok ? (__ldg(mask + (ebase + slot[u]) * H + st.lm.hd[v]) > drop_p) : false;
       }
     }
 #pragma unroll
@@ -92,7 +122,7 @@ struct GatFwdOp {
       float bm = st.m[v];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        l[u] = (ALL || k + u < cnt) ? leaky(st.ar[v] + s[u][v], slope) : DGNN_NEG_INIT;
+        l[u] = (ALL || slot[u] < cnt) ? leaky(st.ar[v] + s[u][v], slope) : DGNN_NEG_INIT;
         bm = fmaxf(bm, l[u]);
       }
       const float sc = fast_exp(st.m[v] - bm);  // 1 when the maximum did not move
@@ -101,7 +131,7 @@ struct GatFwdOp {
       st.m[v] = bm;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        if (ALL || k + u < cnt) {
+        if (ALL || slot[u] < cnt) {
           const float p = fast_exp(l[u] - bm);
           st.z[v] += p;
           if (!MASK || keep[u][v]) fma4(st.acc[v], p, x[u][v]);
@@ -111,12 +141,12 @@ struct GatFwdOp {
   }
 
   __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
-    constexpr int U = Unroll<VPL>::U;
+    constexpr int STEP = Unroll<VPL>::U * EPW;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
       int k = 0;
-      for (; k + U <= cnt; k += U) batch<true>(st, my_c, base, k, cnt);
+      for (; k + STEP <= cnt; k += STEP) batch<true>(st, my_c, base, k, cnt);
       if (k < cnt) batch<false>(st, my_c, base, k, cnt);
     }
   }
@@ -126,11 +156,12 @@ struct GatFwdOp {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
+      if (!st.lm.wr[v]) continue;
       const float sc = st.z[v] > 0.f ? inv_keep / st.z[v] : 0.f;
       float4 a = st.acc[v];
       scale4(a, sc);
       out[r * hf4 + st.lm.q[v]] = a;
-      if (st.lm.lead[v] && edge_max) {
+      if (st.lm.wlead[v] && edge_max) {
         edge_max[r * H + st.lm.hd[v]] = st.m[v];
         edge_sum[r * H + st.lm.hd[v]] = st.z[v];
       }
@@ -140,9 +171,9 @@ struct GatFwdOp {
   __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      if (!st.lm.act[v]) continue;
+      if (!st.lm.wr[v]) continue;
       reinterpret_cast<float4*>(p)[st.lm.q[v]] = st.acc[v];
-      if (st.lm.lead[v]) {
+      if (st.lm.wlead[v]) {
         p[hf4 * 4 + st.lm.hd[v]] = st.m[v];
         p[hf4 * 4 + H + st.lm.hd[v]] = st.z[v];
       }
@@ -238,8 +269,9 @@ k_gat_rowstat_generic(i64 n_rows, int H, int F, const float* attn_row, const flo
 }
 
 // ------------------------------------------------------------ backward cols
-template <int VPL, bool MASK, bool FULL>
+template <int VPL, bool MASK, bool FULL, int LPR>
 struct GatBwdOp {
+  static constexpr int EPW = 32 / LPR;
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 4 : (VPL == 4 ? 3 : 2);
   static constexpr bool HAS_PARTIALS = true;
   i64 n_rows, nnz;      // "rows" of the CSC form = source columns
@@ -263,7 +295,7 @@ struct GatBwdOp {
   int first, last, skip_empty;
 
   struct State {
-    LaneMap<VPL> lm;
+    LaneMap<VPL, LPR> lm;
     float4 x[VPL], acc[VPL];
     float ac[VPL], gc[VPL];
   };
@@ -279,17 +311,35 @@ struct GatBwdOp {
     }
   }
   __device__ __forceinline__ void resume(State& st, i64 c, int lane) const {
-    if (!first) merge_partial(st, state + c * slot_stride, lane);
+    if (!first && st.lm.sg == 0) merge_partial(st, state + c * slot_stride, lane);
+  }
+  // sum the sub-groups' accumulators (lower sub-group first, so all partners agree bit for bit)
+  __device__ __forceinline__ void combine(State& st, int) const {
+#pragma unroll
+    for (int off = LPR; off < 32; off <<= 1) {
+      float4 ao;
+      ao.x = __shfl_xor_sync(DGNN_FULL, st.acc[0].x, off);
+      ao.y = __shfl_xor_sync(DGNN_FULL, st.acc[0].y, off);
+      ao.z = __shfl_xor_sync(DGNN_FULL, st.acc[0].z, off);
+      ao.w = __shfl_xor_sync(DGNN_FULL, st.acc[0].w, off);
+      const float go = __shfl_xor_sync(DGNN_FULL, st.gc[0], off);
+      const bool low = (st.lm.sg & (off / LPR)) == 0;
+      float4 a = low ? st.acc[0] : ao, b = low ? ao : st.acc[0];
+      add4(a, b);
+      st.acc[0] = a;
+      st.gc[0] = low ? st.gc[0] + go : go + st.gc[0];
+    }
   }
 
   template <bool ALL>
   __device__ __forceinline__ void batch(State& st, int my_r, int my_p, int k, int cnt) const {
     constexpr int U = Unroll<VPL>::U;
-    int r[U], pp[U];
+    int r[U], pp[U], slot[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      r[u] = __shfl_sync(DGNN_FULL, my_r, (k + u) & 31);
-      pp[u] = __shfl_sync(DGNN_FULL, my_p, (k + u) & 31);
+      slot[u] = k + u * EPW + st.lm.sg;      // tile slot of this sub-group's u-th edge
+      r[u] = __shfl_sync(DGNN_FULL, my_r, slot[u] & 31);
+      pp[u] = __shfl_sync(DGNN_FULL, my_p, slot[u] & 31);
     }
     float4 pk[U][VPL], g4[U][VPL];
     bool keep[U][VPL];
@@ -297,7 +347,7 @@ struct GatBwdOp {
     for (int u = 0; u < U; ++u) {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
-        const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act[v]);
+        const bool ok = (ALL || slot[u] < cnt) && (FULL || st.lm.act[v]);
         pk[u][v] = ok ? ld4(pack + (i64)r[u] * H + st.lm.hd[v]) : zero4();
         g4[u][v] = ok ? ld4(grad_out + (i64)r[u] * hf4 + st.lm.q[v]) : zero4();
         keep[u][v] = ok;
@@ -312,7 +362,7 @@ struct GatBwdOp {
     head_reduce<U, VPL>(d, f4_shift);  // executed by all lanes, also for slots past cnt
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (ALL || k + u < cnt) {
+      if (ALL || slot[u] < cnt) {
 #pragma unroll
         for (int v = 0; v < VPL; ++v) {
           if (!FULL && !st.lm.act[v]) continue;
@@ -330,13 +380,13 @@ struct GatBwdOp {
   }
 
   __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
-    constexpr int U = Unroll<VPL>::U;
+    constexpr int STEP = Unroll<VPL>::U * EPW;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
       const int my_p = lane < cnt ? __ldg(permute + base + lane) : 0;
       int k = 0;
-      for (; k + U <= cnt; k += U) batch<true>(st, my_r, my_p, k, cnt);
+      for (; k + STEP <= cnt; k += STEP) batch<true>(st, my_r, my_p, k, cnt);
       if (k < cnt) batch<false>(st, my_r, my_p, k, cnt);
     }
   }
@@ -345,18 +395,18 @@ struct GatBwdOp {
     if (!last) { store_partial(st, state + c * slot_stride, lane); return; }
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      if (!st.lm.act[v]) continue;
+      if (!st.lm.wr[v]) continue;
       grad_feat[c * hf4 + st.lm.q[v]] = st.acc[v];
-      if (st.lm.lead[v]) grad_attn_col[c * H + st.lm.hd[v]] = st.gc[v];
+      if (st.lm.wlead[v]) grad_attn_col[c * H + st.lm.hd[v]] = st.gc[v];
     }
   }
 
   __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      if (!st.lm.act[v]) continue;
+      if (!st.lm.wr[v]) continue;
       reinterpret_cast<float4*>(p)[st.lm.q[v]] = st.acc[v];
-      if (st.lm.lead[v]) p[hf4 * 4 + st.lm.hd[v]] = st.gc[v];
+      if (st.lm.wlead[v]) p[hf4 * 4 + st.lm.hd[v]] = st.gc[v];
     }
   }
 
@@ -473,10 +523,10 @@ inline i64 up4(i64 x) { return (x + 3) & ~i64(3); }
 
 struct FastShape {
   bool ok;
-  int hf4, f4_shift, vpl;
+  int hf4, f4_shift, vpl, lpr;
 };
 inline FastShape fast_shape(int h, int f) {
-  FastShape s{false, 0, 0, 0};
+  FastShape s{false, 0, 0, 0, 32};
   if (f % 4) return s;
   const int sh = ilog2_exact(f / 4);
   if (sh < 0) return s;
@@ -486,18 +536,19 @@ inline FastShape fast_shape(int h, int f) {
   s.hf4 = (int)hf4;
   s.f4_shift = sh;
   s.vpl = hf4 <= 32 ? 1 : hf4 <= 64 ? 2 : hf4 <= 128 ? 4 : 8;
+  s.lpr = hf4 <= 8 ? 8 : hf4 <= 16 ? 16 : 32;
   return s;
 }
 
 inline i64 fwd_slot_stride(int h, int f) { return (i64)h * f + up4(2 * (i64)h); }
 inline i64 bwd_slot_stride(int h, int f) { return (i64)h * f + up4((i64)h); }
 
-template <int VPL, bool MASK, bool FULL>
+template <int VPL, bool MASK, bool FULL, int LPR>
 int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
                const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
                float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
                void* ws, float* state, int first, int last, cudaStream_t s) {
-  GatFwdOp<VPL, MASK, FULL> op;
+  GatFwdOp<VPL, MASK, FULL, LPR> op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
   op.col_ind = col_ind; op.attn_row = attn_row; op.attn_col = attn_col;
@@ -509,13 +560,13 @@ int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const voi
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
-template <int VPL, bool MASK, bool FULL>
+template <int VPL, bool MASK, bool FULL, int LPR>
 int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const void* col_ptr, int idx_bits,
                const int* row_ind, const int* permute, const float* pack, const float* mask,
                const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
                float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, unsigned long long* counter,
                float* state, int first, int last, cudaStream_t s) {
-  GatBwdOp<VPL, MASK, FULL> op;
+  GatBwdOp<VPL, MASK, FULL, LPR> op;
   op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
   op.row_ind = row_ind; op.permute = permute; op.pack = reinterpret_cast<const float4*>(pack);
@@ -528,16 +579,20 @@ int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const voi
   return dgnn_launch_trio(op, counter, s);
 }
 
-// FULL = the row is exactly 32*VPL float4 vectors wide: no lane is ever idle
-#define DGNN_DISPATCH_VM(V, MASKED, FULLW, CALL)                                       \
-  return MASKED ? (FULLW ? CALL(V, true, true) : CALL(V, true, false))                 \
-                : (FULLW ? CALL(V, false, true) : CALL(V, false, false));
-#define DGNN_DISPATCH_VPL(vpl, MASKED, FULLW, CALL)         \
-  switch (vpl) {                                            \
-    case 1: DGNN_DISPATCH_VM(1, MASKED, FULLW, CALL)        \
-    case 2: DGNN_DISPATCH_VM(2, MASKED, FULLW, CALL)        \
-    case 4: DGNN_DISPATCH_VM(4, MASKED, FULLW, CALL)        \
-    default: DGNN_DISPATCH_VM(8, MASKED, FULLW, CALL)       \
+// FULL = the row is exactly LPR*VPL float4 vectors wide: no lane is ever idle.
+// LPR (lanes per row) is 32 except for rows of at most 16 / 8 vectors.
+#define DGNN_DISPATCH_VM(V, L, MASKED, FULLW, CALL)                                          \
+  return MASKED ? (FULLW ? CALL(V, true, true, L) : CALL(V, true, false, L))                 \
+                : (FULLW ? CALL(V, false, true, L) : CALL(V, false, false, L));
+#define DGNN_DISPATCH_VPL(vpl, lpr, MASKED, FULLW, CALL)             \
+  switch (vpl) {                                                     \
+    case 1:                                                          \
+      if (lpr == 8) { DGNN_DISPATCH_VM(1, 8, MASKED, FULLW, CALL) }  \
+      if (lpr == 16) { DGNN_DISPATCH_VM(1, 16, MASKED, FULLW, CALL) }\
+      DGNN_DISPATCH_VM(1, 32, MASKED, FULLW, CALL)                   \
+    case 2: DGNN_DISPATCH_VM(2, 32, MASKED, FULLW, CALL)             \
+    case 4: DGNN_DISPATCH_VM(4, 32, MASKED, FULLW, CALL)             \
+    default: DGNN_DISPATCH_VM(8, 32, MASKED, FULLW, CALL)            \
   }
 
 struct BwdLayout {
@@ -614,10 +669,10 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
     if (!workspace || workspace_bytes < dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f))
       return DGNN_ERR_WORKSPACE;
     if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
-#define CALL_FWD(V, M, FW)                                                                           \
-  launch_fwd<V, M, FW>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
+#define CALL_FWD(V, M, FW, L)                                                                        \
+  launch_fwd<V, M, FW, L>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
                    negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, state, first, last, s)
-    DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, fs.hf4 == 32 * fs.vpl, CALL_FWD)
+    DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_FWD)
 #undef CALL_FWD
   }
   if (staged) return DGNN_ERR_SHAPE;   // the staged sweep exists only for the float4 layout
@@ -707,11 +762,11 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
   if (n_cols > 0) {
     if (fs.ok && aligned16(in_feat) && aligned16(grad_out) && aligned16(grad_feat)) {
       int rc;
-#define CALL_BWD(V, M, FW)                                                                              \
-  launch_bwd<V, M, FW>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
+#define CALL_BWD(V, M, FW, L)                                                                           \
+  launch_bwd<V, M, FW, L>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
                    attn_col, grad_out, negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, \
                    col_part, counter, state, first, last, s)
-      auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, mask != nullptr, fs.hf4 == 32 * fs.vpl, CALL_BWD) };
+      auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_BWD) };
 #undef CALL_BWD
       rc = run();
       if (rc) return rc;

@@ -12,10 +12,10 @@ inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 
 struct FastShape {
   bool ok;
-  int hf4, f4_shift, vpl;
+  int hf4, f4_shift, vpl, lpr;
 };
 inline FastShape fast_shape(int h, int f) {
-  FastShape s{false, 0, 0, 0};
+  FastShape s{false, 0, 0, 0, 32};
   if (f % 4) return s;
   const int sh = ilog2_exact(f / 4);
   if (sh < 0) return s;
@@ -25,12 +25,14 @@ inline FastShape fast_shape(int h, int f) {
   s.hf4 = (int)hf4;
   s.f4_shift = sh;
   s.vpl = hf4 <= 32 ? 1 : hf4 <= 64 ? 2 : hf4 <= 128 ? 4 : 8;
+  s.lpr = hf4 <= 8 ? 8 : hf4 <= 16 ? 16 : 32;
   return s;
 }
 
 // ------------------------------------------------------------------- SDDMM
-template <int VPL>
+template <int VPL, int LPR>
 struct SddmmOp {
+  static constexpr int EPW = 32 / LPR;
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
   static constexpr bool HAS_PARTIALS = false;   // outputs are per edge: nothing to fold
   i64 n_rows, nnz;
@@ -46,7 +48,7 @@ struct SddmmOp {
   float* out;
 
   struct State {
-    LaneMap<VPL> lm;
+    LaneMap<VPL, LPR> lm;
     float4 a[VPL];
   };
   __device__ __forceinline__ void init(State& st, i64 r, int lane) const {
@@ -59,14 +61,16 @@ struct SddmmOp {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
-      for (int k = 0; k < cnt; k += U) {
+      for (int k = 0; k < cnt; k += U * EPW) {
         float4 x[U][VPL];
+        int slot[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const int c = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
+          slot[u] = k + u * EPW + st.lm.sg;
+          const int c = __shfl_sync(DGNN_FULL, my_c, slot[u] & 31);
 #pragma unroll
           for (int v = 0; v < VPL; ++v)
-            x[u][v] = (k + u < cnt && st.lm.act[v]) ? ld4(b + (i64)c * hf4 + st.lm.q[v]) : zero4();
+            x[u][v] = (slot[u] < cnt && st.lm.act[v]) ? ld4(b + (i64)c * hf4 + st.lm.q[v]) : zero4();
         }
         float d[U][VPL];
 #pragma unroll
@@ -76,16 +80,17 @@ struct SddmmOp {
         head_reduce<U, VPL>(d, f4_shift);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          if (k + u < cnt) {
+          if (slot[u] < cnt) {
 #pragma unroll
             for (int v = 0; v < VPL; ++v)
-              if (st.lm.lead[v]) out[(base + k + u) * H + st.lm.hd[v]] = d[u][v];
+              if (st.lm.lead[v]) out[(base + slot[u]) * H + st.lm.hd[v]] = d[u][v];
           }
         }
       }
     }
   }
   __device__ __forceinline__ void resume(State&, i64, int) const {}
+  __device__ __forceinline__ void combine(State&, int) const {}
   __device__ __forceinline__ void finalize(State&, i64, int) const {}
   __device__ __forceinline__ void store_partial(State&, float*, int) const {}
   __device__ __forceinline__ void merge_partial(State&, const float*, int) const {}
@@ -137,8 +142,9 @@ __device__ __forceinline__ float gauss_w(const float* pseudo, const float* mu, c
   return expf(-0.5f * acc);
 }
 
-template <int VPL>
+template <int VPL, int LPR>
 struct GmmOp {
+  static constexpr int EPW = 32 / LPR;
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
   static constexpr bool HAS_PARTIALS = true;
   i64 n_rows, nnz;
@@ -156,7 +162,7 @@ struct GmmOp {
   int skip_empty;
 
   struct State {
-    LaneMap<VPL> lm;
+    LaneMap<VPL, LPR> lm;
     float4 acc[VPL];
   };
   __device__ __forceinline__ void init(State& st, i64, int lane) const {
@@ -169,37 +175,53 @@ struct GmmOp {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
-      for (int k = 0; k < cnt; k += U) {
+      for (int k = 0; k < cnt; k += U * EPW) {
         float4 x[U][VPL];
+        int slot[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const int c = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
+          slot[u] = k + u * EPW + st.lm.sg;
+          const int c = __shfl_sync(DGNN_FULL, my_c, slot[u] & 31);
 #pragma unroll
           for (int v = 0; v < VPL; ++v)
-            x[u][v] = (k + u < cnt && st.lm.act[v]) ? ld4(feat + (i64)c * hf4 + st.lm.q[v]) : zero4();
+            x[u][v] = (slot[u] < cnt && st.lm.act[v]) ? ld4(feat + (i64)c * hf4 + st.lm.q[v]) : zero4();
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          if (k + u < cnt) {
+          if (slot[u] < cnt) {
 #pragma unroll
             for (int v = 0; v < VPL; ++v)
-              if (st.lm.act[v]) fma4(st.acc[v], gauss_w(pseudo, mu, sig, base + k + u, st.lm.hd[v], dim), x[u][v]);
+              if (st.lm.act[v]) fma4(st.acc[v], gauss_w(pseudo, mu, sig, base + slot[u], st.lm.hd[v], dim), x[u][v]);
           }
         }
       }
     }
   }
   __device__ __forceinline__ void resume(State&, i64, int) const {}
+  __device__ __forceinline__ void combine(State& st, int) const {
+#pragma unroll
+    for (int off = LPR; off < 32; off <<= 1) {
+      float4 ao;
+      ao.x = __shfl_xor_sync(DGNN_FULL, st.acc[0].x, off);
+      ao.y = __shfl_xor_sync(DGNN_FULL, st.acc[0].y, off);
+      ao.z = __shfl_xor_sync(DGNN_FULL, st.acc[0].z, off);
+      ao.w = __shfl_xor_sync(DGNN_FULL, st.acc[0].w, off);
+      const bool low = (st.lm.sg & (off / LPR)) == 0;
+      float4 a = low ? st.acc[0] : ao, b = low ? ao : st.acc[0];
+      add4(a, b);
+      st.acc[0] = a;
+    }
+  }
   __device__ __forceinline__ void finalize(State& st, i64 r, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
-      if (st.lm.act[v]) out[r * hf4 + st.lm.q[v]] = st.acc[v];
+      if (st.lm.wr[v]) out[r * hf4 + st.lm.q[v]] = st.acc[v];
   }
   __device__ __forceinline__ void store_partial(State& st, float* pf, int) const {
     float4* p = reinterpret_cast<float4*>(pf);
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
-      if (st.lm.act[v]) p[st.lm.q[v]] = st.acc[v];
+      if (st.lm.wr[v]) p[st.lm.q[v]] = st.acc[v];
   }
   __device__ __forceinline__ void merge_partial(State& st, const float* pf, int) const {
     const float4* p = reinterpret_cast<const float4*>(pf);
@@ -295,10 +317,10 @@ __global__ void k_gaussian_bp_final(i64 blocks, int kd, const float* part, float
 
 inline i64 gbp_blocks(i64 nnz) { return (nnz + GBP_EDGES_PER_BLOCK - 1) / GBP_EDGES_PER_BLOCK; }
 
-template <int VPL>
+template <int VPL, int LPR>
 int launch_sddmm(const FastShape& fs, i64 n_rows, i64 nnz, int h, const void* row_ptr, int idx_bits,
                  const int* col_ind, const float* a, const float* b, float* out, void* ws, cudaStream_t s) {
-  SddmmOp<VPL> op;
+  SddmmOp<VPL, LPR> op;
   op.ws = nullptr; op.slot_stride = 0; op.skip_empty = 1;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift; op.col_ind = col_ind;
@@ -306,11 +328,11 @@ int launch_sddmm(const FastShape& fs, i64 n_rows, i64 nnz, int h, const void* ro
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
-template <int VPL>
+template <int VPL, int LPR>
 int launch_gmm(const FastShape& fs, i64 n_rows, i64 nnz, int K, int dim, int f, const void* row_ptr,
                int idx_bits, const int* col_ind, const float* feat, const float* pseudo, const float* mu,
                const float* sig, float* out, void* ws, cudaStream_t s) {
-  GmmOp<VPL> op;
+  GmmOp<VPL, LPR> op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = K; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift; op.dim = dim; op.col_ind = col_ind;
   op.feat = reinterpret_cast<const float4*>(feat); op.pseudo = pseudo; op.mu = mu; op.sig = sig;
@@ -338,12 +360,17 @@ int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr,
   const FastShape fs = fast_shape(h, f);
   if (fs.ok && aligned16(a) && aligned16(b)) {
     if (!workspace || workspace_bytes < DGNN_WS_HEADER) return DGNN_ERR_WORKSPACE;
+#define SD_ARGS fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s
     switch (fs.vpl) {
-      case 1: return launch_sddmm<1>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
-      case 2: return launch_sddmm<2>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
-      case 4: return launch_sddmm<4>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
-      default: return launch_sddmm<8>(fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s);
+      case 1:
+        if (fs.lpr == 8) return launch_sddmm<1, 8>(SD_ARGS);
+        if (fs.lpr == 16) return launch_sddmm<1, 16>(SD_ARGS);
+        return launch_sddmm<1, 32>(SD_ARGS);
+      case 2: return launch_sddmm<2, 32>(SD_ARGS);
+      case 4: return launch_sddmm<4, 32>(SD_ARGS);
+      default: return launch_sddmm<8, 32>(SD_ARGS);
     }
+#undef SD_ARGS
   }
   k_sddmm_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(n_rows, h, f, row_ptr, idx_bits,
                                                                            col_ind, a, b, out);
@@ -388,12 +415,17 @@ int dgnn_gmm_forward(int64_t n_rows, int64_t nnz, int kernels, int dim, int f, c
     if (!workspace || workspace_bytes < dgnn_gmm_forward_workspace_bytes(n_rows, nnz, kernels, f))
       return DGNN_ERR_WORKSPACE;
     if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
+#define GM_ARGS fs, n_rows, nnz, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out, workspace, s
     switch (fs.vpl) {
-      case 1: return launch_gmm<1>(fs, n_rows, nnz, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out, workspace, s);
-      case 2: return launch_gmm<2>(fs, n_rows, nnz, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out, workspace, s);
-      case 4: return launch_gmm<4>(fs, n_rows, nnz, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out, workspace, s);
-      default: return launch_gmm<8>(fs, n_rows, nnz, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out, workspace, s);
+      case 1:
+        if (fs.lpr == 8) return launch_gmm<1, 8>(GM_ARGS);
+        if (fs.lpr == 16) return launch_gmm<1, 16>(GM_ARGS);
+        return launch_gmm<1, 32>(GM_ARGS);
+      case 2: return launch_gmm<2, 32>(GM_ARGS);
+      case 4: return launch_gmm<4, 32>(GM_ARGS);
+      default: return launch_gmm<8, 32>(GM_ARGS);
     }
+#undef GM_ARGS
   }
   k_gmm_generic<<<dgnn_grid(n_rows * kernels, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
       n_rows, kernels, dim, f, row_ptr, idx_bits, col_ind, node_feat, pseudo, mu, inv_sigma, out);
