@@ -143,3 +143,21 @@ def _stream(dev) -> ctypes.c_void_p:
 
 def _workspace(nbytes: int, dev) -> torch.Tensor:
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(dev):
+    """Make `dev` current for allocations and launches; free when it already is (the usual case)."""
+    if torch.cuda.current_device() == (dev.index if dev.index is not None else torch.cuda.current_device()):
+        return _NO_GUARD
+    return torch.cuda.device(dev)

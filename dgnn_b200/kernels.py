@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from . import _C
-from ._C import _cuda_f32, _cuda_i32, _cuda_ptr, _p, _same_bits, _stream, _workspace, check, lib
+from ._C import _cuda_f32, _cuda_i32, _cuda_ptr, _p, _same_bits, _stream, _workspace, check, device_guard, lib
 
 
 def _dims3(t, name):
@@ -43,7 +43,7 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
     else:
         edge_mask = None
     dev = in_feat.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
         edge_max = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if save_stats else None
         edge_sum = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if save_stats else None
@@ -62,7 +62,7 @@ def gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out):
     grad_out = _cuda_f32(grad_out, "grad_out")
     n, h, f = _dims3(out, "out")
     dev = out.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         pack = torch.empty((n, h, 4), dtype=torch.float32, device=dev)
         check(lib().dgnn_gat_rowstat(n, h, f, _p(_cuda_f32(attn_row, "attn_row")), _p(_cuda_f32(edge_max, "edge_max")),
                                      _p(_cuda_f32(edge_sum, "edge_sum")), _p(out), _p(grad_out), _p(pack),
@@ -96,7 +96,7 @@ def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_fe
     else:
         edge_mask = None
     dev = in_feat.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         grad_feat = torch.empty((n_cols, h, f), dtype=torch.float32, device=dev)
         grad_attn_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
         grad_attn_col = torch.empty((n_cols, h), dtype=torch.float32, device=dev)
@@ -136,7 +136,7 @@ def gat_backward(negative_slope, attn_drop, row_ptr, col_ptr, row_ind, permute, 
     else:
         edge_mask = None
     dev = in_feat.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         grad_feat = torch.empty((n, h, f), dtype=torch.float32, device=dev)
         grad_attn_row = torch.empty((n, h), dtype=torch.float32, device=dev)
         grad_attn_col = torch.empty((n, h), dtype=torch.float32, device=dev)
@@ -162,7 +162,7 @@ def gat_logits_forward(feat, attn_l, attn_r):
     attn_l = _cuda_f32(attn_l, "attn_l").reshape(h, f)
     attn_r = _cuda_f32(attn_r, "attn_r").reshape(h, f)
     dev = feat.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         attn_row = torch.empty((n, h), dtype=torch.float32, device=dev)
         attn_col = torch.empty((n, h), dtype=torch.float32, device=dev)
         check(lib().dgnn_gat_logits_forward(n, h, f, _p(feat), _p(attn_l), _p(attn_r), _p(attn_row), _p(attn_col),
@@ -182,7 +182,7 @@ def gat_logits_backward(feat, attn_l, attn_r, grad_row, grad_col, grad_feat):
             and grad_feat.shape == feat.shape):
         raise RuntimeError("dgnn_b200: grad_feat must be a contiguous float32 CUDA tensor shaped like feat")
     dev = feat.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         grad_l = torch.empty((h, f), dtype=torch.float32, device=dev)
         grad_r = torch.empty((h, f), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_gat_logits_backward_workspace_bytes(h, f), dev)
@@ -195,7 +195,7 @@ def gat_logits_backward(feat, attn_l, attn_r, grad_row, grad_col, grad_feat):
 def uniform_fill(shape, seed, offset, device):
     """Uniform (0,1] floats from the library's Philox stream."""
     dev = torch.device(device)
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = torch.empty(shape, dtype=torch.float32, device=dev)
         check(lib().dgnn_uniform_fill(int(seed) & (2**64 - 1), int(offset), out.numel(), _p(out), _stream(dev)),
               "uniform_fill")
@@ -215,7 +215,7 @@ def mhsddmm(row_ptr, col_ind, a, b):
         raise RuntimeError("dgnn_b200: mhsddmm operands must be [V,H,F] with V = len(rowptr) - 1 rows in `grad`")
     nnz = col_ind.numel()
     dev = b.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = torch.empty((nnz, h), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_mhsddmm_workspace_bytes(), dev)
         check(lib().dgnn_mhsddmm(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(a), _p(b), _p(out),
@@ -231,7 +231,7 @@ def mhtranspose(permute, attention):
         raise RuntimeError("dgnn_b200: mhtranspose input must be [E,H]")
     nnz, h = permute.numel(), attention.shape[1]
     dev = attention.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = torch.empty((nnz, h), dtype=torch.float32, device=dev)
         check(lib().dgnn_mhtranspose(nnz, h, _p(permute), _p(attention), _p(out), _stream(dev)), "mhtranspose")
     return out
@@ -251,7 +251,7 @@ def gmm_forward(row_ptr, col_ind, node_feat, pseudo, mu, inv_sigma):
     if mu.shape != (k, dim) or inv_sigma.shape != (k, dim) or pseudo.shape != (nnz, dim):
         raise RuntimeError("dgnn_b200: gmmconv needs mu, sigma [K,dim] and pseudo [E,dim]")
     dev = node_feat.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = torch.empty((n_rows, k, f), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_gmm_forward_workspace_bytes(n_rows, nnz, k, f), dev)
         check(lib().dgnn_gmm_forward(n_rows, nnz, k, dim, f, _p(row_ptr), bits, _p(col_ind), _p(node_feat),
@@ -267,7 +267,7 @@ def gaussian(pseudo, mu, inv_sigma):
     nnz, dim = pseudo.shape
     k = mu.shape[0]
     dev = pseudo.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = torch.empty((nnz, k), dtype=torch.float32, device=dev)
         check(lib().dgnn_gaussian(nnz, k, dim, _p(pseudo), _p(mu), _p(inv_sigma), _p(out), _stream(dev)), "gaussian")
     return out
@@ -283,7 +283,7 @@ def gaussian_bp(pseudo, mu, inv_sigma, grad_gauss):
     if grad_gauss.shape != (nnz, k):
         raise RuntimeError("dgnn_b200: GaussianBp needs grad [E,K]")
     dev = pseudo.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         pseudo_out = torch.empty((nnz, dim), dtype=torch.float32, device=dev)
         mu_out = torch.empty((k, dim), dtype=torch.float32, device=dev)
         sigma_out = torch.empty((k, dim), dtype=torch.float32, device=dev)
@@ -303,7 +303,7 @@ def edgeconv_forward(k, src_ind, h_src, h_dst):
     if h_dst.shape != (m, f) or src_ind.numel() != m * int(k):
         raise RuntimeError("dgnn_b200: edgeconv needs h_src, h_dst [M,F] and src_ind [M*k]")
     dev = h_src.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = torch.empty((m, f), dtype=torch.float32, device=dev)
         max_idx = torch.empty((m, f), dtype=torch.int32, device=dev)
         check(lib().dgnn_edgeconv_forward(m, f, int(k), _p(src_ind), _p(h_src), _p(h_dst), _p(out), _p(max_idx),
@@ -316,7 +316,7 @@ def edgeconv_backward(grad_out, max_idx):
     max_idx = _cuda_i32(max_idx, "max_idx")
     m, f = grad_out.shape
     dev = grad_out.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         grad_src = torch.empty((m, f), dtype=torch.float32, device=dev)
         check(lib().dgnn_edgeconv_backward(m, f, _p(max_idx), _p(grad_out), _p(grad_src), _stream(dev)),
               "edgeconv_backward")
@@ -331,7 +331,7 @@ def csr2csc(row_ptr, col_ind, n_cols=None):
     n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
     n_cols = n_rows if n_cols is None else int(n_cols)
     dev = col_ind.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         col_ptr = torch.empty(n_cols + 1, dtype=row_ptr.dtype, device=dev)
         row_ind = torch.empty(nnz, dtype=torch.int32, device=dev)
         permute = torch.empty(nnz, dtype=torch.int32, device=dev)
@@ -345,7 +345,7 @@ def coo2csr(row_ind, m, dtype=torch.int32):
     row_ind = _cuda_i32(row_ind, "cooRowInd")
     dev = row_ind.device
     bits = 32 if dtype == torch.int32 else 64
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         row_ptr = torch.empty(int(m) + 1, dtype=dtype, device=dev)
         check(lib().dgnn_coo2csr(row_ind.numel(), int(m), _p(row_ind), _p(row_ptr), bits, _stream(dev)), "coo2csr")
     return row_ptr
@@ -374,7 +374,7 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
     _, h, f = _dims3(feat_blk, "in_feat")
     n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
     dev = feat_blk.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         out = emax = esum = None
         if last:
             out = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
@@ -407,7 +407,7 @@ def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_fe
     if grad_blk.shape != (n_rows, h, f) or pack_blk.shape != (n_rows, h, 4) or col_ptr.numel() - 1 != n_cols:
         raise RuntimeError("dgnn_b200: staged backward: block shapes do not match the sub-matrix")
     dev = in_feat.device
-    with torch.cuda.device(dev):
+    with device_guard(dev):
         grad_feat = grad_col = None
         if last:
             grad_feat = torch.empty((n_cols, h, f), dtype=torch.float32, device=dev)
