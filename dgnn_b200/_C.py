@@ -35,7 +35,9 @@ SIGNATURES = {
                                  c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_forward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
     "dgnn_gat_forward_staged": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
-                                        c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
+                                        c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
+    "dgnn_gat_rowstat_bias_workspace_bytes": (c_sz, [c_int, c_int]),
+    "dgnn_gat_rowstat_bias": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_backward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
     "dgnn_gat_backward_cols_staged": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p,
                                               c_p, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
@@ -51,6 +53,7 @@ SIGNATURES = {
     "dgnn_uniform_fill": (c_int, [c_u64, c_u64, c_i64, c_p, c_p]),
     "dgnn_mhsddmm_workspace_bytes": (c_sz, []),
     "dgnn_mhsddmm": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
+    "dgnn_coo_sddmm": (c_int, [c_i64, c_int, c_p, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_mhtranspose": (c_int, [c_i64, c_int, c_p, c_p, c_p, c_p]),
     "dgnn_gmm_forward_workspace_bytes": (c_sz, [c_i64, c_i64, c_int, c_int]),
     "dgnn_gmm_forward": (c_int, [c_i64, c_i64, c_int, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_p,

@@ -44,6 +44,7 @@ struct GatFwdOp {
   // carried in `state` (one slot per row) between calls; first / last mark the ends
   float* state;
   int first, last, skip_empty;
+  const float4* bias;   // optional [H*F] added to the normalised output (layer epilogue)
 
   struct State {
     LaneMap<VPL, LPR> lm;
@@ -160,6 +161,7 @@ struct GatFwdOp {
       const float sc = st.z[v] > 0.f ? inv_keep / st.z[v] : 0.f;
       float4 a = st.acc[v];
       scale4(a, sc);
+      if (bias) add4(a, __ldg(bias + st.lm.q[v]));
       out[r * hf4 + st.lm.q[v]] = a;
       if (st.lm.wlead[v] && edge_max) {
         edge_max[r * H + st.lm.hd[v]] = st.m[v];
@@ -254,6 +256,66 @@ k_gat_rowstat(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, c
       pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), 1.f / __ldg(edge_sum + i), s[v]);
     }
   }
+}
+
+// Same statistics when the forward added a bias to `out`: the row term uses out - bias, and the
+// bias gradient sum_r grad[r,:] is accumulated on the way (a lane owns the same columns in every
+// row; fixed-order fold per CTA into part[cta][hf4], then over CTAs by k_bias_grad_final).
+template <int VPL>
+__global__ void __launch_bounds__(DGNN_THREADS)
+k_gat_rowstat_bias(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, const float* edge_max,
+                   const float* edge_sum, const float4* out, const float4* grad, const float4* bias,
+                   float4* pack, float4* part) {
+  extern __shared__ float4 rs_sm[];   // [DGNN_WARPS][hf4]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  LaneMap<VPL> lm;
+  lm.init(lane, hf4, f4_shift);
+  float4 b4[VPL], gsum[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    b4[v] = lm.act[v] ? ld4(bias + lm.q[v]) : zero4();
+    gsum[v] = zero4();
+  }
+  const i64 stride = (i64)gridDim.x * DGNN_WARPS;
+  for (i64 r = (i64)blockIdx.x * DGNN_WARPS + warp; r < n_rows; r += stride) {
+    float s[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      s[v] = 0.f;
+      if (lm.act[v]) {
+        const float4 g = ld4(grad + r * hf4 + lm.q[v]);
+        float4 o = ld4(out + r * hf4 + lm.q[v]);
+        o.x -= b4[v].x; o.y -= b4[v].y; o.z -= b4[v].z; o.w -= b4[v].w;
+        s[v] = dot4(g, o);
+        add4(gsum[v], g);
+      }
+    }
+    head_reduce<VPL>(s, f4_shift);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (lm.lead[v]) {
+        const i64 i = r * H + lm.hd[v];
+        pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), 1.f / __ldg(edge_sum + i), s[v]);
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPL; ++v)
+    if (lm.act[v]) rs_sm[warp * hf4 + lm.q[v]] = gsum[v];
+  __syncthreads();
+  for (int i = threadIdx.x; i < hf4; i += DGNN_THREADS) {
+    float4 t = zero4();
+    for (int w = 0; w < DGNN_WARPS; ++w) add4(t, rs_sm[w * hf4 + i]);
+    part[(i64)blockIdx.x * hf4 + i] = t;
+  }
+}
+
+__global__ void k_bias_grad_final(int ctas, int hf4, const float4* part, float4* grad_bias) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= hf4) return;
+  float4 t = zero4();
+  for (int c = 0; c < ctas; ++c) add4(t, part[(i64)c * hf4 + i]);
+  grad_bias[i] = t;
 }
 
 __global__ void __launch_bounds__(DGNN_THREADS)
@@ -547,7 +609,7 @@ template <int VPL, bool MASK, bool FULL, int LPR>
 int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
                const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
                float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
-               void* ws, float* state, int first, int last, cudaStream_t s) {
+               void* ws, float* state, int first, int last, const float* bias, cudaStream_t s) {
   GatFwdOp<VPL, MASK, FULL, LPR> op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -557,6 +619,7 @@ int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const voi
   op.out = reinterpret_cast<float4*>(out); op.edge_max = edge_max; op.edge_sum = edge_sum;
   op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER); op.slot_stride = fwd_slot_stride(h, f);
   op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last) ? 1 : 0;
+  op.bias = reinterpret_cast<const float4*>(bias);
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
@@ -644,15 +707,16 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_
                      float* out, float* edge_max, float* edge_sum, void* workspace,
                      size_t workspace_bytes, void* stream) {
   return dgnn_gat_forward_staged(n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,
-                                 negative_slope, attn_drop, edge_mask, out, edge_max, edge_sum, nullptr, 1, 1,
+                                 negative_slope, attn_drop, edge_mask, nullptr, out, edge_max, edge_sum, nullptr, 1, 1,
                                  workspace, workspace_bytes, stream);
 }
 
 int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
                             const int32_t* col_ind, const float* attn_row, const float* attn_col,
                             const float* in_feat, float negative_slope, float attn_drop,
-                            const float* edge_mask, float* out, float* edge_max, float* edge_sum, float* state,
-                            int first, int last, void* workspace, size_t workspace_bytes, void* stream) {
+                            const float* edge_mask, const float* bias, float* out, float* edge_max,
+                            float* edge_sum, float* state, int first, int last, void* workspace,
+                            size_t workspace_bytes, void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
   const bool staged = !(first && last);
@@ -665,17 +729,17 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
   const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const FastShape fs = fast_shape(h, f);
-  if (fs.ok && aligned16(in_feat) && aligned16(out)) {
+  if (fs.ok && aligned16(in_feat) && aligned16(out) && aligned16(bias)) {
     if (!workspace || workspace_bytes < dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f))
       return DGNN_ERR_WORKSPACE;
     if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
 #define CALL_FWD(V, M, FW, L)                                                                        \
   launch_fwd<V, M, FW, L>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
-                   negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, state, first, last, s)
+                   negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, state, first, last, bias, s)
     DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_FWD)
 #undef CALL_FWD
   }
-  if (staged) return DGNN_ERR_SHAPE;   // the staged sweep exists only for the float4 layout
+  if (staged || bias) return DGNN_ERR_SHAPE;   // staged sweeps and the bias epilogue exist only for the float4 layout
   k_gat_fwd_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
       n_rows, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, mask, negative_slope,
       attn_drop, (float)(1.0 / (1.0 - (double)attn_drop)), out, edge_max, edge_sum);
@@ -707,6 +771,47 @@ int dgnn_gat_rowstat(int64_t n_rows, int h, int f, const float* attn_row, const 
     k_gat_rowstat_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
         n_rows, h, f, attn_row, edge_max, edge_sum, out, grad_out, pk);
   }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+size_t dgnn_gat_rowstat_bias_workspace_bytes(int h, int f) {
+  if (h <= 0 || f <= 0) return 256;
+  return up256((size_t)148 * 8 * h * f * sizeof(float)) + 256;    // room for up to 1184 CTAs
+}
+
+int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f, const float* attn_row, const float* edge_max,
+                          const float* edge_sum, const float* out, const float* grad_out, const float* bias,
+                          float* pack, float* grad_bias, void* workspace, size_t workspace_bytes, void* stream) {
+  if (n_rows < 0 || h <= 0 || f <= 0) return DGNN_ERR_SHAPE;
+  if (!bias || !grad_bias) return DGNN_ERR_NULL;
+  if (n_rows > 0 && (!attn_row || !edge_max || !edge_sum || !out || !grad_out || !pack)) return DGNN_ERR_NULL;
+  const FastShape fs = fast_shape(h, f);
+  if (!fs.ok) return DGNN_ERR_SHAPE;
+  if (!aligned16(pack) || !aligned16(out) || !aligned16(grad_out) || !aligned16(bias) || !aligned16(grad_bias))
+    return DGNN_ERR_ALIGN;
+  if (!workspace || workspace_bytes < dgnn_gat_rowstat_bias_workspace_bytes(h, f)) return DGNN_ERR_WORKSPACE;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  float4* part = reinterpret_cast<float4*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  i64 ctas = (i64)sms * 4;
+  if (ctas > 148 * 8) ctas = 148 * 8;
+  const i64 need = (n_rows + DGNN_WARPS - 1) / DGNN_WARPS;
+  if (need < ctas) ctas = need < 1 ? 1 : need;
+  const size_t smem = (size_t)DGNN_WARPS * fs.hf4 * sizeof(float4);   // <= 32 KB
+  const float4* o4 = reinterpret_cast<const float4*>(out);
+  const float4* g4 = reinterpret_cast<const float4*>(grad_out);
+  const float4* b4 = reinterpret_cast<const float4*>(bias);
+  float4* pk = reinterpret_cast<float4*>(pack);
+  switch (fs.vpl) {
+    case 1: k_gat_rowstat_bias<1><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
+    case 2: k_gat_rowstat_bias<2><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
+    case 4: k_gat_rowstat_bias<4><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
+    default: k_gat_rowstat_bias<8><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
+  }
+  k_bias_grad_final<<<dgnn_grid(fs.hf4, 128), 128, 0, s>>>((int)ctas, fs.hf4, part, reinterpret_cast<float4*>(grad_bias));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }

@@ -115,6 +115,24 @@ k_sddmm_generic(i64 n_rows, int H, int F, const void* indptr, int idx_bits, cons
   }
 }
 
+// ------------------------------------------------- single-head COO SDDMM
+// out[e] = <d1[row[e], :], d2[col[e], :]> for edges in any order: one warp per edge
+template <typename V>
+__global__ void __launch_bounds__(DGNN_THREADS)
+k_coo_sddmm(i64 nnz, int kv, const int* row, const int* col, const V* d1, const V* d2, float* out) {
+  const int lane = threadIdx.x & 31;
+  const i64 e = (i64)blockIdx.x * DGNN_WARPS + (threadIdx.x >> 5);
+  if (e >= nnz) return;
+  const i64 r = __ldg(row + e), c = __ldg(col + e);
+  float acc = 0.f;
+  for (int i = lane; i < kv; i += 32) {
+    if constexpr (sizeof(V) == 16) acc += dot4(__ldg(d1 + r * kv + i), __ldg(d2 + c * kv + i));
+    else acc = fmaf(__ldg(d1 + r * kv + i), __ldg(d2 + c * kv + i), acc);
+  }
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(DGNN_FULL, acc, o);
+  if (lane == 0) out[e] = acc;
+}
+
 // --------------------------------------------------------------- transpose
 __global__ void k_transpose4(i64 nnz, int h4, const int* permute, const float4* in, float4* out) {
   const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
@@ -374,6 +392,22 @@ int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr,
   }
   k_sddmm_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(n_rows, h, f, row_ptr, idx_bits,
                                                                            col_ind, a, b, out);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+int dgnn_coo_sddmm(int64_t nnz, int k, const int32_t* row_ind, const int32_t* col_ind, const float* d1,
+                   const float* d2, float* out, void* stream) {
+  if (nnz < 0 || k <= 0) return DGNN_ERR_SHAPE;
+  if (nnz == 0) return DGNN_OK;
+  if (!row_ind || !col_ind || !d1 || !d2 || !out) return DGNN_ERR_NULL;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned grid = dgnn_grid(nnz, DGNN_WARPS);
+  if (k % 4 == 0 && aligned16(d1) && aligned16(d2))
+    k_coo_sddmm<float4><<<grid, DGNN_THREADS, 0, s>>>(nnz, k / 4, row_ind, col_ind, reinterpret_cast<const float4*>(d1),
+                                                     reinterpret_cast<const float4*>(d2), out);
+  else
+    k_coo_sddmm<float><<<grid, DGNN_THREADS, 0, s>>>(nnz, k, row_ind, col_ind, d1, d2, out);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }

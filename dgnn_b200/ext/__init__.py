@@ -1,11 +1,12 @@
 """Python modules with the names and call conventions of the reference's six
-compiled extension modules (setup.py:28-35 of the reference), each a thin
+compiled extension modules (setup.py:28-35 of the reference) and of its unbuilt
+single-head `sddmm` module, each a thin
 wrapper over the C ABI.  `install()` registers them under their top-level
 names so that `import fused_gatconv as fused_gat` (operators/fused_gatconv.py:4
 of the reference) resolves to this package."""
 import sys
 
-from . import format_conversion, fused_edgeconv, fused_gatconv, fused_gmmconv, mhsddmm, mhtranspose
+from . import format_conversion, fused_edgeconv, fused_gatconv, fused_gmmconv, mhsddmm, mhtranspose, sddmm
 
 _MODULES = {
     "fused_gatconv": fused_gatconv,
@@ -14,6 +15,7 @@ _MODULES = {
     "mhsddmm": mhsddmm,
     "mhtranspose": mhtranspose,
     "format_conversion": format_conversion,
+    "sddmm": sddmm,
 }
 
 

@@ -19,9 +19,10 @@ def _dims3(t, name):
 
 # ------------------------------------------------------------------- GAT
 def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop=0.0,
-                edge_mask=None, save_stats=True):
+                edge_mask=None, save_stats=True, bias=None):
     """Fused GAT forward.  Returns (out, edge_max, edge_sum); the statistics are
-    None when save_stats is False (inference)."""
+    None when save_stats is False (inference).  `bias` [H*F] is added to the output
+    inside the kernel when given."""
     attn_row = _cuda_f32(attn_row, "attn_row")
     attn_col = _cuda_f32(attn_col, "attn_col")
     in_feat = _cuda_f32(in_feat, "in_feat")
@@ -49,11 +50,35 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
         edge_sum = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if save_stats else None
         ws_bytes = lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f)
         ws = _workspace(ws_bytes, dev)
-        check(lib().dgnn_gat_forward(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
-                                     _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
-                                     _p(edge_mask), _p(out), _p(edge_max), _p(edge_sum), _p(ws), ws.numel(),
-                                     _stream(dev)), "gat_forward")
+        if bias is None:
+            check(lib().dgnn_gat_forward(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
+                                         _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
+                                         _p(edge_mask), _p(out), _p(edge_max), _p(edge_sum), _p(ws), ws.numel(),
+                                         _stream(dev)), "gat_forward")
+        else:
+            bias = _cuda_f32(bias, "bias").reshape(h * f)
+            check(lib().dgnn_gat_forward_staged(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
+                                                _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
+                                                _p(edge_mask), _p(bias), _p(out), _p(edge_max), _p(edge_sum), None,
+                                                1, 1, _p(ws), ws.numel(), _stream(dev)), "gat_forward(bias)")
     return out, edge_max, edge_sum
+
+
+def gat_rowstat_bias(attn_row, edge_max, edge_sum, out, grad_out, bias):
+    """Row statistics when `out` includes the fused bias; returns (pack [N,H,4], grad_bias [H*F])."""
+    out = _cuda_f32(out, "out")
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    n, h, f = _dims3(out, "out")
+    bias = _cuda_f32(bias, "bias").reshape(h * f)
+    dev = out.device
+    with device_guard(dev):
+        pack = torch.empty((n, h, 4), dtype=torch.float32, device=dev)
+        grad_bias = torch.empty(h * f, dtype=torch.float32, device=dev)
+        ws = _workspace(lib().dgnn_gat_rowstat_bias_workspace_bytes(h, f), dev)
+        check(lib().dgnn_gat_rowstat_bias(n, h, f, _p(_cuda_f32(attn_row, "attn_row")), _p(_cuda_f32(edge_max, "edge_max")),
+                                          _p(_cuda_f32(edge_sum, "edge_sum")), _p(out), _p(grad_out), _p(bias), _p(pack),
+                                          _p(grad_bias), _p(ws), ws.numel(), _stream(dev)), "gat_rowstat_bias")
+    return pack, grad_bias
 
 
 def gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out):
@@ -223,6 +248,22 @@ def mhsddmm(row_ptr, col_ind, a, b):
     return out
 
 
+def coo_sddmm(row_ind, col_ind, d1, d2):
+    """out[e] = <d1[row_ind[e]], d2[col_ind[e]]> for a COO edge list in any order."""
+    row_ind = _cuda_i32(row_ind, "rowind")
+    col_ind = _cuda_i32(col_ind, "colind")
+    d1 = _cuda_f32(d1, "D1")
+    d2 = _cuda_f32(d2, "D2")
+    if d1.dim() != 2 or d2.dim() != 2 or d1.shape[1] != d2.shape[1] or row_ind.numel() != col_ind.numel():
+        raise RuntimeError("dgnn_b200: coo_sddmm needs D1 [m,k], D2 [n,k] and two index arrays of equal length")
+    nnz, k = row_ind.numel(), d1.shape[1]
+    dev = d1.device
+    with device_guard(dev):
+        out = torch.empty(nnz, dtype=torch.float32, device=dev)
+        check(lib().dgnn_coo_sddmm(nnz, k, _p(row_ind), _p(col_ind), _p(d1), _p(d2), _p(out), _stream(dev)), "coo_sddmm")
+    return out
+
+
 def mhtranspose(permute, attention):
     """out[i,:] = attention[permute[i],:]."""
     permute = _cuda_i32(permute, "permute")
@@ -382,7 +423,7 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
             esum = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f), dev)
         check(lib().dgnn_gat_forward_staged(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
-                                            _p(attn_col_blk), _p(feat_blk), float(negative_slope), 0.0, None,
+                                            _p(attn_col_blk), _p(feat_blk), float(negative_slope), 0.0, None, None,
                                             _p(out), _p(emax), _p(esum), _p(state), int(bool(first)), int(bool(last)),
                                             _p(ws), ws.numel(), _stream(dev)), "gat_forward_staged")
     return (out, emax, esum) if last else None

@@ -53,8 +53,12 @@ class GATConv(nn.Module):
         fused_logits = h.is_cuda and kernels.logits_supported(heads, width)
         if self.training and fused_logits:
             # logits, aggregation and their backward as one autograd node (same math as the branch below)
+            # without a residual branch the bias is added in the aggregation kernel's epilogue
+            fuse_bias = self.bias is not None and self.res_fc is None
             rst = GATLayerFuse(h, self.attn_l, self.attn_r, row_ptr, col_ind, col_ptr, row_ind, permute,
-                               self.negative_slope, self.attn_drop)
+                               self.negative_slope, self.attn_drop, self.bias if fuse_bias else None)
+            if fuse_bias:
+                return self.activation(rst) if self.activation else rst
         else:
             if fused_logits and not torch.is_grad_enabled():
                 attn_row, attn_col = kernels.gat_logits_forward(h, self.attn_l, self.attn_r)

@@ -40,36 +40,52 @@ class FusedGATFunction(torch.autograd.Function):
         return grad_attn_row, grad_attn_col, None, None, None, None, None, None, grad_feat, None
 
 
-def GATLayerFuse(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, permute, negative_slope, attn_drop):
-    """Attention logits + fused aggregation as one autograd node: the same result as
-    GATConvFuse((attn_l*h).sum(-1), (attn_r*h).sum(-1), ..., h, attn_drop) (the
-    composition in layers/gatconv_layer.py:74-80 of the reference) with the logits
-    and their gradients computed by streaming kernels, and the three gradient
+def GATLayerFuse(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, permute, negative_slope, attn_drop,
+                 bias=None):
+    """Attention logits + fused aggregation (+ bias) as one autograd node: the same result as
+    GATConvFuse((attn_l*h).sum(-1), (attn_r*h).sum(-1), ..., h, attn_drop) + bias (the
+    composition in layers/gatconv_layer.py:74-87 of the reference) with the logits and their
+    gradients computed by streaming kernels, the bias added in the aggregation kernel's
+    epilogue, its gradient reduced inside the row-statistics pass, and the three gradient
     contributions to h summed in place."""
     return FusedGATLayerFunction.apply(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, permute,
-                                       negative_slope, attn_drop)
+                                       negative_slope, attn_drop, bias)
 
 
 class FusedGATLayerFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, permute, negative_slope, attn_drop):
+    def forward(ctx, h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, permute, negative_slope, attn_drop, bias):
         h = h.contiguous()
         attn_row, attn_col = kernels.gat_logits_forward(h, attn_l, attn_r)
-        out_feat, edge_max, edge_sum, edge_mask = fused_gat.gat_forward(
-            attn_row, attn_col, row_ptr, col_ind, negative_slope, h, attn_drop)
-        ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h,
-                              attn_row, attn_col, out_feat, attn_l, attn_r)
+        attn_drop = float(attn_drop)
+        edge_mask = fused_gat.make_edge_mask(col_ind.numel(), h.shape[1], attn_drop, h.device)
+        out_feat, edge_max, edge_sum = kernels.gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h,
+                                                           attn_drop, edge_mask if attn_drop > 0.0 else None, True, bias)
+        saved = [row_ptr, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
+                 attn_l, attn_r]
+        if bias is not None:
+            saved.append(bias)
+        ctx.save_for_backward(*saved)
+        ctx.has_bias = bias is not None
         ctx.negative_slope = negative_slope
         ctx.attn_drop = attn_drop
         return out_feat
 
     @staticmethod
     def backward(ctx, grad_out):
-        (row_ptr, col_ind, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col,
-         out_feat, attn_l, attn_r) = ctx.saved_tensors
+        (row_ptr, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
+         attn_l, attn_r) = ctx.saved_tensors[:13]
         grad_out = grad_out.contiguous()
-        grad_h, grad_attn_row, grad_attn_col = fused_gat.gat_backward(
-            ctx.negative_slope, ctx.attn_drop, row_ptr, col_ind, col_ptr, row_ind, permute, edge_max, edge_sum,
-            edge_mask, h, attn_row, attn_col, grad_out, out_feat)
+        mask = edge_mask if ctx.attn_drop > 0.0 else None
+        grad_bias = None
+        if ctx.has_bias:
+            bias = ctx.saved_tensors[13]
+            pack, grad_bias = kernels.gat_rowstat_bias(attn_row, edge_max, edge_sum, out_feat, grad_out, bias)
+            grad_bias = grad_bias.view_as(bias)
+        else:
+            pack = kernels.gat_rowstat(attn_row, edge_max, edge_sum, out_feat, grad_out)
+        grad_h, grad_attn_row, grad_attn_col = kernels.gat_backward_cols(
+            row_ptr, col_ptr, row_ind, permute, pack, mask, h, attn_col, grad_out, ctx.negative_slope, ctx.attn_drop)
         grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_h)
-        return grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None, None, None, None, None
+        return (grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None, None, None, None, None,
+                grad_bias)

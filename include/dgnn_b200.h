@@ -73,14 +73,16 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f,
  * col_ind of that sub-matrix, attn_col / in_feat of that block) and the per-row softmax
  * state (max, sum, accumulator; dgnn_gat_forward_state_bytes) is carried in `state`.
  * first != 0 starts from an empty state, last != 0 normalises and writes out / edge_max /
- * edge_sum (they may be NULL otherwise).  first = last = 1 is dgnn_gat_forward.  No
- * counterpart in the reference, which is single-GPU. */
+ * edge_sum (they may be NULL otherwise).  first = last = 1 is dgnn_gat_forward.  `bias`
+ * (NULL or [h*f]) is added to the normalised output by the last call: the bias add of the
+ * layer (dgNN/layers/gatconv_layer.py:86-87) as a kernel epilogue.  No counterpart in the
+ * reference, which is single-GPU. */
 size_t dgnn_gat_forward_state_bytes(int64_t n_rows, int h, int f);
 int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f,
                             const void* row_ptr, int idx_bits, const int32_t* col_ind,
                             const float* attn_row, const float* attn_col, const float* in_feat,
                             float negative_slope, float attn_drop, const float* edge_mask,
-                            float* out, float* edge_max, float* edge_sum,
+                            const float* bias, float* out, float* edge_max, float* edge_sum,
                             float* state, int first, int last,
                             void* workspace, size_t workspace_bytes, void* stream);
 
@@ -91,6 +93,16 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f,
 int dgnn_gat_rowstat(int64_t n_rows, int h, int f,
                      const float* attn_row, const float* edge_max, const float* edge_sum,
                      const float* out, const float* grad_out, float* pack, void* stream);
+
+/* Row statistics when `out` carries the fused bias: S uses out - bias, and grad_bias [h*f] =
+ * sum_r grad_out[r,:] is produced on the way (fixed-order reduction).  Float4 layout only
+ * (f = 4*2^k, h*f <= 1024; DGNN_ERR_SHAPE otherwise). */
+size_t dgnn_gat_rowstat_bias_workspace_bytes(int h, int f);
+int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f,
+                          const float* attn_row, const float* edge_max, const float* edge_sum,
+                          const float* out, const float* grad_out, const float* bias,
+                          float* pack, float* grad_bias,
+                          void* workspace, size_t workspace_bytes, void* stream);
 
 /* Column pass of the backward over the CSC form of an [n_rows x n_cols] block:
  *   grad_feat[c,h,:]   = sum_{e in col c} keep*alpha/(1-p) * grad_out[row_e,h,:]
@@ -170,6 +182,11 @@ int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f,
                  const void* row_ptr, int idx_bits, const int32_t* col_ind,
                  const float* a, const float* b, float* out,
                  void* workspace, size_t workspace_bytes, void* stream);
+/* Single-head SDDMM over an edge list in any order: out[e] = <d1[row_ind[e],:], d2[col_ind[e],:]>,
+ * d1 [m,k], d2 [n,k]; stands where sddmm.coo_sddmm stands (dgNN/src/sddmm/sddmm.cpp:12-27, a module
+ * the reference does not build).  sddmm.csr_sddmm (sddmm.cpp:29-44) is dgnn_mhsddmm with h = 1. */
+int dgnn_coo_sddmm(int64_t nnz, int k, const int32_t* row_ind, const int32_t* col_ind,
+                   const float* d1, const float* d2, float* out, void* stream);
 /* out[i,:] = in[permute[i],:] for [nnz,h] fp32; replaces mhtranspose.mhtranspose
  * (dgNN/src/csr2csc/mhtranspose.cc:10-18, mhtranspose_kernel.cu:6-47). */
 int dgnn_mhtranspose(int64_t nnz, int h, const int32_t* permute,

@@ -179,7 +179,8 @@ def test_logits_kernels_match_tensor_ops(cuda, h, f):
     assert_close(gr, (g_col.double()[:, :, None] * xd).sum(0).float(), "grad attn_r", atol=1e-3)
 
 
-def test_layer_fused_path_equals_composed_path(cuda):
+@pytest.mark.parametrize("residual", [True, False])
+def test_layer_fused_path_equals_composed_path(cuda, residual):
     """GATConv's single-node training path (GATLayerFuse) against the reference composition
     (tensor-op logits + GATConvFuse), outputs and every parameter gradient."""
     from dgnn_b200.layers import GATConv
@@ -189,7 +190,10 @@ def test_layer_fused_path_equals_composed_path(cuda):
     cp, ri, pm = [t.int().to(cuda) for t in scipy_csc(rp, ci)]
     rp, ci = rp.to(cuda), ci.to(cuda)
     torch.manual_seed(0)
-    layer = GATConv(256, 32, 8, residual=True).to(cuda).train()   # in_feats == heads*out_feats: identity residual
+    # residual: in_feats == heads*out_feats gives the identity branch; without it the bias goes into the kernel epilogue
+    layer = GATConv(256, 32, 8, residual=residual).to(cuda).train()
+    with torch.no_grad():
+        layer.bias.uniform_(-1.0, 1.0)
     feat = torch.randn(n, 256, device=cuda)
     cot = torch.randn(n, 8, 32, device=cuda)
     out = layer(rp, ci, cp, ri, pm, feat)
@@ -198,7 +202,9 @@ def test_layer_fused_path_equals_composed_path(cuda):
     layer.zero_grad()
     h = torch.matmul(feat, layer.W).view(-1, 8, 32)
     ref = GATConvFuse((h * layer.attn_l).sum(-1), (h * layer.attn_r).sum(-1), rp, ci, cp, ri, pm, 0.2, h, 0.0)
-    ref = ref + layer.res_fc(h).view(-1, 8, 32) + layer.bias.view(-1, 8, 32)
+    if residual:
+        ref = ref + layer.res_fc(h).view(-1, 8, 32)
+    ref = ref + layer.bias.view(-1, 8, 32)
     ref.backward(cot)
     assert_close(out, ref, "layer output")
     for k, p in layer.named_parameters():

@@ -197,3 +197,37 @@ def test_c2_config_gmm_layer(cuda):
                             (layer.inv_sigma.grad, sig.grad, "d inv_sigma")):
         scale = max(1.0, float(want.abs().max()))
         assert_close(got, want.float(), name, rtol=1e-3, atol=1e-4 * scale)
+
+
+def test_single_head_sddmm_module(cuda):
+    """sddmm.coo_sddmm / sddmm.csr_sddmm (the reference's unbuilt single-head module)."""
+    from dgnn_b200.ext import sddmm
+    rp, ci = _graph("medium")
+    n = rp.numel() - 1
+    g = torch.Generator().manual_seed(4)
+    for k in (64, 30, 7):
+        d1, d2 = torch.randn(n, k, generator=g), torch.randn(n, k, generator=g)
+        rows = orc.edge_rows(rp)
+        ref = (d1[rows] * d2[ci.long()]).sum(-1)
+        out = sddmm.csr_sddmm(rp.to(cuda), ci.to(cuda), d1.to(cuda), d2.to(cuda))
+        assert_close(out, ref, f"csr_sddmm k={k}")
+        perm = torch.randperm(ci.numel(), generator=g)          # COO edges in a scrambled order
+        out = sddmm.coo_sddmm(rows[perm].int().to(cuda), ci[perm].to(cuda), d1.to(cuda), d2.to(cuda))
+        assert_close(out, ref[perm], f"coo_sddmm k={k}")
+
+
+def test_build_graph_and_knn_on_device(cuda):
+    from dgnn_b200 import graph
+    g = torch.Generator().manual_seed(6)
+    n, e = 500, 6000
+    src, dst = torch.randint(0, n, (e,), generator=g), torch.randint(0, n, (e,), generator=g)
+    gr = graph.build_graph(src.to(cuda), dst.to(cuda), n)
+    rp, ci = synth.csr_from_edges(dst.numpy(), src.numpy(), n)
+    cp, ri, pm = scipy_csc(rp, ci)
+    assert_equal(gr.row_ptr, rp, "row_ptr"); assert_equal(gr.col_ind, ci, "col_ind")
+    assert_equal(gr.col_ptr, cp, "col_ptr"); assert_equal(gr.row_ind, ri, "row_ind"); assert_equal(gr.permute, pm, "permute")
+    gl = graph.build_graph(src.to(cuda), dst.to(cuda), n, add_self_loops=True)
+    deg = (gl.row_ptr[1:] - gl.row_ptr[:-1])
+    assert int(deg.min()) >= 1
+    x = synth.unit_sphere_clouds(5, 128, seed=1, device=cuda)
+    assert_equal(graph.knn_graph(x, 8, chunk=2), synth.knn_src_ind(x, 8), "kNN src_ind")
