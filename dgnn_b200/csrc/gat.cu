@@ -14,6 +14,7 @@
 // streaming row reduction of d_e yields grad_attn_row.  Two feature gathers in
 // total for forward+backward instead of three, and no float atomics.
 #include "common.cuh"
+#include "gat_sh.cuh"
 
 namespace {
 
@@ -605,12 +606,12 @@ inline FastShape fast_shape(int h, int f) {
 inline i64 fwd_slot_stride(int h, int f) { return (i64)h * f + up4(2 * (i64)h); }
 inline i64 bwd_slot_stride(int h, int f) { return (i64)h * f + up4((i64)h); }
 
-template <int VPL, bool MASK, bool FULL, int LPR>
-int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
-               const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
-               float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
-               void* ws, float* state, int first, int last, const float* bias, cudaStream_t s) {
-  GatFwdOp<VPL, MASK, FULL, LPR> op;
+template <class Op>
+int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
+                  const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
+                  float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
+                  void* ws, float* state, int first, int last, const float* bias, cudaStream_t s) {
+  Op op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
   op.col_ind = col_ind; op.attn_row = attn_row; op.attn_col = attn_col;
@@ -623,13 +624,25 @@ int launch_fwd(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const voi
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
-template <int VPL, bool MASK, bool FULL, int LPR>
-int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const void* col_ptr, int idx_bits,
-               const int* row_ind, const int* permute, const float* pack, const float* mask,
-               const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
-               float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, unsigned long long* counter,
-               float* state, int first, int last, cudaStream_t s) {
-  GatBwdOp<VPL, MASK, FULL, LPR> op;
+// Rows of more than 32 vectors whose heads hold at least VPL vectors use the same-head lane
+// layout (gat_sh.cuh); everything else the plain one.
+inline bool same_head_layout(const FastShape& fs) { return fs.vpl > 1 && (1 << fs.f4_shift) >= fs.vpl; }
+
+template <int VPL, bool MASK, bool FULL, int LPR, class... A>
+int launch_fwd(const FastShape& fs, A... a) {
+  if constexpr (VPL > 1) {
+    if (same_head_layout(fs)) return launch_fwd_op<GatFwdOpSH<VPL, MASK, FULL>>(fs, a...);
+  }
+  return launch_fwd_op<GatFwdOp<VPL, MASK, FULL, LPR>>(fs, a...);
+}
+
+template <class Op>
+int launch_bwd_op(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const void* col_ptr, int idx_bits,
+                  const int* row_ind, const int* permute, const float* pack, const float* mask,
+                  const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
+                  float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, unsigned long long* counter,
+                  float* state, int first, int last, cudaStream_t s) {
+  Op op;
   op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
   op.row_ind = row_ind; op.permute = permute; op.pack = reinterpret_cast<const float4*>(pack);
@@ -640,6 +653,14 @@ int launch_bwd(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const voi
   op.grad_edge = grad_edge; op.ws = ws; op.slot_stride = bwd_slot_stride(h, f);
   op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last) ? 1 : 0;
   return dgnn_launch_trio(op, counter, s);
+}
+
+template <int VPL, bool MASK, bool FULL, int LPR, class... A>
+int launch_bwd(const FastShape& fs, A... a) {
+  if constexpr (VPL > 1) {
+    if (same_head_layout(fs)) return launch_bwd_op<GatBwdOpSH<VPL, MASK, FULL>>(fs, a...);
+  }
+  return launch_bwd_op<GatBwdOp<VPL, MASK, FULL, LPR>>(fs, a...);
 }
 
 // FULL = the row is exactly LPR*VPL float4 vectors wide: no lane is ever idle.

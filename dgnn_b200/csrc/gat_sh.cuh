@@ -1,0 +1,314 @@
+// "Same-head" lane layout for the fused GAT forward / backward operators.
+//
+// A row of H*F floats is HF4 float4 vectors, VPL per lane.  In the plain layout lane l
+// owns vectors l, l+32, ... which usually belong to VPL different heads, so every
+// per-head scalar (score, exp, softmax weight, SDDMM reduction) is computed VPL times
+// per lane.  When a head holds at least VPL vectors (VPL divides F/4) the vectors can be
+// dealt out so that all VPL vectors of a lane lie in ONE head: the head's F/4 vectors go
+// to LPH = F/(4*VPL) neighbouring lanes, lane j of the head taking vectors j, j+LPH, ...
+// Every load instruction then still reads LPH*16 contiguous bytes per head, while the
+// per-head work drops to one score / exp / weight per lane and edge and the SDDMM
+// reduction to log2(LPH) shuffles (2 instead of 6 per edge at 8 heads x 32).
+#pragma once
+#include "common.cuh"
+
+template <int VPL> struct Log2;
+template <> struct Log2<2> { static constexpr int v = 1; };
+template <> struct Log2<4> { static constexpr int v = 2; };
+template <> struct Log2<8> { static constexpr int v = 3; };
+
+template <int VPL>
+struct HeadLanes {
+  int hd;         // head of this lane
+  bool act;       // lane holds part of a head
+  bool lead;      // first lane of its head: writes the per-head scalars
+  int q[VPL];     // vectors of this lane
+  int lph_shift;  // log2(lanes per head)
+  __device__ __forceinline__ void init(int lane, int H, int f4_shift) {
+    lph_shift = f4_shift - Log2<VPL>::v;
+    const int hl = lane >> lph_shift, j = lane & ((1 << lph_shift) - 1);
+    act = hl < H;
+    hd = act ? hl : 0;
+    lead = act && j == 0;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) q[v] = (hd << f4_shift) + (v << lph_shift) + j;
+  }
+};
+
+// sum d[u] over the lanes of the head (uniform, all lanes take part)
+template <int U>
+__device__ __forceinline__ void lanes_reduce(float (&d)[U], int lph_shift) {
+#pragma unroll
+  for (int s = 0; s < 5; ++s) {
+    if (s < lph_shift) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) d[u] += __shfl_xor_sync(DGNN_FULL, d[u], 1 << s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ forward
+template <int VPL, bool MASK, bool FULL>
+struct GatFwdOpSH {
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
+  static constexpr bool HAS_PARTIALS = true;
+  static constexpr int U = VPL <= 2 ? 4 : 2;
+  i64 n_rows, nnz;
+  const void* indptr;
+  int idx_bits;
+  int H, hf4, f4_shift;
+  const int* col_ind;
+  const float* attn_row;
+  const float* attn_col;
+  const float4* in_feat;
+  const float* mask;
+  float slope, drop_p, inv_keep;
+  float4* out;
+  float* edge_max;
+  float* edge_sum;
+  float* ws;
+  i64 slot_stride;
+  float* state;
+  int first, last, skip_empty;
+  const float4* bias;
+
+  struct State {
+    HeadLanes<VPL> lm;
+    float ar, m, z;
+    float4 acc[VPL];
+  };
+
+  __device__ __forceinline__ void init(State& st, i64 r, int lane) const {
+    st.lm.init(lane, H, f4_shift);
+    st.ar = st.lm.act ? __ldg(attn_row + r * H + st.lm.hd) : 0.f;
+    st.m = DGNN_NEG_INIT;
+    st.z = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) st.acc[v] = zero4();
+  }
+  __device__ __forceinline__ void resume(State& st, i64 r, int lane) const {
+    if (!first) merge_partial(st, state + r * slot_stride, lane);
+  }
+  __device__ __forceinline__ void combine(State&, int) const {}
+
+  template <bool ALL>
+  __device__ __forceinline__ void batch(State& st, int my_c, i64 ebase, int k, int cnt) const {
+    int c[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) c[u] = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
+    float s[U];
+    float4 x[U][VPL];
+    bool keep[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act);
+      s[u] = ok ? __ldg(attn_col + (i64)c[u] * H + st.lm.hd) : 0.f;
+      keep[u] = ok;
+      if (MASK) keep[u] = ok ? (__ldg(mask + (ebase + k + u) * H + st.lm.hd) > drop_p) : false;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4(in_feat + (i64)c[u] * hf4 + st.lm.q[v]) : zero4();
+    }
+    if (!FULL && !st.lm.act) return;
+    float l[U];
+    float bm = st.m;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      l[u] = (ALL || k + u < cnt) ? leaky(st.ar + s[u], slope) : DGNN_NEG_INIT;
+      bm = fmaxf(bm, l[u]);
+    }
+    const float sc = fast_exp(st.m - bm);  // 1 when the maximum did not move
+    st.z *= sc;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) scale4(st.acc[v], sc);
+    st.m = bm;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (ALL || k + u < cnt) {
+        const float p = fast_exp(l[u] - bm);
+        st.z += p;
+        if (!MASK || keep[u]) {
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) fma4(st.acc[v], p, x[u][v]);
+        }
+      }
+    }
+  }
+
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+    for (i64 base = e0; base < e1; base += 32) {
+      const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
+      const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
+      int k = 0;
+      for (; k + U <= cnt; k += U) batch<true>(st, my_c, base, k, cnt);
+      if (k < cnt) batch<false>(st, my_c, base, k, cnt);
+    }
+  }
+
+  __device__ __forceinline__ void finalize(State& st, i64 r, int lane) const {
+    if (!last) { store_partial(st, state + r * slot_stride, lane); return; }
+    if (!st.lm.act) return;
+    const float sc = st.z > 0.f ? inv_keep / st.z : 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      float4 a = st.acc[v];
+      scale4(a, sc);
+      if (bias) add4(a, __ldg(bias + st.lm.q[v]));
+      out[r * hf4 + st.lm.q[v]] = a;
+    }
+    if (st.lm.lead && edge_max) {
+      edge_max[r * H + st.lm.hd] = st.m;
+      edge_sum[r * H + st.lm.hd] = st.z;
+    }
+  }
+
+  __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
+    if (!st.lm.act) return;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) reinterpret_cast<float4*>(p)[st.lm.q[v]] = st.acc[v];
+    if (st.lm.lead) {
+      p[hf4 * 4 + st.lm.hd] = st.m;
+      p[hf4 * 4 + H + st.lm.hd] = st.z;
+    }
+  }
+
+  __device__ __forceinline__ void merge_partial(State& st, const float* p, int) const {
+    if (!st.lm.act) return;
+    const float mi = p[hf4 * 4 + st.lm.hd];
+    const float zi = p[hf4 * 4 + H + st.lm.hd];
+    const float mn = fmaxf(st.m, mi);
+    const float s1 = fast_exp(st.m - mn), s2 = fast_exp(mi - mn);
+    st.z = st.z * s1 + zi * s2;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      scale4(st.acc[v], s1);
+      fma4(st.acc[v], s2, reinterpret_cast<const float4*>(p)[st.lm.q[v]]);
+    }
+    st.m = mn;
+  }
+};
+
+// ------------------------------------------------------------ backward cols
+template <int VPL, bool MASK, bool FULL>
+struct GatBwdOpSH {
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? 4 : (VPL == 4 ? 3 : 2);
+  static constexpr bool HAS_PARTIALS = true;
+  static constexpr int U = VPL <= 2 ? 4 : 2;
+  i64 n_rows, nnz;      // "rows" of the CSC form = source columns
+  const void* indptr;   // col_ptr
+  int idx_bits;
+  int H, hf4, f4_shift;
+  const int* row_ind;
+  const int* permute;
+  const float4* pack;
+  const float* mask;
+  const float4* in_feat;
+  const float* attn_col;
+  const float4* grad_out;
+  float slope, drop_p, inv_keep;
+  float4* grad_feat;
+  float* grad_attn_col;
+  float* grad_edge;  // [nnz,H] in CSR order
+  float* ws;
+  i64 slot_stride;
+  float* state;
+  int first, last, skip_empty;
+
+  struct State {
+    HeadLanes<VPL> lm;
+    float4 x[VPL], acc[VPL];
+    float ac, gc;
+  };
+
+  __device__ __forceinline__ void init(State& st, i64 c, int lane) const {
+    st.lm.init(lane, H, f4_shift);
+    st.ac = st.lm.act ? __ldg(attn_col + c * H + st.lm.hd) : 0.f;
+    st.gc = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      st.x[v] = st.lm.act ? ld4(in_feat + c * hf4 + st.lm.q[v]) : zero4();
+      st.acc[v] = zero4();
+    }
+  }
+  __device__ __forceinline__ void resume(State& st, i64 c, int lane) const {
+    if (!first) merge_partial(st, state + c * slot_stride, lane);
+  }
+  __device__ __forceinline__ void combine(State&, int) const {}
+
+  template <bool ALL>
+  __device__ __forceinline__ void batch(State& st, int my_r, int my_p, int k, int cnt) const {
+    int r[U], pp[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      r[u] = __shfl_sync(DGNN_FULL, my_r, (k + u) & 31);
+      pp[u] = __shfl_sync(DGNN_FULL, my_p, (k + u) & 31);
+    }
+    float4 pk[U], g4[U][VPL];
+    bool keep[U];
+    float d[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act);
+      pk[u] = ok ? ld4(pack + (i64)r[u] * H + st.lm.hd) : zero4();
+      keep[u] = ok;
+      if (MASK) keep[u] = ok ? (__ldg(mask + (i64)pp[u] * H + st.lm.hd) > drop_p) : false;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4(grad_out + (i64)r[u] * hf4 + st.lm.q[v]) : zero4();
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      d[u] = 0.f;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) d[u] += dot4(g4[u][v], st.x[v]);
+    }
+    lanes_reduce<U>(d, st.lm.lph_shift);  // executed by all lanes, also for slots past cnt
+    if (!FULL && !st.lm.act) return;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (ALL || k + u < cnt) {
+        const float l = leaky(pk[u].x + st.ac, slope);
+        const float alpha = fast_exp(l - pk[u].y) * pk[u].z;   // pack.z = 1 / edge_sum
+        const float kp = (!MASK || keep[u]) ? inv_keep : 0.f;
+        float de = alpha * (d[u] * kp - pk[u].w);
+        de = l < 0.f ? de * slope : de;
+        st.gc += de;
+        const float w = alpha * kp;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) fma4(st.acc[v], w, g4[u][v]);
+        if (st.lm.lead) grad_edge[(i64)pp[u] * H + st.lm.hd] = de;
+      }
+    }
+  }
+
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+    for (i64 base = e0; base < e1; base += 32) {
+      const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
+      const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
+      const int my_p = lane < cnt ? __ldg(permute + base + lane) : 0;
+      int k = 0;
+      for (; k + U <= cnt; k += U) batch<true>(st, my_r, my_p, k, cnt);
+      if (k < cnt) batch<false>(st, my_r, my_p, k, cnt);
+    }
+  }
+
+  __device__ __forceinline__ void finalize(State& st, i64 c, int lane) const {
+    if (!last) { store_partial(st, state + c * slot_stride, lane); return; }
+    if (!st.lm.act) return;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) grad_feat[c * hf4 + st.lm.q[v]] = st.acc[v];
+    if (st.lm.lead) grad_attn_col[c * H + st.lm.hd] = st.gc;
+  }
+
+  __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
+    if (!st.lm.act) return;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) reinterpret_cast<float4*>(p)[st.lm.q[v]] = st.acc[v];
+    if (st.lm.lead) p[hf4 * 4 + st.lm.hd] = st.gc;
+  }
+
+  __device__ __forceinline__ void merge_partial(State& st, const float* p, int) const {
+    if (!st.lm.act) return;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) add4(st.acc[v], reinterpret_cast<const float4*>(p)[st.lm.q[v]]);
+    st.gc += p[hf4 * 4 + st.lm.hd];
+  }
+};
