@@ -31,7 +31,7 @@ SLOPE = 0.2
 # DRAM bytes (read + write) per call at the full-size workload from one ncu capture of
 # dram__bytes_read.sum + dram__bytes_write.sum (profiles/); None until captured
 TRAFFIC_FWD_BYTES = 64.8e9
-TRAFFIC_BWD_BYTES = 88.2e9
+TRAFFIC_BWD_BYTES = 88.8e9
 
 
 def parse():

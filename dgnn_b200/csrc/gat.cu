@@ -817,7 +817,7 @@ int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f, const float* attn_row, c
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  i64 ctas = (i64)sms * 4;
+  i64 ctas = (i64)sms * 8;
   if (ctas > 148 * 8) ctas = 148 * 8;
   const i64 need = (n_rows + DGNN_WARPS - 1) / DGNN_WARPS;
   if (need < ctas) ctas = need < 1 ? 1 : need;

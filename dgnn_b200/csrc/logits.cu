@@ -49,21 +49,34 @@ k_logits_fwd(i64 n, int H, int hf4, int f4_shift, const float4* feat, const floa
     r4[v] = lm.act[v] ? ld4(ar + lm.q[v]) : zero4();
   }
   const i64 stride = (i64)gridDim.x * LG_WARPS;
-  for (i64 r = (i64)blockIdx.x * LG_WARPS + (threadIdx.x >> 5); r < n; r += stride) {
-    float dl[VPL], dr[VPL];
+  // two rows per iteration: twice the loads in flight per warp
+  for (i64 r = (i64)blockIdx.x * LG_WARPS + (threadIdx.x >> 5); r < n; r += 2 * stride) {
+    const i64 r2 = r + stride;
+    const bool two = r2 < n;
+    float4 xa[VPL], xb[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      const float4 x = lm.act[v] ? ld4(feat + r * hf4 + lm.q[v]) : zero4();
-      dl[v] = dot4(x, l4[v]);
-      dr[v] = dot4(x, r4[v]);
+      xa[v] = lm.act[v] ? ld4(feat + r * hf4 + lm.q[v]) : zero4();
+      xb[v] = (two && lm.act[v]) ? ld4(feat + r2 * hf4 + lm.q[v]) : zero4();
     }
-    head_reduce<VPL>(dl, f4_shift);
-    head_reduce<VPL>(dr, f4_shift);
+    float d[4][VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      d[0][v] = dot4(xa[v], l4[v]);
+      d[1][v] = dot4(xa[v], r4[v]);
+      d[2][v] = dot4(xb[v], l4[v]);
+      d[3][v] = dot4(xb[v], r4[v]);
+    }
+    head_reduce<4, VPL>(d, f4_shift);
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (lm.lead[v]) {
-        attn_row[r * H + lm.hd[v]] = dl[v];
-        attn_col[r * H + lm.hd[v]] = dr[v];
+        attn_row[r * H + lm.hd[v]] = d[0][v];
+        attn_col[r * H + lm.hd[v]] = d[1][v];
+        if (two) {
+          attn_row[r2 * H + lm.hd[v]] = d[2][v];
+          attn_col[r2 * H + lm.hd[v]] = d[3][v];
+        }
       }
     }
   }
