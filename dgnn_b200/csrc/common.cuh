@@ -22,6 +22,7 @@ constexpr int DGNN_WARPS = 8;          // warps per CTA in the row kernels
 constexpr int DGNN_THREADS = DGNN_WARPS * 32;
 constexpr int DGNN_ROW_WARPS = 4;      // warps per CTA in the strided short-row kernel
 constexpr int DGNN_ROW_THREADS = DGNN_ROW_WARPS * 32;
+constexpr i64 DGNN_SMALL_NNZ = 16 * 1024;  // graphs up to this many entries run as one launch per operator
 constexpr int DGNN_CHUNK_WARPS = 4;    // warps that share one (chunk, long row) piece
 constexpr float DGNN_NEG_INIT = -1e38f;  // initial running maximum (matches the reference)
 
@@ -164,6 +165,24 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const
   }
 }
 
+// Small graphs (at most DGNN_SMALL_NNZ entries): one launch, one warp per row whatever its
+// length, no counter and no chunk / merge kernels -- launch latency is all that matters there.
+template <class Op>
+__global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows_small(const Op op) {
+  const int lane = threadIdx.x & 31;
+  const i64 r = (i64)blockIdx.x * DGNN_ROW_WARPS + (threadIdx.x >> 5);
+  if (r >= op.n_rows) return;
+  const i64 lb = ldp(op.indptr, op.idx_bits, r);
+  const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
+  if (op.skip_empty && hb == lb) return;
+  typename Op::State st;
+  op.init(st, r, lane);
+  op.resume(st, r, lane);
+  op.range(st, r, lb, hb, lane);
+  op.combine(st, lane);
+  op.finalize(st, r, lane);
+}
+
 // Long rows: one CTA of DGNN_CHUNK_WARPS warps per (chunk, slot).  The piece of the
 // row inside the chunk is cut into equal sub-ranges, one per warp; the warps'
 // states are folded in edge order through shared memory and warp 0 writes the
@@ -232,6 +251,11 @@ static inline i64 dgnn_num_chunks(i64 nnz) { return (nnz + DGNN_SEG - 1) / DGNN_
 template <class Op>
 static inline int dgnn_launch_trio(const Op& op, unsigned long long* counter, cudaStream_t s) {
   if (op.n_rows <= 0) return DGNN_OK;
+  if (op.nnz <= DGNN_SMALL_NNZ) {
+    k_rows_small<Op><<<dgnn_grid(op.n_rows, DGNN_ROW_WARPS), DGNN_ROW_THREADS, 0, s>>>(op);
+    cudaError_t e0 = cudaGetLastError();
+    return e0 == cudaSuccess ? DGNN_OK : (int)e0;
+  }
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned long long), s);
   if (e != cudaSuccess) return (int)e;
   {

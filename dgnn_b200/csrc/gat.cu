@@ -531,13 +531,13 @@ k_gat_bwd_cols_generic(i64 n_cols, int H, int F, const void* col_ptr, int idx_bi
 // one thread per (row, head); long rows go through chunk partials like the
 // feature kernels so that every sum has a fixed order
 __global__ void k_rowred_rows(i64 n_rows, int H, const void* indptr, int idx_bits,
-                              const float* grad_edge, float* grad_attn_row) {
+                              const float* grad_edge, float* grad_attn_row, int all_rows) {
   const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_rows * H) return;
   const i64 r = t / H;
   const int h = (int)(t % H);
   const i64 lb = ldp(indptr, idx_bits, r), hb = ldp(indptr, idx_bits, r + 1);
-  if (hb - lb > DGNN_SEG) return;
+  if (hb - lb > DGNN_SEG && !all_rows) return;
   float s = 0.f;
   for (i64 e = lb; e < hb; ++e) s += __ldg(grad_edge + e * H + h);
   grad_attn_row[t] = s;
@@ -906,8 +906,9 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
   }
   if (n_rows > 0) {
     const int tb = 256;
-    k_rowred_rows<<<dgnn_grid(n_rows * h, tb), tb, 0, s>>>(n_rows, h, row_ptr, idx_bits, grad_edge, grad_attn_row);
-    if (nnz > DGNN_SEG) {
+    const int small = nnz <= DGNN_SMALL_NNZ ? 1 : 0;   // same rule as the feature kernels: one launch for small graphs
+    k_rowred_rows<<<dgnn_grid(n_rows * h, tb), tb, 0, s>>>(n_rows, h, row_ptr, idx_bits, grad_edge, grad_attn_row, small);
+    if (nnz > DGNN_SEG && !small) {
       const i64 nc = dgnn_num_chunks(nnz);
       k_rowred_chunks<<<dgnn_grid(2 * nc * h, tb), tb, 0, s>>>(n_rows, nnz, h, row_ptr, idx_bits, grad_edge, row_part);
       k_rowred_merge<<<dgnn_grid(nc * h, tb), tb, 0, s>>>(n_rows, nnz, h, row_ptr, idx_bits, row_part, grad_attn_row);
