@@ -20,7 +20,7 @@ import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REF = "/root/reference"
+DEFAULT_REF = os.environ.get("DGNN_REFERENCE_ROOT", "/root/reference")
 
 EXTENSIONS = {
     "fused_gatconv": ["dgNN/src/fused_gatconv/fused_gatconv.cpp", "dgNN/src/fused_gatconv/fused_gatconv_kernel.cu"],

@@ -21,6 +21,9 @@ from test_oracle_golden import compare, oracle_outputs  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
+# timing records of the side-by-side tests go here
+RESULTS_DIR = os.environ.get("DGNN_RESULTS_DIR", os.path.join(os.path.dirname(HERE), "gpurun_out"))
+
 
 @pytest.fixture(scope="module")
 def ref(cuda):
@@ -114,7 +117,7 @@ def test_side_by_side_timing(cuda, ref):
     t_ref, t_our = _time(ref_step), _time(our_step)
     rec = dict(workload="rmat n=300k e=12M h=8 f=32 fused GAT fwd+bwd", ref_ms=t_ref, ours_ms=t_our, speedup=t_ref / t_our)
     print("SIDE_BY_SIDE", json.dumps(rec))
-    out_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")
+    out_dir = RESULTS_DIR
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "side_by_side.json"), "w") as fh:
         json.dump(rec, fh)
@@ -124,7 +127,7 @@ def test_side_by_side_timing(cuda, ref):
 def test_side_by_side_other_ops(cuda, ref):
     """Every other operator against the reference's kernel on the same GPU, at sizes and shapes the
     reference kernels handle (int32, widths that are multiples of 32, one Gaussian kernel): results agree
-    and both times are recorded in gpurun_out/side_by_side_ops.json."""
+    and both times are recorded in side_by_side_ops.json in the results folder."""
     rec = {}
     n, e, h, f = 300_000, 12_000_000, 8, 32
     rp, ci = synth.rmat_graph(n, e, seed=4, device=cuda, ptr_dtype=torch.int32)
@@ -173,7 +176,7 @@ def test_side_by_side_other_ops(cuda, ref):
 
     out = {k: {"ref_ms": round(v[0], 4), "ours_ms": round(v[1], 4), "speedup": round(v[0] / v[1], 2)} for k, v in rec.items()}
     print("SIDE_BY_SIDE_OPS", json.dumps(out))
-    out_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")
+    out_dir = RESULTS_DIR
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "side_by_side_ops.json"), "w") as fh:
         json.dump(out, fh, indent=1)
@@ -204,7 +207,7 @@ def test_side_by_side_small_graph(cuda, ref):
     t_ref, t_our = _time(ref_step, 50, 5), _time(our_step, 50, 5)
     rec = dict(workload="2708 nodes / 13264 edges, 4 x 64, fused GAT fwd+bwd", ref_ms=t_ref, ours_ms=t_our, speedup=t_ref / t_our)
     print("SIDE_BY_SIDE_SMALL", json.dumps(rec))
-    out_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")
+    out_dir = RESULTS_DIR
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "side_by_side_small.json"), "w") as fh:
         json.dump(rec, fh)
