@@ -141,27 +141,35 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 //   finalize(State&, row, lane), store_partial(State&, float* p, lane),
 //   merge_partial(State&, const float* p, lane)
 // ---------------------------------------------------------------------------
-// Short rows: every warp of a fixed pool draws the next row from a counter.  Rows
-// come out in id order, so whatever skew the ids carry (R-MAT: low ids are the
-// heavy ones) is spread over all warps and the tail consists of single rows.
+// Short rows: every warp of a fixed pool draws the next `batch` rows (1..31) from a
+// counter.  Rows come out in id order, so whatever skew the ids carry (R-MAT: low
+// ids are the heavy ones) is spread over all warps and the tail consists of a few
+// rows.  The batch grows as the average row gets shorter, which keeps the rate of
+// atomics on the one counter far below what the memory system serialises, and the
+// batch's index pointers arrive in one coalesced load.
 template <class Op>
-__global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op, unsigned long long* next_row) {
+__global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op, unsigned long long* next_row, const int batch) {
   const int lane = threadIdx.x & 31;
   for (;;) {
     unsigned long long t = 0;
-    if (lane == 0) t = atomicAdd(next_row, 1ULL);
-    const i64 r = (i64)__shfl_sync(DGNN_FULL, t, 0);
-    if (r >= op.n_rows) break;
-    const i64 lb = ldp(op.indptr, op.idx_bits, r);
-    const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
-    if (hb - lb > DGNN_SEG) continue;  // long row: chunk + merge kernels own it
-    if (op.skip_empty && hb == lb) continue;  // middle stage of a staged sweep: the carried state stays as it is
-    typename Op::State st;
-    op.init(st, r, lane);
-    op.resume(st, r, lane);
-    op.range(st, r, lb, hb, lane);
-    op.combine(st, lane);
-    op.finalize(st, r, lane);
+    if (lane == 0) t = atomicAdd(next_row, (unsigned long long)batch);
+    const i64 r0 = (i64)__shfl_sync(DGNN_FULL, t, 0);
+    if (r0 >= op.n_rows) break;
+    const int cnt = (int)((op.n_rows - r0 < batch) ? op.n_rows - r0 : batch);
+    const i64 mine = lane <= cnt ? ldp(op.indptr, op.idx_bits, r0 + lane) : 0;
+    for (int i = 0; i < cnt; ++i) {
+      const i64 r = r0 + i;
+      const i64 lb = __shfl_sync(DGNN_FULL, mine, i);
+      const i64 hb = __shfl_sync(DGNN_FULL, mine, i + 1);
+      if (hb - lb > DGNN_SEG) continue;  // long row: chunk + merge kernels own it
+      if (op.skip_empty && hb == lb) continue;  // middle stage of a staged sweep: the carried state stays as it is
+      typename Op::State st;
+      op.init(st, r, lane);
+      op.resume(st, r, lane);
+      op.range(st, r, lb, hb, lane);
+      op.combine(st, lane);
+      op.finalize(st, r, lane);
+    }
   }
 }
 
@@ -264,7 +272,11 @@ static inline int dgnn_launch_trio(const Op& op, unsigned long long* counter, cu
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const i64 pool = (i64)sms * Op::MIN_BLOCKS;     // resident CTAs: one wave, rows are drawn dynamically
     const i64 need = (op.n_rows + DGNN_ROW_WARPS - 1) / DGNN_ROW_WARPS;
-    k_rows<Op><<<(unsigned)(need < pool ? need : pool), DGNN_ROW_THREADS, 0, s>>>(op, counter);
+    // rows per draw: about 64 edges' worth, one row once the average row has 32 edges or more
+    const i64 avg = op.nnz / op.n_rows;
+    int batch = avg >= 32 ? 1 : (int)(64 / (avg > 2 ? avg : 2));
+    if (batch > 31) batch = 31;  // the batch's pointers plus one fit the 32 lanes
+    k_rows<Op><<<(unsigned)(need < pool ? need : pool), DGNN_ROW_THREADS, 0, s>>>(op, counter, batch);
   }
   if (op.nnz > DGNN_SEG) {
     const i64 nc = dgnn_num_chunks(op.nnz);
