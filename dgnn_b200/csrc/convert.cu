@@ -13,12 +13,14 @@
 
 namespace {
 
-constexpr int RS_THREADS = 256;
-constexpr int RS_IPT = 16;                       // items per thread
-constexpr int RS_TILE = RS_THREADS * RS_IPT;     // 4096 items per tile
+constexpr int RS_TILE = 4096;                    // items per tile
+constexpr int RADIX = 256;
+constexpr int HIST_THREADS = RADIX;              // histogram kernel: one counter per thread
+constexpr int HIST_IPT = RS_TILE / HIST_THREADS;
+constexpr int RS_THREADS = 512;                  // scatter kernel
+constexpr int RS_IPT = RS_TILE / RS_THREADS;     // 8 items per thread
 constexpr int RS_WARPS = RS_THREADS / 32;
 constexpr int RS_WARP_ITEMS = 32 * RS_IPT;       // consecutive items owned by one warp
-constexpr int RADIX = 256;
 
 constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_IPT = 8;
@@ -126,40 +128,56 @@ __global__ void k_write_ptr(i64 n_plus_1, const unsigned* scanned, void* out, in
 
 // ---- radix passes -----------------------------------------------------------
 // tile_hist layout: [digit][tile]
-__global__ void __launch_bounds__(RS_THREADS)
+__global__ void __launch_bounds__(HIST_THREADS)
 k_radix_hist(const unsigned* keys, i64 n, int shift, unsigned* tile_hist, i64 ntiles) {
   __shared__ unsigned h[RADIX];
   h[threadIdx.x] = 0;
   __syncthreads();
   const i64 base = (i64)blockIdx.x * RS_TILE;
 #pragma unroll
-  for (int i = 0; i < RS_IPT; ++i) {
-    const i64 idx = base + (i64)i * RS_THREADS + threadIdx.x;
+  for (int i = 0; i < HIST_IPT; ++i) {
+    const i64 idx = base + (i64)i * HIST_THREADS + threadIdx.x;
     if (idx < n) atomicAdd(&h[(__ldg(keys + idx) >> shift) & (RADIX - 1)], 1u);
   }
   __syncthreads();
   tile_hist[(i64)threadIdx.x * ntiles + blockIdx.x] = h[threadIdx.x];
 }
 
+// One tile of a stable pass.  (1) Every warp ranks its 256 consecutive items by
+// digit with match_any votes taken in index order.  (2) The per-warp digit counts
+// are turned into the position of every item inside the tile sorted by digit, and
+// keys and payload are put in that order through shared memory.  (3) The sorted
+// tile is written out: items of one digit are neighbours both in the tile and in
+// the output, so a warp's store covers a few runs of consecutive addresses instead
+// of 32 scattered words.
 // FIRST: keys are the CSR column ids, payload (position,row) is generated here.
 // LAST: keys are not written.
 template <bool FIRST, bool LAST>
-__global__ void __launch_bounds__(RS_THREADS)
-k_radix_scatter(const unsigned* keys_in, const int* pos_in, const int* row_in, unsigned* keys_out,
-                int* pos_out, int* row_out, i64 n, int shift, const unsigned* tile_off, i64 ntiles,
-                const void* row_ptr, int idx_bits, i64 n_rows) {
-  __shared__ unsigned cnt[RS_WARPS][RADIX];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < RS_WARPS * RADIX; i += RS_THREADS) (&cnt[0][0])[i] = 0;
+__global__ void __launch_bounds__(RS_THREADS, 2)
+k_radix_scatter(const unsigned* __restrict__ keys_in, const int* __restrict__ pos_in, const int* __restrict__ row_in,
+                unsigned* __restrict__ keys_out, int* __restrict__ pos_out, int* __restrict__ row_out, i64 n, int shift,
+                const unsigned* __restrict__ tile_off, i64 ntiles, const void* __restrict__ row_ptr, int idx_bits,
+                i64 n_rows) {
+  __shared__ unsigned cnt[RS_WARPS][RADIX];  // per-warp digit counts, then per-warp start inside the sorted tile
+  __shared__ unsigned gbase[RADIX];          // start of the digit's run in the output minus its start in the tile
+  __shared__ unsigned buf[RS_TILE];          // exchange buffer
+  __shared__ unsigned wsum[RADIX / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < RS_WARPS * RADIX; i += RS_THREADS) (&cnt[0][0])[i] = 0;
   __syncthreads();
-  const i64 wbase = (i64)blockIdx.x * RS_TILE + (i64)warp * RS_WARP_ITEMS;
+  const i64 tbase = (i64)blockIdx.x * RS_TILE;
+  const i64 wbase = tbase + (i64)warp * RS_WARP_ITEMS;
+  const int n_tile = (int)(n - tbase < RS_TILE ? n - tbase : RS_TILE);
   unsigned key[RS_IPT];
-  unsigned rank[RS_IPT];
+  unsigned lpos[RS_IPT];  // rank among the warp's items of the same digit, then position in the sorted tile
 #pragma unroll
   for (int t = 0; t < RS_IPT; ++t) {
     const i64 idx = wbase + t * 32 + lane;
-    const bool valid = idx < n;
-    key[t] = valid ? __ldg(keys_in + idx) : 0u;
+    key[t] = idx < n ? __ldg(keys_in + idx) : 0u;
+  }
+#pragma unroll
+  for (int t = 0; t < RS_IPT; ++t) {
+    const bool valid = wbase + t * 32 + lane < n;
     const unsigned d = (key[t] >> shift) & (RADIX - 1);
     const unsigned peers = __match_any_sync(DGNN_FULL, valid ? d : (unsigned)RADIX);
     const int leader = __ffs(peers) - 1;
@@ -169,22 +187,68 @@ k_radix_scatter(const unsigned* keys_in, const int* pos_in, const int* row_in, u
       cnt[warp][d] = base + __popc(peers);
     }
     base = __shfl_sync(DGNN_FULL, base, leader);
-    rank[t] = base + __popc(peers & ((1u << lane) - 1u));
+    lpos[t] = base + __popc(peers & ((1u << lane) - 1u));
     __syncwarp();
   }
   __syncthreads();
-  {  // per digit: exclusive prefix over the warps of this tile + global tile offset
-    const int d = threadIdx.x;
-    unsigned run = tile_off[(i64)d * ntiles + blockIdx.x];
+  unsigned total = 0, incl = 0;
+  if (tid < RADIX) {  // exclusive prefix of digit tid over the warps, and the digit's total
 #pragma unroll
     for (int w = 0; w < RS_WARPS; ++w) {
-      const unsigned c = cnt[w][d];
-      cnt[w][d] = run;
-      run += c;
+      const unsigned c = cnt[w][tid];
+      cnt[w][tid] = total;
+      total += c;
+    }
+    incl = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned v = __shfl_up_sync(DGNN_FULL, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+  }
+  __syncthreads();
+  if (tid < RADIX) {
+    unsigned lstart = incl - total;  // where the digit's run starts in the sorted tile
+    for (int w = 0; w < warp; ++w) lstart += wsum[w];
+    gbase[tid] = tile_off[(i64)tid * ntiles + blockIdx.x] - lstart;
+#pragma unroll
+    for (int w = 0; w < RS_WARPS; ++w) cnt[w][tid] += lstart;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int t = 0; t < RS_IPT; ++t) {
+    if (wbase + t * 32 + lane < n) {
+      lpos[t] += cnt[warp][(key[t] >> shift) & (RADIX - 1)];
+      buf[lpos[t]] = key[t];
     }
   }
   __syncthreads();
-  // row of the first / last entry this warp owns (FIRST pass only)
+  unsigned dst[RS_IPT];
+#pragma unroll
+  for (int k = 0; k < RS_IPT; ++k) {
+    const int i = k * RS_THREADS + tid;
+    if (i < n_tile) {
+      const unsigned kk = buf[i];
+      dst[k] = gbase[(kk >> shift) & (RADIX - 1)] + (unsigned)i;
+      if (!LAST) keys_out[dst[k]] = kk;
+    }
+  }
+  __syncthreads();
+  // payload 1: CSR position
+#pragma unroll
+  for (int t = 0; t < RS_IPT; ++t) {
+    const i64 idx = wbase + t * 32 + lane;
+    if (idx < n) buf[lpos[t]] = FIRST ? (unsigned)idx : (unsigned)__ldg(pos_in + idx);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < RS_IPT; ++k) {
+    const int i = k * RS_THREADS + tid;
+    if (i < n_tile) pos_out[dst[k]] = (int)buf[i];
+  }
+  __syncthreads();
+  // payload 2: row id (FIRST: looked up between the rows of the warp's first and last entry)
   i64 r_lo = 0, r_hi = 0;
   if (FIRST && wbase < n) {
     const i64 last = (wbase + RS_WARP_ITEMS <= n ? wbase + RS_WARP_ITEMS : n) - 1;
@@ -195,11 +259,8 @@ k_radix_scatter(const unsigned* keys_in, const int* pos_in, const int* row_in, u
   for (int t = 0; t < RS_IPT; ++t) {
     const i64 idx = wbase + t * 32 + lane;
     if (idx >= n) continue;
-    const unsigned d = (key[t] >> shift) & (RADIX - 1);
-    const i64 dst = (i64)cnt[warp][d] + rank[t];
-    int pos, row;
+    int row;
     if (FIRST) {
-      pos = (int)idx;
       i64 lo = r_lo, hi = r_hi + 1;  // row_ptr[lo] <= idx < row_ptr[hi]
       while (hi - lo > 1) {
         const i64 mid = (lo + hi) >> 1;
@@ -207,12 +268,15 @@ k_radix_scatter(const unsigned* keys_in, const int* pos_in, const int* row_in, u
       }
       row = (int)lo;
     } else {
-      pos = __ldg(pos_in + idx);
       row = __ldg(row_in + idx);
     }
-    if (!LAST) keys_out[dst] = key[t];
-    pos_out[dst] = pos;
-    row_out[dst] = row;
+    buf[lpos[t]] = (unsigned)row;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < RS_IPT; ++k) {
+    const int i = k * RS_THREADS + tid;
+    if (i < n_tile) row_out[dst[k]] = (int)buf[i];
   }
 }
 
@@ -282,7 +346,7 @@ int dgnn_csr2csc_impl(i64 n_rows, i64 n_cols, i64 nnz, const void* row_ptr, int 
       unsigned* kout = last ? nullptr : reinterpret_cast<unsigned*>(wsb + L.keys[p & 1]);
       int* pout = last ? permute : reinterpret_cast<int*>(wsb + L.pos[p & 1]);
       int* rout = last ? row_ind : reinterpret_cast<int*>(wsb + L.row[p & 1]);
-      k_radix_hist<<<grid, RS_THREADS, 0, s>>>(kin, nnz, shift, tile_hist, L.ntiles);
+      k_radix_hist<<<grid, HIST_THREADS, 0, s>>>(kin, nnz, shift, tile_hist, L.ntiles);
       rc = exclusive_scan(tile_hist, (i64)RADIX * L.ntiles, scratch, s);
       if (rc) return rc;
 #define RS_ARGS kin, pin, rin, kout, pout, rout, nnz, shift, tile_hist, L.ntiles, row_ptr, idx_bits, n_rows
