@@ -227,6 +227,36 @@ def uniform_fill(shape, seed, offset, device):
     return out
 
 
+# ------------------------------------------------------- dense projection
+def project_supported(m, n, k) -> bool:
+    """Shapes the tensor-core projection handles (n % 128 == 0, k % 4 == 0, k <= 128)."""
+    return bool(lib().dgnn_project_supported(int(m), int(n), int(k)))
+
+
+def project_forward(x, w, check_status=False):
+    """out[M,N] = x[M,K] @ w[N,K]^T in fp32 accuracy on the tcgen05 tensor cores (3 x tf32 split).
+    check_status=True synchronises and raises if a wait inside the kernel ran out."""
+    x = _cuda_f32(x, "x")
+    w = _cuda_f32(w, "w")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise RuntimeError("dgnn_b200: project_forward expects x [M,K] and w [N,K]")
+    m, k = x.shape
+    n = w.shape[0]
+    dev = x.device
+    with device_guard(dev):
+        out = torch.empty((m, n), dtype=torch.float32, device=dev)
+        nbytes = lib().dgnn_project_workspace_bytes(n)
+        ws = _workspace(nbytes, dev)
+        check(lib().dgnn_project_forward(m, n, k, _p(x), _p(w), _p(out), _p(ws), nbytes, _stream(dev)), "project_forward")
+        if check_status:
+            import ctypes
+            st = ctypes.c_int(0)
+            check(lib().dgnn_project_status(_p(ws), _stream(dev), ctypes.byref(st)), "project_status")
+            if st.value != 0:
+                raise RuntimeError(f"dgnn_b200: project_forward gave up in wait {st.value}; the result is invalid")
+    return out
+
+
 # ------------------------------------------------------- SDDMM / transpose
 def mhsddmm(row_ptr, col_ind, a, b):
     """out[e,h] = <a[row_e,h,:], b[col_e,h,:]>, [E,H]."""

@@ -1,0 +1,65 @@
+"""Tensor-core node projection (dgnn_project_forward) against an fp64 matmul, through the C ABI."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(m, k, n, seed):
+    from dgnn_b200 import kernels
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(m, k, device=dev, generator=g) * 3.0
+    w = (torch.rand(n, k, device=dev, generator=g) - 0.5) * 0.7
+    out = kernels.project_forward(x, w, check_status=True)
+    ref = x.double() @ w.double().t()
+    bound = x.abs().double() @ w.abs().double().t()      # sum of |x||w| per output
+    err = (out.double() - ref).abs()
+    # 3 x tf32: ~2^-21 per product plus fp32 accumulation over k <= 128 terms
+    assert bool((err <= 4e-6 * bound + 1e-30).all()), float((err / (bound + 1e-30)).max())
+    return out
+
+
+@pytest.mark.parametrize("m", [1, 127, 128, 129, 1000, 40000])
+def test_project_rows(m):
+    _check(m, 100, 256, seed=m)
+
+
+@pytest.mark.parametrize("k", [4, 8, 32, 36, 64, 100, 128])
+def test_project_inner(k):
+    _check(777, k, 256, seed=k)
+
+
+@pytest.mark.parametrize("n", [128, 256, 512])
+def test_project_columns(n):
+    _check(3001, 100, n, seed=n)
+
+
+def test_project_matches_fp32_matmul_level():
+    """The split product is as close to the exact result as the fp32 library GEMM is."""
+    from dgnn_b200 import kernels
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(9)
+    x = torch.randn(20000, 100, device=dev, generator=g)
+    w = torch.randn(256, 100, device=dev, generator=g)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        lib32 = x @ w.t()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    ref = x.double() @ w.double().t()
+    out = kernels.project_forward(x, w, check_status=True)
+    e_mine = float((out.double() - ref).abs().max())
+    e_lib = float((lib32.double() - ref).abs().max())
+    assert e_mine <= 4.0 * e_lib + 1e-6, (e_mine, e_lib)
+
+
+def test_project_rejects_unsupported_shapes():
+    from dgnn_b200 import kernels
+    assert not kernels.project_supported(10, 100, 100)   # n not a multiple of 128
+    assert not kernels.project_supported(10, 256, 130)   # k too large
+    assert not kernels.project_supported(10, 256, 6)     # k not a multiple of 4
+    assert kernels.project_supported(10, 256, 100)
+    with pytest.raises(RuntimeError):
+        kernels.project_forward(torch.zeros(4, 6, device="cuda"), torch.zeros(256, 6, device="cuda"))
