@@ -158,6 +158,7 @@ class PhaseTimer:
                                     ("gat_backward_cols", "bwd_cols", 6),
                                     ("gat_forward_staged", "fwd", 3),
                                     ("gat_backward_cols_staged", "bwd_cols", 6),
+                                    ("project_forward", "project", 2),     # weight split, projection
                                     ("gat_logits_forward", "logits_fwd", 1),
                                     ("gat_logits_backward", "logits_bwd", 2)):
             inner = getattr(module, name)
@@ -240,6 +241,7 @@ def run_reference_arm(args, rank):
 
 def run_ours(args, rank, world, local):
     from dgnn_b200 import dist as gdist
+    from dgnn_b200.operators.projection import project
     from dgnn_b200 import kernels
 
     if not torch.cuda.is_available():
@@ -319,7 +321,7 @@ def run_ours(args, rank, world, local):
 
         def step(x_in):
             # the same layer on this rank's node block: projection, logits + sharded aggregation, bias
-            h = torch.matmul(x_in, W).view(-1, H, F)
+            h = project(x_in, W).view(-1, H, F)
             out = agg(h) + bias.view(-1, H, F)
             loss = torch.dot(out.reshape(-1), cot.view(-1))
             loss.backward()

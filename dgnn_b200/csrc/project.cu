@@ -6,13 +6,17 @@
 // three products are accumulated in fp32 in tensor memory:
 //     x*w ~= x_lo*w_hi + x_hi*w_lo + x_hi*w_hi          (the dropped lo*lo term is ~2^-22)
 // Layout of the work: a persistent CTA per SM owns one 128-column group of the output
-// and walks over 128-row tiles of x.  Its 128 rows of w (hi and lo) stay resident in
-// shared memory for the whole kernel; x tiles arrive by TMA (128-byte swizzle, zero
-// fill beyond M and K) into a 3-stage ring of 32-float k-blocks, four converter
-// warps split every k-block into hi and lo in place, one thread issues the MMAs into
-// one of two 128x128 fp32 accumulators in tensor memory, and four epilogue warps drain
-// the other accumulator to global memory meanwhile.  The two column groups of one row
-// tile run at the same time on neighbouring CTAs, so x is read from HBM once.
+// and walks over 128-row tiles of x.  Its 128 rows of w (hi and lo, split once by a
+// small kernel and fetched by TMA with the 128-byte swizzle) stay resident in shared
+// memory for the whole kernel.  Eight converter warps read x straight from global
+// memory into registers -- a whole tile per CTA is in flight, which is what hides the
+// latency of HBM -- and write hi and lo of every 32-float k-block into a 3-stage ring in
+// the same swizzled K-major layout.  One thread issues the MMAs into one of two 128x128
+// fp32 accumulators in tensor memory, and four epilogue warps drain the other
+// accumulator to global memory meanwhile (w is the M operand of the MMA, so an
+// accumulator lane is an output column and a warp's store covers one 128-byte line).
+// The two column groups of one row tile run at the same time on neighbouring CTAs, so
+// x comes from HBM once and from L2 the second time.
 //
 // Every wait on an mbarrier is bounded: when a wait runs out the CTA raises a flag,
 // all roles leave their loops, tensor memory is freed and a status word is written.
@@ -29,16 +33,18 @@ constexpr int PJ_BM = 128;            // rows of x per tile = accumulator lanes
 constexpr int PJ_BN = 128;            // output columns per CTA = accumulator columns
 constexpr int PJ_KB = 32;             // floats per k-block: one 128-byte swizzled row
 constexpr int PJ_MAX_KB = 4;          // K <= 128
-constexpr int PJ_STAGES = 3;
+constexpr int PJ_STAGES = 2;
+constexpr int PJ_OUT_ROWS = 32;       // rows of the tile per TMA store
+constexpr int PJ_OUT_BYTES = PJ_OUT_ROWS * PJ_BN * 4;  // 16 KB staging buffer, two of them
 constexpr int PJ_TILE_BYTES = PJ_BM * PJ_KB * 4;  // 16 KB: one k-block of 128 rows
-constexpr int PJ_EPI_WARPS = 4, PJ_CONV_WARPS = 4;
+constexpr int PJ_EPI_WARPS = 4, PJ_CONV_WARPS = 8;
 constexpr int PJ_WARP_TMA = 4, PJ_WARP_MMA = 5, PJ_WARP_CONV0 = 6;
-constexpr int PJ_THREADS = (PJ_WARP_CONV0 + PJ_CONV_WARPS) * 32;  // 320
+constexpr int PJ_THREADS = (PJ_WARP_CONV0 + PJ_CONV_WARPS) * 32;  // 448
 constexpr int PJ_TMEM_COLS = 2 * PJ_BN;
-constexpr size_t PJ_SMEM = (size_t)(2 * PJ_MAX_KB + 2 * PJ_STAGES) * PJ_TILE_BYTES + 1024;  // + alignment slack
+constexpr size_t PJ_SMEM = (size_t)(2 * PJ_MAX_KB + 2 * PJ_STAGES) * PJ_TILE_BYTES + 2 * PJ_OUT_BYTES + 1024;  // + alignment slack
 constexpr i64 PJ_TIMEOUT = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
-// tcgen05 instruction descriptor: fp32 accumulate, tf32 A and B, both K-major, M = 128, N = 128
+// tcgen05 instruction descriptor: fp32 accumulate, tf32 A and B, both K-major, M = 128 (columns of out), N = 128 (rows of x)
 constexpr uint32_t PJ_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(PJ_BN >> 3) << 17) | ((uint32_t)(PJ_BM >> 4) << 24);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -63,18 +69,43 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok;
 }
-// bounded wait: false when the CTA is giving up (this wait ran out, or another one did)
+#ifdef PJ_PROFILE
+__device__ long long pj_dbg[64];
+#define PJ_STAMP(cond, slot) if (blockIdx.x == 0 && (cond) && (threadIdx.x & 31) == 0) pj_dbg[slot] = clock64()
+#define PJ_T0() const long long pj_t0 = clock64(); long long pj_w = 0
+#define PJ_WAIT(expr) ([&]() { const long long a_ = clock64(); const bool r_ = (expr); pj_w += clock64() - a_; return r_; }())
+#define PJ_DONE(slot) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { pj_dbg[2 * (slot)] = pj_w; pj_dbg[2 * (slot) + 1] = clock64() - pj_t0; }
+#else
+#define PJ_STAMP(cond, slot)
+#define PJ_T0()
+#define PJ_WAIT(expr) (expr)
+#define PJ_DONE(slot)
+#endif
+// bounded wait: false when the CTA is giving up (this wait ran out, or another one did).  The common path
+// is nothing but try_wait (which parks the thread for a while by itself); the clock and the give-up flag
+// are looked at once per 64 failed tries, so waiting warps leave the issue slots and the memory pipe to
+// the warps that have work.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int who) {
-  if (mbar_try(bar, parity)) return true;
+#pragma unroll 1
+  for (int spin = 0; spin < 64; ++spin)
+    if (mbar_try(bar, parity)) return true;
   const i64 t0 = clock64();
   for (;;) {
-    if (mbar_try(bar, parity)) return true;
+#pragma unroll 1
+    for (int spin = 0; spin < 64; ++spin)
+      if (mbar_try(bar, parity)) return true;
     if (*give_up) return false;
     if (clock64() - t0 > PJ_TIMEOUT) {
       *give_up = who;
       return false;
     }
   }
+}
+// the same for a whole warp: lane 0 waits, the others learn the outcome from it
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* give_up, int who) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, give_up, who);
+  return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -83,6 +114,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(PJ_EPI_WARPS * 32) : "memory"); }
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
@@ -117,14 +154,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// w[N,K] -> split[2][N][128]: hi then lo, zero beyond K
-__global__ void k_split_w(const float* __restrict__ w, int n, int k, float* __restrict__ split) {
+// w -> split[2][N][128]: hi then lo, zero beyond K.  w is [N,K] (an nn.Linear weight) or, with w_kn, [K,N]
+__global__ void k_split_w(const float* __restrict__ w, int n, int k, int w_kn, float* __restrict__ split) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n * PJ_MAX_KB * PJ_KB) return;
   const int row = t / (PJ_MAX_KB * PJ_KB), col = t % (PJ_MAX_KB * PJ_KB);
   float hi = 0.f, lo = 0.f;
   if (col < k) {
-    const float v = __ldg(w + (size_t)row * k + col);
+    const float v = __ldg(w + (w_kn ? (size_t)col * n + row : (size_t)row * k + col));
     hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
     lo = v - hi;
   }
@@ -133,16 +170,17 @@ __global__ void k_split_w(const float* __restrict__ w, int n, int k, float* __re
 }
 
 struct PjBars {  // mbarriers of one CTA
-  unsigned long long full[PJ_STAGES], conv[PJ_STAGES], empty[PJ_STAGES], wfull, tfull[2], tempty[2];
+  unsigned long long conv[PJ_STAGES], empty[PJ_STAGES], wfull, tfull[2], tempty[2];
 };
 
 __global__ void __launch_bounds__(PJ_THREADS, 1)
-k_project(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, float* __restrict__ out,
+k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_out, const float* __restrict__ x,
           const i64 m, const int n, const int k, const i64 ntiles, const int groups, int* __restrict__ status) {
   extern __shared__ unsigned char pj_smem_raw[];
   __shared__ PjBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int give_up_s;
+  __shared__ int epi_ok_s;
   volatile int* give_up = &give_up_s;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -150,6 +188,8 @@ k_project(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUt
   const uint32_t w_hi = base, w_lo = base + PJ_MAX_KB * PJ_TILE_BYTES;
   const uint32_t ring = base + 2 * PJ_MAX_KB * PJ_TILE_BYTES;  // stage s: hi at ring + s*32 KB, lo 16 KB behind it
   unsigned char* ring_ptr = pj_smem_raw + (base - smem_u32(pj_smem_raw)) + 2 * PJ_MAX_KB * PJ_TILE_BYTES;
+  const uint32_t stage_out = ring + PJ_STAGES * 2 * PJ_TILE_BYTES;  // two [32 rows][128 columns] buffers for the stores
+  float* stage_out_ptr = reinterpret_cast<float*>(ring_ptr + PJ_STAGES * 2 * PJ_TILE_BYTES);
 
   const int nkb = (k + PJ_KB - 1) / PJ_KB;
   const int group = blockIdx.x % groups;
@@ -158,14 +198,17 @@ k_project(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUt
   if (tid == 0) {
     give_up_s = 0;
     for (int s = 0; s < PJ_STAGES; ++s) {
-      mbar_init(smem_u32(&bars.full[s]), 1);
-      mbar_init(smem_u32(&bars.conv[s]), PJ_CONV_WARPS * 32);
+      #ifdef PJ_CONV_BAR
+      mbar_init(smem_u32(&bars.conv[s]), 1);
+#else
+      mbar_init(smem_u32(&bars.conv[s]), PJ_CONV_WARPS);  // one arrival per warp: 256 arrivals on one word would serialise
+#endif
       mbar_init(smem_u32(&bars.empty[s]), 1);
     }
     mbar_init(smem_u32(&bars.wfull), 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars.tfull[a]), 1);
-      mbar_init(smem_u32(&bars.tempty[a]), PJ_EPI_WARPS * 32);
+      mbar_init(smem_u32(&bars.tempty[a]), PJ_EPI_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -179,110 +222,146 @@ k_project(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUt
   const uint32_t tmem = tmem_slot;
 
   if (warp == PJ_WARP_TMA) {
-    if (lane == 0) {
-      // the CTA's 128 rows of w, hi and lo, once
+    if (lane == 0) {  // the CTA's 128 rows of w, hi and lo, once
       mbar_expect_tx(smem_u32(&bars.wfull), (uint32_t)(2 * nkb * PJ_TILE_BYTES));
       for (int kb = 0; kb < nkb; ++kb) {
         tma_load_2d(w_hi + kb * PJ_TILE_BYTES, &map_w, kb * PJ_KB, group * PJ_BN, smem_u32(&bars.wfull));
         tma_load_2d(w_lo + kb * PJ_TILE_BYTES, &map_w, kb * PJ_KB, n + group * PJ_BN, smem_u32(&bars.wfull));
       }
-      uint32_t it = 0;
-      bool ok = true;
-      for (i64 tile = first; ok && tile < ntiles; tile += stride) {
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const uint32_t s = it % PJ_STAGES, ph = (it / PJ_STAGES) & 1u;
-          if (!(ok = mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 1))) break;
-          mbar_expect_tx(smem_u32(&bars.full[s]), PJ_TILE_BYTES);
-          tma_load_2d(ring + s * 2 * PJ_TILE_BYTES, &map_x, kb * PJ_KB, (int)(tile * PJ_BM), smem_u32(&bars.full[s]));
-        }
-      }
-      if (!ok) {  // giving up: let the copies in flight land before the CTA's shared memory goes away
-        const i64 t0 = clock64();
-        while (clock64() - t0 < 2000000) {}
-      }
     }
   } else if (warp == PJ_WARP_MMA) {
     if (lane == 0) {
+      PJ_T0();
       bool ok = mbar_wait(smem_u32(&bars.wfull), 0, give_up, 2);
       uint32_t it = 0, j = 0;
       for (i64 tile = first; ok && tile < ntiles; tile += stride, ++j) {
         const uint32_t a = j & 1u;
-        if (!(ok = mbar_wait(smem_u32(&bars.tempty[a]), ((j >> 1) & 1u) ^ 1u, give_up, 3))) break;
+        if (!(ok = PJ_WAIT(mbar_wait(smem_u32(&bars.tempty[a]), ((j >> 1) & 1u) ^ 1u, give_up, 3)))) break;
         tc_fence_after();
+        PJ_STAMP(j == 20, 10);
         const uint32_t d = tmem + a * PJ_BN;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t s = it % PJ_STAGES, ph = (it / PJ_STAGES) & 1u;
-          if (!(ok = mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4))) break;
+          if (!(ok = PJ_WAIT(mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4)))) break;
           tc_fence_after();
+          PJ_STAMP(j == 20, 11 + kb);
           const uint64_t a_hi = umma_desc(ring + s * 2 * PJ_TILE_BYTES), a_lo = umma_desc(ring + s * 2 * PJ_TILE_BYTES + PJ_TILE_BYTES);
           const uint64_t b_hi = umma_desc(w_hi + kb * PJ_TILE_BYTES), b_lo = umma_desc(w_lo + kb * PJ_TILE_BYTES);
           const int left = k - kb * PJ_KB;
           const int steps = left >= PJ_KB ? PJ_KB / 8 : (left + 7) / 8;  // MMAs of K = 8 floats (32 bytes) each
           for (int q = 0; q < steps; ++q) {
             const uint64_t adv = (uint64_t)(q * 2);  // 32 bytes further along the swizzled row, in 16-byte units
-            umma_tf32(d, a_lo + adv, b_hi + adv, (kb | q) != 0);
-            umma_tf32(d, a_hi + adv, b_lo + adv, 1u);
-            umma_tf32(d, a_hi + adv, b_hi + adv, 1u);
+            // w is the M operand and x the N operand: the accumulator holds the tile transposed
+            umma_tf32(d, b_hi + adv, a_lo + adv, (kb | q) != 0);
+            umma_tf32(d, b_lo + adv, a_hi + adv, 1u);
+            umma_tf32(d, b_hi + adv, a_hi + adv, 1u);
           }
           umma_commit(smem_u32(&bars.empty[s]));  // the stage may be refilled once these MMAs have read it
         }
         if (ok) umma_commit(smem_u32(&bars.tfull[a]));
+        PJ_STAMP(j == 20, 15);
       }
+      PJ_DONE(0);
     }
   } else if (warp >= PJ_WARP_CONV0) {
-    const int ct = tid - PJ_WARP_CONV0 * 32;  // 0..127
+    // Converter warps: x goes global -> registers -> (hi, lo) in the swizzled K-major layout the MMA reads.
+    // A thread owns 16-byte chunk `ch` of rows rw + 32*i of every k-block; the registers of k-block kb are
+    // refilled with the next tile's data as soon as they have been stored, so a whole tile is in flight.
+    const int ct = tid - PJ_WARP_CONV0 * 32;  // 0..255
+    const int ch = ct & 7, rw = ct >> 3;
+    const uint32_t soff = (uint32_t)rw * 128u + (uint32_t)((ch ^ (rw & 7)) << 4);  // rows rw+32i share rw & 7
+    float4 v[PJ_MAX_KB][4];
+    auto fetch = [&](i64 tile, int kb) {
+      const int col = kb * PJ_KB + ch * 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const i64 row = tile * PJ_BM + rw + 32 * i;
+        v[kb][i] = (tile < ntiles && row < m && col < k) ? __ldg(reinterpret_cast<const float4*>(x + row * k + col))
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    };
+#pragma unroll
+    for (int kb = 0; kb < PJ_MAX_KB; ++kb)
+      if (kb < nkb) fetch(first, kb);
     uint32_t it = 0;
     bool ok = true;
+    PJ_T0();
     for (i64 tile = first; ok && tile < ntiles; tile += stride) {
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
-        const uint32_t s = it % PJ_STAGES, ph = (it / PJ_STAGES) & 1u;
-        ok = mbar_wait(smem_u32(&bars.full[s]), ph, give_up, 5);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        float4* hi = reinterpret_cast<float4*>(ring_ptr + (size_t)s * 2 * PJ_TILE_BYTES);
-        float4* lo = hi + PJ_TILE_BYTES / 16;
 #pragma unroll
-        for (int u = 0; u < PJ_TILE_BYTES / 16 / (PJ_CONV_WARPS * 32); ++u) {
-          const int i = u * (PJ_CONV_WARPS * 32) + ct;
-          const float4 v = hi[i];
+      for (int kb = 0; kb < PJ_MAX_KB; ++kb) {
+        if (kb >= nkb) break;
+        const uint32_t s = it % PJ_STAGES, ph = (it / PJ_STAGES) & 1u;
+        ++it;
+        ok = PJ_WAIT(mbar_wait_warp(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5));
+        if (!ok) break;
+        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + kb + 1, 20 + kb);
+        unsigned char* hi = ring_ptr + (size_t)s * 2 * PJ_TILE_BYTES + soff;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 a = v[kb][i];
           float4 h, l;
-          h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
-          h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
-          h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
-          h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
-          hi[i] = h;
-          lo[i] = l;
+          h.x = __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u); l.x = a.x - h.x;
+          h.y = __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u); l.y = a.y - h.y;
+          h.z = __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u); l.z = a.z - h.z;
+          h.w = __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u); l.w = a.w - h.w;
+          *reinterpret_cast<float4*>(hi + i * 32 * 128) = h;
+          *reinterpret_cast<float4*>(hi + i * 32 * 128 + PJ_TILE_BYTES) = l;
         }
+        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 40);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
-        mbar_arrive(smem_u32(&bars.conv[s]));
+        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 41);
+#ifdef PJ_CONV_BAR
+        asm volatile("bar.sync 2, %0;" ::"n"(PJ_CONV_WARPS * 32) : "memory");
+        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 43);
+        if (ct == 0) mbar_arrive(smem_u32(&bars.conv[s]));
+#else
+        __syncwarp();
+        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 43);
+        if (lane == 0) mbar_arrive(smem_u32(&bars.conv[s]));
+#endif
+        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + kb + 1, 24 + kb);
+        fetch(tile + stride, kb);
+        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 42);
       }
     }
-  } else {  // epilogue warps 0..3: warp w reads accumulator lanes 32w .. 32w+31
-    uint32_t j = 0;
-    bool ok = true;
-    const int col0 = group * PJ_BN;
-    for (i64 tile = first; ok && tile < ntiles; tile += stride, ++j) {
+    if (warp == PJ_WARP_CONV0) { PJ_DONE(1); }
+  } else {
+    // Epilogue warps 0..3: accumulator lane = output column, accumulator column = row of the tile.  32 rows
+    // at a time go registers -> shared memory ([row][column], a warp writes 32 neighbouring floats) -> one
+    // TMA store of 32 x 128 floats, which also clips the rows beyond m.  Thread 0 does the waiting.
+    uint32_t j = 0, nstore = 0;
+    const int cw = warp * 32 + lane;  // warp w reads lanes 32w .. 32w+31
+    PJ_T0();
+    for (i64 tile = first; tile < ntiles; tile += stride, ++j) {
       const uint32_t a = j & 1u;
-      ok = mbar_wait(smem_u32(&bars.tfull[a]), (j >> 1) & 1u, give_up, 6);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (tid == 0) epi_ok_s = PJ_WAIT(mbar_wait(smem_u32(&bars.tfull[a]), (j >> 1) & 1u, give_up, 6)) ? 1 : 0;
+      epi_sync();
+      if (!epi_ok_s) break;
       tc_fence_after();
-      const i64 row = tile * PJ_BM + warp * 32 + lane;
-      float* dst = out + row * n + col0;
+      PJ_STAMP(warp == 0 && j == 20, 30);
 #pragma unroll 1
-      for (int c = 0; c < PJ_BN; c += 32) {
+      for (int c = 0; c < PJ_BM; c += PJ_OUT_ROWS, ++nstore) {
         uint32_t r[32];
         tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + a * PJ_BN + c, r);
-        if (row < m) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            *reinterpret_cast<float4*>(dst + c + 4 * q) = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        if (c + PJ_OUT_ROWS == PJ_BM) {  // the accumulator is in registers: hand it back to the MMA thread
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars.tempty[a]));
         }
+        const uint32_t b = nstore & 1u;
+        if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store that used buffer b has read it
+        epi_sync();
+        float* st = stage_out_ptr + b * (PJ_OUT_BYTES / 4) + cw;
+#pragma unroll
+        for (int q = 0; q < 32; ++q) st[q * PJ_BN] = __uint_as_float(r[q]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epi_sync();
+        if (tid == 0) tma_store_2d(&map_out, group * PJ_BN, (int)(tile * PJ_BM + c), stage_out + b * PJ_OUT_BYTES);
+        PJ_STAMP(warp == 0 && j == 20, 31 + c / PJ_OUT_ROWS);
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bars.tempty[a]));
     }
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (warp == 0) { PJ_DONE(2); }
   }
 
   tc_fence_before();
@@ -310,17 +389,17 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-// [rows, cols] fp32 row-major matrix, boxes of 128 rows x 32 floats, 128-byte swizzle, zero fill outside
-int make_map(CUtensorMap* map, const float* ptr, i64 rows, i64 cols, i64 pitch_floats) {
+// tensor map of a [rows, cols] fp32 row-major matrix with boxes of box_rows x box_cols, zero fill outside
+int make_map(CUtensorMap* map, const float* ptr, i64 rows, i64 cols, int box_rows, int box_cols, bool swizzle128) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return (int)cudaErrorNotSupported;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)pitch_floats * 4};
-  const cuuint32_t box[2] = {PJ_KB, PJ_BM};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, elem,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? DGNN_OK : (int)cudaErrorInvalidValue;
 }
 
@@ -338,13 +417,13 @@ int dgnn_project_supported(int64_t m, int n, int k) {
   return m > 0 && n > 0 && n % PJ_BN == 0 && k > 0 && k % 4 == 0 && k <= PJ_MAX_KB * PJ_KB && m < (int64_t(1) << 31) - PJ_BM;
 }
 
-int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w, float* out, void* workspace,
+int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w, int w_kn, float* out, void* workspace,
                          size_t workspace_bytes, void* stream) {
   if (m < 0 || n <= 0 || k <= 0) return DGNN_ERR_SHAPE;
   if (m == 0) return DGNN_OK;
   if (!dgnn_project_supported(m, n, k)) return DGNN_ERR_SHAPE;
   if (!x || !w || !out) return DGNN_ERR_NULL;
-  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)workspace) & 15) return DGNN_ERR_ALIGN;
+  if (((uintptr_t)x | (uintptr_t)out | (uintptr_t)workspace) & 15) return DGNN_ERR_ALIGN;
   if (!workspace || workspace_bytes < dgnn_project_workspace_bytes(n)) return DGNN_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int* status = static_cast<int*>(workspace);
@@ -352,16 +431,16 @@ int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w
 
   cudaError_t e = cudaFuncSetAttribute(k_project, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PJ_SMEM);  // per device
   if (e != cudaSuccess) return (int)e;
-  CUtensorMap map_x, map_w;
-  int rc = make_map(&map_x, x, m, k, k);
+  CUtensorMap map_w, map_out;
+  int rc = make_map(&map_w, split, (i64)2 * n, PJ_MAX_KB * PJ_KB, PJ_BM, PJ_KB, true);
   if (rc) return rc;
-  rc = make_map(&map_w, split, (i64)2 * n, PJ_MAX_KB * PJ_KB, PJ_MAX_KB * PJ_KB);
+  rc = make_map(&map_out, out, m, n, PJ_OUT_ROWS, PJ_BN, false);
   if (rc) return rc;
 
   e = cudaMemsetAsync(status, 0, sizeof(int), s);
   if (e != cudaSuccess) return (int)e;
   const int items = n * PJ_MAX_KB * PJ_KB;
-  k_split_w<<<(items + 255) / 256, 256, 0, s>>>(w, n, k, split);
+  k_split_w<<<(items + 255) / 256, 256, 0, s>>>(w, n, k, w_kn, split);
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -371,7 +450,7 @@ int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w
   i64 per_group = sms / groups > 0 ? sms / groups : 1;
   if (per_group > ntiles) per_group = ntiles;
   const unsigned grid = (unsigned)(per_group * groups);
-  k_project<<<grid, PJ_THREADS, PJ_SMEM, s>>>(map_x, map_w, out, m, n, k, ntiles, groups, status);
+  k_project<<<grid, PJ_THREADS, PJ_SMEM, s>>>(map_w, map_out, x, m, n, k, ntiles, groups, status);
   e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
@@ -386,5 +465,11 @@ int dgnn_project_status(const void* workspace, void* stream, int* status_out) {
   e = cudaStreamSynchronize(s);
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
+
+#ifdef PJ_PROFILE
+int dgnn_project_profile(long long* out64) {
+  return (int)cudaMemcpyFromSymbol(out64, pj_dbg, sizeof(long long) * 64);
+}
+#endif
 
 }  // extern "C"

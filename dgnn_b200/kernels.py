@@ -233,21 +233,23 @@ def project_supported(m, n, k) -> bool:
     return bool(lib().dgnn_project_supported(int(m), int(n), int(k)))
 
 
-def project_forward(x, w, check_status=False):
-    """out[M,N] = x[M,K] @ w[N,K]^T in fp32 accuracy on the tcgen05 tensor cores (3 x tf32 split).
-    check_status=True synchronises and raises if a wait inside the kernel ran out."""
+def project_forward(x, w, w_kn=False, check_status=False):
+    """out[M,N] = x[M,K] @ W in fp32 accuracy on the tcgen05 tensor cores (3 x tf32 split); w is an
+    nn.Linear weight [N,K], or [K,N] with w_kn=True.  check_status=True synchronises and raises if a
+    wait inside the kernel ran out."""
     x = _cuda_f32(x, "x")
     w = _cuda_f32(w, "w")
-    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
-        raise RuntimeError("dgnn_b200: project_forward expects x [M,K] and w [N,K]")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[0 if w_kn else 1]:
+        raise RuntimeError("dgnn_b200: project_forward expects x [M,K] and w [N,K] (or [K,N] with w_kn)")
     m, k = x.shape
-    n = w.shape[0]
+    n = w.shape[1 if w_kn else 0]
     dev = x.device
     with device_guard(dev):
         out = torch.empty((m, n), dtype=torch.float32, device=dev)
         nbytes = lib().dgnn_project_workspace_bytes(n)
         ws = _workspace(nbytes, dev)
-        check(lib().dgnn_project_forward(m, n, k, _p(x), _p(w), _p(out), _p(ws), nbytes, _stream(dev)), "project_forward")
+        check(lib().dgnn_project_forward(m, n, k, _p(x), _p(w), int(bool(w_kn)), _p(out), _p(ws), nbytes, _stream(dev)),
+              "project_forward")
         if check_status:
             import ctypes
             st = ctypes.c_int(0)

@@ -1,5 +1,5 @@
-"""GATConv layer: dense projection and attention logits in torch, the sparse
-softmax-aggregation through the fused operator.  Constructor arguments,
+"""GATConv layer: dense projection on the tensor cores (operators/projection.py), attention
+logits and the sparse softmax-aggregation through the fused operators.  Constructor arguments,
 parameter names (W, attn_l, attn_r, bias, res_fc), initialisation and forward
 signature follow dgNN/layers/gatconv_layer.py:7-92 of the reference, so
 state_dicts interchange."""
@@ -10,6 +10,7 @@ from torch import nn
 
 from .. import kernels
 from ..operators.fused_gatconv import GATConvFuse, GATConvFuse_inference, GATLayerFuse
+from ..operators.projection import project
 
 
 class GATConv(nn.Module):
@@ -48,7 +49,7 @@ class GATConv(nn.Module):
 
     def forward(self, row_ptr, col_ind, col_ptr, row_ind, permute, feat):
         heads, width = self.num_heads, self.out_feats
-        h = self.feat_drop(torch.matmul(feat, self.W).view(-1, heads, width))
+        h = self.feat_drop(project(feat, self.W).view(-1, heads, width))
         # destination (row) logits use attn_l, source (column) logits use attn_r
         fused_logits = h.is_cuda and kernels.logits_supported(heads, width)
         if self.training and fused_logits:

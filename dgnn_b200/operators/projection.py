@@ -1,0 +1,33 @@
+"""Dense node projection h = feat @ W in front of the fused GAT operator
+(`torch.matmul(feat, self.W)`, dgNN/layers/gatconv_layer.py:71 of the reference).
+
+The forward runs on the tcgen05 tensor cores (dgnn_project_forward: operands split
+into two tf32 parts, three products, fp32 accumulation -- fp32 accuracy) for the
+shapes that kernel handles; other shapes, and the two backward products, are plain
+library GEMMs through torch."""
+import torch
+
+from .. import kernels
+
+
+class ProjectFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, feat, weight):
+        ctx.save_for_backward(feat, weight)
+        return kernels.project_forward(feat, weight, w_kn=True)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        feat, weight = ctx.saved_tensors
+        grad_feat = grad_out @ weight.t() if ctx.needs_input_grad[0] else None
+        grad_weight = feat.t() @ grad_out if ctx.needs_input_grad[1] else None
+        return grad_feat, grad_weight
+
+
+def project(feat, weight):
+    """feat [M,K] @ weight [K,N] -> [M,N]."""
+    if (feat.is_cuda and feat.dtype == torch.float32 and weight.dtype == torch.float32 and feat.dim() == 2
+            and feat.is_contiguous() and weight.is_contiguous()
+            and kernels.project_supported(feat.shape[0], weight.shape[1], feat.shape[1])):
+        return ProjectFunction.apply(feat, weight)
+    return torch.matmul(feat, weight)

@@ -170,16 +170,17 @@ int dgnn_gat_logits_backward(int64_t n, int h, int f, const float* feat,
                              float* grad_feat, float* grad_l, float* grad_r,
                              void* workspace, size_t workspace_bytes, void* stream);
 
-/* Dense node projection in front of the operator: out[m,n] = x[m,k] * w[n,k]^T, fp32 in and out
- * (the bias-free nn.Linear `self.fc`, dgNN/layers/gatconv_layer.py:41,72).  Runs on the tcgen05
- * tensor cores with every operand split into two tf32 parts and three products accumulated in
- * fp32 (relative error ~2^-21, the level of an fp32 FMA chain).  Supported: n a multiple of 128,
- * k a multiple of 4 and at most 128, m below 2^31 (dgnn_project_supported; DGNN_ERR_SHAPE
- * otherwise, the caller then uses a library GEMM).  x, w, out 16-byte aligned and dense.
- * Every wait inside the kernel is bounded; dgnn_project_status returns 0 unless one ran out. */
+/* Dense node projection in front of the operator: out[m,n] = x[m,k] * W, fp32 in and out, W given
+ * as [k,n] (w_kn = 1: `torch.matmul(feat, self.W)`, dgNN/layers/gatconv_layer.py:71) or as an
+ * nn.Linear weight [n,k] (w_kn = 0).  Runs on the tcgen05 tensor cores with every operand split into
+ * two tf32 parts and three products accumulated in fp32 (relative error ~2^-21, the level of an fp32
+ * FMA chain).  Supported: n a multiple of 128, k a multiple of 4 and at most 128, m below 2^31
+ * (dgnn_project_supported; DGNN_ERR_SHAPE otherwise, the caller then uses a library GEMM).  x and out
+ * dense and 16-byte aligned.  Every wait inside the kernel is bounded; dgnn_project_status returns 0
+ * unless one ran out. */
 int dgnn_project_supported(int64_t m, int n, int k);
 size_t dgnn_project_workspace_bytes(int n);
-int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w, float* out,
+int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w, int w_kn, float* out,
                          void* workspace, size_t workspace_bytes, void* stream);
 int dgnn_project_status(const void* workspace, void* stream, int* status_out);
 

@@ -63,3 +63,16 @@ def test_project_rejects_unsupported_shapes():
     assert kernels.project_supported(10, 256, 100)
     with pytest.raises(RuntimeError):
         kernels.project_forward(torch.zeros(4, 6, device="cuda"), torch.zeros(256, 6, device="cuda"))
+
+
+def test_project_weight_as_k_by_n():
+    """W stored [K,N] as the GAT layer keeps it."""
+    from dgnn_b200 import kernels
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(21)
+    x = torch.randn(5000, 100, device=dev, generator=g)
+    w = torch.randn(100, 256, device=dev, generator=g)
+    out = kernels.project_forward(x, w, w_kn=True, check_status=True)
+    ref = x.double() @ w.double()
+    bound = x.abs().double() @ w.abs().double()
+    assert bool(((out.double() - ref).abs() <= 4e-6 * bound).all())
