@@ -159,6 +159,7 @@ class PhaseTimer:
                                     ("gat_forward_staged", "fwd", 3),
                                     ("gat_backward_cols_staged", "bwd_cols", 6),
                                     ("project_forward", "project", 2),     # weight split, projection
+                                    ("project_wgrad", "project_wgrad", 2),  # partial products, fixed-order sum
                                     ("gat_logits_forward", "logits_fwd", 1),
                                     ("gat_logits_backward", "logits_bwd", 2)):
             inner = getattr(module, name)

@@ -53,6 +53,8 @@ SIGNATURES = {
     "dgnn_project_supported": (c_int, [c_i64, c_int, c_int]),
     "dgnn_project_workspace_bytes": (c_sz, [c_int]),
     "dgnn_project_forward": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_sz, c_p]),
+    "dgnn_project_wgrad_workspace_bytes": (c_sz, [c_int]),
+    "dgnn_project_wgrad": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_int, c_p, c_sz, c_p]),
     "dgnn_project_status": (c_int, [c_p, c_p, c_p]),
     "dgnn_uniform_fill": (c_int, [c_u64, c_u64, c_i64, c_p, c_p]),
     "dgnn_mhsddmm_workspace_bytes": (c_sz, []),

@@ -69,18 +69,6 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok;
 }
-#ifdef PJ_PROFILE
-__device__ long long pj_dbg[64];
-#define PJ_STAMP(cond, slot) if (blockIdx.x == 0 && (cond) && (threadIdx.x & 31) == 0) pj_dbg[slot] = clock64()
-#define PJ_T0() const long long pj_t0 = clock64(); long long pj_w = 0
-#define PJ_WAIT(expr) ([&]() { const long long a_ = clock64(); const bool r_ = (expr); pj_w += clock64() - a_; return r_; }())
-#define PJ_DONE(slot) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { pj_dbg[2 * (slot)] = pj_w; pj_dbg[2 * (slot) + 1] = clock64() - pj_t0; }
-#else
-#define PJ_STAMP(cond, slot)
-#define PJ_T0()
-#define PJ_WAIT(expr) (expr)
-#define PJ_DONE(slot)
-#endif
 // bounded wait: false when the CTA is giving up (this wait ran out, or another one did).  The common path
 // is nothing but try_wait (which parks the thread for a while by itself); the clock and the give-up flag
 // are looked at once per 64 failed tries, so waiting warps leave the issue slots and the memory pipe to
@@ -101,13 +89,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
-// the same for a whole warp: lane 0 waits, the others learn the outcome from it
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* give_up, int who) {
-  bool ok = true;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, give_up, who);
-  return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -119,6 +100,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+__device__ __forceinline__ void conv_sync() { asm volatile("bar.sync 2, %0;" ::"n"(PJ_CONV_WARPS * 32) : "memory"); }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(PJ_EPI_WARPS * 32) : "memory"); }
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart
@@ -180,7 +162,7 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   __shared__ PjBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int give_up_s;
-  __shared__ int epi_ok_s;
+  __shared__ int epi_ok_s, conv_ok_s;
   volatile int* give_up = &give_up_s;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -198,17 +180,13 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   if (tid == 0) {
     give_up_s = 0;
     for (int s = 0; s < PJ_STAGES; ++s) {
-      #ifdef PJ_CONV_BAR
-      mbar_init(smem_u32(&bars.conv[s]), 1);
-#else
-      mbar_init(smem_u32(&bars.conv[s]), PJ_CONV_WARPS);  // one arrival per warp: 256 arrivals on one word would serialise
-#endif
+            mbar_init(smem_u32(&bars.conv[s]), 1);
       mbar_init(smem_u32(&bars.empty[s]), 1);
     }
     mbar_init(smem_u32(&bars.wfull), 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars.tfull[a]), 1);
-      mbar_init(smem_u32(&bars.tempty[a]), PJ_EPI_WARPS);
+      mbar_init(smem_u32(&bars.tempty[a]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -231,20 +209,17 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     }
   } else if (warp == PJ_WARP_MMA) {
     if (lane == 0) {
-      PJ_T0();
       bool ok = mbar_wait(smem_u32(&bars.wfull), 0, give_up, 2);
       uint32_t it = 0, j = 0;
       for (i64 tile = first; ok && tile < ntiles; tile += stride, ++j) {
         const uint32_t a = j & 1u;
-        if (!(ok = PJ_WAIT(mbar_wait(smem_u32(&bars.tempty[a]), ((j >> 1) & 1u) ^ 1u, give_up, 3)))) break;
+        if (!(ok = mbar_wait(smem_u32(&bars.tempty[a]), ((j >> 1) & 1u) ^ 1u, give_up, 3))) break;
         tc_fence_after();
-        PJ_STAMP(j == 20, 10);
         const uint32_t d = tmem + a * PJ_BN;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t s = it % PJ_STAGES, ph = (it / PJ_STAGES) & 1u;
-          if (!(ok = PJ_WAIT(mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4)))) break;
+          if (!(ok = mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4))) break;
           tc_fence_after();
-          PJ_STAMP(j == 20, 11 + kb);
           const uint64_t a_hi = umma_desc(ring + s * 2 * PJ_TILE_BYTES), a_lo = umma_desc(ring + s * 2 * PJ_TILE_BYTES + PJ_TILE_BYTES);
           const uint64_t b_hi = umma_desc(w_hi + kb * PJ_TILE_BYTES), b_lo = umma_desc(w_lo + kb * PJ_TILE_BYTES);
           const int left = k - kb * PJ_KB;
@@ -259,9 +234,7 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           umma_commit(smem_u32(&bars.empty[s]));  // the stage may be refilled once these MMAs have read it
         }
         if (ok) umma_commit(smem_u32(&bars.tfull[a]));
-        PJ_STAMP(j == 20, 15);
       }
-      PJ_DONE(0);
     }
   } else if (warp >= PJ_WARP_CONV0) {
     // Converter warps: x goes global -> registers -> (hi, lo) in the swizzled K-major layout the MMA reads.
@@ -285,16 +258,17 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       if (kb < nkb) fetch(first, kb);
     uint32_t it = 0;
     bool ok = true;
-    PJ_T0();
     for (i64 tile = first; ok && tile < ntiles; tile += stride) {
 #pragma unroll
       for (int kb = 0; kb < PJ_MAX_KB; ++kb) {
         if (kb >= nkb) break;
         const uint32_t s = it % PJ_STAGES, ph = (it / PJ_STAGES) & 1u;
         ++it;
-        ok = PJ_WAIT(mbar_wait_warp(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5));
-        if (!ok) break;
-        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + kb + 1, 20 + kb);
+        // one thread waits for the stage, the hardware barrier tells the others (and keeps the eight warps
+        // on the same number of barriers whatever the outcome)
+        if (ct == 0) conv_ok_s = mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5) ? 1 : 0;
+        conv_sync();
+        if (!(ok = conv_ok_s != 0)) break;
         unsigned char* hi = ring_ptr + (size_t)s * 2 * PJ_TILE_BYTES + soff;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -307,61 +281,45 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           *reinterpret_cast<float4*>(hi + i * 32 * 128) = h;
           *reinterpret_cast<float4*>(hi + i * 32 * 128 + PJ_TILE_BYTES) = l;
         }
-        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 40);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
-        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 41);
-#ifdef PJ_CONV_BAR
-        asm volatile("bar.sync 2, %0;" ::"n"(PJ_CONV_WARPS * 32) : "memory");
-        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 43);
+        // the eight warps meet at the hardware barrier and one thread arrives: 256 arrivals on one mbarrier
+        // word serialise, and a per-warp arrival behind __syncwarp measured several times slower than this
+        conv_sync();
         if (ct == 0) mbar_arrive(smem_u32(&bars.conv[s]));
-#else
-        __syncwarp();
-        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 43);
-        if (lane == 0) mbar_arrive(smem_u32(&bars.conv[s]));
-#endif
-        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + kb + 1, 24 + kb);
         fetch(tile + stride, kb);
-        PJ_STAMP(warp == PJ_WARP_CONV0 && it == 20 * (uint32_t)nkb + 2 && kb == 1, 42);
       }
     }
-    if (warp == PJ_WARP_CONV0) { PJ_DONE(1); }
   } else {
     // Epilogue warps 0..3: accumulator lane = output column, accumulator column = row of the tile.  32 rows
     // at a time go registers -> shared memory ([row][column], a warp writes 32 neighbouring floats) -> one
     // TMA store of 32 x 128 floats, which also clips the rows beyond m.  Thread 0 does the waiting.
     uint32_t j = 0, nstore = 0;
     const int cw = warp * 32 + lane;  // warp w reads lanes 32w .. 32w+31
-    PJ_T0();
     for (i64 tile = first; tile < ntiles; tile += stride, ++j) {
       const uint32_t a = j & 1u;
-      if (tid == 0) epi_ok_s = PJ_WAIT(mbar_wait(smem_u32(&bars.tfull[a]), (j >> 1) & 1u, give_up, 6)) ? 1 : 0;
+      if (tid == 0) epi_ok_s = mbar_wait(smem_u32(&bars.tfull[a]), (j >> 1) & 1u, give_up, 6) ? 1 : 0;
       epi_sync();
       if (!epi_ok_s) break;
       tc_fence_after();
-      PJ_STAMP(warp == 0 && j == 20, 30);
 #pragma unroll 1
       for (int c = 0; c < PJ_BM; c += PJ_OUT_ROWS, ++nstore) {
         uint32_t r[32];
         tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + a * PJ_BN + c, r);
-        if (c + PJ_OUT_ROWS == PJ_BM) {  // the accumulator is in registers: hand it back to the MMA thread
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bars.tempty[a]));
-        }
+        const bool last = c + PJ_OUT_ROWS == PJ_BM;
+        if (last) tc_fence_before();
         const uint32_t b = nstore & 1u;
         if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store that used buffer b has read it
         epi_sync();
+        if (last && tid == 0) mbar_arrive(smem_u32(&bars.tempty[a]));  // the accumulator is in registers: back to the MMA thread
         float* st = stage_out_ptr + b * (PJ_OUT_BYTES / 4) + cw;
 #pragma unroll
         for (int q = 0; q < 32; ++q) st[q * PJ_BN] = __uint_as_float(r[q]);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         epi_sync();
         if (tid == 0) tma_store_2d(&map_out, group * PJ_BN, (int)(tile * PJ_BM + c), stage_out + b * PJ_OUT_BYTES);
-        PJ_STAMP(warp == 0 && j == 20, 31 + c / PJ_OUT_ROWS);
       }
     }
     if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    if (warp == 0) { PJ_DONE(2); }
   }
 
   tc_fence_before();
@@ -371,6 +329,187 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PJ_TMEM_COLS) : "memory");
   }
   if (tid == 0 && give_up_s != 0) atomicMax(status, give_up_s);
+}
+
+// ---------------------------------------------------------------------------
+// Weight gradient of the projection: grad_w[k,n] = sum_m x[m,k] * g[m,n], the same three-product tf32
+// split.  The reduction runs over the rows m, which is the slow index of both x and g, so both are
+// "MN-major" operands: a stage holds 32 rows of m as rows of 128 bytes (32 consecutive n, or k) per
+// 32-wide chunk, exactly as they lie in global memory, and one MMA of K = 8 consumes eight rows of every
+// chunk (start address + 1024 bytes per K step).  A CTA owns one 128-column group of g and every (gridDim/groups)-th block of 32 rows,
+// accumulates D[n_local, k] in tensor memory over all its rows and writes one partial; a second small
+// kernel adds the partials in a fixed order.  No resident operand, so the ring has three 64 KB stages.
+// ---------------------------------------------------------------------------
+constexpr int WG_ROWS = 32;                              // rows of m per stage
+constexpr int WG_CHUNK_BYTES = WG_ROWS * 128;            // one 32-wide chunk of a stage: 4 KB
+constexpr int WG_PART_BYTES = 4 * WG_CHUNK_BYTES;        // 128 columns of one operand part: 16 KB
+constexpr int WG_STAGE_BYTES = 4 * WG_PART_BYTES;        // g_hi, g_lo, x_hi, x_lo
+constexpr int WG_STAGES = 3;
+constexpr size_t WG_SMEM = (size_t)WG_STAGES * WG_STAGE_BYTES + 1024;
+// instruction descriptor: fp32 accumulate, tf32 operands, both MN-major, M = 128 (n), N = 128 (k)
+constexpr uint32_t WG_IDESC = PJ_IDESC | (1u << 15) | (1u << 16);
+
+// MN-major tf32 operands have one shared-memory layout: rows of 128 bytes (32 consecutive n or k of one m),
+// atoms of 4 rows, the 32-byte piece index of a row XORed with the row's index inside its atom ("128-byte
+// swizzle with a 32-byte base", layout type 1).  Leading offset = distance between 32-wide chunks, stride
+// offset = distance between 4-row atoms.
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(WG_CHUNK_BYTES >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)1 << 61);
+}
+__device__ __forceinline__ void umma_tf32_mn(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(WG_IDESC), "r"(accumulate)
+      : "memory");
+}
+
+struct WgBars {
+  unsigned long long conv[WG_STAGES], empty[WG_STAGES], done;
+};
+
+__global__ void __launch_bounds__(PJ_THREADS, 1)
+k_project_wgrad(const float* __restrict__ x, const float* __restrict__ g, float* __restrict__ partial, const i64 m,
+                const int n, const int k, const i64 nsteps, const int groups, int* __restrict__ status) {
+  extern __shared__ unsigned char pj_smem_raw[];
+  __shared__ WgBars bars;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int give_up_s;
+  __shared__ int conv_ok_s;
+  volatile int* give_up = &give_up_s;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t ring = (smem_u32(pj_smem_raw) + 1023u) & ~1023u;
+  unsigned char* ring_ptr = pj_smem_raw + (ring - smem_u32(pj_smem_raw));
+  const int group = blockIdx.x % groups;
+  const i64 first = blockIdx.x / groups, stride = gridDim.x / groups;
+
+  if (tid == 0) {
+    give_up_s = 0;
+    for (int s = 0; s < WG_STAGES; ++s) {
+      mbar_init(smem_u32(&bars.conv[s]), 1);
+      mbar_init(smem_u32(&bars.empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bars.done), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == PJ_WARP_MMA) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(PJ_BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == PJ_WARP_MMA) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (i64 t = first; ok && t < nsteps; t += stride, ++it) {
+        const uint32_t s = it % WG_STAGES, ph = (it / WG_STAGES) & 1u;
+        if (!(ok = mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4))) break;
+        tc_fence_after();
+        const uint32_t st = ring + s * WG_STAGE_BYTES;
+#pragma unroll
+        for (int q = 0; q < WG_ROWS / 8; ++q) {  // eight rows (1024 bytes) of every chunk per MMA
+          const uint64_t g_hi = umma_desc_mn(st + q * 1024), g_lo = umma_desc_mn(st + WG_PART_BYTES + q * 1024);
+          const uint64_t x_hi = umma_desc_mn(st + 2 * WG_PART_BYTES + q * 1024), x_lo = umma_desc_mn(st + 3 * WG_PART_BYTES + q * 1024);
+          umma_tf32_mn(tmem, g_lo, x_hi, (it | (uint32_t)q) != 0);
+          umma_tf32_mn(tmem, g_hi, x_lo, 1u);
+          umma_tf32_mn(tmem, g_hi, x_hi, 1u);
+        }
+        umma_commit(smem_u32(&bars.empty[s]));
+      }
+      if (ok) umma_commit(smem_u32(&bars.done));
+    }
+  } else if (warp >= PJ_WARP_CONV0) {
+    // thread -> 16-byte piece p of row r of every chunk; the same piece of the next step is requested as
+    // soon as this one has been stored, so a whole step (28 KB) per CTA is in flight
+    const int ct = tid - PJ_WARP_CONV0 * 32;
+    const int p = ct & 7, r = ct >> 3;
+    const uint32_t soff = (uint32_t)r * 128u + (uint32_t)((((p >> 1) ^ (r & 3)) << 5) | ((p & 1) << 4));
+    float4 vg[4], vx[4];
+    auto fetch = [&](i64 t) {
+      const i64 row = t * WG_ROWS + r;
+      const bool in = t < nsteps && row < m;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int col = c * 32 + p * 4;
+        vg[c] = in ? __ldg(reinterpret_cast<const float4*>(g + row * n + group * PJ_BN + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        vx[c] = (in && col < k) ? __ldg(reinterpret_cast<const float4*>(x + row * k + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    };
+    auto split_store = [&](const float4& a, unsigned char* hi) {
+      float4 h, l;
+      h.x = __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u); l.x = a.x - h.x;
+      h.y = __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u); l.y = a.y - h.y;
+      h.z = __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u); l.z = a.z - h.z;
+      h.w = __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u); l.w = a.w - h.w;
+      *reinterpret_cast<float4*>(hi) = h;
+      *reinterpret_cast<float4*>(hi + WG_PART_BYTES) = l;
+    };
+    fetch(first);
+    uint32_t it = 0;
+    bool ok = true;
+    for (i64 t = first; ok && t < nsteps; t += stride, ++it) {
+      const uint32_t s = it % WG_STAGES, ph = (it / WG_STAGES) & 1u;
+      if (ct == 0) conv_ok_s = mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5) ? 1 : 0;
+      conv_sync();
+      if (!(ok = conv_ok_s != 0)) break;
+      unsigned char* st = ring_ptr + (size_t)s * WG_STAGE_BYTES + soff;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        split_store(vg[c], st + c * WG_CHUNK_BYTES);
+        split_store(vx[c], st + 2 * WG_PART_BYTES + c * WG_CHUNK_BYTES);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      conv_sync();
+      if (ct == 0) mbar_arrive(smem_u32(&bars.conv[s]));
+      fetch(t + stride);
+    }
+  } else if (warp < PJ_EPI_WARPS) {
+    // after the last MMA: accumulator lane = column n of the group, accumulator column = k
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(smem_u32(&bars.done), 0, give_up, 6);
+    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+    if (ok) {
+      tc_fence_after();
+      float* dst = partial + ((size_t)blockIdx.x * PJ_BN + warp * 32 + lane) * PJ_BN;
+#pragma unroll 1
+      for (int c = 0; c < PJ_BN; c += 32) {
+        uint32_t rr[32];
+        tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c, rr);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(dst + c + 4 * q) = make_float4(__uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]),
+                                                                   __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3]));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == PJ_WARP_MMA) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PJ_BN) : "memory");
+  }
+  if (tid == 0 && give_up_s != 0) atomicMax(status, give_up_s);
+}
+
+// grad_w = sum of the partials of one column group, in CTA order; written [k,n] (w_kn) or [n,k]
+__global__ void k_wgrad_reduce(const float* __restrict__ partial, int ctas_per_group, int groups, int n, int k, int w_kn,
+                               float* __restrict__ grad_w) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n * k) return;
+  const int col = t / k, kk = t % k;  // consecutive threads read consecutive k of one partial row
+  const int group = col / PJ_BN, nl = col % PJ_BN;
+  float acc = 0.f;
+  for (int j = 0; j < ctas_per_group; ++j)
+    acc += __ldg(partial + ((size_t)(group + groups * j) * PJ_BN + nl) * PJ_BN + kk);
+  grad_w[w_kn ? (size_t)kk * n + col : (size_t)col * k + kk] = acc;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -455,7 +594,47 @@ int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
 
-/* 0 while every wait inside the last dgnn_project_forward on this workspace completed; otherwise the
+size_t dgnn_project_wgrad_workspace_bytes(int n) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  (void)n;
+  return PJ_WS_HEADER + (size_t)sms * PJ_BN * PJ_BN * sizeof(float);
+}
+
+int dgnn_project_wgrad(int64_t m, int n, int k, const float* x, const float* grad_out, float* grad_w, int w_kn,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  if (m < 0 || n <= 0 || k <= 0) return DGNN_ERR_SHAPE;
+  if (!dgnn_project_supported(m > 0 ? m : 1, n, k)) return DGNN_ERR_SHAPE;
+  if (!x || !grad_out || !grad_w) return DGNN_ERR_NULL;
+  if (((uintptr_t)x | (uintptr_t)grad_out | (uintptr_t)workspace) & 15) return DGNN_ERR_ALIGN;
+  if (!workspace || workspace_bytes < dgnn_project_wgrad_workspace_bytes(n)) return DGNN_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = static_cast<int*>(workspace);
+  float* partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + PJ_WS_HEADER);
+  cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), s);
+  if (e != cudaSuccess) return (int)e;
+  if (m == 0) {
+    e = cudaMemsetAsync(grad_w, 0, (size_t)n * k * sizeof(float), s);
+    return e == cudaSuccess ? DGNN_OK : (int)e;
+  }
+  e = cudaFuncSetAttribute(k_project_wgrad, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WG_SMEM);  // per device
+  if (e != cudaSuccess) return (int)e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int groups = n / PJ_BN;
+  const i64 nsteps = (m + WG_ROWS - 1) / WG_ROWS;
+  i64 per_group = sms / groups > 0 ? sms / groups : 1;
+  if (per_group > nsteps) per_group = nsteps;  // every CTA gets at least one step, so every partial is written
+  const unsigned grid = (unsigned)(per_group * groups);
+  k_project_wgrad<<<grid, PJ_THREADS, WG_SMEM, s>>>(x, grad_out, partial, m, n, k, nsteps, groups, status);
+  k_wgrad_reduce<<<(n * k + 255) / 256, 256, 0, s>>>(partial, (int)per_group, groups, n, k, w_kn, grad_w);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+/* 0 while every wait inside the last dgnn_project_forward / dgnn_project_wgrad on this workspace completed; otherwise the
  * number of the wait that ran out (results are then invalid).  Synchronises the stream. */
 int dgnn_project_status(const void* workspace, void* stream, int* status_out) {
   if (!workspace || !status_out) return DGNN_ERR_NULL;
@@ -466,10 +645,5 @@ int dgnn_project_status(const void* workspace, void* stream, int* status_out) {
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
 
-#ifdef PJ_PROFILE
-int dgnn_project_profile(long long* out64) {
-  return (int)cudaMemcpyFromSymbol(out64, pj_dbg, sizeof(long long) * 64);
-}
-#endif
 
 }  // extern "C"

@@ -259,6 +259,31 @@ def project_forward(x, w, w_kn=False, check_status=False):
     return out
 
 
+def project_wgrad(x, grad_out, w_kn=False, check_status=False):
+    """grad_w = x[M,K]^T @ grad_out[M,N] on the tensor cores (3 x tf32 split), returned [N,K] or, with
+    w_kn=True, [K,N]."""
+    x = _cuda_f32(x, "x")
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    if x.dim() != 2 or grad_out.dim() != 2 or x.shape[0] != grad_out.shape[0]:
+        raise RuntimeError("dgnn_b200: project_wgrad expects x [M,K] and grad_out [M,N]")
+    m, k = x.shape
+    n = grad_out.shape[1]
+    dev = x.device
+    with device_guard(dev):
+        grad_w = torch.empty((k, n) if w_kn else (n, k), dtype=torch.float32, device=dev)
+        nbytes = lib().dgnn_project_wgrad_workspace_bytes(n)
+        ws = _workspace(nbytes, dev)
+        check(lib().dgnn_project_wgrad(m, n, k, _p(x), _p(grad_out), _p(grad_w), int(bool(w_kn)), _p(ws), nbytes,
+                                       _stream(dev)), "project_wgrad")
+        if check_status:
+            import ctypes
+            st = ctypes.c_int(0)
+            check(lib().dgnn_project_status(_p(ws), _stream(dev), ctypes.byref(st)), "project_status")
+            if st.value != 0:
+                raise RuntimeError(f"dgnn_b200: project_wgrad gave up in wait {st.value}; the result is invalid")
+    return grad_w
+
+
 # ------------------------------------------------------- SDDMM / transpose
 def mhsddmm(row_ptr, col_ind, a, b):
     """out[e,h] = <a[row_e,h,:], b[col_e,h,:]>, [E,H]."""

@@ -1,10 +1,11 @@
 """Dense node projection h = feat @ W in front of the fused GAT operator
 (`torch.matmul(feat, self.W)`, dgNN/layers/gatconv_layer.py:71 of the reference).
 
-The forward runs on the tcgen05 tensor cores (dgnn_project_forward: operands split
-into two tf32 parts, three products, fp32 accumulation -- fp32 accuracy) for the
-shapes that kernel handles; other shapes, and the two backward products, are plain
-library GEMMs through torch."""
+The forward and the weight gradient run on the tcgen05 tensor cores
+(dgnn_project_forward / dgnn_project_wgrad: operands split into two tf32 parts,
+three products, fp32 accumulation -- fp32 accuracy) for the shapes those kernels
+handle; other shapes, and the gradient with respect to the input features, are
+plain library GEMMs through torch."""
 import torch
 
 from .. import kernels
@@ -20,7 +21,9 @@ class ProjectFunction(torch.autograd.Function):
     def backward(ctx, grad_out):
         feat, weight = ctx.saved_tensors
         grad_feat = grad_out @ weight.t() if ctx.needs_input_grad[0] else None
-        grad_weight = feat.t() @ grad_out if ctx.needs_input_grad[1] else None
+        grad_weight = None
+        if ctx.needs_input_grad[1]:
+            grad_weight = kernels.project_wgrad(feat, grad_out.contiguous(), w_kn=True)
         return grad_feat, grad_weight
 
 

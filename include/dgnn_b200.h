@@ -182,6 +182,14 @@ int dgnn_project_supported(int64_t m, int n, int k);
 size_t dgnn_project_workspace_bytes(int n);
 int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w, int w_kn, float* out,
                          void* workspace, size_t workspace_bytes, void* stream);
+/* Weight gradient of the projection, grad_w = x^T * grad_out (k x n, written [k,n] with w_kn = 1 or
+ * [n,k] with w_kn = 0), same shapes, accuracy and tensor-core path as dgnn_project_forward; the
+ * reduction over the m rows is split over the CTAs and the partials are added in a fixed order, so
+ * the result is reproducible.  In the reference this product is autograd's backward of
+ * `torch.matmul(feat, self.W)` (dgNN/layers/gatconv_layer.py:71). */
+size_t dgnn_project_wgrad_workspace_bytes(int n);
+int dgnn_project_wgrad(int64_t m, int n, int k, const float* x, const float* grad_out, float* grad_w, int w_kn,
+                       void* workspace, size_t workspace_bytes, void* stream);
 int dgnn_project_status(const void* workspace, void* stream, int* status_out);
 
 /* Uniform floats in (0,1] from a counter-based Philox4x32-10 stream; stands in

@@ -76,3 +76,46 @@ def test_project_weight_as_k_by_n():
     ref = x.double() @ w.double()
     bound = x.abs().double() @ w.abs().double()
     assert bool(((out.double() - ref).abs() <= 4e-6 * bound).all())
+
+
+def _check_wgrad(m, k, n, seed, w_kn):
+    from dgnn_b200 import kernels
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(m, k, device=dev, generator=g)
+    go = torch.randn(m, n, device=dev, generator=g) * 0.5
+    gw = kernels.project_wgrad(x, go, w_kn=w_kn, check_status=True)
+    ref = x.double().t() @ go.double()                      # [K,N]
+    bound = x.abs().double().t() @ go.abs().double()
+    if not w_kn:
+        ref, bound = ref.t(), bound.t()
+    err = (gw.double() - ref).abs()
+    # split products ~2^-21 each, fp32 accumulation over m terms in the tensor core and across partials
+    assert bool((err <= 2e-5 * bound + 1e-30).all()), float((err / (bound + 1e-30)).max())
+
+
+@pytest.mark.parametrize("m", [1, 31, 32, 33, 1000, 4736, 100000])
+def test_project_wgrad_rows(m):
+    _check_wgrad(m, 100, 256, seed=m, w_kn=True)
+
+
+@pytest.mark.parametrize("k,n", [(4, 128), (32, 128), (36, 256), (128, 256), (100, 512)])
+def test_project_wgrad_shapes(k, n):
+    _check_wgrad(5000, k, n, seed=k + n, w_kn=False)
+
+
+def test_projection_function_gradients():
+    """The autograd node of the layer's projection against torch.matmul in fp64."""
+    from dgnn_b200.operators.projection import project
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(3000, 100, device=dev, generator=g, requires_grad=True)
+    w = torch.randn(100, 256, device=dev, generator=g, requires_grad=True)
+    cot = torch.randn(3000, 256, device=dev, generator=g)
+    out = project(x, w)
+    out.backward(cot)
+    xd, wd = x.detach().double().requires_grad_(), w.detach().double().requires_grad_()
+    (xd @ wd).backward(cot.double())
+    assert torch.allclose(out.double(), xd @ wd, rtol=1e-5, atol=1e-4)
+    assert torch.allclose(w.grad.double(), wd.grad, rtol=1e-4, atol=1e-3)
+    assert torch.allclose(x.grad.double(), xd.grad, rtol=1e-4, atol=1e-3)
