@@ -4,7 +4,7 @@ line per measurement: time, algorithmic bytes, achieved GB/s and the fraction of
 the measured HBM copy peak.  bench.py stays the headline benchmark; this script
 covers the remaining operators.
 
-    python bench_ops.py [--suite small|edgeconv|micro|all] [--iters 20]
+    python bench_ops.py [--suite small|edgeconv|micro|project|all] [--iters 20]
 
 Timing: CUDA events around each call on the launching stream, 3 warm-up calls,
 an L2 flush (256 MB write) before every timed call of the small configurations.
@@ -182,9 +182,32 @@ def suite_micro(iters, edges, degrees, heads, cap_gb):
         torch.cuda.empty_cache()
 
 
+def suite_project(iters, rows):
+    """The dense node projection of the bench configuration (in=100 -> 8 x 32) on the tensor cores, forward and
+    weight gradient, beside the fp32 library GEMM (TF32 off) that torch.matmul runs for the same product."""
+    dev = torch.device("cuda")
+    k, n = 100, 256
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(rows, k, device=dev, generator=g)
+    w = torch.randn(k, n, device=dev, generator=g)
+    go = torch.randn(rows, n, device=dev, generator=g)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    cfg = f"projection {rows} x {k} -> {n}"
+    flops = 2.0 * rows * k * n
+    for name, fn, nbytes in (("project_forward (tcgen05, 3 x tf32)", lambda: kernels.project_forward(x, w, w_kn=True), 4 * rows * (k + n)),
+                             ("torch.matmul fp32 (library)", lambda: x @ w, 4 * rows * (k + n)),
+                             ("project_wgrad (tcgen05, 3 x tf32)", lambda: kernels.project_wgrad(x, go, w_kn=True), 4 * rows * (k + n)),
+                             ("x.t() @ grad fp32 (library)", lambda: x.t() @ go, 4 * rows * (k + n))):
+        ms = timed(fn, iters, False)
+        report(name, cfg, ms, nbytes, fp32_equivalent_tflops=round(flops / (ms * 1e-3) / 1e12, 1))
+    torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--suite", default="all", choices=["small", "edgeconv", "micro", "all"])
+    ap.add_argument("--suite", default="all", choices=["small", "edgeconv", "micro", "project", "all"])
+    ap.add_argument("--project-rows", type=int, default=2_400_000)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--micro-edges", type=int, default=256_000_000)
     ap.add_argument("--micro-degrees", default="4,16,64,128")
@@ -197,6 +220,8 @@ def main():
         suite_small(args.iters)
     if args.suite in ("edgeconv", "all"):
         suite_edgeconv(args.iters)
+    if args.suite in ("project", "all"):
+        suite_project(args.iters, args.project_rows)
     if args.suite in ("micro", "all"):
         suite_micro(args.iters, args.micro_edges, [int(d) for d in args.micro_degrees.split(",")],
                     [int(h) for h in args.micro_heads.split(",")], args.cap_gb)
