@@ -87,6 +87,28 @@ def suite_small(iters):
     report("gat_forward", cfg, timed(lambda: kernels.gat_forward(ar, ac, rp, ci, 0.2, x), iters, True), fb)
     report("gat_backward", cfg, timed(lambda: kernels.gat_backward(0.2, 0.0, rp, cp, ri, pm, emax, esum, None, x, out, ar, ac, go), iters, True), bb)
     report("csr2csc", cfg, timed(lambda: kernels.csr2csc(rp, ci), iters, True), 2 * (n + 1) * 4 + 20 * e)
+    # the whole layer step of config 1 (in = 1433 -> 4 x 64), eager and replayed from a CUDA graph
+    from dgnn_b200.layers import GATConv
+    torch.manual_seed(1)
+    layer = GATConv(1433, f, h).to(dev).train()
+    xin = (torch.rand(n, 1433, device=dev, generator=g) < 0.013).float()
+    cot = torch.randn(n, h, f, device=dev, generator=g)
+
+    def layer_step():
+        layer.zero_grad(set_to_none=False)
+        (layer(rp, ci, cp, ri, pm, xin) * cot).sum().backward()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            layer_step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer_step()
+    layer_b = fb + bb + 4 * n * 1433 + 2 * 4 * 1433 * h * f
+    report("GATConv layer fwd+bwd, eager", cfg, timed(layer_step, iters, True), layer_b)
+    report("GATConv layer fwd+bwd, CUDA graph replay", cfg, timed(graph.replay, iters, True), layer_b)
     # config 2: MoNet, 3 kernels, 16 channels, pseudo dim 2
     k, fo, dim = 3, 16, 2
     feat = torch.randn(n, k, fo, device=dev, generator=g)
