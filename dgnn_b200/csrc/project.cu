@@ -1,5 +1,5 @@
-// Dense node projection out[M,N] = x[M,K] * w[N,K]^T (the nn.Linear without bias in
-// front of the fused GAT operator) on the sm_100a tensor cores, accurate to fp32.
+// Dense node projection out[M,N] = x[M,K] * W (the `feat @ W` in front of the fused GAT
+// operator) and its weight gradient on the sm_100a tensor cores, accurate to fp32.
 //
 // tcgen05.mma kind::tf32 keeps 11 significant bits of each operand, so every operand
 // is split into hi = the top 19 bits of the fp32 word and lo = x - hi (exact), and
@@ -10,11 +10,12 @@
 // small kernel and fetched by TMA with the 128-byte swizzle) stay resident in shared
 // memory for the whole kernel.  Eight converter warps read x straight from global
 // memory into registers -- a whole tile per CTA is in flight, which is what hides the
-// latency of HBM -- and write hi and lo of every 32-float k-block into a 3-stage ring in
+// latency of HBM -- and write hi and lo of every 32-float k-block into a 2-stage ring in
 // the same swizzled K-major layout.  One thread issues the MMAs into one of two 128x128
-// fp32 accumulators in tensor memory, and four epilogue warps drain the other
-// accumulator to global memory meanwhile (w is the M operand of the MMA, so an
-// accumulator lane is an output column and a warp's store covers one 128-byte line).
+// fp32 accumulators in tensor memory, and four epilogue warps drain the other one
+// meanwhile: 32 rows at a time through shared memory and a TMA store (w is the M operand
+// of the MMA, so an accumulator lane is an output column and a warp writes one 128-byte
+// line of the staging buffer).
 // The two column groups of one row tile run at the same time on neighbouring CTAs, so
 // x comes from HBM once and from L2 the second time.
 //
