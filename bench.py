@@ -298,14 +298,14 @@ def run_ours(args, rank, world, local):
             n_loc = int((shard.local_ids >= 0).sum())
             x = gdist.scatter_rows(seeded_normal((n, IN), 45, dev), shard)
             cot = gdist.scatter_rows(seeded_normal((n, H, F), 46, dev), shard)
-            agg = lambda h_: gdist.pipelined_gat_layer(h_, al, ar_, shard, SLOPE)
+            agg = lambda h_: gdist.pipelined_gat_layer(h_, al, ar_, shard, SLOPE, bias=bias)
         else:
             shard = gdist.build_shard(rp, ci, rank, world)
             r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
             n_loc = r1 - r0
             x = seeded_normal((n, IN), 45, dev)[r0:r1].contiguous()
             cot = seeded_normal((n, H, F), 46, dev)[r0:r1].contiguous()
-            agg = lambda h_: gdist.sharded_gat_layer(h_, al, ar_, shard, SLOPE)
+            agg = lambda h_: gdist.sharded_gat_layer(h_, al, ar_, shard, SLOPE) + bias.view(-1, H, F)
         del rp, ci
         torch.cuda.empty_cache()
         inner_ag = gdist._all_gather_rows
@@ -323,7 +323,7 @@ def run_ours(args, rank, world, local):
         def step(x_in):
             # the same layer on this rank's node block: projection, logits + sharded aggregation, bias
             h = project(x_in, W).view(-1, H, F)
-            out = agg(h) + bias.view(-1, H, F)
+            out = agg(h)
             loss = torch.dot(out.reshape(-1), cot.view(-1))
             loss.backward()
             for p in params:            # data-parallel parameter gradients

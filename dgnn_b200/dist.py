@@ -287,7 +287,7 @@ def _gather_slices(x_loc, shard, group):
     return bufs, works
 
 
-def _pipe_forward(attn_row, attn_col, h, shard, slope, group, backend):
+def _pipe_forward(attn_row, attn_col, h, shard, slope, group, backend, bias=None):
     col_bufs, col_works = _gather_slices(attn_col, shard, group)
     feat_bufs, feat_works = _gather_slices(h, shard, group)
     state = backend.gat_forward_state(shard.blk, h.shape[1], h.shape[2], h.device)
@@ -296,13 +296,15 @@ def _pipe_forward(attn_row, attn_col, h, shard, slope, group, backend):
         col_works[p].wait()
         feat_works[p].wait()
         ptr, col = shard.fwd[p]
-        res = backend.gat_forward_staged(attn_row, col_bufs[p], ptr, col, slope, feat_bufs[p], state,
-                                         p == 0, p == shard.stages - 1)
+        last = p == shard.stages - 1
+        extra = {"bias": bias} if (bias is not None and last) else {}
+        res = backend.gat_forward_staged(attn_row, col_bufs[p], ptr, col, slope, feat_bufs[p], state, p == 0, last, **extra)
     return res
 
 
-def _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum, grad_out, shard, slope, group, backend):
-    pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)
+def _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum, grad_out, shard, slope, group, backend, pack=None):
+    if pack is None:
+        pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)
     pack_bufs, pack_works = _gather_slices(pack, shard, group)
     grad_bufs, grad_works = _gather_slices(grad_out, shard, group)
     state = backend.gat_backward_state(shard.blk, h.shape[1], h.shape[2], h.device)
@@ -353,32 +355,41 @@ class PipelinedGATFunction(torch.autograd.Function):
 
 
 class PipelinedGATLayerFunction(torch.autograd.Function):
-    """Attention logits + pipelined aggregation as one autograd node (CUDA only)."""
+    """Attention logits + pipelined aggregation (+ bias in the last stage's epilogue) as one autograd
+    node (CUDA only)."""
 
     @staticmethod
-    def forward(ctx, h, attn_l, attn_r, shard, negative_slope, group):
+    def forward(ctx, h, attn_l, attn_r, bias, shard, negative_slope, group):
         h = h.contiguous()
         attn_row, attn_col = kernels.gat_logits_forward(h, attn_l, attn_r)
-        out, edge_max, edge_sum = _pipe_forward(attn_row, attn_col, h, shard, negative_slope, group, kernels)
-        ctx.save_for_backward(attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r)
-        ctx.shard, ctx.slope, ctx.group = shard, negative_slope, group
+        out, edge_max, edge_sum = _pipe_forward(attn_row, attn_col, h, shard, negative_slope, group, kernels, bias=bias)
+        ctx.save_for_backward(attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r,
+                              bias if bias is not None else h.new_empty(0))
+        ctx.shard, ctx.slope, ctx.group, ctx.has_bias = shard, negative_slope, group, bias is not None
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r = ctx.saved_tensors
-        grad_h, grad_row, grad_col = _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum,
-                                                   grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group, kernels)
+        attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r, bias = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        pack = grad_bias = None
+        if ctx.has_bias:   # `out` carries the bias: the row statistics subtract it, its gradient falls out of the same pass
+            pack, grad_bias = kernels.gat_rowstat_bias(attn_row, edge_max, edge_sum, out, grad_out, bias)
+            grad_bias = grad_bias.view_as(bias)
+        grad_h, grad_row, grad_col = _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum, grad_out, ctx.shard,
+                                                   ctx.slope, ctx.group, kernels, pack=pack)
         grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_row, grad_col, grad_h)
-        return grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None
+        return grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), grad_bias, None, None, None
 
 
 def pipelined_gat(attn_row, attn_col, in_feat, shard, negative_slope=0.2, group=None, backend=kernels):
     return PipelinedGATFunction.apply(attn_row, attn_col, in_feat, shard, negative_slope, group, backend)
 
 
-def pipelined_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None):
-    return PipelinedGATLayerFunction.apply(h, attn_l, attn_r, shard, negative_slope, group)
+def pipelined_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None, bias=None):
+    """h [blk,H,F] -> logits, pipelined aggregation and (optionally) the bias add, one autograd node.  Rows that
+    pad the last block also receive the bias; they carry no node."""
+    return PipelinedGATLayerFunction.apply(h, attn_l, attn_r, bias, shard, negative_slope, group)
 
 
 def scatter_rows(x_global, shard):

@@ -461,9 +461,10 @@ def gat_backward_state(n_cols, h, f, device):
     return torch.empty(max(nbytes // 4, 4), dtype=torch.float32, device=device)
 
 
-def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope, feat_blk, state, first, last):
+def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope, feat_blk, state, first, last, bias=None):
     """One stage of the forward over the edges whose source lies in one column block.
-    Returns (out, edge_max, edge_sum) from the last stage, None before."""
+    Returns (out, edge_max, edge_sum) from the last stage, None before.  `bias` [H*F] is added to the
+    output by the last stage when given."""
     attn_row = _cuda_f32(attn_row, "attn_row")
     attn_col_blk = _cuda_f32(attn_col_blk, "attn_col")
     feat_blk = _cuda_f32(feat_blk, "in_feat")
@@ -479,8 +480,11 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
             emax = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
             esum = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f), dev)
+        if bias is not None:
+            bias = _cuda_f32(bias, "bias").reshape(h * f)
         check(lib().dgnn_gat_forward_staged(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
-                                            _p(attn_col_blk), _p(feat_blk), float(negative_slope), 0.0, None, None,
+                                            _p(attn_col_blk), _p(feat_blk), float(negative_slope), 0.0, None,
+                                            _p(bias) if bias is not None else None,
                                             _p(out), _p(emax), _p(esum), _p(state), int(bool(first)), int(bool(last)),
                                             _p(ws), ws.numel(), _stream(dev)), "gat_forward_staged")
     return (out, emax, esum) if last else None

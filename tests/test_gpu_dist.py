@@ -49,6 +49,26 @@ def _worker(rank, world, port, n, e, h, f, q):
         pout.backward(gdist.scatter_rows(go, pshard))
         real = pshard.local_ids >= 0
         pid = pshard.local_ids[real]
+        # the layer node (logits + aggregation + bias in the last stage) against the single-GPU layer node
+        from dgnn_b200.operators import GATLayerFuse
+        al, arr = torch.randn(1, h, f, device=dev, generator=g), torch.randn(1, h, f, device=dev, generator=g)
+        bias = torch.randn(h * f, device=dev, generator=g)
+        ref_in = [t.clone().requires_grad_() for t in (x, al, arr, bias)]
+        ref_out = GATLayerFuse(ref_in[0], ref_in[1], ref_in[2], rp, ci, cp, ri, pm, 0.2, 0.0, ref_in[3])
+        ref_out.backward(go)
+        lay_in = [gdist.scatter_rows(x, pshard).requires_grad_()] + [t.clone().requires_grad_() for t in (al, arr, bias)]
+        lay_out = gdist.pipelined_gat_layer(lay_in[0], lay_in[1], lay_in[2], pshard, 0.2, bias=lay_in[3])
+        lay_out.backward(gdist.scatter_rows(go, pshard))
+        for t in lay_in[1:]:
+            dist.all_reduce(t.grad)                      # parameter gradients are sums over the ranks' rows
+
+        def rel(a, b):
+            return float((a - b).abs().max() / (b.abs().max() + 1e-6))
+        # tolerance relative to the aggregation itself: where it cancels against the bias, |out| says nothing about the error
+        agg_ref = ref_out.detach()[pid] - bias.view(1, h, f)
+        layer_out_err = float(((lay_out.detach()[real] - ref_out.detach()[pid]).abs() / (1e-5 + 1e-4 * (agg_ref.abs() + bias.view(1, h, f).abs()))).max())
+        layer_grad_err = max(rel(lay_in[0].grad[real], ref_in[0].grad[pid]), rel(lay_in[1].grad, ref_in[1].grad),
+                             rel(lay_in[2].grad, ref_in[2].grad), rel(lay_in[3].grad, ref_in[3].grad)) / 1e-4
         torch.cuda.synchronize()
 
         def worst(a, b):
@@ -56,7 +76,7 @@ def _worker(rank, world, port, n, e, h, f, q):
         q.put((rank, r1 - r0, worst(out.detach(), o1[r0:r1]), worst(loc[2].grad, gf[r0:r1]),
                worst(loc[0].grad, gr[r0:r1]), worst(loc[1].grad, gc[r0:r1]),
                worst(pout.detach()[real], o1[pid]), worst(ploc[2].grad[real], gf[pid]),
-               worst(ploc[0].grad[real], gr[pid]), worst(ploc[1].grad[real], gc[pid])))
+               worst(ploc[0].grad[real], gr[pid]), worst(ploc[1].grad[real], gc[pid]), layer_out_err, layer_grad_err))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -80,7 +100,10 @@ def test_sharded_gat_nccl_equals_single_gpu(cuda):
     assert sum(r[1] for r in results) == n
     # rows longer than the split threshold are cut at different edge positions in a shard, so the
     # comparison is to fp32 tolerance (error / (1e-5 + 1e-4 |ref|) <= 1; 2 for the attention gradients)
-    for rank, _, w_out, w_feat, w_row, w_col, p_out, p_feat, p_row, p_col in results:
+    for rank, _, w_out, w_feat, w_row, w_col, p_out, p_feat, p_row, p_col, layer_out_err, layer_grad_err in results:
+        # layer node with the fused bias: output to 1e-4 relative / 1e-5 absolute, gradients within 4e-4 of their
+        # largest entry (the same band as the staged sums below)
+        assert layer_out_err <= 1.0 and layer_grad_err <= 4.0, (rank, layer_out_err, layer_grad_err)
         assert w_out <= 1.0 and w_feat <= 1.0 and w_col <= 2.0 and w_row <= 2.0, (rank, w_out, w_feat, w_row, w_col)
         # the staged sums run in a different order over hub columns of >100 k edges: wider band for the gradients
         assert p_out <= 1.0 and p_feat <= 4.0 and p_col <= 4.0 and p_row <= 4.0, (rank, p_out, p_feat, p_row, p_col)
