@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--cpu-sample-edges", type=int, default=2_000_000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--peer-copies", type=int, default=1,
+                    help="1: the sharded layer fetches remote slices with peer-to-peer copies instead of NCCL all-gathers")
     ap.add_argument("--trace", default="", help="write a torch.profiler summary of two steps (rank 0) to this file")
     ap.add_argument("--stages", type=int, default=-1,
                     help="gather pipeline stages of the sharded path (-1: 1 up to 2 GPUs, 2 beyond; 0: contiguous blocks)")
@@ -295,6 +297,8 @@ def run_ours(args, rank, world, local):
         del cp, ri, pm
         if args.stages > 0:
             shard = gdist.build_pipe_shard(rp, ci, rank, world, stages=args.stages, seed=7)
+            if args.peer_copies:
+                gdist.enable_peer_copies(shard)
             n_loc = int((shard.local_ids >= 0).sum())
             x = gdist.scatter_rows(seeded_normal((n, IN), 45, dev), shard)
             cot = gdist.scatter_rows(seeded_normal((n, H, F), 46, dev), shard)

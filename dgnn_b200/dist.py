@@ -210,6 +210,7 @@ class PipeShard:
     local_ids: torch.Tensor       # original node id of every local row (-1 for padding)
     fwd: list                     # per stage: (row_ptr [blk+1], col_ind -> buffer row)
     bwd: list                     # per stage: (row_ptr [world*slice+1], col_ptr [blk+1], row_ind -> buffer row, permute)
+    peer: object = None           # PeerGather when the slices travel as peer-to-peer copies instead of all-gathers
 
 
 def _expand_segments(ptr, ids):
@@ -276,6 +277,94 @@ def build_pipe_shard(row_ptr, col_ind, rank, world, stages=4, seed=0, csr2csc=No
     return PipeShard(rank, world, stages, n, blk, sl, local_ids, fwd, bwd)
 
 
+class _StreamEvent:
+    """Stands in for the Work object of an asynchronous collective: wait() orders the current stream after it."""
+
+    def __init__(self, event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
+
+
+class PeerGather:
+    """Slices fetched from the peers' memory by copy engines instead of an NCCL all-gather.
+
+    Every rank keeps one staging buffer per gathered tensor in symmetric memory (torch.distributed's
+    allocator: every rank can map every other rank's buffer over NVLink).  A gather is: copy the local
+    block into the staging buffer, a one-element NCCL all-reduce as the barrier ("every rank's block is
+    written"), then plain device-to-device copies of slice p of every peer into this rank's
+    [world*slice, ...] buffer on a copy stream, peers visited in rotated order so that each peer serves
+    one reader at a time.  The copies take no SM away from the kernels they overlap with and reach the
+    NVLink rate of a peer copy; an all-reduce before the next overwrite of the staging buffer makes
+    sure every peer has finished reading it.  No multicast, no kernel of this library touches peer memory."""
+
+    def __init__(self, group):
+        import os
+        # the copies are plain peer reads: no multicast object is needed, and none should be bound to the buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.group = group
+        self.stream = torch.cuda.Stream()
+        self.staging = {}
+        self.flag = None
+
+    def _staging(self, tag, x_loc):
+        import torch.distributed._symmetric_memory as symm
+        key = (tag, tuple(x_loc.shape), x_loc.dtype)
+        if key not in self.staging:          # collective: every rank reaches this in the same order
+            buf = symm.empty(tuple(x_loc.shape), dtype=x_loc.dtype, device=x_loc.device)
+            handle = symm.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            self.staging[key] = (buf, handle, {})
+        return self.staging[key]
+
+    def _barrier(self, dev):
+        if self.flag is None:
+            self.flag = torch.zeros(1, dtype=torch.float32, device=dev)
+        dist.all_reduce(self.flag, group=self.group)
+
+    def gather_many(self, items, shard):
+        """items: [(tag, x_loc [blk, ...]), ...] -> [(buffers, works), ...], one barrier pair for all of them."""
+        dev = items[0][1].device
+        cur = torch.cuda.current_stream()
+        staged = [self._staging(tag, x) for tag, x in items]
+        self._barrier(dev)                    # every peer has finished reading the previous content
+        for (buf, _, _), (_, x) in zip(staged, items):
+            buf.copy_(x)
+        self._barrier(dev)                    # every rank's blocks are in place
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        results = []
+        for _, x in items:
+            tail = tuple(x.shape[1:])
+            results.append(([x.new_empty((shard.world * shard.slice,) + tail) for _ in range(shard.stages)], []))
+        lo, hi = shard.rank * shard.slice, (shard.rank + 1) * shard.slice
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(ready)
+            for p in range(shard.stages):
+                sl = slice(p * shard.slice, (p + 1) * shard.slice)
+                for (buf, handle, views), (_, x), (bufs, works) in zip(staged, items, results):
+                    bufs[p][lo:hi].copy_(buf[sl], non_blocking=True)           # own rows, off the compute stream too
+                    for i in range(1, shard.world):
+                        q = (shard.rank + i) % shard.world
+                        if q not in views:
+                            views[q] = handle.get_buffer(q, tuple(x.shape), x.dtype)
+                        bufs[p][q * shard.slice:(q + 1) * shard.slice].copy_(views[q][sl], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(self.stream)
+                    works.append(_StreamEvent(ev))
+        for bufs, _ in results:
+            for bb in bufs:
+                bb.record_stream(self.stream)
+        return results
+
+
+def _gather_many(items, shard, group):
+    """Start the gathers of the `stages` slices of several [blk, ...] tensors; [(buffers, works), ...]."""
+    if shard.peer is not None and items[0][1].is_cuda and shard.world > 1:
+        return shard.peer.gather_many([(tag, x.contiguous()) for tag, x in items], shard)
+    return [_gather_slices(x, shard, group) for _, x in items]
+
+
 def _gather_slices(x_loc, shard, group):
     """Start the all-gathers of the `stages` slices of x_loc [blk, ...]; returns (buffers, works)."""
     bufs, works = [], []
@@ -288,8 +377,7 @@ def _gather_slices(x_loc, shard, group):
 
 
 def _pipe_forward(attn_row, attn_col, h, shard, slope, group, backend, bias=None):
-    col_bufs, col_works = _gather_slices(attn_col, shard, group)
-    feat_bufs, feat_works = _gather_slices(h, shard, group)
+    (col_bufs, col_works), (feat_bufs, feat_works) = _gather_many([("attn_col", attn_col), ("feat", h)], shard, group)
     state = backend.gat_forward_state(shard.blk, h.shape[1], h.shape[2], h.device)
     res = None
     for p in range(shard.stages):
@@ -305,8 +393,7 @@ def _pipe_forward(attn_row, attn_col, h, shard, slope, group, backend, bias=None
 def _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum, grad_out, shard, slope, group, backend, pack=None):
     if pack is None:
         pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)
-    pack_bufs, pack_works = _gather_slices(pack, shard, group)
-    grad_bufs, grad_works = _gather_slices(grad_out, shard, group)
+    (pack_bufs, pack_works), (grad_bufs, grad_works) = _gather_many([("pack", pack), ("grad_out", grad_out)], shard, group)
     state = backend.gat_backward_state(shard.blk, h.shape[1], h.shape[2], h.device)
     parts = []
     grad_feat = grad_col = None
@@ -390,6 +477,14 @@ def pipelined_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None
     """h [blk,H,F] -> logits, pipelined aggregation and (optionally) the bias add, one autograd node.  Rows that
     pad the last block also receive the bias; they carry no node."""
     return PipelinedGATLayerFunction.apply(h, attn_l, attn_r, bias, shard, negative_slope, group)
+
+
+def enable_peer_copies(shard, group=None):
+    """Switch a PipeShard on CUDA ranks of one NVLink domain from NCCL all-gathers to peer-to-peer copies
+    (see PeerGather); returns the shard."""
+    if shard.world > 1:
+        shard.peer = PeerGather(group)
+    return shard
 
 
 def scatter_rows(x_global, shard):

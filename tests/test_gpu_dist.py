@@ -49,6 +49,14 @@ def _worker(rank, world, port, n, e, h, f, q):
         pout.backward(gdist.scatter_rows(go, pshard))
         real = pshard.local_ids >= 0
         pid = pshard.local_ids[real]
+        # the same again with the slices fetched by peer-to-peer copies: identical data, identical kernels
+        gdist.enable_peer_copies(pshard)
+        qloc = [gdist.scatter_rows(t, pshard).requires_grad_() for t in (ar, ac, x)]
+        qout = gdist.pipelined_gat(*qloc, pshard, 0.2)
+        qout.backward(gdist.scatter_rows(go, pshard))
+        torch.cuda.synchronize()
+        peer_same = bool(torch.equal(qout, pout) and all(torch.equal(a.grad, b.grad) for a, b in zip(qloc, ploc)))
+        pshard.peer = None
         # the layer node (logits + aggregation + bias in the last stage) against the single-GPU layer node
         from dgnn_b200.operators import GATLayerFuse
         al, arr = torch.randn(1, h, f, device=dev, generator=g), torch.randn(1, h, f, device=dev, generator=g)
@@ -76,7 +84,7 @@ def _worker(rank, world, port, n, e, h, f, q):
         q.put((rank, r1 - r0, worst(out.detach(), o1[r0:r1]), worst(loc[2].grad, gf[r0:r1]),
                worst(loc[0].grad, gr[r0:r1]), worst(loc[1].grad, gc[r0:r1]),
                worst(pout.detach()[real], o1[pid]), worst(ploc[2].grad[real], gf[pid]),
-               worst(ploc[0].grad[real], gr[pid]), worst(ploc[1].grad[real], gc[pid]), layer_out_err, layer_grad_err))
+               worst(ploc[0].grad[real], gr[pid]), worst(ploc[1].grad[real], gc[pid]), layer_out_err, layer_grad_err, peer_same))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -100,7 +108,8 @@ def test_sharded_gat_nccl_equals_single_gpu(cuda):
     assert sum(r[1] for r in results) == n
     # rows longer than the split threshold are cut at different edge positions in a shard, so the
     # comparison is to fp32 tolerance (error / (1e-5 + 1e-4 |ref|) <= 1; 2 for the attention gradients)
-    for rank, _, w_out, w_feat, w_row, w_col, p_out, p_feat, p_row, p_col, layer_out_err, layer_grad_err in results:
+    for rank, _, w_out, w_feat, w_row, w_col, p_out, p_feat, p_row, p_col, layer_out_err, layer_grad_err, peer_same in results:
+        assert peer_same, rank
         # layer node with the fused bias: output to 1e-4 relative / 1e-5 absolute, gradients within 4e-4 of their
         # largest entry (the same band as the staged sums below)
         assert layer_out_err <= 1.0 and layer_grad_err <= 4.0, (rank, layer_out_err, layer_grad_err)
