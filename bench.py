@@ -49,7 +49,7 @@ def parse():
                     help="1: the sharded layer fetches remote slices with peer-to-peer copies instead of NCCL all-gathers")
     ap.add_argument("--trace", default="", help="write a torch.profiler summary of two steps (rank 0) to this file")
     ap.add_argument("--stages", type=int, default=-1,
-                    help="gather pipeline stages of the sharded path (-1: 1 up to 2 GPUs, 2 beyond; 0: contiguous blocks)")
+                    help="gather pipeline stages of the sharded path (-1: 2; 0: contiguous blocks)")
     return ap.parse_args()
 
 
@@ -258,7 +258,7 @@ def run_ours(args, rank, world, local):
 
     n, nnz = args.nodes, args.edges
     if args.stages < 0:
-        args.stages = 1 if world <= 2 else 2
+        args.stages = 2
     rp, ci = make_graph(args, dev)
     W, al, ar_ = make_params(dev)
     W.requires_grad_(); al.requires_grad_(); ar_.requires_grad_()
@@ -446,7 +446,7 @@ def run_ours(args, rank, world, local):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"GATConv layer fwd+bwd, R-MAT {n} nodes / {nnz} edges (a=0.57,b=c=0.19), in={IN}, {H} heads x {F}, "
-                               f"int64 row_ptr, row-block sharded over {world} GPU(s)" + (f", {args.stages}-stage gather pipeline" if world > 1 and args.stages > 0 else ""),
+                               f"int64 row_ptr, row-block sharded over {world} GPU(s)" + (f", {args.stages}-stage gather pipeline, " + ("peer-to-peer slice copies" if args.peer_copies else "NCCL all-gathers") if world > 1 and args.stages > 0 else ""),
                    "l2": "inputs (2.46 GB feature tensor per pass) exceed the 126 MB L2; no flush needed",
                    "csr2csc_ms": csr2csc_ms},
         "gpu_launches": timer.launches,

@@ -483,7 +483,14 @@ def enable_peer_copies(shard, group=None):
     """Switch a PipeShard on CUDA ranks of one NVLink domain from NCCL all-gathers to peer-to-peer copies
     (see PeerGather); returns the shard."""
     if shard.world > 1:
-        shard.peer = PeerGather(group)
+        peer = PeerGather(group)
+        try:                                   # collective probe: symmetric memory may be unavailable on a platform
+            peer._staging("probe", torch.zeros(16, dtype=torch.float32, device=shard.local_ids.device))
+        except Exception as exc:               # every rank sees the same platform, so every rank falls back together
+            import warnings
+            warnings.warn(f"dgnn_b200: peer-to-peer slice copies unavailable ({exc}); using NCCL all-gathers")
+            return shard
+        shard.peer = peer
     return shard
 
 
