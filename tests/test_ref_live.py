@@ -202,8 +202,11 @@ def test_side_by_side_small_graph(cuda, ref):
         out, emax, esum = kernels.gat_forward(ar, ac, rp, ci, 0.2, x)
         return (out,) + kernels.gat_backward(0.2, 0.0, rp, cp, ri, pm, emax, esum, None, x, out, ar, ac, go)
 
-    for u, v in zip(ref_step(), our_step()):
-        assert float(((u - v).abs() / (2e-5 + 1e-4 * u.abs())).max()) < 2.0
+    # the reference's backward adds with float atomics, so its own result moves from run to run where terms
+    # cancel: the band is relative to each entry plus a part in 10^5 of the tensor's largest entry
+    for u, v, name in zip(ref_step(), our_step(), ("out", "grad_feat", "grad_attn_row", "grad_attn_col")):
+        tol = 2e-5 + 1e-4 * u.abs() + 1e-5 * float(u.abs().max())
+        assert float(((u - v).abs() / tol).max()) < 2.0, name
     t_ref, t_our = _time(ref_step, 50, 5), _time(our_step, 50, 5)
     rec = dict(workload="2708 nodes / 13264 edges, 4 x 64, fused GAT fwd+bwd", ref_ms=t_ref, ours_ms=t_our, speedup=t_ref / t_our)
     print("SIDE_BY_SIDE_SMALL", json.dumps(rec))
