@@ -305,6 +305,7 @@ class PeerGather:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         self.group = group
         self.stream = torch.cuda.Stream()
+        self.own_stream = torch.cuda.Stream()   # local rows go on their own stream, beside the peer copies
         self.staging = {}
         self.flag = None
 
@@ -338,23 +339,35 @@ class PeerGather:
             tail = tuple(x.shape[1:])
             results.append(([x.new_empty((shard.world * shard.slice,) + tail) for _ in range(shard.stages)], []))
         lo, hi = shard.rank * shard.slice, (shard.rank + 1) * shard.slice
+        entered = torch.cuda.Event()
+        entered.record(cur)
+        with torch.cuda.stream(self.own_stream):          # this rank's own rows of every stage buffer
+            self.own_stream.wait_event(entered)
+            for (_, x), (bufs, _) in zip(items, results):
+                for p in range(shard.stages):
+                    bufs[p][lo:hi].copy_(x[p * shard.slice:(p + 1) * shard.slice], non_blocking=True)
+            own_done = torch.cuda.Event()
+            own_done.record(self.own_stream)
         with torch.cuda.stream(self.stream):
             self.stream.wait_event(ready)
             for p in range(shard.stages):
                 sl = slice(p * shard.slice, (p + 1) * shard.slice)
                 for (buf, handle, views), (_, x), (bufs, works) in zip(staged, items, results):
-                    bufs[p][lo:hi].copy_(buf[sl], non_blocking=True)           # own rows, off the compute stream too
                     for i in range(1, shard.world):
                         q = (shard.rank + i) % shard.world
                         if q not in views:
                             views[q] = handle.get_buffer(q, tuple(x.shape), x.dtype)
                         bufs[p][q * shard.slice:(q + 1) * shard.slice].copy_(views[q][sl], non_blocking=True)
+                    if p == 0:
+                        self.stream.wait_event(own_done)
                     ev = torch.cuda.Event()
                     ev.record(self.stream)
                     works.append(_StreamEvent(ev))
-        for bufs, _ in results:
+        for (_, x), (bufs, _) in zip(items, results):
+            x.record_stream(self.own_stream)
             for bb in bufs:
                 bb.record_stream(self.stream)
+                bb.record_stream(self.own_stream)
         return results
 
 
