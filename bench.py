@@ -3,8 +3,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (BASELINE.json configs[3]): seeded R-MAT graph, 2.4 M nodes, 120 M directed
-edges (a=0.57, b=c=0.19), CSR with int64 row_ptr; features 2.4M x 100 N(0,1); 8 heads x 32.
+Workload (the large sharded-graph configuration of the GAT benchmark): seeded R-MAT graph, 2.4 M nodes,
+120 M directed edges (a=0.57, b=c=0.19), CSR with int64 row_ptr; features 2.4M x 100 N(0,1); 8 heads x 32.
 A step is the whole layer through the public API (projection GEMM, attention logits,
 fused softmax-aggregation, and the backward of all of it).  Prints ONE JSON line.
 The public datasets the reference trains on are not available offline; the graph and
@@ -28,10 +28,12 @@ if ROOT not in sys.path:
 
 H, F, IN = 8, 32, 100
 SLOPE = 0.2
-# DRAM bytes (read + write) per call at the full-size workload from one ncu capture of
-# dram__bytes_read.sum + dram__bytes_write.sum (profiles/); None until captured
-TRAFFIC_FWD_BYTES = 64.8e9
-TRAFFIC_BWD_BYTES = 88.8e9
+# DRAM bytes (read + write) per edge of the forward call and of the backward calls, from ncu's
+# dram__bytes_read.sum + dram__bytes_write.sum over the kernels of one call on the R-MAT 300 k-node /
+# 12 M-edge case (same average degree and skew; traffic grows in proportion to the edges), scaled to the
+# workload's edge count at run time.  None = not captured for the current kernels.
+TRAFFIC_FWD_BYTES_PER_EDGE = None
+TRAFFIC_BWD_BYTES_PER_EDGE = None
 
 
 def parse():
@@ -45,11 +47,11 @@ def parse():
     ap.add_argument("--cpu-sample-edges", type=int, default=2_000_000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--peer-copies", type=int, default=1,
-                    help="1: the sharded layer fetches remote slices with peer-to-peer copies instead of NCCL all-gathers")
-    ap.add_argument("--trace", default="", help="write a torch.profiler summary of two steps (rank 0) to this file")
-    ap.add_argument("--stages", type=int, default=-1,
-                    help="gather pipeline stages of the sharded path (-1: 2; 0: contiguous blocks)")
+    ap.add_argument("--stages", type=int, default=3,
+                    help="sweeps per pass of the sharded layer: stage 0 = own nodes, the others one halo chunk each")
+    ap.add_argument("--pull-ctas", type=int, default=48, help="grid bound of the halo fetch kernel (0: unbounded)")
+    ap.add_argument("--gather-fallback", action="store_true",
+                    help="halo rows through all-gathers instead of peer loads from symmetric memory")
     return ap.parse_args()
 
 
@@ -154,12 +156,11 @@ class PhaseTimer:
         after each name is how many kernels of this library one call launches."""
         timer = self
         for name, key, launches in (("gat_forward", "fwd", 3),          # rows, chunks, merge
-                                    ("gat_backward", "bwd", 7),         # rowstat, 3 column-pass, 3 row-reduce
-                                    ("gat_rowstat", "bwd_stat", 1),
-                                    ("gat_rowstat_bias", "bwd_stat", 2),
-                                    ("gat_backward_cols", "bwd_cols", 6),
+                                    ("gat_rowstat_full", "bwd_stat", 2),   # row statistics, bias-gradient fold
+                                    ("gat_backward_cols", "bwd_cols", 3),
                                     ("gat_forward_staged", "fwd", 3),
-                                    ("gat_backward_cols_staged", "bwd_cols", 6),
+                                    ("gat_backward_cols_staged", "bwd_cols", 3),
+                                    ("halo_pull", "halo_pull", 1),
                                     ("project_forward", "project", 2),     # weight split, projection
                                     ("project_wgrad", "project_wgrad", 2),  # partial products, fixed-order sum
                                     ("gat_logits_forward", "logits_fwd", 1),
@@ -242,26 +243,33 @@ def run_reference_arm(args, rank):
     print(json.dumps(line))
 
 
+def check_values(out_sample_sum, loss, params, world):
+    """Numbers that must agree between runs on different GPU counts: the loss of the last step, the sum of the
+    layer output over a fixed seeded sample of nodes, and the squared norms of the parameter gradients
+    (computed in fp64 outside the timed region)."""
+    vals = {"loss": float(loss.detach()), "out_sample_sum": float(out_sample_sum)}
+    for name, p in params:
+        vals["grad_" + name + "_sq"] = float((p.grad.double() ** 2).sum())
+    return vals
+
+
 def run_ours(args, rank, world, local):
     from dgnn_b200 import dist as gdist
-    from dgnn_b200.operators.projection import project
     from dgnn_b200 import kernels
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
-    torch.backends.cuda.matmul.allow_tf32 = False      # fp32 parity for the projection GEMM
+    torch.backends.cuda.matmul.allow_tf32 = False      # fp32 parity for any library GEMM
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # halo rows are plain peer loads
         dist.init_process_group("nccl", device_id=dev)
 
     n, nnz = args.nodes, args.edges
-    if args.stages < 0:
-        args.stages = 2
     rp, ci = make_graph(args, dev)
     W, al, ar_ = make_params(dev)
-    W.requires_grad_(); al.requires_grad_(); ar_.requires_grad_()
     timer = PhaseTimer()
     timer.wrap(kernels)
 
@@ -274,8 +282,7 @@ def run_ours(args, rank, world, local):
         torch.cuda.synchronize(); t_c.append(s.elapsed_time(e))
     csr2csc_ms = min(t_c)
 
-    bias = torch.zeros(H * F, device=dev, requires_grad=True)
-    params = [W, al, ar_, bias]
+    sample = torch.randperm(n, generator=torch.Generator().manual_seed(47))[:4096].to(dev)   # nodes of the output checksum
     if world == 1:
         from dgnn_b200.layers import GATConv
         x = seeded_normal((n, IN), 45, dev)
@@ -283,59 +290,50 @@ def run_ours(args, rank, world, local):
         layer = GATConv(IN, F, H, negative_slope=SLOPE).to(dev).train()     # the public layer, default options
         with torch.no_grad():
             layer.W.copy_(W); layer.attn_l.copy_(al); layer.attn_r.copy_(ar_)
-        params = list(layer.parameters())
-        W, al, ar_ = layer.W, layer.attn_l, layer.attn_r
 
         def step(x_in):
             out = layer(rp, ci, cp, ri, pm, x_in)
             loss = torch.dot(out.view(-1), cot.view(-1))       # dense fp32 cotangent for the backward
             loss.backward()
-            return loss
-        n_loc = n
+            return loss, out
+
+        def sample_sum(out):
+            return out.detach()[sample].double().sum()
+        hc = None
     else:
         import torch.distributed as dist
         del cp, ri, pm
-        if args.stages > 0:
-            shard = gdist.build_pipe_shard(rp, ci, rank, world, stages=args.stages, seed=7)
-            if args.peer_copies:
-                gdist.enable_peer_copies(shard)
-            n_loc = int((shard.local_ids >= 0).sum())
-            x = gdist.scatter_rows(seeded_normal((n, IN), 45, dev), shard)
-            cot = gdist.scatter_rows(seeded_normal((n, H, F), 46, dev), shard)
-            agg = lambda h_: gdist.pipelined_gat_layer(h_, al, ar_, shard, SLOPE, bias=bias)
-        else:
-            shard = gdist.build_shard(rp, ci, rank, world)
-            r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
-            n_loc = r1 - r0
-            x = seeded_normal((n, IN), 45, dev)[r0:r1].contiguous()
-            cot = seeded_normal((n, H, F), 46, dev)[r0:r1].contiguous()
-            agg = lambda h_: gdist.sharded_gat_layer(h_, al, ar_, shard, SLOPE) + bias.view(-1, H, F)
-        del rp, ci
+        shard = gdist.build_halo_shard(rp, ci, rank, world, stages=args.stages, seed=7)
+        transport = gdist.GatherTransport(shard) if args.gather_fallback else gdist.make_transport(shard, None, args.pull_ctas)
+        layer = gdist.ShardedGATConv(IN, F, H, shard, negative_slope=SLOPE, transport=transport).to(dev).train()
+        with torch.no_grad():
+            layer.W.copy_(W); layer.attn_l.copy_(al); layer.attn_r.copy_(ar_)
+        x = shard.scatter_rows(seeded_normal((n, IN), 45, dev))
+        cot = shard.scatter_rows(seeded_normal((n, H, F), 46, dev))
+        owner_of = torch.full((n,), -1, dtype=torch.long, device=dev)
+        real = shard.local_ids >= 0
+        owner_of[shard.local_ids[real]] = torch.arange(shard.blk, device=dev)[real]
+        my_sample = owner_of[sample]
+        my_sample = my_sample[my_sample >= 0]
+        del rp, ci, owner_of
         torch.cuda.empty_cache()
-        inner_ag = gdist._all_gather_rows
-        timer.spans["all_gather"] = []
-
-        def timed_all_gather(*a, **k):
-            if not timer.active:
-                return inner_ag(*a, **k)
-            s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s_.record(); r_ = inner_ag(*a, **k); e_.record()
-            timer.spans["all_gather"].append((s_, e_))
-            return r_
-        gdist._all_gather_rows = timed_all_gather
 
         def step(x_in):
-            # the same layer on this rank's node block: projection, logits + sharded aggregation, bias
-            h = project(x_in, W).view(-1, H, F)
-            out = agg(h)
+            out = layer(x_in)                                  # the same layer on this rank's node block
             loss = torch.dot(out.reshape(-1), cot.view(-1))
             loss.backward()
-            for p in params:            # data-parallel parameter gradients
-                dist.all_reduce(p.grad)
-            return loss
+            layer.allreduce_grads()                            # replicated parameters: one flat all-reduce
+            return loss, out
+
+        def sample_sum(out):
+            t = out.detach()[my_sample].double().sum()
+            dist.all_reduce(t)
+            return t
+        hc = layer._context()
+    params = list(layer.named_parameters())
 
     def zero_grads():
-        for p in params:
+        for _, p in params:
             p.grad = None
 
     def sync_all():
@@ -348,21 +346,12 @@ def run_ours(args, rank, world, local):
         step(x)
         zero_grads()
     sync_all()
-    if args.trace:
-        from torch.profiler import ProfilerActivity, profile
-        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
-            for _ in range(2):
-                step(x)
-                zero_grads()
-            sync_all()
-        if rank == 0:
-            with open(args.trace, "w") as fh:
-                fh.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70))
-            prof.export_chrome_trace(args.trace + ".json")
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     timer.active = True
+    if hc is not None:
+        hc.exposed_ms = []
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     for _ in range(args.steps):
@@ -377,6 +366,23 @@ def run_ours(args, rank, world, local):
         t = torch.tensor([ms], device=dev)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t[0])
+    exposed = None
+    if hc is not None:
+        exposed = {}
+        for phase, chunk, a, b in hc.exposed_ms:
+            key = f"{phase}_wait_chunk{chunk}"
+            exposed[key] = exposed.get(key, 0.0) + a.elapsed_time(b) / args.steps
+        hc.exposed_ms = None
+
+    # one more step outside the timed region for the values that different GPU counts must agree on
+    loss, out = step(x)
+    if world > 1:
+        lt = loss.detach().double().clone()
+        torch.distributed.all_reduce(lt)
+        loss = lt
+    check = check_values(sample_sum(out), loss, params, world)
+    zero_grads()
+    del out
 
     # end to end: features come from pinned host memory every step, the loss goes back
     e2e = None
@@ -405,7 +411,7 @@ def run_ours(args, rank, world, local):
                 if i + 1 < k:
                     prefetch(i + 1)
                 main.wait_event(ready[i % 2])
-                loss_host.copy_(step(bufs[i % 2]), non_blocking=True)
+                loss_host.copy_(step(bufs[i % 2])[0], non_blocking=True)
                 consumed[i % 2].record(main)
                 zero_grads()
 
@@ -427,7 +433,9 @@ def run_ours(args, rank, world, local):
     phases = None
     if world > 1:
         mine = {k: (sum(a.elapsed_time(b) for a, b in v) / args.steps) for k, v in timer.spans.items() if v}
-        mine["n_loc"] = n_loc
+        mine.update(exposed or {})
+        mine["halo_rows_fwd"], mine["halo_rows_bwd"] = shard.fwd.n_halo, shard.bwd.n_halo
+        mine["transport"] = type(transport).__name__
         phases = [None] * world
         torch.distributed.all_gather_object(phases, mine)
     if rank != 0:
@@ -438,42 +446,48 @@ def run_ours(args, rank, world, local):
 
     peak, peak_kind = load_peaks()
     fwd_b, bwd_b = algorithmic_bytes(n, nnz, H, F, 8)
-    fwd_ms, bwd_ms = timer.mean_ms("fwd"), timer.mean_ms("bwd")
-    if bwd_ms is None and timer.mean_ms("bwd_cols"):      # the layer calls the two halves of dgnn_gat_backward itself
+    fwd_ms, bwd_ms = timer.mean_ms("fwd"), None
+    if timer.mean_ms("bwd_cols") and timer.mean_ms("bwd_stat"):      # the layer calls the two halves of the backward itself
         bwd_ms = timer.mean_ms("bwd_stat") + timer.mean_ms("bwd_cols")
+    sharded = (f", node blocks over {world} GPUs, {args.stages} sweeps per pass, halo rows by "
+               + ("all-gathers" if args.gather_fallback else "peer loads from symmetric memory")) if world > 1 else ""
     line = {
         "metric": "GAT layer fwd+bwd edges/sec", "value": nnz / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"GATConv layer fwd+bwd, R-MAT {n} nodes / {nnz} edges (a=0.57,b=c=0.19), in={IN}, {H} heads x {F}, "
-                               f"int64 row_ptr, row-block sharded over {world} GPU(s)" + (f", {args.stages}-stage gather pipeline, " + ("peer-to-peer slice copies" if args.peer_copies else "NCCL all-gathers") if world > 1 and args.stages > 0 else ""),
+                               f"int64 row_ptr" + sharded,
                    "l2": "inputs (2.46 GB feature tensor per pass) exceed the 126 MB L2; no flush needed",
                    "csr2csc_ms": csr2csc_ms},
         "gpu_launches": timer.launches,
         "clocks": clocks,
+        "check": check,
     }
     if e2e:
         line["e2e"] = e2e
     if phases:
         line["phases_ms_per_step_by_rank"] = phases
     if world == 1 and fwd_ms and bwd_ms:
-        # one "launch" = the kernels of one C-ABI call; the backward call dominates the step
+        # one "launch" = the kernels of one C-ABI call; the backward calls dominate the step
         ach_b = bwd_b / (bwd_ms * 1e-3) / 1e9
-        line["roofline"] = {"bound": "hbm", "kernel": "dgnn_gat_rowstat_bias + dgnn_gat_backward_cols: k_gat_rowstat_bias + k_rows/k_chunks/k_merge<GatBwdOp> + k_rowred_*",
+        line["roofline"] = {"bound": "hbm", "kernel": "dgnn_gat_rowstat_full + dgnn_gat_backward_cols: k_gat_rowstat_full + k_rows/k_chunks/k_merge<GatBwdOp>",
                             "achieved": ach_b, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_b / peak,
-                            "traffic": TRAFFIC_BWD_BYTES, "algorithmic_bytes": bwd_b, "ms": bwd_ms}
+                            "traffic": TRAFFIC_BWD_BYTES_PER_EDGE * nnz if TRAFFIC_BWD_BYTES_PER_EDGE else None,
+                            "algorithmic_bytes": bwd_b, "ms": bwd_ms}
         ach = fwd_b / (fwd_ms * 1e-3) / 1e9
-        line["roofline_fwd"] = {"bound": "hbm", "kernel": "dgnn_gat_forward: k_rows/k_chunks/k_merge<GatFwdOp>",
+        line["roofline_fwd"] = {"bound": "hbm", "kernel": "dgnn_gat_forward_staged: k_rows/k_chunks/k_merge<GatFwdOp>",
                                 "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                                "traffic": TRAFFIC_FWD_BYTES, "algorithmic_bytes": fwd_b, "ms": fwd_ms}
+                                "traffic": TRAFFIC_FWD_BYTES_PER_EDGE * nnz if TRAFFIC_FWD_BYTES_PER_EDGE else None,
+                                "algorithmic_bytes": fwd_b, "ms": fwd_ms}
         tot = (fwd_b + bwd_b) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
         line["fused_op"] = {"ms": fwd_ms + bwd_ms, "edges_per_s": nnz / ((fwd_ms + bwd_ms) * 1e-3), "achieved_gbs": tot,
                             "frac_of_peak": tot / peak,
                             "note": "algorithmic bytes count every gathered row in full; hub rows are served from L2, so this can exceed the DRAM copy peak"}
     if world == 1 and not args.no_cpu_baseline:
+        from dgnn_b200.operators.projection import project
         with torch.no_grad():
-            h = torch.matmul(x, W).view(-1, H, F)
-            a_row, a_col = kernels.gat_logits_forward(h, al, ar_)
+            h = project(x, layer.W).view(-1, H, F)
+            a_row, a_col = kernels.gat_logits_forward(h, layer.attn_l, layer.attn_r)
         eps, desc, cores = cpu_sample(rp, ci, a_row, a_col, h, cot, args.cpu_sample_edges, 3)
         line["cpu_baseline"] = {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc}
     print(json.dumps(line))

@@ -34,8 +34,12 @@ SIGNATURES = {
     "dgnn_gat_forward": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
                                  c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_forward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
+    "dgnn_gat_fast_shape": (c_int, [c_int, c_int]),
     "dgnn_gat_forward_staged": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
-                                        c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
+                                        c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
+    "dgnn_gat_rowstat_full": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_f, c_p, c_p,
+                                      c_p, c_p, c_p, c_sz, c_p]),
+    "dgnn_gat_backward_cols_workspace_bytes": (c_sz, [c_i64, c_int, c_int, c_int]),
     "dgnn_gat_rowstat_bias_workspace_bytes": (c_sz, [c_int, c_int]),
     "dgnn_gat_rowstat_bias": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_backward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
@@ -57,6 +61,10 @@ SIGNATURES = {
     "dgnn_project_wgrad": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_int, c_p, c_sz, c_p]),
     "dgnn_project_status": (c_int, [c_p, c_p, c_p]),
     "dgnn_uniform_fill": (c_int, [c_u64, c_u64, c_i64, c_p, c_p]),
+    "dgnn_uniform_fill_edges": (c_int, [c_u64, c_u64, c_i64, c_int, c_p, c_p, c_p]),
+    "dgnn_halo_max_ranks": (c_int, []),
+    "dgnn_halo_rank_shift": (c_int, []),
+    "dgnn_halo_pull": (c_int, [c_i64, c_p, c_int, c_i64, c_p, c_p, c_int, c_p, c_p, c_int, c_int, c_p, c_p]),
     "dgnn_mhsddmm_workspace_bytes": (c_sz, []),
     "dgnn_mhsddmm": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_coo_sddmm": (c_int, [c_i64, c_int, c_p, c_p, c_p, c_p, c_p, c_p]),

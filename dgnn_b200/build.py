@@ -14,8 +14,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdgnn_b200.so")
-SOURCES = ["gat.cu", "logits.cu", "sddmm_gmm.cu", "edgeconv.cu", "convert.cu", "project.cu", "misc.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(HERE, "..", "include", "dgnn_b200.h")]
+SOURCES = ["gat.cu", "logits.cu", "sddmm_gmm.cu", "edgeconv.cu", "convert.cu", "project.cu", "halo.cu", "misc.cu"]
+import glob
+HEADERS = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + [os.path.join(HERE, "..", "include", "dgnn_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC",

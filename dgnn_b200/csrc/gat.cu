@@ -21,7 +21,7 @@ namespace {
 template <int VPL> struct Unroll { static constexpr int U = VPL <= 2 ? 4 : 2; };
 
 // ------------------------------------------------------------------ forward
-template <int VPL, bool MASK, bool FULL, int LPR>
+template <int VPL, bool MASK, bool FULL, int LPR, bool NEG>
 struct GatFwdOp {
   static constexpr int EPW = 32 / LPR;
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
@@ -46,11 +46,15 @@ struct GatFwdOp {
   float* state;
   int first, last, skip_empty;
   const float4* bias;   // optional [H*F] added to the normalised output (layer epilogue)
+  // NEG: the share of the result that comes from edges on the negative side of the LeakyReLU
+  float4* out_neg;      // [n_rows, H*F], normalised like out (no bias)
+  float* a_neg;         // [n_rows, H]: sum of alpha over those edges
 
   struct State {
     LaneMap<VPL, LPR> lm;
-    float ar[VPL], m[VPL], z[VPL];
+    float ar[VPL], m[VPL], z[VPL], zn[NEG ? VPL : 1];
     float4 acc[VPL];
+    float4 accn[NEG ? VPL : 1];
   };
 
   __device__ __forceinline__ void init(State& st, i64 r, int lane) const {
@@ -61,6 +65,7 @@ struct GatFwdOp {
       st.m[v] = DGNN_NEG_INIT;
       st.z[v] = 0.f;
       st.acc[v] = zero4();
+      if (NEG) { st.zn[v] = 0.f; st.accn[v] = zero4(); }
     }
   }
   __device__ __forceinline__ void resume(State& st, i64 r, int lane) const {
@@ -89,6 +94,22 @@ struct GatFwdOp {
       if (!low) { const float4 t = a; a = b; b = t; }
       add4(a, b);
       st.acc[0] = a;
+      if (NEG) {
+        const float no = __shfl_xor_sync(DGNN_FULL, st.zn[0], off);
+        float4 co;
+        co.x = __shfl_xor_sync(DGNN_FULL, st.accn[0].x, off);
+        co.y = __shfl_xor_sync(DGNN_FULL, st.accn[0].y, off);
+        co.z = __shfl_xor_sync(DGNN_FULL, st.accn[0].z, off);
+        co.w = __shfl_xor_sync(DGNN_FULL, st.accn[0].w, off);
+        const float na = low ? st.zn[0] * s1 : no * s2, nb = low ? no * s2 : st.zn[0] * s1;
+        st.zn[0] = na + nb;
+        float4 c = st.accn[0], d = co;
+        scale4(c, s1);
+        scale4(d, s2);
+        if (!low) { const float4 t = c; c = d; d = t; }
+        add4(c, d);
+        st.accn[0] = c;
+      }
       st.m[0] = mn;
     }
   }
@@ -119,7 +140,6 @@ struct GatFwdOp {
     }
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      if (!FULL && !st.lm.act[v]) continue;
       float l[U];
       float bm = st.m[v];
 #pragma unroll
@@ -127,16 +147,27 @@ struct GatFwdOp {
         l[u] = (ALL || slot[u] < cnt) ? leaky(st.ar[v] + s[u][v], slope) : DGNN_NEG_INIT;
         bm = fmaxf(bm, l[u]);
       }
-      const float sc = fast_exp(st.m[v] - bm);  // 1 when the maximum did not move
-      st.z[v] *= sc;
-      scale4(st.acc[v], sc);
-      st.m[v] = bm;
+      // rescale only when the running maximum moved for some lane of the warp
+      const bool moved = __any_sync(DGNN_FULL, bm > st.m[v]);
+      if (!FULL && !st.lm.act[v]) { st.m[v] = bm; continue; }
+      if (moved) {
+        const float sc = fast_exp(st.m[v] - bm);
+        st.z[v] *= sc;
+        scale4(st.acc[v], sc);
+        if (NEG) { st.zn[v] *= sc; scale4(st.accn[v], sc); }
+        st.m[v] = bm;
+      }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (ALL || slot[u] < cnt) {
           const float p = fast_exp(l[u] - bm);
           st.z[v] += p;
-          if (!MASK || keep[u][v]) fma4(st.acc[v], p, x[u][v]);
+          const float pn = l[u] < 0.f ? p : 0.f;
+          if (NEG) st.zn[v] += pn;
+          if (!MASK || keep[u][v]) {
+            fma4(st.acc[v], p, x[u][v]);
+            if (NEG) fma4(st.accn[v], pn, x[u][v]);
+          }
         }
       }
     }
@@ -164,21 +195,30 @@ struct GatFwdOp {
       scale4(a, sc);
       if (bias) add4(a, __ldg(bias + st.lm.q[v]));
       out[r * hf4 + st.lm.q[v]] = a;
+      if (NEG) {
+        float4 an = st.accn[v];
+        scale4(an, sc);
+        out_neg[r * hf4 + st.lm.q[v]] = an;
+      }
       if (st.lm.wlead[v] && edge_max) {
         edge_max[r * H + st.lm.hd[v]] = st.m[v];
         edge_sum[r * H + st.lm.hd[v]] = st.z[v];
       }
+      if (NEG && st.lm.wlead[v]) a_neg[r * H + st.lm.hd[v]] = st.z[v] > 0.f ? st.zn[v] / st.z[v] : 0.f;
     }
   }
 
+  // slot layout: [acc H*F | m H | z H | (NEG: zn H) | pad to 4 | (NEG: accn H*F)]
   __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.wr[v]) continue;
       reinterpret_cast<float4*>(p)[st.lm.q[v]] = st.acc[v];
+      if (NEG) reinterpret_cast<float4*>(p + slot_stride - hf4 * 4)[st.lm.q[v]] = st.accn[v];
       if (st.lm.wlead[v]) {
         p[hf4 * 4 + st.lm.hd[v]] = st.m[v];
         p[hf4 * 4 + H + st.lm.hd[v]] = st.z[v];
+        if (NEG) p[hf4 * 4 + 2 * H + st.lm.hd[v]] = st.zn[v];
       }
     }
   }
@@ -195,6 +235,11 @@ struct GatFwdOp {
       st.z[v] = st.z[v] * s1 + zi * s2;
       scale4(st.acc[v], s1);
       fma4(st.acc[v], s2, ai);
+      if (NEG) {
+        st.zn[v] = st.zn[v] * s1 + p[hf4 * 4 + 2 * H + st.lm.hd[v]] * s2;
+        scale4(st.accn[v], s1);
+        fma4(st.accn[v], s2, reinterpret_cast<const float4*>(p + slot_stride - hf4 * 4)[st.lm.q[v]]);
+      }
       st.m[v] = mn;
     }
   }
@@ -259,14 +304,20 @@ k_gat_rowstat(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, c
   }
 }
 
-// Same statistics when the forward added a bias to `out`: the row term uses out - bias, and the
-// bias gradient sum_r grad[r,:] is accumulated on the way (a lane owns the same columns in every
-// row; fixed-order fold per CTA into part[cta][hf4], then over CTAs by k_bias_grad_final).
+// The same statistics in one pass with everything the layer's backward needs from the destination rows:
+//  * bias != NULL: the forward added it to `out`, so the row term uses out - bias, and the bias gradient
+//    sum_r grad[r,:] is accumulated on the way (a lane owns the same columns in every row; fixed-order
+//    fold per CTA into part[cta][hf4], then over CTAs by k_bias_grad_final);
+//  * out_neg != NULL: grad_attn_row[r,h] = (1 - slope) * (S * a_neg - <grad, out_neg>), which equals the
+//    sum over the row's edges of alpha (g - S) (slope where the LeakyReLU is on its negative side) of the
+//    reference (fused_backward_kernel, fused_gatconv_kernel.cu:931-957) with no per-edge array;
+//  * grad_copy != NULL: grad is also written there (the buffer that the other ranks read on the sharded path).
 template <int VPL>
 __global__ void __launch_bounds__(DGNN_THREADS)
-k_gat_rowstat_bias(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, const float* edge_max,
+k_gat_rowstat_full(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, const float* edge_max,
                    const float* edge_sum, const float4* out, const float4* grad, const float4* bias,
-                   float4* pack, float4* part) {
+                   const float4* out_neg, const float* a_neg, float one_minus_slope,
+                   float4* pack, float* grad_attn_row, float4* grad_copy, float4* part) {
   extern __shared__ float4 rs_sm[];   // [DGNN_WARPS][hf4]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   LaneMap<VPL> lm;
@@ -274,40 +325,46 @@ k_gat_rowstat_bias(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_r
   float4 b4[VPL], gsum[VPL];
 #pragma unroll
   for (int v = 0; v < VPL; ++v) {
-    b4[v] = lm.act[v] ? ld4(bias + lm.q[v]) : zero4();
+    b4[v] = (bias && lm.act[v]) ? ld4(bias + lm.q[v]) : zero4();
     gsum[v] = zero4();
   }
   const i64 stride = (i64)gridDim.x * DGNN_WARPS;
   for (i64 r = (i64)blockIdx.x * DGNN_WARPS + warp; r < n_rows; r += stride) {
-    float s[VPL];
+    float s[VPL], t[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       s[v] = 0.f;
+      t[v] = 0.f;
       if (lm.act[v]) {
         const float4 g = ld4(grad + r * hf4 + lm.q[v]);
         float4 o = ld4(out + r * hf4 + lm.q[v]);
         o.x -= b4[v].x; o.y -= b4[v].y; o.z -= b4[v].z; o.w -= b4[v].w;
         s[v] = dot4(g, o);
+        if (out_neg) t[v] = dot4(g, ld4(out_neg + r * hf4 + lm.q[v]));
+        if (grad_copy) grad_copy[r * hf4 + lm.q[v]] = g;
         add4(gsum[v], g);
       }
     }
     head_reduce<VPL>(s, f4_shift);
+    if (out_neg) head_reduce<VPL>(t, f4_shift);
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (lm.lead[v]) {
         const i64 i = r * H + lm.hd[v];
         pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), 1.f / __ldg(edge_sum + i), s[v]);
+        if (out_neg) grad_attn_row[i] = one_minus_slope * (s[v] * __ldg(a_neg + i) - t[v]);
       }
     }
   }
+  if (!part) return;
 #pragma unroll
   for (int v = 0; v < VPL; ++v)
     if (lm.act[v]) rs_sm[warp * hf4 + lm.q[v]] = gsum[v];
   __syncthreads();
   for (int i = threadIdx.x; i < hf4; i += DGNN_THREADS) {
-    float4 t = zero4();
-    for (int w = 0; w < DGNN_WARPS; ++w) add4(t, rs_sm[w * hf4 + i]);
-    part[(i64)blockIdx.x * hf4 + i] = t;
+    float4 t4 = zero4();
+    for (int w = 0; w < DGNN_WARPS; ++w) add4(t4, rs_sm[w * hf4 + i]);
+    part[(i64)blockIdx.x * hf4 + i] = t4;
   }
 }
 
@@ -436,7 +493,7 @@ struct GatBwdOp {
           de = l < 0.f ? de * slope : de;
           st.gc[v] += de;
           fma4(st.acc[v], alpha * kp, g4[u][v]);
-          if (st.lm.lead[v]) grad_edge[(i64)pp[u] * H + st.lm.hd[v]] = de;
+          if (grad_edge && st.lm.lead[v]) grad_edge[(i64)pp[u] * H + st.lm.hd[v]] = de;
         }
       }
     }
@@ -447,7 +504,8 @@ struct GatBwdOp {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
-      const int my_p = lane < cnt ? __ldg(permute + base + lane) : 0;
+      // without a permutation the mask (if any) is laid out in CSC order: the position is the index
+      const int my_p = lane < cnt ? (permute ? __ldg(permute + base + lane) : (int)(base + lane)) : 0;
       int k = 0;
       for (; k + STEP <= cnt; k += STEP) batch<true>(st, my_r, my_p, k, cnt);
       if (k < cnt) batch<false>(st, my_r, my_p, k, cnt);
@@ -499,7 +557,7 @@ k_gat_bwd_cols_generic(i64 n_cols, int H, int F, const void* col_ptr, int idx_bi
   float gc = 0.f;
   for (i64 e = lb; e < hb; ++e) {
     const i64 r = row_ind[e];
-    const i64 pp = permute[e];
+    const i64 pp = permute ? (i64)permute[e] : e;
     const float4 pk = pack[r * H + h];
     float d = 0.f;
     for (int f = lane; f < F; f += 32)
@@ -511,7 +569,7 @@ k_gat_bwd_cols_generic(i64 n_cols, int H, int F, const void* col_ptr, int idx_bi
     float de = alpha * (d * kp - pk.w);
     if (l < 0.f) de *= slope;
     gc += de;
-    if (lane == 0) grad_edge[pp * H + h] = de;
+    if (lane == 0 && grad_edge) grad_edge[pp * H + h] = de;
   }
   if (lane == 0) grad_attn_col[c * H + h] = gc;
   for (int fb = lane; fb < F; fb += 32) {
@@ -519,7 +577,7 @@ k_gat_bwd_cols_generic(i64 n_cols, int H, int F, const void* col_ptr, int idx_bi
     for (i64 e = lb; e < hb; ++e) {
       const i64 r = row_ind[e];
       const float4 pk = pack[r * H + h];
-      const float kp = (!mask || __ldg(mask + (i64)permute[e] * H + h) > drop_p) ? inv_keep : 0.f;
+      const float kp = (!mask || __ldg(mask + (permute ? (i64)permute[e] : e) * H + h) > drop_p) ? inv_keep : 0.f;
       const float alpha = expf(leaky(pk.x + ac, slope) - pk.y) * pk.z;
       acc = fmaf(alpha * kp, __ldg(grad_out + (r * H + h) * F + fb), acc);
     }
@@ -603,14 +661,18 @@ inline FastShape fast_shape(int h, int f) {
   return s;
 }
 
-inline i64 fwd_slot_stride(int h, int f) { return (i64)h * f + up4(2 * (i64)h); }
+// floats per forward partial / carried-state slot; `neg` adds the negative-side accumulators
+inline i64 fwd_slot_stride(int h, int f, bool neg) {
+  return neg ? 2 * (i64)h * f + up4(3 * (i64)h) : (i64)h * f + up4(2 * (i64)h);
+}
 inline i64 bwd_slot_stride(int h, int f) { return (i64)h * f + up4((i64)h); }
 
 template <class Op>
 int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const void* row_ptr, int idx_bits,
                   const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
                   float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
-                  void* ws, float* state, int first, int last, const float* bias, cudaStream_t s) {
+                  void* ws, float* state, int first, int last, const float* bias, float* out_neg, float* a_neg,
+                  cudaStream_t s) {
   Op op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -618,9 +680,11 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
   op.in_feat = reinterpret_cast<const float4*>(in_feat); op.mask = mask;
   op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
   op.out = reinterpret_cast<float4*>(out); op.edge_max = edge_max; op.edge_sum = edge_sum;
-  op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER); op.slot_stride = fwd_slot_stride(h, f);
+  op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER);
+  op.slot_stride = fwd_slot_stride(h, f, out_neg != nullptr);
   op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last) ? 1 : 0;
   op.bias = reinterpret_cast<const float4*>(bias);
+  op.out_neg = reinterpret_cast<float4*>(out_neg); op.a_neg = a_neg;
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
@@ -628,12 +692,12 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
 // layout (gat_sh.cuh); everything else the plain one.
 inline bool same_head_layout(const FastShape& fs) { return fs.vpl > 1 && (1 << fs.f4_shift) >= fs.vpl; }
 
-template <int VPL, bool MASK, bool FULL, int LPR, class... A>
+template <int VPL, bool MASK, bool FULL, int LPR, bool NEG, class... A>
 int launch_fwd(const FastShape& fs, A... a) {
   if constexpr (VPL > 1) {
-    if (same_head_layout(fs)) return launch_fwd_op<GatFwdOpSH<VPL, MASK, FULL>>(fs, a...);
+    if (same_head_layout(fs)) return launch_fwd_op<GatFwdOpSH<VPL, MASK, FULL, NEG>>(fs, a...);
   }
-  return launch_fwd_op<GatFwdOp<VPL, MASK, FULL, LPR>>(fs, a...);
+  return launch_fwd_op<GatFwdOp<VPL, MASK, FULL, LPR, NEG>>(fs, a...);
 }
 
 template <class Op>
@@ -682,15 +746,17 @@ int launch_bwd(const FastShape& fs, A... a) {
 struct BwdLayout {
   size_t counter, grad_edge, col_part, row_part, pack, total;
 };
-inline BwdLayout bwd_layout(i64 n_rows, i64 nnz, int h, int f) {
+// `edge`: room for the per-edge term d_e and the long-row partials of its row reduction (only the entry
+// points that return grad_attn_row from the column pass need them)
+inline BwdLayout bwd_layout(i64 n_rows, i64 nnz, int h, int f, bool edge) {
   BwdLayout L;
   const i64 nc = dgnn_num_chunks(nnz);
   size_t off = 0;
   L.counter = off;   off += DGNN_WS_HEADER;
-  L.grad_edge = off; off += up256((size_t)nnz * h * sizeof(float));
+  L.grad_edge = off; off += edge ? up256((size_t)nnz * h * sizeof(float)) : 0;
   L.col_part = off;  off += up256((size_t)(2 * nc) * bwd_slot_stride(h, f) * sizeof(float));
-  L.row_part = off;  off += up256((size_t)(2 * nc) * h * sizeof(float));
-  L.pack = off;      off += up256((size_t)n_rows * h * 4 * sizeof(float));
+  L.row_part = off;  off += edge ? up256((size_t)(2 * nc) * h * sizeof(float)) : 0;
+  L.pack = off;      off += edge ? up256((size_t)n_rows * h * 4 * sizeof(float)) : 0;
   L.total = off + 256;
   return L;
 }
@@ -707,15 +773,17 @@ int check_common(i64 n, i64 nnz, int h, int f, int idx_bits) {
 
 extern "C" {
 
+int dgnn_gat_fast_shape(int h, int f) { return (h > 0 && f > 0 && fast_shape(h, f).ok) ? 1 : 0; }
+
 size_t dgnn_gat_forward_workspace_bytes(int64_t n_rows, int64_t nnz, int h, int f) {
   (void)n_rows;
   if (nnz <= DGNN_SEG || h <= 0 || f <= 0) return DGNN_WS_HEADER;
-  return DGNN_WS_HEADER + up256((size_t)(2 * dgnn_num_chunks(nnz)) * fwd_slot_stride(h, f) * sizeof(float));
+  return DGNN_WS_HEADER + up256((size_t)(2 * dgnn_num_chunks(nnz)) * fwd_slot_stride(h, f, true) * sizeof(float));
 }
 
 size_t dgnn_gat_forward_state_bytes(int64_t n_rows, int h, int f) {
   if (n_rows < 0 || h <= 0 || f <= 0) return 0;
-  return (size_t)n_rows * fwd_slot_stride(h, f) * sizeof(float);
+  return (size_t)n_rows * fwd_slot_stride(h, f, true) * sizeof(float);
 }
 size_t dgnn_gat_backward_state_bytes(int64_t n_cols, int h, int f) {
   if (n_cols < 0 || h <= 0 || f <= 0) return 0;
@@ -728,21 +796,22 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_
                      float* out, float* edge_max, float* edge_sum, void* workspace,
                      size_t workspace_bytes, void* stream) {
   return dgnn_gat_forward_staged(n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,
-                                 negative_slope, attn_drop, edge_mask, nullptr, out, edge_max, edge_sum, nullptr, 1, 1,
-                                 workspace, workspace_bytes, stream);
+                                 negative_slope, attn_drop, edge_mask, nullptr, out, edge_max, edge_sum, nullptr,
+                                 nullptr, nullptr, 1, 1, workspace, workspace_bytes, stream);
 }
 
 int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
                             const int32_t* col_ind, const float* attn_row, const float* attn_col,
                             const float* in_feat, float negative_slope, float attn_drop,
                             const float* edge_mask, const float* bias, float* out, float* edge_max,
-                            float* edge_sum, float* state, int first, int last, void* workspace,
-                            size_t workspace_bytes, void* stream) {
+                            float* edge_sum, float* out_neg, float* a_neg, float* state, int first, int last,
+                            void* workspace, size_t workspace_bytes, void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
   const bool staged = !(first && last);
   if (staged && (!state || !aligned16(state))) return state ? DGNN_ERR_ALIGN : DGNN_ERR_NULL;
   if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
+  if ((out_neg == nullptr) != (a_neg == nullptr)) return DGNN_ERR_NULL;
   if (n_rows == 0) return DGNN_OK;
   if (!row_ptr || !attn_row || (last && !out) || (nnz > 0 && (!col_ind || !attn_col || !in_feat))) return DGNN_ERR_NULL;
   if ((edge_max == nullptr) != (edge_sum == nullptr)) return DGNN_ERR_NULL;
@@ -750,17 +819,21 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
   const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const FastShape fs = fast_shape(h, f);
-  if (fs.ok && aligned16(in_feat) && aligned16(out) && aligned16(bias)) {
+  if (fs.ok && aligned16(in_feat) && aligned16(out) && aligned16(bias) && aligned16(out_neg)) {
     if (!workspace || workspace_bytes < dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f))
       return DGNN_ERR_WORKSPACE;
     if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
-#define CALL_FWD(V, M, FW, L)                                                                        \
-  launch_fwd<V, M, FW, L>(fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,   \
-                   negative_slope, attn_drop, mask, out, edge_max, edge_sum, workspace, state, first, last, bias, s)
+#define FWD_ARGS                                                                                             \
+  fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, negative_slope, attn_drop, \
+      mask, out, edge_max, edge_sum, workspace, state, first, last, bias, out_neg, a_neg, s
+#define CALL_FWD(V, M, FW, L) \
+  (out_neg ? launch_fwd<V, M, FW, L, true>(FWD_ARGS) : launch_fwd<V, M, FW, L, false>(FWD_ARGS))
     DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_FWD)
 #undef CALL_FWD
+#undef FWD_ARGS
   }
-  if (staged || bias) return DGNN_ERR_SHAPE;   // staged sweeps and the bias epilogue exist only for the float4 layout
+  // staged sweeps, the bias epilogue and the negative-side outputs exist only for the float4 layout
+  if (staged || bias || out_neg) return DGNN_ERR_SHAPE;
   k_gat_fwd_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
       n_rows, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, mask, negative_slope,
       attn_drop, (float)(1.0 / (1.0 - (double)attn_drop)), out, edge_max, edge_sum);
@@ -801,19 +874,23 @@ size_t dgnn_gat_rowstat_bias_workspace_bytes(int h, int f) {
   return up256((size_t)148 * 8 * h * f * sizeof(float)) + 256;    // room for up to 1184 CTAs
 }
 
-int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f, const float* attn_row, const float* edge_max,
+int dgnn_gat_rowstat_full(int64_t n_rows, int h, int f, const float* attn_row, const float* edge_max,
                           const float* edge_sum, const float* out, const float* grad_out, const float* bias,
-                          float* pack, float* grad_bias, void* workspace, size_t workspace_bytes, void* stream) {
+                          const float* out_neg, const float* a_neg, float negative_slope, float* pack,
+                          float* grad_attn_row, float* grad_bias, float* grad_copy, void* workspace,
+                          size_t workspace_bytes, void* stream) {
   if (n_rows < 0 || h <= 0 || f <= 0) return DGNN_ERR_SHAPE;
-  if (!bias || !grad_bias) return DGNN_ERR_NULL;
+  if ((bias == nullptr) != (grad_bias == nullptr)) return DGNN_ERR_NULL;
+  if ((out_neg == nullptr) != (a_neg == nullptr) || (out_neg == nullptr) != (grad_attn_row == nullptr)) return DGNN_ERR_NULL;
   if (n_rows > 0 && (!attn_row || !edge_max || !edge_sum || !out || !grad_out || !pack)) return DGNN_ERR_NULL;
   const FastShape fs = fast_shape(h, f);
   if (!fs.ok) return DGNN_ERR_SHAPE;
-  if (!aligned16(pack) || !aligned16(out) || !aligned16(grad_out) || !aligned16(bias) || !aligned16(grad_bias))
+  if (!aligned16(pack) || !aligned16(out) || !aligned16(grad_out) || !aligned16(bias) || !aligned16(grad_bias) ||
+      !aligned16(out_neg) || !aligned16(grad_copy))
     return DGNN_ERR_ALIGN;
-  if (!workspace || workspace_bytes < dgnn_gat_rowstat_bias_workspace_bytes(h, f)) return DGNN_ERR_WORKSPACE;
+  if (bias && (!workspace || workspace_bytes < dgnn_gat_rowstat_bias_workspace_bytes(h, f))) return DGNN_ERR_WORKSPACE;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  float4* part = reinterpret_cast<float4*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  float4* part = bias ? reinterpret_cast<float4*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255)) : nullptr;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -825,22 +902,42 @@ int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f, const float* attn_row, c
   const float4* o4 = reinterpret_cast<const float4*>(out);
   const float4* g4 = reinterpret_cast<const float4*>(grad_out);
   const float4* b4 = reinterpret_cast<const float4*>(bias);
+  const float4* n4 = reinterpret_cast<const float4*>(out_neg);
   float4* pk = reinterpret_cast<float4*>(pack);
+  float4* gc4 = reinterpret_cast<float4*>(grad_copy);
+  const float oms = 1.f - negative_slope;
+#define ROWSTAT(V)                                                                                              \
+  k_gat_rowstat_full<V><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row,     \
+      edge_max, edge_sum, o4, g4, b4, n4, a_neg, oms, pk, grad_attn_row, gc4, part)
   switch (fs.vpl) {
-    case 1: k_gat_rowstat_bias<1><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
-    case 2: k_gat_rowstat_bias<2><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
-    case 4: k_gat_rowstat_bias<4><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
-    default: k_gat_rowstat_bias<8><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row, edge_max, edge_sum, o4, g4, b4, pk, part); break;
+    case 1: ROWSTAT(1); break;
+    case 2: ROWSTAT(2); break;
+    case 4: ROWSTAT(4); break;
+    default: ROWSTAT(8); break;
   }
-  k_bias_grad_final<<<dgnn_grid(fs.hf4, 128), 128, 0, s>>>((int)ctas, fs.hf4, part, reinterpret_cast<float4*>(grad_bias));
+#undef ROWSTAT
+  if (bias) k_bias_grad_final<<<dgnn_grid(fs.hf4, 128), 128, 0, s>>>((int)ctas, fs.hf4, part, reinterpret_cast<float4*>(grad_bias));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f, const float* attn_row, const float* edge_max,
+                          const float* edge_sum, const float* out, const float* grad_out, const float* bias,
+                          float* pack, float* grad_bias, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!bias || !grad_bias) return DGNN_ERR_NULL;
+  return dgnn_gat_rowstat_full(n_rows, h, f, attn_row, edge_max, edge_sum, out, grad_out, bias, nullptr, nullptr, 0.f,
+                               pack, nullptr, grad_bias, nullptr, workspace, workspace_bytes, stream);
 }
 
 size_t dgnn_gat_backward_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f) {
   (void)n_cols;
   if (n_rows < 0 || nnz < 0 || h <= 0 || f <= 0) return 256;
-  return bwd_layout(n_rows, nnz, h, f).total;
+  return bwd_layout(n_rows, nnz, h, f, true).total;
+}
+
+size_t dgnn_gat_backward_cols_workspace_bytes(int64_t nnz, int h, int f, int with_grad_attn_row) {
+  if (nnz < 0 || h <= 0 || f <= 0) return 256;
+  return bwd_layout(0, nnz, h, f, with_grad_attn_row != 0).total;
 }
 
 int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f, const void* row_ptr,
@@ -867,18 +964,19 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
   if (staged && (!state || !aligned16(state))) return state ? DGNN_ERR_ALIGN : DGNN_ERR_NULL;
   st = check_common(n_cols, nnz, h, f, idx_bits);
   if (st) return st;
-  if (nnz > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;  // permute is int32
+  if (nnz > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;  // CSR / CSC positions are int32
   if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
-  if (!row_ptr || !col_ptr) return DGNN_ERR_NULL;
+  const bool edge = grad_attn_row != nullptr;   // the per-edge term and its row reduction are wanted
+  if (!col_ptr || (edge && !row_ptr)) return DGNN_ERR_NULL;
   if (n_cols > 0 && (!in_feat || !attn_col || (last && (!grad_feat || !grad_attn_col)))) return DGNN_ERR_NULL;
-  if (n_rows > 0 && (!pack || !grad_out || !grad_attn_row)) return DGNN_ERR_NULL;
-  if (nnz > 0 && (!row_ind || !permute)) return DGNN_ERR_NULL;
+  if (n_rows > 0 && (!pack || !grad_out)) return DGNN_ERR_NULL;
+  if (nnz > 0 && (!row_ind || (edge && !permute))) return DGNN_ERR_NULL;
   if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
-  const BwdLayout L = bwd_layout(n_rows, nnz, h, f);
-  if (!workspace || workspace_bytes < L.total) return DGNN_ERR_WORKSPACE;
+  const BwdLayout L = bwd_layout(n_rows, nnz, h, f, edge);
+  if (!workspace || workspace_bytes < bwd_layout(0, nnz, h, f, edge).total) return DGNN_ERR_WORKSPACE;
   if (!aligned16(pack)) return DGNN_ERR_ALIGN;
   char* wsb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
-  float* grad_edge = reinterpret_cast<float*>(wsb + L.grad_edge);
+  float* grad_edge = edge ? reinterpret_cast<float*>(wsb + L.grad_edge) : nullptr;
   float* col_part = reinterpret_cast<float*>(wsb + L.col_part);
   float* row_part = reinterpret_cast<float*>(wsb + L.row_part);
   unsigned long long* counter = reinterpret_cast<unsigned long long*>(wsb + L.counter);
@@ -904,7 +1002,7 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
           (float)(1.0 / (1.0 - (double)attn_drop)), grad_feat, grad_attn_col, grad_edge);
     }
   }
-  if (n_rows > 0) {
+  if (edge && n_rows > 0) {
     const int tb = 256;
     const int small = nnz <= DGNN_SMALL_NNZ ? 1 : 0;   // same rule as the feature kernels: one launch for small graphs
     k_rowred_rows<<<dgnn_grid(n_rows * h, tb), tb, 0, s>>>(n_rows, h, row_ptr, idx_bits, grad_edge, grad_attn_row, small);
@@ -927,7 +1025,8 @@ int dgnn_gat_backward(int64_t n, int64_t nnz, int h, int f, const void* row_ptr,
   int st = check_common(n, nnz, h, f, idx_bits);
   if (st) return st;
   if (n == 0) return DGNN_OK;
-  const BwdLayout L = bwd_layout(n, nnz, h, f);
+  if (!grad_attn_row) return DGNN_ERR_NULL;
+  const BwdLayout L = bwd_layout(n, nnz, h, f, true);
   if (!workspace || workspace_bytes < L.total) return DGNN_ERR_WORKSPACE;
   char* wsb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
   float* pack = reinterpret_cast<float*>(wsb + L.pack);

@@ -48,7 +48,9 @@ __device__ __forceinline__ void lanes_reduce(float (&d)[U], int lph_shift) {
 }
 
 // ------------------------------------------------------------------ forward
-template <int VPL, bool MASK, bool FULL>
+// NEG: also accumulate the part of the row's result that comes from edges on the negative side of
+// the LeakyReLU (out_neg, a_neg); the backward derives grad_attn_row from it without a per-edge array.
+template <int VPL, bool MASK, bool FULL, bool NEG>
 struct GatFwdOpSH {
   static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
   static constexpr bool HAS_PARTIALS = true;
@@ -71,11 +73,14 @@ struct GatFwdOpSH {
   float* state;
   int first, last, skip_empty;
   const float4* bias;
+  float4* out_neg;
+  float* a_neg;
 
   struct State {
     HeadLanes<VPL> lm;
-    float ar, m, z;
+    float ar, m, z, zn;
     float4 acc[VPL];
+    float4 accn[NEG ? VPL : 1];
   };
 
   __device__ __forceinline__ void init(State& st, i64 r, int lane) const {
@@ -83,8 +88,13 @@ struct GatFwdOpSH {
     st.ar = st.lm.act ? __ldg(attn_row + r * H + st.lm.hd) : 0.f;
     st.m = DGNN_NEG_INIT;
     st.z = 0.f;
+    st.zn = 0.f;
 #pragma unroll
     for (int v = 0; v < VPL; ++v) st.acc[v] = zero4();
+    if (NEG) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) st.accn[v] = zero4();
+    }
   }
   __device__ __forceinline__ void resume(State& st, i64 r, int lane) const {
     if (!first) merge_partial(st, state + r * slot_stride, lane);
@@ -108,7 +118,6 @@ struct GatFwdOpSH {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4(in_feat + (i64)c[u] * hf4 + st.lm.q[v]) : zero4();
     }
-    if (!FULL && !st.lm.act) return;
     float l[U];
     float bm = st.m;
 #pragma unroll
@@ -116,19 +125,36 @@ struct GatFwdOpSH {
       l[u] = (ALL || k + u < cnt) ? leaky(st.ar + s[u], slope) : DGNN_NEG_INIT;
       bm = fmaxf(bm, l[u]);
     }
-    const float sc = fast_exp(st.m - bm);  // 1 when the maximum did not move
-    st.z *= sc;
+    // after the first few edges of a row the running maximum rarely moves: rescale only when it did
+    // for some head of the warp (a lane whose maximum stayed multiplies by exp(0) = 1, as before)
+    const bool moved = __any_sync(DGNN_FULL, bm > st.m);
+    if (!FULL && !st.lm.act) { st.m = bm; return; }
+    if (moved) {
+      const float sc = fast_exp(st.m - bm);
+      st.z *= sc;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) scale4(st.acc[v], sc);
-    st.m = bm;
+      for (int v = 0; v < VPL; ++v) scale4(st.acc[v], sc);
+      if (NEG) {
+        st.zn *= sc;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) scale4(st.accn[v], sc);
+      }
+      st.m = bm;
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (ALL || k + u < cnt) {
         const float p = fast_exp(l[u] - bm);
         st.z += p;
+        const float pn = l[u] < 0.f ? p : 0.f;
+        if (NEG) st.zn += pn;
         if (!MASK || keep[u]) {
 #pragma unroll
           for (int v = 0; v < VPL; ++v) fma4(st.acc[v], p, x[u][v]);
+          if (NEG) {
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) fma4(st.accn[v], pn, x[u][v]);
+          }
         }
       }
     }
@@ -155,12 +181,22 @@ struct GatFwdOpSH {
       if (bias) add4(a, __ldg(bias + st.lm.q[v]));
       out[r * hf4 + st.lm.q[v]] = a;
     }
+    if (NEG) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        float4 a = st.accn[v];
+        scale4(a, sc);
+        out_neg[r * hf4 + st.lm.q[v]] = a;
+      }
+    }
     if (st.lm.lead && edge_max) {
       edge_max[r * H + st.lm.hd] = st.m;
       edge_sum[r * H + st.lm.hd] = st.z;
     }
+    if (NEG && st.lm.lead) a_neg[r * H + st.lm.hd] = st.z > 0.f ? st.zn / st.z : 0.f;
   }
 
+  // slot layout: [acc H*F | m H | z H | (NEG: zn H) | pad to 4 | (NEG: accn H*F)]
   __device__ __forceinline__ void store_partial(State& st, float* p, int) const {
     if (!st.lm.act) return;
 #pragma unroll
@@ -168,6 +204,12 @@ struct GatFwdOpSH {
     if (st.lm.lead) {
       p[hf4 * 4 + st.lm.hd] = st.m;
       p[hf4 * 4 + H + st.lm.hd] = st.z;
+      if (NEG) p[hf4 * 4 + 2 * H + st.lm.hd] = st.zn;
+    }
+    if (NEG) {
+      float4* pn = reinterpret_cast<float4*>(p + slot_stride - hf4 * 4);
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) pn[st.lm.q[v]] = st.accn[v];
     }
   }
 
@@ -182,6 +224,15 @@ struct GatFwdOpSH {
     for (int v = 0; v < VPL; ++v) {
       scale4(st.acc[v], s1);
       fma4(st.acc[v], s2, reinterpret_cast<const float4*>(p)[st.lm.q[v]]);
+    }
+    if (NEG) {
+      st.zn = st.zn * s1 + p[hf4 * 4 + 2 * H + st.lm.hd] * s2;
+      const float4* pn = reinterpret_cast<const float4*>(p + slot_stride - hf4 * 4);
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        scale4(st.accn[v], s1);
+        fma4(st.accn[v], s2, pn[st.lm.q[v]]);
+      }
     }
     st.m = mn;
   }
@@ -274,7 +325,7 @@ struct GatBwdOpSH {
         const float w = alpha * kp;
 #pragma unroll
         for (int v = 0; v < VPL; ++v) fma4(st.acc[v], w, g4[u][v]);
-        if (st.lm.lead) grad_edge[(i64)pp[u] * H + st.lm.hd] = de;
+        if (grad_edge && st.lm.lead) grad_edge[(i64)pp[u] * H + st.lm.hd] = de;
       }
     }
   }
@@ -283,7 +334,8 @@ struct GatBwdOpSH {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
-      const int my_p = lane < cnt ? __ldg(permute + base + lane) : 0;
+      // without a permutation the mask (if any) is laid out in CSC order: the position is the index
+      const int my_p = lane < cnt ? (permute ? __ldg(permute + base + lane) : (int)(base + lane)) : 0;
       int k = 0;
       for (; k + U <= cnt; k += U) batch<true>(st, my_r, my_p, k, cnt);
       if (k < cnt) batch<false>(st, my_r, my_p, k, cnt);

@@ -1,21 +1,25 @@
-"""Destination-row-block sharding of the fused GAT operator over torch.distributed.
+"""Row-block sharding of the fused GAT layer over the GPUs of one NVLink domain.
 
-The reference is single-GPU.  Here rank g owns a contiguous block of nodes:
+The reference is single-GPU.  Here the nodes are relabelled by a seeded random permutation and dealt
+out in equal blocks, one per rank (in-edges, out-edges and node counts are balanced at once):
 
-  forward   rank g aggregates its destination rows A[block_g, :] and needs
-            attn_col and in_feat of every source node  -> two all-gathers;
-  backward  rank g owns the same nodes as SOURCE columns, A[:, block_g]: it
-            needs grad_out and the row statistics pack of every destination
-            row (two all-gathers) and produces grad_feat / grad_attn_col for
-            its own nodes with no reduction; grad_attn_row comes out as
-            per-rank partial sums over all rows -> one all-reduce of [N,H].
+  forward   rank g aggregates the destination rows it owns, A[block_g, :], and needs the projected
+            features and the source attention term of every node its in-edges reference;
+  backward  rank g owns the same nodes as SOURCE columns, A[:, block_g], and needs grad_out and the
+            row statistics `pack` of every destination its out-edges reference.  grad_feat and
+            grad_attn_col come out column-owned; grad_attn_row is computed by the row owner from its
+            own rows (kernels.gat_rowstat_full), so nothing is reduced across ranks.
 
-Blocks are chosen by a cost prefix (in-edges for the forward, out-edges for the
-backward, a per-node term for the dense projection around the operator), so
-they hold different node counts; the all-gathers therefore move uneven row
-ranges straight into their place in one [N, ...] buffer (node ids stay global,
-nothing is padded).  Gathered tensors land in this GPU's own memory before any
-kernel reads them.
+Only the DISTINCT referenced rows travel ("halo"): on an R-MAT graph of 2.4 M nodes / 120 M edges a
+rank of 8 references 0.88 M of the 2.1 M remote nodes (0.74 M of 1.2 M with 2 ranks).  Every rank
+keeps, per gathered tensor, one buffer [own rows | halo rows]; its graph arrays index that buffer.
+The own rows are written in place by the producing kernels (projection, logits, row statistics), a
+barrier says "every rank's own rows are written", and the halo rows are then fetched from the owners'
+buffers by kernels.halo_pull (plain loads over NVLink from symmetric memory, on a side stream) chunk
+by chunk, while the aggregation kernels sweep the edges whose rows are already there: stage 0 = edges
+between own nodes (no transfer needed), stage k = edges whose far end lies in halo chunk k.  The
+per-row softmax state (forward) / per-column accumulators (backward) are carried between the sweeps
+by the staged kernels.  No kernel waits on another rank; no multicast; no TMA on peer memory.
 """
 from __future__ import annotations
 
@@ -26,191 +30,54 @@ import torch.distributed as dist
 
 from . import kernels
 
-# relative cost of one in-edge (forward gather), one out-edge (backward gather) and
-# one node (projection GEMM + elementwise work of the layer), measured on a B200
-COST_IN_EDGE, COST_OUT_EDGE, COST_NODE = 1.0, 2.8, 40.0
-
-
-def balanced_node_blocks(row_ptr: torch.Tensor, world: int, col_ptr: torch.Tensor | None = None,
-                         node_cost: float = 0.0) -> list[int]:
-    """Boundaries b[0..world] of contiguous node blocks with about equal cost.
-    With only `row_ptr` the cost of a node is its in-degree (equal in-edge counts);
-    with `col_ptr` the out-degree and a per-node term are added with the weights above."""
-    rp = row_ptr.long()
-    n = rp.numel() - 1
-    if col_ptr is None:
-        prefix = rp.to(torch.float64)
-    else:
-        cp = col_ptr.long()
-        ids = torch.arange(n + 1, device=rp.device, dtype=torch.float64)
-        prefix = COST_IN_EDGE * rp.to(torch.float64) + COST_OUT_EDGE * cp.to(torch.float64) + node_cost * ids
-    total = float(prefix[-1])
-    targets = torch.tensor([total * g / world for g in range(1, world)], dtype=torch.float64, device=rp.device)
-    inner = torch.searchsorted(prefix[:-1].contiguous(), targets, right=False).tolist() if world > 1 else []
-    bounds = [0] + [min(max(int(b), 0), n) for b in inner] + [n]
-    for i in range(1, len(bounds)):          # keep the boundaries monotone
-        bounds[i] = max(bounds[i], bounds[i - 1])
-    return bounds
-
-
-@dataclass
-class GatShard:
-    """Per-rank graph pieces; node ids are global."""
-    rank: int
-    world: int
-    bounds: list          # node block boundaries, len world+1
-    n: int                # number of nodes of the whole graph
-    n_loc: int
-    # forward: local destination rows x all source columns
-    fwd_row_ptr: torch.Tensor
-    fwd_col_ind: torch.Tensor
-    # backward: all destination rows x local source columns
-    bwd_row_ptr: torch.Tensor   # CSR index pointer of the block, over all rows
-    bwd_col_ptr: torch.Tensor   # CSC index pointer, local columns
-    bwd_row_ind: torch.Tensor   # row id of each CSC entry
-    bwd_permute: torch.Tensor   # CSR position (within the block) of each CSC entry
-
-
-def build_shard(row_ptr, col_ind, rank, world, csr2csc=None, bounds=None) -> GatShard:
-    """Cut rank's pieces out of the global CSR (rows = destinations).  `csr2csc`
-    is the conversion routine (defaults to the CUDA kernel); every rank calls
-    this with the same global graph."""
-    csr2csc = csr2csc or kernels.csr2csc
-    rp = row_ptr.long()
-    n = rp.numel() - 1
-    ptr_dtype = row_ptr.dtype
-    col_ptr, row_ind, _ = csr2csc(row_ptr, col_ind)
-    cp = col_ptr.long()
-    bounds = bounds or balanced_node_blocks(rp, world, cp, COST_NODE)
-    r0, r1 = bounds[rank], bounds[rank + 1]
-    # forward piece: rows r0..r1 of the CSR
-    lo, hi = int(rp[r0]), int(rp[r1])
-    fwd_row_ptr = (rp[r0:r1 + 1] - lo).to(ptr_dtype).contiguous()
-    fwd_col_ind = col_ind[lo:hi].to(torch.int32).contiguous()
-    # backward piece: columns r0..r1 of the CSC
-    clo, chi = int(cp[r0]), int(cp[r1])
-    bwd_col_ptr = (cp[r0:r1 + 1] - clo).to(ptr_dtype).contiguous()
-    bwd_row_ind = row_ind[clo:chi].to(torch.int32).contiguous()
-    # CSR of the block = "CSC" of its transpose; perm[i] = CSC position of CSR entry i
-    bwd_row_ptr, _, perm = csr2csc(bwd_col_ptr, bwd_row_ind, n)
-    permute = torch.empty_like(perm)
-    permute[perm.long()] = torch.arange(perm.numel(), dtype=perm.dtype, device=perm.device)
-    return GatShard(rank, world, bounds, n, r1 - r0, fwd_row_ptr, fwd_col_ind,
-                    bwd_row_ptr.to(ptr_dtype).contiguous(), bwd_col_ptr, bwd_row_ind, permute.to(torch.int32).contiguous())
-
-
-def _all_gather_rows(x_loc: torch.Tensor, bounds: list, group) -> torch.Tensor:
-    """[n_loc, ...] on every rank -> [N, ...]: rank g's rows land at bounds[g]:bounds[g+1]."""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    out = x_loc.new_empty((bounds[-1],) + tuple(x_loc.shape[1:]))
-    views = [out[bounds[g]: bounds[g + 1]] for g in range(world)]
-    x_loc = x_loc.contiguous()
-    if dist.get_backend(group) == "nccl":
-        # uneven row ranges: NCCL runs this as one group of broadcasts straight into the views
-        dist.all_gather(views, x_loc, group=group)
-    else:
-        views[rank].copy_(x_loc)
-        for g in range(world):
-            if views[g].numel():
-                dist.broadcast(views[g], src=dist.get_global_rank(group, g) if group is not None else g, group=group)
-    return out
-
-
-def _sharded_forward(attn_row, attn_col, in_feat, shard, negative_slope, group, backend):
-    attn_col_all = _all_gather_rows(attn_col, shard.bounds, group)
-    feat_all = _all_gather_rows(in_feat, shard.bounds, group)
-    return backend.gat_forward(attn_row, attn_col_all, shard.fwd_row_ptr, shard.fwd_col_ind, negative_slope, feat_all)
-
-
-def _sharded_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum, grad_out, shard, negative_slope, group,
-                      backend):
-    pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)      # [n_loc,H,4]
-    pack_all = _all_gather_rows(pack, shard.bounds, group)
-    grad_all = _all_gather_rows(grad_out, shard.bounds, group)
-    grad_feat, grad_row_part, grad_col = backend.gat_backward_cols(
-        shard.bwd_row_ptr, shard.bwd_col_ptr, shard.bwd_row_ind, shard.bwd_permute, pack_all, None,
-        in_feat, attn_col, grad_all, negative_slope)
-    dist.all_reduce(grad_row_part, group=group)
-    r0, r1 = shard.bounds[shard.rank], shard.bounds[shard.rank + 1]
-    return grad_feat, grad_row_part[r0:r1].contiguous(), grad_col
-
-
-class ShardedGATFunction(torch.autograd.Function):
-    """Fused GAT on this rank's node block.  Inputs and outputs are the local
-    rows: attn_row, attn_col [n_loc,H], in_feat [n_loc,H,F] -> out [n_loc,H,F]."""
-
-    @staticmethod
-    def forward(ctx, attn_row, attn_col, in_feat, shard, negative_slope, group, backend):
-        out, edge_max, edge_sum = _sharded_forward(attn_row, attn_col, in_feat, shard, negative_slope, group, backend)
-        ctx.save_for_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum)
-        ctx.shard, ctx.slope, ctx.group, ctx.backend = shard, negative_slope, group, backend
-        return out
-
-    @staticmethod
-    def backward(ctx, grad_out):
-        attn_row, attn_col, in_feat, out, edge_max, edge_sum = ctx.saved_tensors
-        grad_feat, grad_row, grad_col = _sharded_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum,
-                                                         grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group,
-                                                         ctx.backend)
-        return grad_row, grad_col, grad_feat, None, None, None, None
-
-
-class ShardedGATLayerFunction(torch.autograd.Function):
-    """Attention logits + sharded aggregation as one autograd node (CUDA only):
-    h [n_loc,H,F], attn_l, attn_r [1,H,F] -> out [n_loc,H,F]."""
-
-    @staticmethod
-    def forward(ctx, h, attn_l, attn_r, shard, negative_slope, group):
-        h = h.contiguous()
-        attn_row, attn_col = kernels.gat_logits_forward(h, attn_l, attn_r)
-        out, edge_max, edge_sum = _sharded_forward(attn_row, attn_col, h, shard, negative_slope, group, kernels)
-        ctx.save_for_backward(attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r)
-        ctx.shard, ctx.slope, ctx.group = shard, negative_slope, group
-        return out
-
-    @staticmethod
-    def backward(ctx, grad_out):
-        attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r = ctx.saved_tensors
-        grad_h, grad_row, grad_col = _sharded_backward(attn_row, attn_col, h, out, edge_max, edge_sum,
-                                                      grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group, kernels)
-        grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_row, grad_col, grad_h)
-        return grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None
-
-
-def sharded_gat(attn_row, attn_col, in_feat, shard, negative_slope=0.2, group=None, backend=kernels):
-    """out_loc = fused GAT over the sharded graph; differentiable in the three tensors."""
-    return ShardedGATFunction.apply(attn_row, attn_col, in_feat, shard, negative_slope, group, backend)
-
-
-def sharded_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None):
-    """Logits + sharded aggregation; differentiable in h and the attention vectors."""
-    return ShardedGATLayerFunction.apply(h, attn_l, attn_r, shard, negative_slope, group)
+HALO_SHIFT = 27          # codes = owner << 27 | row inside the owner's block (dgnn_halo_rank_shift)
+HALO_MAX_RANKS = 16      # dgnn_halo_max_ranks
 
 
 # ---------------------------------------------------------------------------
-# Pipelined sharding: random node relabelling, equal blocks, staged all-gathers
+# graph pieces of one rank
 # ---------------------------------------------------------------------------
 @dataclass
-class PipeShard:
-    """Pieces of the graph for one rank of the pipelined sharded operator.
+class HaloSide:
+    """One direction of a rank's sub-matrix, cut into sweeps (stages).
 
-    Nodes are relabelled by a seeded random permutation and dealt out in equal
-    blocks of `blk` nodes per rank (ids past the real node count are padding
-    without edges), so in-edges, out-edges and node counts are all balanced.
-    Every block is cut into `stages` slices; stage p all-gathers slice p of every
-    rank ([world*slice, ...] buffer, row g*slice + i = node i of rank g's slice p)
-    while the kernels work on the edges of stage p-1."""
+    forward:  segments = destination rows of the block, entries = their in-edges, `ind` = buffer row
+              of the source;  backward: segments = source columns of the block, entries = their
+              out-edges, `ind` = buffer row of the destination.  Buffer rows 0..blk-1 are the rank's
+              own nodes, row blk+i is halo row i."""
+    n_halo: int
+    codes: torch.Tensor               # [n_halo] int32: owner << HALO_SHIFT | row in the owner's block
+    chunk_off: list                   # halo rows of chunk c are chunk_off[c]:chunk_off[c+1]
+    ptr: list                         # per stage: index pointer [blk+1] int32
+    ind: list                         # per stage: buffer row of every entry, int32
+    edge_id: list | None = None       # per stage: position of the entry in the CSR of the whole graph (int32)
+
+
+@dataclass
+class HaloShard:
     rank: int
     world: int
-    stages: int
-    n: int
-    blk: int
-    slice: int
-    local_ids: torch.Tensor       # original node id of every local row (-1 for padding)
-    fwd: list                     # per stage: (row_ptr [blk+1], col_ind -> buffer row)
-    bwd: list                     # per stage: (row_ptr [world*slice+1], col_ptr [blk+1], row_ind -> buffer row, permute)
-    peer: object = None           # PeerGather when the slices travel as peer-to-peer copies instead of all-gathers
+    stages: int                       # sweeps per pass: stage 0 = own nodes, 1.. = halo chunks (1 stage: everything)
+    n: int                            # nodes of the whole graph
+    blk: int                          # nodes per rank (the last ids of the padded id space carry no node)
+    local_ids: torch.Tensor           # original node id of every local row (-1 for padding)
+    fwd: HaloSide = None
+    bwd: HaloSide = None
+
+    @property
+    def chunks(self):
+        return max(self.stages - 1, 1)
+
+    def chunk_stage(self, c):
+        """The stage that needs halo chunk c."""
+        return c + 1 if self.stages > 1 else 0
+
+    def scatter_rows(self, x_global):
+        """Rows of a global [N, ...] tensor in this rank's local order (padding rows are zero)."""
+        out = x_global.new_zeros((self.blk,) + tuple(x_global.shape[1:]))
+        real = self.local_ids >= 0
+        out[real] = x_global[self.local_ids[real]]
+        return out
 
 
 def _expand_segments(ptr, ids):
@@ -225,60 +92,92 @@ def _expand_segments(ptr, ids):
     return pos, seg
 
 
-def build_pipe_shard(row_ptr, col_ind, rank, world, stages=4, seed=0, csr2csc=None) -> PipeShard:
-    """Every rank calls this with the same global CSR (rows = destinations) and seed."""
+def _build_side(ptr, ind, edge_pos, local_ids, inv, rank, blk, n_pad, stages, want_ids) -> HaloSide:
+    dev = ind.device
+    chunks = max(stages - 1, 1)
+    pos, seg = _expand_segments(ptr, local_ids)
+    other = inv[ind[pos].long()]                                   # relabelled id of the far end
+    own = (other // blk) == rank
+    uniq = torch.unique(other[~own])                               # ascending = (owner, row in block)
+    u_chunk = ((uniq % blk) * chunks) // blk                       # position slice inside the owner's block
+    order = torch.argsort(u_chunk * n_pad + uniq)                  # chunk-major, then owner, then row
+    place = torch.empty_like(order)
+    place[order] = torch.arange(order.numel(), device=dev)         # halo row of uniq[i]
+    codes = (((uniq // blk) << HALO_SHIFT) | (uniq % blk))[order].to(torch.int32).contiguous()
+    counts = torch.bincount(u_chunk, minlength=chunks).tolist() if uniq.numel() else [0] * chunks
+    chunk_off = [0]
+    for c in counts:
+        chunk_off.append(chunk_off[-1] + int(c))
+    buf = other % blk
+    stage = torch.zeros_like(other)
+    if uniq.numel():
+        rem = ~own
+        hidx = torch.searchsorted(uniq, other[rem])
+        buf[rem] = blk + place[hidx]
+        if stages > 1:
+            stage[rem] = 1 + u_chunk[hidx]
+    ptrs, inds, ids = [], [], []
+    eid = pos if edge_pos is None else edge_pos[pos].long()
+    for p in range(stages):
+        m = stage == p
+        sp = torch.zeros(blk + 1, dtype=torch.long, device=dev)
+        torch.cumsum(torch.bincount(seg[m], minlength=blk), 0, out=sp[1:])
+        ptrs.append(sp.to(torch.int32))
+        inds.append(buf[m].to(torch.int32).contiguous())
+        if want_ids:
+            ids.append(eid[m].to(torch.int32).contiguous())
+    return HaloSide(int(uniq.numel()), codes, chunk_off, ptrs, inds, ids if want_ids else None)
+
+
+def build_halo_shard(row_ptr, col_ind, rank, world, stages=3, seed=0, csr2csc=None, edge_ids=False,
+                     relabel=True) -> HaloShard:
+    """Cut rank's pieces out of the global CSR (rows = destinations).  Every rank calls this with the same
+    graph, seed and options.  `edge_ids` keeps, for every local entry, its position in the global CSR (needed
+    for attention dropout: the mask of an edge is a function of that position, the same on the rank that
+    holds the edge in its forward piece and on the rank that holds it in its backward piece).
+    relabel=False keeps the node order (contiguous equal blocks)."""
+    if world > HALO_MAX_RANKS:
+        raise ValueError(f"dgnn_b200: at most {HALO_MAX_RANKS} ranks")
     csr2csc = csr2csc or kernels.csr2csc
     dev = col_ind.device
     rp = row_ptr.long()
     n = rp.numel() - 1
-    blk = -(-n // (world * stages)) * stages
-    sl = blk // stages
+    if col_ind.numel() >= 2**31:
+        raise ValueError("dgnn_b200: edge positions are int32")
+    blk = max(-(-n // world), 1)
+    if blk > (1 << HALO_SHIFT):
+        raise ValueError("dgnn_b200: block too large for the halo row codes")
     n_pad = world * blk
-    g = torch.Generator(device="cpu").manual_seed(seed)
     order = torch.full((n_pad,), -1, dtype=torch.long)
-    order[:n] = torch.randperm(n, generator=g)
-    order = order[torch.randperm(n_pad, generator=g)].to(dev)        # padding spread over all blocks
+    if relabel:
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        order[:n] = torch.randperm(n, generator=g)
+        order = order[torch.randperm(n_pad, generator=g)]            # padding spread over all blocks
+    else:
+        order[:n] = torch.arange(n)
+    order = order.to(dev)
     inv = torch.empty(n, dtype=torch.long, device=dev)
     real = order >= 0
     inv[order[real]] = torch.arange(n_pad, device=dev)[real]
     local_ids = order[rank * blk: (rank + 1) * blk].contiguous()
+    shard = HaloShard(rank, world, int(stages), n, blk, local_ids)
+    shard.fwd = _build_side(rp, col_ind, None, local_ids, inv, rank, blk, n_pad, stages, edge_ids)
+    col_ptr, row_ind, permute = csr2csc(row_ptr, col_ind)
+    shard.bwd = _build_side(col_ptr.long(), row_ind, permute if edge_ids else None, local_ids, inv, rank, blk, n_pad,
+                            stages, edge_ids)
+    return shard
 
-    def buffer_row(new_id):
-        """(stage, row inside the stage's gathered buffer) of a relabelled node id."""
-        owner, rem = new_id // blk, new_id % blk
-        return rem // sl, owner * sl + rem % sl
 
-    # forward: local destination rows, all sources, split by the stage of the source
-    pos, row = _expand_segments(rp, local_ids)
-    stage, buf = buffer_row(inv[col_ind[pos].long()])
-    fwd = []
-    for p in range(stages):
-        m = stage == p
-        ptr = torch.zeros(blk + 1, dtype=torch.long, device=dev)
-        torch.cumsum(torch.bincount(row[m], minlength=blk), 0, out=ptr[1:])
-        fwd.append((ptr.to(torch.int32), buf[m].to(torch.int32).contiguous()))
-    del pos, row, stage, buf
-    # backward: local source columns, all destinations, split by the stage of the destination
-    col_ptr, row_ind, _ = csr2csc(row_ptr, col_ind)
-    pos, col = _expand_segments(col_ptr.long(), local_ids)
-    stage, buf = buffer_row(inv[row_ind[pos].long()])
-    bwd = []
-    for p in range(stages):
-        m = stage == p
-        cptr = torch.zeros(blk + 1, dtype=torch.long, device=dev)
-        torch.cumsum(torch.bincount(col[m], minlength=blk), 0, out=cptr[1:])
-        cptr = cptr.to(torch.int32)
-        rind = buf[m].to(torch.int32).contiguous()
-        # CSR of the sub-matrix = "CSC" of its transpose; perm[i] = CSC position of CSR entry i
-        rptr, _, perm = csr2csc(cptr, rind, world * sl)
-        permute = torch.empty_like(perm)
-        permute[perm.long()] = torch.arange(perm.numel(), dtype=perm.dtype, device=perm.device)
-        bwd.append((rptr.to(torch.int32).contiguous(), cptr, rind, permute.to(torch.int32).contiguous()))
-    return PipeShard(rank, world, stages, n, blk, sl, local_ids, fwd, bwd)
+# ---------------------------------------------------------------------------
+# transports: where the buffers live and how halo rows arrive
+# ---------------------------------------------------------------------------
+class _Done:
+    def wait(self):
+        pass
 
 
 class _StreamEvent:
-    """Stands in for the Work object of an asynchronous collective: wait() orders the current stream after it."""
+    """wait() orders the current stream after the event."""
 
     def __init__(self, event):
         self.event = event
@@ -287,229 +186,413 @@ class _StreamEvent:
         torch.cuda.current_stream().wait_event(self.event)
 
 
-class PeerGather:
-    """Slices fetched from the peers' memory by copy engines instead of an NCCL all-gather.
+def _decode(codes):
+    c = codes.long()
+    return c >> HALO_SHIFT, c & ((1 << HALO_SHIFT) - 1)
 
-    Every rank keeps one staging buffer per gathered tensor in symmetric memory (torch.distributed's
-    allocator: every rank can map every other rank's buffer over NVLink).  A gather is: copy the local
-    block into the staging buffer, a one-element NCCL all-reduce as the barrier ("every rank's block is
-    written"), then plain device-to-device copies of slice p of every peer into this rank's
-    [world*slice, ...] buffer on a copy stream, peers visited in rotated order so that each peer serves
-    one reader at a time.  The copies take no SM away from the kernels they overlap with and reach the
-    NVLink rate of a peer copy; an all-reduce before the next overwrite of the staging buffer makes
-    sure every peer has finished reading it.  No multicast, no kernel of this library touches peer memory."""
 
-    def __init__(self, group):
-        import os
-        # the copies are plain peer reads: no multicast object is needed, and none should be bound to the buffers
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        self.group = group
-        self.stream = torch.cuda.Stream()
-        self.own_stream = torch.cuda.Stream()   # local rows go on their own stream, beside the peer copies
-        self.staging = {}
-        self.flag = None
+class GatherTransport:
+    """Fallback that needs nothing but torch.distributed collectives (gloo on CPU, NCCL without symmetric
+    memory): the own blocks are all-gathered and the halo rows picked out of the result."""
 
-    def _staging(self, tag, x_loc):
-        import torch.distributed._symmetric_memory as symm
-        key = (tag, tuple(x_loc.shape), x_loc.dtype)
-        if key not in self.staging:          # collective: every rank reaches this in the same order
-            buf = symm.empty(tuple(x_loc.shape), dtype=x_loc.dtype, device=x_loc.device)
-            handle = symm.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
-            self.staging[key] = (buf, handle, {})
-        return self.staging[key]
+    def __init__(self, shard, group=None):
+        self.shard, self.group = shard, group
+        self.caps = (shard.fwd.n_halo, shard.bwd.n_halo)
 
-    def _barrier(self, dev):
-        if self.flag is None:
-            self.flag = torch.zeros(1, dtype=torch.float32, device=dev)
-        dist.all_reduce(self.flag, group=self.group)
+    def empty(self, tag, rows, tail, device):
+        return torch.empty((rows,) + tuple(tail), dtype=torch.float32, device=device)
 
-    def gather_many(self, items, shard):
-        """items: [(tag, x_loc [blk, ...]), ...] -> [(buffers, works), ...], one barrier pair for all of them."""
-        dev = items[0][1].device
-        cur = torch.cuda.current_stream()
-        staged = [self._staging(tag, x) for tag, x in items]
-        self._barrier(dev)                    # every peer has finished reading the previous content
-        for (buf, _, _), (_, x) in zip(staged, items):
-            buf.copy_(x)
-        self._barrier(dev)                    # every rank's blocks are in place
+    def barrier(self):
+        pass
+
+    def start_pulls(self, side, bufs, tags):
+        sh = self.shard
+        owner, loc = _decode(side.codes)
+        for buf in bufs:
+            own = buf[:sh.blk].contiguous()
+            full = own.new_empty((sh.world,) + tuple(own.shape))
+            dist.all_gather_into_tensor(full.view(-1, *own.shape[1:]), own, group=self.group)
+            buf[sh.blk: sh.blk + side.n_halo] = full[owner, loc]
+        return [_Done() for _ in range(sh.chunks)]
+
+
+class PullTransport:
+    """Halo rows fetched out of the owners' buffers by kernels.halo_pull on a side stream (CUDA), chunk by
+    chunk.  Sub-classes say where the owners' buffers are: `SymmetricTransport` (one process per GPU,
+    torch.distributed symmetric memory: every rank maps every other rank's buffer over NVLink) and
+    `LocalTransport` (all ranks emulated in one process on one device, for tests)."""
+
+    def __init__(self, shard, pull_ctas=0):
+        self.shard = shard
+        self.pull_ctas = int(pull_ctas)
+        self.stream = None
+        self.status = None
+
+    # -- to be provided --
+    def owners(self, tag):
+        raise NotImplementedError
+
+    def barrier(self):
+        raise NotImplementedError
+
+    # -- shared --
+    def start_pulls(self, side, bufs, tags):
+        sh = self.shard
+        if side.n_halo == 0:
+            return [_Done() for _ in range(sh.chunks)]
+        srcs = [self.owners(t) for t in tags]
+        if not bufs[0].is_cuda:                                   # emulation on the CPU: plain indexing
+            owner, loc = _decode(side.codes)
+            for buf, src in zip(bufs, srcs):
+                stacked = torch.stack([s[:sh.blk] for s in src], 0)
+                buf[sh.blk: sh.blk + side.n_halo] = stacked[owner, loc]
+            return [_Done() for _ in range(sh.chunks)]
+        dev = bufs[0].device
+        if self.stream is None:
+            self.stream = torch.cuda.Stream(device=dev, priority=-1)
+            self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         ready = torch.cuda.Event()
-        ready.record(cur)
-        results = []
-        for _, x in items:
-            tail = tuple(x.shape[1:])
-            results.append(([x.new_empty((shard.world * shard.slice,) + tail) for _ in range(shard.stages)], []))
-        lo, hi = shard.rank * shard.slice, (shard.rank + 1) * shard.slice
-        entered = torch.cuda.Event()
-        entered.record(cur)
-        with torch.cuda.stream(self.own_stream):          # this rank's own rows of every stage buffer
-            self.own_stream.wait_event(entered)
-            for (_, x), (bufs, _) in zip(items, results):
-                for p in range(shard.stages):
-                    bufs[p][lo:hi].copy_(x[p * shard.slice:(p + 1) * shard.slice], non_blocking=True)
-            own_done = torch.cuda.Event()
-            own_done.record(self.own_stream)
+        ready.record(torch.cuda.current_stream(dev))
+        works = []
+        own_views = [[s[:sh.blk] for s in src] for src in srcs]
         with torch.cuda.stream(self.stream):
             self.stream.wait_event(ready)
-            for p in range(shard.stages):
-                sl = slice(p * shard.slice, (p + 1) * shard.slice)
-                for (buf, handle, views), (_, x), (bufs, works) in zip(staged, items, results):
-                    for i in range(1, shard.world):
-                        q = (shard.rank + i) % shard.world
-                        if q not in views:
-                            views[q] = handle.get_buffer(q, tuple(x.shape), x.dtype)
-                        bufs[p][q * shard.slice:(q + 1) * shard.slice].copy_(views[q][sl], non_blocking=True)
-                    if p == 0:
-                        self.stream.wait_event(own_done)
-                    ev = torch.cuda.Event()
-                    ev.record(self.stream)
-                    works.append(_StreamEvent(ev))
-        for (_, x), (bufs, _) in zip(items, results):
-            x.record_stream(self.own_stream)
-            for bb in bufs:
-                bb.record_stream(self.stream)
-                bb.record_stream(self.own_stream)
-        return results
+            for c in range(sh.chunks):
+                lo, hi = side.chunk_off[c], side.chunk_off[c + 1]
+                if hi > lo:
+                    dsts = [b[sh.blk + lo: sh.blk + hi] for b in bufs]
+                    kernels.halo_pull(side.codes[lo:hi], own_views[0], dsts[0],
+                                      own_views[1] if len(bufs) > 1 else None, dsts[1] if len(bufs) > 1 else None,
+                                      max_ctas=self.pull_ctas, status=self.status)
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+                works.append(_StreamEvent(ev))
+        return works
+
+    def check(self):
+        """Raise if a fetch met a row code outside its owner's block (synchronises)."""
+        if self.status is not None and int(self.status.item()) != 0:
+            raise RuntimeError("dgnn_b200: a halo fetch skipped rows whose code lies outside the owner's block")
 
 
-def _gather_many(items, shard, group):
-    """Start the gathers of the `stages` slices of several [blk, ...] tensors; [(buffers, works), ...]."""
-    if shard.peer is not None and items[0][1].is_cuda and shard.world > 1:
-        return shard.peer.gather_many([(tag, x.contiguous()) for tag, x in items], shard)
-    return [_gather_slices(x, shard, group) for _, x in items]
+class LocalTransport(PullTransport):
+    """All ranks in one process on one device: `registry[rank][tag]` holds every emulated rank's buffer.  The
+    caller runs the phases of all ranks in lockstep (prepare on every rank, then sweep on every rank), which is
+    what the barrier stands for."""
+
+    def __init__(self, shard, registry, pull_ctas=0):
+        super().__init__(shard, pull_ctas)
+        self.registry = registry
+        self.caps = None            # set by the caller: (max forward halo, max backward halo) over all ranks
+
+    def empty(self, tag, rows, tail, device):
+        buf = torch.empty((rows,) + tuple(tail), dtype=torch.float32, device=device)
+        self.registry.setdefault(self.shard.rank, {})[tag] = buf
+        return buf
+
+    def owners(self, tag):
+        return [self.registry[r][tag] for r in range(self.shard.world)]
+
+    def barrier(self):
+        pass
 
 
-def _gather_slices(x_loc, shard, group):
-    """Start the all-gathers of the `stages` slices of x_loc [blk, ...]; returns (buffers, works)."""
-    bufs, works = [], []
-    for p in range(shard.stages):
-        part = x_loc[p * shard.slice: (p + 1) * shard.slice]
-        buf = x_loc.new_empty((shard.world * shard.slice,) + tuple(x_loc.shape[1:]))
-        works.append(dist.all_gather_into_tensor(buf, part.contiguous(), group=group, async_op=True))
-        bufs.append(buf)
-    return bufs, works
+class SymmetricTransport(PullTransport):
+    """One process per GPU.  The buffers live in torch.distributed's symmetric memory, so the producing kernels
+    write where the peers read; the barrier is a one-element NCCL all-reduce on the compute stream.  Two barriers
+    per training step (one per pass) also keep a rank from overwriting rows that a peer is still fetching: a
+    rank's writes of pass k+1 come after its barrier of pass k, which every peer enters only after its own sweeps
+    -- and therefore its fetches -- of the pass before.  No multicast object is created."""
+
+    def __init__(self, shard, group=None, pull_ctas=0):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads only
+        super().__init__(shard, pull_ctas)
+        self.group = group if group is not None else dist.group.WORLD
+        dev = shard.local_ids.device
+        caps = torch.tensor([shard.fwd.n_halo, shard.bwd.n_halo], dtype=torch.int64, device=dev)
+        dist.all_reduce(caps, op=dist.ReduceOp.MAX, group=self.group)     # symmetric buffers have one size on all ranks
+        self.caps = (int(caps[0]), int(caps[1]))
+        self.flag = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.peers = {}
+
+    def empty(self, tag, rows, tail, device):
+        import torch.distributed._symmetric_memory as symm
+        shape = (rows,) + tuple(tail)
+        buf = symm.empty(shape, dtype=torch.float32, device=device)
+        handle = symm.rendezvous(buf, self.group)                          # collective: same order on every rank
+        self.peers[tag] = [buf if q == self.shard.rank else handle.get_buffer(q, shape, torch.float32)
+                           for q in range(self.shard.world)]
+        return buf
+
+    def owners(self, tag):
+        return self.peers[tag]
+
+    def barrier(self):
+        dist.all_reduce(self.flag, group=self.group)
 
 
-def _pipe_forward(attn_row, attn_col, h, shard, slope, group, backend, bias=None):
-    (col_bufs, col_works), (feat_bufs, feat_works) = _gather_many([("attn_col", attn_col), ("feat", h)], shard, group)
-    state = backend.gat_forward_state(shard.blk, h.shape[1], h.shape[2], h.device)
-    res = None
-    for p in range(shard.stages):
-        col_works[p].wait()
-        feat_works[p].wait()
-        ptr, col = shard.fwd[p]
-        last = p == shard.stages - 1
-        extra = {"bias": bias} if (bias is not None and last) else {}
-        res = backend.gat_forward_staged(attn_row, col_bufs[p], ptr, col, slope, feat_bufs[p], state, p == 0, last, **extra)
-    return res
-
-
-def _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum, grad_out, shard, slope, group, backend, pack=None):
-    if pack is None:
-        pack = backend.gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out)
-    (pack_bufs, pack_works), (grad_bufs, grad_works) = _gather_many([("pack", pack), ("grad_out", grad_out)], shard, group)
-    state = backend.gat_backward_state(shard.blk, h.shape[1], h.shape[2], h.device)
-    parts = []
-    grad_feat = grad_col = None
-    for p in range(shard.stages):
-        pack_works[p].wait()
-        grad_works[p].wait()
-        rptr, cptr, rind, perm = shard.bwd[p]
-        part, grad_feat, grad_col = backend.gat_backward_cols_staged(
-            rptr, cptr, rind, perm, pack_bufs[p], h, attn_col, grad_bufs[p], slope, state, p == 0,
-            p == shard.stages - 1)
-        parts.append(part)                                     # [world*slice, H]: partial sums for the rows of stage p
-    hh = h.shape[1]
-    # [stages, world, slice, H] -> sum over ranks, keep the rows this rank owns
-    allp = torch.stack(parts, 0).view(shard.stages, shard.world, shard.slice, hh)
-    if dist.get_backend(group) == "nccl":
-        send = allp.permute(1, 0, 2, 3).contiguous()           # [world, stages, slice, H]
-        mine = send.new_empty((shard.stages, shard.slice, hh))
-        dist.reduce_scatter_tensor(mine, send, group=group)
-    else:
-        allp = allp.contiguous()
-        dist.all_reduce(allp, group=group)
-        mine = allp[:, shard.rank]
-    return grad_feat, mine.reshape(shard.blk, hh).contiguous(), grad_col
-
-
-class PipelinedGATFunction(torch.autograd.Function):
-    """Fused GAT on this rank's block of the relabelled graph, with the gathers of the
-    source features (forward) and of grad_out (backward) overlapped with the kernels.
-    attn_row, attn_col [blk,H], in_feat [blk,H,F] (rows in PipeShard.local_ids order)."""
-
-    @staticmethod
-    def forward(ctx, attn_row, attn_col, in_feat, shard, negative_slope, group, backend):
-        out, edge_max, edge_sum = _pipe_forward(attn_row.contiguous(), attn_col.contiguous(), in_feat.contiguous(),
-                                                shard, negative_slope, group, backend)
-        ctx.save_for_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum)
-        ctx.shard, ctx.slope, ctx.group, ctx.backend = shard, negative_slope, group, backend
-        return out
-
-    @staticmethod
-    def backward(ctx, grad_out):
-        attn_row, attn_col, in_feat, out, edge_max, edge_sum = ctx.saved_tensors
-        grad_feat, grad_row, grad_col = _pipe_backward(attn_row, attn_col, in_feat, out, edge_max, edge_sum,
-                                                      grad_out.contiguous(), ctx.shard, ctx.slope, ctx.group,
-                                                      ctx.backend)
-        return grad_row, grad_col, grad_feat, None, None, None, None
-
-
-class PipelinedGATLayerFunction(torch.autograd.Function):
-    """Attention logits + pipelined aggregation (+ bias in the last stage's epilogue) as one autograd
-    node (CUDA only)."""
-
-    @staticmethod
-    def forward(ctx, h, attn_l, attn_r, bias, shard, negative_slope, group):
-        h = h.contiguous()
-        attn_row, attn_col = kernels.gat_logits_forward(h, attn_l, attn_r)
-        out, edge_max, edge_sum = _pipe_forward(attn_row, attn_col, h, shard, negative_slope, group, kernels, bias=bias)
-        ctx.save_for_backward(attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r,
-                              bias if bias is not None else h.new_empty(0))
-        ctx.shard, ctx.slope, ctx.group, ctx.has_bias = shard, negative_slope, group, bias is not None
-        return out
-
-    @staticmethod
-    def backward(ctx, grad_out):
-        attn_row, attn_col, h, out, edge_max, edge_sum, attn_l, attn_r, bias = ctx.saved_tensors
-        grad_out = grad_out.contiguous()
-        pack = grad_bias = None
-        if ctx.has_bias:   # `out` carries the bias: the row statistics subtract it, its gradient falls out of the same pass
-            pack, grad_bias = kernels.gat_rowstat_bias(attn_row, edge_max, edge_sum, out, grad_out, bias)
-            grad_bias = grad_bias.view_as(bias)
-        grad_h, grad_row, grad_col = _pipe_backward(attn_row, attn_col, h, out, edge_max, edge_sum, grad_out, ctx.shard,
-                                                   ctx.slope, ctx.group, kernels, pack=pack)
-        grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_row, grad_col, grad_h)
-        return grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), grad_bias, None, None, None
-
-
-def pipelined_gat(attn_row, attn_col, in_feat, shard, negative_slope=0.2, group=None, backend=kernels):
-    return PipelinedGATFunction.apply(attn_row, attn_col, in_feat, shard, negative_slope, group, backend)
-
-
-def pipelined_gat_layer(h, attn_l, attn_r, shard, negative_slope=0.2, group=None, bias=None):
-    """h [blk,H,F] -> logits, pipelined aggregation and (optionally) the bias add, one autograd node.  Rows that
-    pad the last block also receive the bias; they carry no node."""
-    return PipelinedGATLayerFunction.apply(h, attn_l, attn_r, bias, shard, negative_slope, group)
-
-
-def enable_peer_copies(shard, group=None):
-    """Switch a PipeShard on CUDA ranks of one NVLink domain from NCCL all-gathers to peer-to-peer copies
-    (see PeerGather); returns the shard."""
-    if shard.world > 1:
-        peer = PeerGather(group)
-        try:                                   # collective probe: symmetric memory may be unavailable on a platform
-            peer._staging("probe", torch.zeros(16, dtype=torch.float32, device=shard.local_ids.device))
-        except Exception as exc:               # every rank sees the same platform, so every rank falls back together
+def make_transport(shard, group=None, pull_ctas=0):
+    """SymmetricTransport on CUDA ranks when symmetric memory works on this platform, else GatherTransport."""
+    if shard.world > 1 and shard.local_ids.is_cuda and dist.is_initialized() and dist.get_backend(group) == "nccl":
+        try:
+            t = SymmetricTransport(shard, group, pull_ctas)
+            t.empty("probe", 16, (4,), shard.local_ids.device)             # collective probe: all ranks fail together
+            return t
+        except Exception as exc:
             import warnings
-            warnings.warn(f"dgnn_b200: peer-to-peer slice copies unavailable ({exc}); using NCCL all-gathers")
-            return shard
-        shard.peer = peer
-    return shard
+            warnings.warn(f"dgnn_b200: symmetric memory unavailable ({exc}); halo rows travel through all-gathers")
+    return GatherTransport(shard, group)
 
 
-def scatter_rows(x_global, shard):
-    """Rows of a global [N, ...] tensor in this rank's local order (padding rows are zero)."""
-    out = x_global.new_zeros((shard.blk,) + tuple(x_global.shape[1:]))
-    real = shard.local_ids >= 0
-    out[real] = x_global[shard.local_ids[real]]
-    return out
+# ---------------------------------------------------------------------------
+# the sharded operator
+# ---------------------------------------------------------------------------
+class HaloContext:
+    """Buffers and settings of one sharded GAT layer instance: [own | halo] buffers for the features and the
+    source attention term (forward) and for grad_out and the row statistics (backward).  One forward may be
+    in flight per context: the backward reads what the forward left in the buffers."""
+
+    def __init__(self, shard, transport, heads, width, negative_slope=0.2, backend=kernels, tag="gat"):
+        self.shard, self.transport, self.backend = shard, transport, backend
+        self.h, self.f, self.slope = int(heads), int(width), float(negative_slope)
+        dev = shard.local_ids.device
+        cap_f, cap_b = transport.caps
+        blk = shard.blk
+        self.X = transport.empty(tag + ".x", blk + cap_f, (heads, width), dev)
+        self.AC = transport.empty(tag + ".ac", blk + cap_f, (heads,), dev)
+        self.G = transport.empty(tag + ".g", blk + cap_b, (heads, width), dev)
+        self.PK = transport.empty(tag + ".pk", blk + cap_b, (heads, 4), dev)
+        self.tags = (tag + ".x", tag + ".ac", tag + ".g", tag + ".pk")
+        self.version = 0
+        self.exposed_ms = None        # set by measure_waits(): events around every wait for a halo chunk
+
+    @property
+    def h_own(self):
+        """[blk, H, F] view of the feature buffer's own rows: let the projection write here."""
+        return self.X.detach()[:self.shard.blk]      # detached: writes through it leave no autograd history on the buffer
+
+
+def _masks(ctx, side, attn_drop, seed):
+    if not attn_drop > 0.0:
+        return [None] * len(side.ptr)
+    if side.edge_id is None:
+        raise RuntimeError("dgnn_b200: attention dropout on the sharded layer needs build_halo_shard(edge_ids=True)")
+    return [ctx.backend.uniform_fill_edges(e, ctx.h, seed) for e in side.edge_id]
+
+
+def halo_forward_prepare(ctx: HaloContext, h=None, attn_l=None, attn_r=None, attn_row=None, attn_col=None):
+    """Write this rank's own rows of the forward buffers.  Layer form: h [blk,H,F] (copied unless it already is
+    ctx.h_own) and the attention vectors -> logits computed here.  Operator form: attn_row / attn_col given."""
+    blk = ctx.shard.blk
+    if h.data_ptr() != ctx.X.data_ptr():
+        ctx.X[:blk].copy_(h)
+    if attn_l is not None:
+        attn_row, _ = ctx.backend.gat_logits_forward(ctx.X[:blk], attn_l, attn_r, out_col=ctx.AC[:blk])
+    else:
+        ctx.AC[:blk].copy_(attn_col)
+    ctx.version += 1
+    return attn_row
+
+
+def halo_forward_sweep(ctx: HaloContext, attn_row, bias=None, attn_drop=0.0, seed=0, train=True):
+    """Fetch the halo chunks and sweep the stages.  Returns (out, edge_max, edge_sum, out_neg, a_neg); the last
+    four are None when train is False."""
+    sh, be = ctx.shard, ctx.backend
+    works = ctx.transport.start_pulls(sh.fwd, [ctx.X, ctx.AC], ctx.tags[0:2])
+    masks = _masks(ctx, sh.fwd, attn_drop, seed)
+    state = be.gat_forward_state(sh.blk, ctx.h, ctx.f, ctx.X.device)
+    waited, res = 0, None
+    for p in range(sh.stages):
+        while waited < sh.chunks and sh.chunk_stage(waited) <= p:
+            _timed_wait(ctx, works[waited], "fwd", waited)
+            waited += 1
+        last = p == sh.stages - 1
+        res = be.gat_forward_staged(attn_row, ctx.AC, sh.fwd.ptr[p], sh.fwd.ind[p], ctx.slope, ctx.X, state, p == 0, last,
+                                    bias=bias if last else None, attn_drop=attn_drop, edge_mask=masks[p], neg=train,
+                                    save_stats=train)
+    if train:
+        return res
+    return res[0], None, None, None, None
+
+
+def halo_backward_prepare(ctx: HaloContext, attn_row, edge_max, edge_sum, out, out_neg, a_neg, grad_out, bias=None):
+    """Row statistics of the own rows into the backward buffers; returns (grad_attn_row, grad_bias)."""
+    blk = ctx.shard.blk
+    _, grad_row, grad_bias = ctx.backend.gat_rowstat_full(attn_row, edge_max, edge_sum, out, grad_out, ctx.slope, bias=bias,
+                                                          out_neg=out_neg, a_neg=a_neg, pack=ctx.PK[:blk],
+                                                          grad_copy=ctx.G[:blk])
+    return grad_row, grad_bias
+
+
+def halo_backward_sweep(ctx: HaloContext, attn_drop=0.0, seed=0):
+    """Fetch the halo chunks of grad_out / pack and sweep the stages over this rank's source columns.
+    Returns (grad_feat [blk,H,F], grad_attn_col [blk,H])."""
+    sh, be = ctx.shard, ctx.backend
+    works = ctx.transport.start_pulls(sh.bwd, [ctx.G, ctx.PK], ctx.tags[2:4])
+    masks = _masks(ctx, sh.bwd, attn_drop, seed)
+    state = be.gat_backward_state(sh.blk, ctx.h, ctx.f, ctx.X.device)
+    waited = 0
+    grad_feat = grad_col = None
+    for p in range(sh.stages):
+        while waited < sh.chunks and sh.chunk_stage(waited) <= p:
+            _timed_wait(ctx, works[waited], "bwd", waited)
+            waited += 1
+        _, grad_feat, grad_col = be.gat_backward_cols_staged(
+            None, sh.bwd.ptr[p], sh.bwd.ind[p], None, ctx.PK, ctx.X[:sh.blk], ctx.AC[:sh.blk], ctx.G, ctx.slope, state,
+            p == 0, p == sh.stages - 1, attn_drop=attn_drop, edge_mask=masks[p], row_grad=False)
+    return grad_feat, grad_col
+
+
+def _timed_wait(ctx, work, phase, chunk):
+    """wait() for a halo chunk; with ctx.exposed_ms set, bracket it with events so that the time the compute
+    stream spends waiting for the transfer can be reported."""
+    if ctx.exposed_ms is None or not ctx.X.is_cuda:
+        work.wait()
+        return
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    work.wait()
+    b.record()
+    ctx.exposed_ms.append((phase, chunk, a, b))
+
+
+class HaloGATFunction(torch.autograd.Function):
+    """Fused GAT on this rank's block.  Layer form (logits=True): inputs (h, attn_l, attn_r, bias); operator form:
+    (in_feat, attn_row, attn_col, None).  Output [blk,H,F] in HaloShard.local_ids order."""
+
+    @staticmethod
+    def forward(ctx, a, b, c, bias, hc, logits, attn_drop, seed):
+        if logits:
+            attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_l=b, attn_r=c)
+        else:
+            attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_row=b.contiguous(), attn_col=c.contiguous())
+        hc.transport.barrier()
+        out, edge_max, edge_sum, out_neg, a_neg = halo_forward_sweep(hc, attn_row, bias, attn_drop, seed, train=True)
+        ctx.save_for_backward(attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c,
+                              bias if bias is not None else out.new_empty(0))
+        ctx.hc, ctx.logits, ctx.has_bias, ctx.attn_drop, ctx.seed, ctx.version = hc, logits, bias is not None, attn_drop, seed, hc.version
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        hc = ctx.hc
+        if hc.version != ctx.version:
+            raise RuntimeError("dgnn_b200: the sharded layer ran another forward before this backward; its buffers "
+                               "hold one forward at a time (use one HaloContext / layer per use in the graph)")
+        attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c, bias = ctx.saved_tensors
+        grad_row, grad_bias = halo_backward_prepare(hc, attn_row, edge_max, edge_sum, out, out_neg, a_neg,
+                                                    grad_out.contiguous(), bias if ctx.has_bias else None)
+        hc.transport.barrier()
+        grad_feat, grad_col = halo_backward_sweep(hc, ctx.attn_drop, ctx.seed)
+        if grad_bias is not None:
+            grad_bias = grad_bias.view_as(bias)
+        if ctx.logits:
+            grad_l, grad_r = hc.backend.gat_logits_backward(hc.h_own, b, c, grad_row, grad_col, grad_feat)
+            return grad_feat, grad_l.view_as(b), grad_r.view_as(c), grad_bias, None, None, None, None
+        return grad_feat, grad_row, grad_col, grad_bias, None, None, None, None
+
+
+def sharded_gat(attn_row, attn_col, in_feat, hc: HaloContext, attn_drop=0.0, seed=0):
+    """The fused operator (GATConvFuse of the reference, operators/fused_gatconv.py:6-34) on this rank's block:
+    attn_row, attn_col [blk,H], in_feat [blk,H,F] in HaloShard.local_ids order; differentiable in all three."""
+    return HaloGATFunction.apply(in_feat, attn_row, attn_col, None, hc, False, float(attn_drop), int(seed))
+
+
+def sharded_gat_layer(h, attn_l, attn_r, hc: HaloContext, bias=None, attn_drop=0.0, seed=0):
+    """Attention logits + sharded aggregation (+ bias in the last sweep's epilogue) as one autograd node."""
+    return HaloGATFunction.apply(h, attn_l, attn_r, bias, hc, True, float(attn_drop), int(seed))
+
+
+# ---------------------------------------------------------------------------
+# the layer
+# ---------------------------------------------------------------------------
+class ShardedGATConv(torch.nn.Module):
+    """GATConv of the reference (layers/gatconv_layer.py:7-92: same constructor arguments, parameter names,
+    initialisation, residual / bias / activation order) on one rank's node block of a HaloShard.
+
+    forward(feat) takes the input features of the rank's own nodes [blk, in_feats] in HaloShard.local_ids
+    order (HaloShard.scatter_rows of a global tensor) and returns [blk, heads, out_feats] in the same order.
+    Parameters are replicated: call allreduce_grads() after backward (one flat all-reduce).  Attention dropout
+    draws the mask of an edge from (seed, step, position of the edge in the whole graph's CSR), so every rank
+    sees the same mask for an edge; it needs build_halo_shard(edge_ids=True)."""
+
+    def __init__(self, in_feats, out_feats, num_heads, shard, feat_drop=0., attn_drop=0., negative_slope=0.2,
+                 residual=False, activation=None, bias=True, group=None, transport=None, seed=0, pull_ctas=0):
+        super().__init__()
+        from .layers.gatconv_layer import GATConv
+        proto = GATConv(in_feats, out_feats, num_heads, feat_drop, attn_drop, negative_slope, residual, activation, bias)
+        self.in_feats, self.out_feats, self.num_heads = in_feats, out_feats, num_heads
+        self.negative_slope, self.attn_drop, self.activation = negative_slope, attn_drop, activation
+        self.W, self.attn_l, self.attn_r = proto.W, proto.attn_l, proto.attn_r
+        self.feat_drop = proto.feat_drop
+        if proto.bias is not None:
+            self.bias = proto.bias
+        else:
+            self.register_buffer("bias", None)
+        if proto.res_fc is not None:
+            self.res_fc = proto.res_fc
+        else:
+            self.register_buffer("res_fc", None)
+        self.shard, self.group = shard, group
+        self.transport = transport if transport is not None else make_transport(shard, group, pull_ctas)
+        self.hc = None
+        self.seed, self.step = int(seed), 0
+
+    def _context(self):
+        if self.hc is None:
+            self.hc = HaloContext(self.shard, self.transport, self.num_heads, self.out_feats, self.negative_slope)
+        return self.hc
+
+    def forward(self, feat):
+        from .operators.projection import project
+        hc = self._context()
+        heads, width = self.num_heads, self.out_feats
+        plain = self.feat_drop.p == 0.0 or not self.training
+        h = project(feat, self.W, out=hc.h_own.view(self.shard.blk, heads * width) if plain else None)
+        h = self.feat_drop(h.view(-1, heads, width))
+        fuse_bias = self.bias is not None and self.res_fc is None
+        self.step += 1
+        if self.training and torch.is_grad_enabled():
+            rst = sharded_gat_layer(h, self.attn_l, self.attn_r, hc, self.bias if fuse_bias else None,
+                                    self.attn_drop, self.seed * 1000003 + self.step)
+        else:
+            with torch.no_grad():
+                attn_row = halo_forward_prepare(hc, h=h.contiguous(), attn_l=self.attn_l, attn_r=self.attn_r)
+                hc.transport.barrier()
+                rst = halo_forward_sweep(hc, attn_row, self.bias if fuse_bias else None, train=False)[0]
+        if self.res_fc is not None:
+            rst = rst + self.res_fc(h).view(-1, heads, width)       # as in the reference: applied to the projected features
+        if self.bias is not None and not fuse_bias:
+            rst = rst + self.bias.view(-1, heads, width)
+        return self.activation(rst) if self.activation else rst
+
+    def allreduce_grads(self):
+        """Sum the parameter gradients over the ranks with one all-reduce of a flat buffer."""
+        ps = [p for p in self.parameters() if p.grad is not None]
+        if not ps or self.shard.world == 1 or not dist.is_initialized():
+            return
+        flat = torch.cat([p.grad.reshape(-1) for p in ps])
+        dist.all_reduce(flat, group=self.group)
+        off = 0
+        for p in ps:
+            p.grad.copy_(flat[off: off + p.numel()].view_as(p.grad))
+            off += p.numel()
+
+
+# ---------------------------------------------------------------------------
+# EdgeConv: batched point clouds are split by batch
+# ---------------------------------------------------------------------------
+def split_clouds(points, k, rank, world, knn=None):
+    """Deal the clouds of a batch [B,P,D] to the ranks (contiguous, as equal as possible) and build this
+    rank's kNN graph with ids local to its points: returns (points_loc [B_loc,P,D], src_ind [B_loc*P*k] int32,
+    (b0, b1)).  Clouds never share edges (the caller-side loop of script/train/train_edgeconv.py:48-52 builds
+    one kNN graph per batch), so EdgeConv on the pieces needs no exchange: the per-rank outputs concatenated in
+    rank order equal the single-GPU result bit for bit."""
+    from . import graph
+    b = points.shape[0]
+    b0, b1 = (b * rank) // world, (b * (rank + 1)) // world
+    loc = points[b0:b1].contiguous()
+    knn = knn or graph.knn_graph
+    src = knn(loc, k) if b1 > b0 else torch.zeros(0, dtype=torch.int32, device=points.device)
+    return loc, src, (b0, b1)

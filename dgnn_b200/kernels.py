@@ -18,11 +18,20 @@ def _dims3(t, name):
 
 
 # ------------------------------------------------------------------- GAT
+def gat_fast_shape(h, f) -> bool:
+    """True when (h, f) runs on the float4 layout (f = 4*2^k, h*f <= 1024): the shapes that have the
+    staged sweeps, the bias epilogue and the negative-side outputs."""
+    return bool(lib().dgnn_gat_fast_shape(int(h), int(f)))
+
+
 def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop=0.0,
-                edge_mask=None, save_stats=True, bias=None):
+                edge_mask=None, save_stats=True, bias=None, neg=False):
     """Fused GAT forward.  Returns (out, edge_max, edge_sum); the statistics are
     None when save_stats is False (inference).  `bias` [H*F] is added to the output
-    inside the kernel when given."""
+    inside the kernel when given.  With neg=True (float4 layout only) two more tensors
+    follow: out_neg [N,H,F] and a_neg [N,H], the share of the result that comes from
+    edges on the negative side of the LeakyReLU (gat_rowstat_full turns them into
+    grad_attn_row)."""
     attn_row = _cuda_f32(attn_row, "attn_row")
     attn_col = _cuda_f32(attn_col, "attn_col")
     in_feat = _cuda_f32(in_feat, "in_feat")
@@ -50,18 +59,62 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
         edge_sum = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if save_stats else None
         ws_bytes = lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f)
         ws = _workspace(ws_bytes, dev)
-        if bias is None:
+        out_neg = a_neg = None
+        if neg:
+            out_neg = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
+            a_neg = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+        if bias is None and not neg:
             check(lib().dgnn_gat_forward(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
                                          _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
                                          _p(edge_mask), _p(out), _p(edge_max), _p(edge_sum), _p(ws), ws.numel(),
                                          _stream(dev)), "gat_forward")
         else:
-            bias = _cuda_f32(bias, "bias").reshape(h * f)
+            if bias is not None:
+                bias = _cuda_f32(bias, "bias").reshape(h * f)
             check(lib().dgnn_gat_forward_staged(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
                                                 _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
-                                                _p(edge_mask), _p(bias), _p(out), _p(edge_max), _p(edge_sum), None,
-                                                1, 1, _p(ws), ws.numel(), _stream(dev)), "gat_forward(bias)")
+                                                _p(edge_mask), _p(bias), _p(out), _p(edge_max), _p(edge_sum),
+                                                _p(out_neg), _p(a_neg), None,
+                                                1, 1, _p(ws), ws.numel(), _stream(dev)), "gat_forward(bias/neg)")
+    if neg:
+        return out, edge_max, edge_sum, out_neg, a_neg
     return out, edge_max, edge_sum
+
+
+def gat_rowstat_full(attn_row, edge_max, edge_sum, out, grad_out, negative_slope, bias=None, out_neg=None,
+                     a_neg=None, pack=None, grad_copy=None):
+    """One pass over the destination rows for the backward: returns (pack [N,H,4], grad_attn_row [N,H]
+    or None, grad_bias [H*F] or None).  grad_attn_row needs out_neg / a_neg of gat_forward(neg=True);
+    grad_bias needs the bias that the forward added to `out`.  `pack` and `grad_copy` (a copy of
+    grad_out) are written into the given tensors when passed (buffers that other ranks read)."""
+    out = _cuda_f32(out, "out")
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    n, h, f = _dims3(out, "out")
+    dev = out.device
+    with device_guard(dev):
+        if pack is None:
+            pack = torch.empty((n, h, 4), dtype=torch.float32, device=dev)
+        elif not (pack.is_cuda and pack.is_contiguous() and pack.dtype == torch.float32 and pack.shape == (n, h, 4)):
+            raise RuntimeError("dgnn_b200: pack must be a contiguous float32 CUDA tensor [N,H,4]")
+        if grad_copy is not None and not (grad_copy.is_cuda and grad_copy.is_contiguous()
+                                          and grad_copy.dtype == torch.float32 and grad_copy.shape == grad_out.shape):
+            raise RuntimeError("dgnn_b200: grad_copy must be a contiguous float32 CUDA tensor shaped like grad_out")
+        grad_row = grad_bias = None
+        ws = None
+        if bias is not None:
+            bias = _cuda_f32(bias, "bias").reshape(h * f)
+            grad_bias = torch.empty(h * f, dtype=torch.float32, device=dev)
+            ws = _workspace(lib().dgnn_gat_rowstat_bias_workspace_bytes(h, f), dev)
+        if out_neg is not None:
+            out_neg = _cuda_f32(out_neg, "out_neg")
+            a_neg = _cuda_f32(a_neg, "a_neg")
+            grad_row = torch.empty((n, h), dtype=torch.float32, device=dev)
+        check(lib().dgnn_gat_rowstat_full(n, h, f, _p(_cuda_f32(attn_row, "attn_row")), _p(_cuda_f32(edge_max, "edge_max")),
+                                          _p(_cuda_f32(edge_sum, "edge_sum")), _p(out), _p(grad_out), _p(bias),
+                                          _p(out_neg), _p(a_neg), float(negative_slope), _p(pack), _p(grad_row),
+                                          _p(grad_bias), _p(grad_copy), _p(ws), ws.numel() if ws is not None else 0,
+                                          _stream(dev)), "gat_rowstat_full")
+    return pack, grad_row, grad_bias
 
 
 def gat_rowstat_bias(attn_row, edge_max, edge_sum, out, grad_out, bias):
@@ -96,22 +149,30 @@ def gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out):
 
 
 def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_feat, attn_col, grad_out,
-                      negative_slope, attn_drop=0.0):
+                      negative_slope, attn_drop=0.0, row_grad=True):
     """Column pass of the backward on an [n_rows x n_cols] block (see the header).
-    Returns (grad_feat [n_cols,H,F], grad_attn_row [n_rows,H], grad_attn_col [n_cols,H])."""
+    Returns (grad_feat [n_cols,H,F], grad_attn_row [n_rows,H], grad_attn_col [n_cols,H]).
+    With row_grad=False grad_attn_row is None (it comes from gat_rowstat_full), the per-edge array is
+    skipped, row_ptr / permute may be None and an edge_mask is indexed by CSC position."""
     in_feat = _cuda_f32(in_feat, "in_feat")
     attn_col = _cuda_f32(attn_col, "attn_col")
     grad_out = _cuda_f32(grad_out, "grad_out")
     pack = _cuda_f32(pack, "pack")
     row_ind = _cuda_i32(row_ind, "row_ind")
-    permute = _cuda_i32(permute, "permute")
-    row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
-    col_ptr, cbits = _cuda_ptr(col_ptr, "col_ptr")
-    if cbits != bits:
-        col_ptr = _same_bits(bits, col_ptr, "col_ptr")
+    col_ptr, bits = _cuda_ptr(col_ptr, "col_ptr")
+    if row_grad:
+        permute = _cuda_i32(permute, "permute")
+        row_ptr, rbits = _cuda_ptr(row_ptr, "row_ptr")
+        if rbits != bits:
+            row_ptr = _same_bits(bits, row_ptr, "row_ptr")
+    else:
+        permute = _cuda_i32(permute, "permute") if permute is not None else None
+        row_ptr = None
     n_cols, h, f = _dims3(in_feat, "in_feat")
-    n_rows = row_ptr.numel() - 1
+    n_rows = grad_out.shape[0]
     nnz = row_ind.numel()
+    if row_grad and row_ptr.numel() - 1 != n_rows:
+        raise RuntimeError("dgnn_b200: row_ptr length must be grad_out.shape[0] + 1")
     if col_ptr.numel() - 1 != n_cols:
         raise RuntimeError("dgnn_b200: col_ptr length must be in_feat.shape[0] + 1")
     if grad_out.shape != (n_rows, h, f) or pack.shape != (n_rows, h, 4):
@@ -123,9 +184,9 @@ def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_fe
     dev = in_feat.device
     with device_guard(dev):
         grad_feat = torch.empty((n_cols, h, f), dtype=torch.float32, device=dev)
-        grad_attn_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+        grad_attn_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if row_grad else None
         grad_attn_col = torch.empty((n_cols, h), dtype=torch.float32, device=dev)
-        ws = _workspace(lib().dgnn_gat_backward_workspace_bytes(n_rows, n_cols, nnz, h, f), dev)
+        ws = _workspace(lib().dgnn_gat_backward_cols_workspace_bytes(nnz, h, f, int(row_grad)), dev)
         check(lib().dgnn_gat_backward_cols(n_rows, n_cols, nnz, h, f, _p(row_ptr), _p(col_ptr), bits, _p(row_ind),
                                            _p(permute), _p(pack), _p(edge_mask), _p(in_feat), _p(attn_col),
                                            _p(grad_out), float(negative_slope), float(attn_drop), _p(grad_feat),
@@ -180,16 +241,20 @@ def logits_supported(h, f):
     return f % 4 == 0 and f4 > 0 and (f4 & (f4 - 1)) == 0 and h * f <= 1024
 
 
-def gat_logits_forward(feat, attn_l, attn_r):
-    """attn_row, attn_col [N,H] from feat [N,H,F] and the attention vectors [.., H, F]."""
+def gat_logits_forward(feat, attn_l, attn_r, out_row=None, out_col=None):
+    """attn_row, attn_col [N,H] from feat [N,H,F] and the attention vectors [.., H, F]; written into
+    out_row / out_col when given (contiguous float32 [N,H] on the same device)."""
     feat = _cuda_f32(feat, "feat")
     n, h, f = _dims3(feat, "feat")
     attn_l = _cuda_f32(attn_l, "attn_l").reshape(h, f)
     attn_r = _cuda_f32(attn_r, "attn_r").reshape(h, f)
     dev = feat.device
+    for t, name in ((out_row, "out_row"), (out_col, "out_col")):
+        if t is not None and not (t.is_cuda and t.is_contiguous() and t.dtype == torch.float32 and t.shape == (n, h)):
+            raise RuntimeError(f"dgnn_b200: {name} must be a contiguous float32 CUDA tensor [{n},{h}]")
     with device_guard(dev):
-        attn_row = torch.empty((n, h), dtype=torch.float32, device=dev)
-        attn_col = torch.empty((n, h), dtype=torch.float32, device=dev)
+        attn_row = torch.empty((n, h), dtype=torch.float32, device=dev) if out_row is None else out_row
+        attn_col = torch.empty((n, h), dtype=torch.float32, device=dev) if out_col is None else out_col
         check(lib().dgnn_gat_logits_forward(n, h, f, _p(feat), _p(attn_l), _p(attn_r), _p(attn_row), _p(attn_col),
                                             _stream(dev)), "gat_logits_forward")
     return attn_row, attn_col
@@ -227,16 +292,66 @@ def uniform_fill(shape, seed, offset, device):
     return out
 
 
+def uniform_fill_edges(edge_id, h, seed, offset=0):
+    """[len(edge_id), h] floats: row i holds elements edge_id[i]*h .. +h of the stream of
+    uniform_fill(seed, offset), i.e. the values that uniform_fill((nnz, h), seed, offset) puts in row edge_id[i]."""
+    edge_id = _cuda_i32(edge_id, "edge_id")
+    dev = edge_id.device
+    with device_guard(dev):
+        out = torch.empty((edge_id.numel(), int(h)), dtype=torch.float32, device=dev)
+        check(lib().dgnn_uniform_fill_edges(int(seed) & (2**64 - 1), int(offset), edge_id.numel(), int(h), _p(edge_id),
+                                            _p(out), _stream(dev)), "uniform_fill_edges")
+    return out
+
+
+def halo_pull(codes, src_a, dst_a, src_b=None, dst_b=None, max_ctas=0, status=None):
+    """dst_a[i] = src_a[rank_i][idx_i] for every code (rank_i << dgnn_halo_rank_shift | idx_i); src_a is the list
+    of the owners' buffers (tensors on this device or peer mappings), all [src_rows, ...] of one row size.
+    A second tensor pair with the same row list can ride along.  Enqueued on the current stream."""
+    import ctypes
+    codes = _cuda_i32(codes, "codes")
+    n = codes.numel()
+    dev = dst_a.device
+
+    def table(srcs, dst, name):
+        rows = srcs[0].shape[0]
+        row_bytes = (dst.numel() // max(n, 1)) * 4
+        for t in srcs:
+            if not (t.is_cuda and t.is_contiguous() and t.dtype == torch.float32 and t.shape[0] == rows
+                    and t.shape[1:] == dst.shape[1:]):
+                raise RuntimeError(f"dgnn_b200: halo_pull {name}: owners' buffers must be contiguous float32 [rows, ...] "
+                                   "with the row shape of the destination")
+        if not (dst.is_cuda and dst.is_contiguous() and dst.dtype == torch.float32 and dst.shape[0] == n):
+            raise RuntimeError(f"dgnn_b200: halo_pull {name}: destination must be contiguous float32 [len(codes), ...]")
+        arr = (ctypes.c_void_p * len(srcs))(*[t.data_ptr() for t in srcs])
+        return arr, rows, row_bytes
+
+    if n == 0:
+        return
+    arr_a, rows, rb_a = table(src_a, dst_a, "a")
+    arr_b, rb_b = None, 0
+    if src_b is not None:
+        if len(src_b) != len(src_a):
+            raise RuntimeError("dgnn_b200: halo_pull: both tensors need one buffer per rank")
+        arr_b, rows_b, rb_b = table(src_b, dst_b, "b")
+        if rows_b != rows:
+            raise RuntimeError("dgnn_b200: halo_pull: both tensors must have the same number of rows per owner")
+    with device_guard(dev):
+        check(lib().dgnn_halo_pull(n, _p(codes), len(src_a), rows, arr_a, _p(dst_a), rb_a, arr_b,
+                                   _p(dst_b) if dst_b is not None else None, rb_b, int(max_ctas),
+                                   _p(status), _stream(dev)), "halo_pull")
+
+
 # ------------------------------------------------------- dense projection
 def project_supported(m, n, k) -> bool:
     """Shapes the tensor-core projection handles (n % 128 == 0, k % 4 == 0, k <= 128)."""
     return bool(lib().dgnn_project_supported(int(m), int(n), int(k)))
 
 
-def project_forward(x, w, w_kn=False, check_status=False):
+def project_forward(x, w, w_kn=False, check_status=False, out=None):
     """out[M,N] = x[M,K] @ W in fp32 accuracy on the tcgen05 tensor cores (3 x tf32 split); w is an
     nn.Linear weight [N,K], or [K,N] with w_kn=True.  check_status=True synchronises and raises if a
-    wait inside the kernel ran out."""
+    wait inside the kernel ran out.  `out` (contiguous float32 [M,N]) receives the result when given."""
     x = _cuda_f32(x, "x")
     w = _cuda_f32(w, "w")
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[0 if w_kn else 1]:
@@ -244,8 +359,12 @@ def project_forward(x, w, w_kn=False, check_status=False):
     m, k = x.shape
     n = w.shape[1 if w_kn else 0]
     dev = x.device
+    if out is not None and not (out.is_cuda and out.is_contiguous() and out.dtype == torch.float32
+                                and out.shape == (m, n) and out.data_ptr() % 16 == 0):
+        raise RuntimeError(f"dgnn_b200: project_forward: out must be a contiguous, 16-byte aligned float32 CUDA tensor [{m},{n}]")
     with device_guard(dev):
-        out = torch.empty((m, n), dtype=torch.float32, device=dev)
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.float32, device=dev)
         nbytes = lib().dgnn_project_workspace_bytes(n)
         ws = _workspace(nbytes, dev)
         check(lib().dgnn_project_forward(m, n, k, _p(x), _p(w), int(bool(w_kn)), _p(out), _p(ws), nbytes, _stream(dev)),
@@ -461,10 +580,13 @@ def gat_backward_state(n_cols, h, f, device):
     return torch.empty(max(nbytes // 4, 4), dtype=torch.float32, device=device)
 
 
-def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope, feat_blk, state, first, last, bias=None):
+def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope, feat_blk, state, first, last, bias=None,
+                       attn_drop=0.0, edge_mask=None, neg=False, save_stats=True):
     """One stage of the forward over the edges whose source lies in one column block.
-    Returns (out, edge_max, edge_sum) from the last stage, None before.  `bias` [H*F] is added to the
-    output by the last stage when given."""
+    Returns (out, edge_max, edge_sum[, out_neg, a_neg]) from the last stage, None before.  `bias` [H*F] is
+    added to the output by the last stage when given; `edge_mask` [nnz,H] (with attn_drop > 0) follows the
+    order of this stage's col_ind; neg=True must be passed to every stage of a sweep that wants the
+    negative-side outputs (the carried state holds their accumulators)."""
     attn_row = _cuda_f32(attn_row, "attn_row")
     attn_col_blk = _cuda_f32(attn_col_blk, "attn_col")
     feat_blk = _cuda_f32(feat_blk, "in_feat")
@@ -472,53 +594,79 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
     row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
     _, h, f = _dims3(feat_blk, "in_feat")
     n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
+    if attn_drop > 0.0:
+        edge_mask = _cuda_f32(edge_mask, "edge_mask")
+        if edge_mask.shape != (nnz, h):
+            raise RuntimeError(f"dgnn_b200: edge_mask must be [{nnz},{h}]")
+    else:
+        edge_mask = None
     dev = feat_blk.device
     with device_guard(dev):
-        out = emax = esum = None
+        out = emax = esum = out_neg = a_neg = None
         if last:
             out = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
-            emax = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
-            esum = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+            if save_stats:
+                emax = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+                esum = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+        if neg:   # every stage gets the pointers: they select the kernel variant whose state carries the accumulators
+            out_neg = torch.empty((n_rows, h, f) if last else (1, h, f), dtype=torch.float32, device=dev)
+            a_neg = torch.empty((n_rows, h) if last else (1, h), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f), dev)
         if bias is not None:
             bias = _cuda_f32(bias, "bias").reshape(h * f)
         check(lib().dgnn_gat_forward_staged(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
-                                            _p(attn_col_blk), _p(feat_blk), float(negative_slope), 0.0, None,
-                                            _p(bias) if bias is not None else None,
-                                            _p(out), _p(emax), _p(esum), _p(state), int(bool(first)), int(bool(last)),
+                                            _p(attn_col_blk), _p(feat_blk), float(negative_slope), float(attn_drop),
+                                            _p(edge_mask), _p(bias) if bias is not None else None,
+                                            _p(out), _p(emax), _p(esum), _p(out_neg), _p(a_neg), _p(state),
+                                            int(bool(first)), int(bool(last)),
                                             _p(ws), ws.numel(), _stream(dev)), "gat_forward_staged")
-    return (out, emax, esum) if last else None
+    if not last:
+        return None
+    return (out, emax, esum, out_neg, a_neg) if neg else (out, emax, esum)
 
 
 def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_feat, attn_col, grad_blk,
-                             negative_slope, state, first, last):
+                             negative_slope, state, first, last, attn_drop=0.0, edge_mask=None, row_grad=True):
     """One stage of the backward column pass over the edges whose destination lies in one
-    row block.  Returns (grad_attn_row of the block's rows, grad_feat or None, grad_attn_col or None)."""
+    row block.  Returns (grad_attn_row of the block's rows or None, grad_feat or None, grad_attn_col or None).
+    With row_grad=False (grad_attn_row comes from gat_rowstat_full) row_ptr and permute may be None and an
+    `edge_mask` [nnz,H] follows the order of this stage's row_ind."""
     in_feat = _cuda_f32(in_feat, "in_feat")
     attn_col = _cuda_f32(attn_col, "attn_col")
     grad_blk = _cuda_f32(grad_blk, "grad_out")
     pack_blk = _cuda_f32(pack_blk, "pack")
     row_ind = _cuda_i32(row_ind, "row_ind")
-    permute = _cuda_i32(permute, "permute")
-    row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
-    col_ptr, cbits = _cuda_ptr(col_ptr, "col_ptr")
-    if cbits != bits:
-        col_ptr = _same_bits(bits, col_ptr, "col_ptr")
+    col_ptr, bits = _cuda_ptr(col_ptr, "col_ptr")
+    if row_grad:
+        permute = _cuda_i32(permute, "permute")
+        row_ptr, rbits = _cuda_ptr(row_ptr, "row_ptr")
+        if rbits != bits:
+            row_ptr = _same_bits(bits, row_ptr, "row_ptr")
+    else:
+        permute = _cuda_i32(permute, "permute") if permute is not None else None
+        row_ptr = None
     n_cols, h, f = _dims3(in_feat, "in_feat")
-    n_rows, nnz = row_ptr.numel() - 1, row_ind.numel()
-    if grad_blk.shape != (n_rows, h, f) or pack_blk.shape != (n_rows, h, 4) or col_ptr.numel() - 1 != n_cols:
+    n_rows, nnz = grad_blk.shape[0], row_ind.numel()
+    if (grad_blk.shape != (n_rows, h, f) or pack_blk.shape != (n_rows, h, 4) or col_ptr.numel() - 1 != n_cols
+            or (row_grad and row_ptr.numel() - 1 != n_rows)):
         raise RuntimeError("dgnn_b200: staged backward: block shapes do not match the sub-matrix")
+    if attn_drop > 0.0:
+        edge_mask = _cuda_f32(edge_mask, "edge_mask")
+        if edge_mask.shape != (nnz, h):
+            raise RuntimeError(f"dgnn_b200: edge_mask must be [{nnz},{h}]")
+    else:
+        edge_mask = None
     dev = in_feat.device
     with device_guard(dev):
         grad_feat = grad_col = None
         if last:
             grad_feat = torch.empty((n_cols, h, f), dtype=torch.float32, device=dev)
             grad_col = torch.empty((n_cols, h), dtype=torch.float32, device=dev)
-        grad_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
-        ws = _workspace(lib().dgnn_gat_backward_workspace_bytes(n_rows, n_cols, nnz, h, f), dev)
+        grad_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if row_grad else None
+        ws = _workspace(lib().dgnn_gat_backward_cols_workspace_bytes(nnz, h, f, int(row_grad)), dev)
         check(lib().dgnn_gat_backward_cols_staged(n_rows, n_cols, nnz, h, f, _p(row_ptr), _p(col_ptr), bits,
-                                                  _p(row_ind), _p(permute), _p(pack_blk), None, _p(in_feat),
-                                                  _p(attn_col), _p(grad_blk), float(negative_slope), 0.0,
+                                                  _p(row_ind), _p(permute), _p(pack_blk), _p(edge_mask), _p(in_feat),
+                                                  _p(attn_col), _p(grad_blk), float(negative_slope), float(attn_drop),
                                                   _p(grad_feat), _p(grad_row), _p(grad_col), _p(state),
                                                   int(bool(first)), int(bool(last)), _p(ws), ws.numel(), _stream(dev)),
               "gat_backward_cols_staged")

@@ -17,23 +17,48 @@ def GATConvFuse_inference(attn_row, attn_col, row_ptr, col_ind, negative_slope, 
 
 
 class FusedGATFunction(torch.autograd.Function):
+    """On the float4 layout (kernels.gat_fast_shape) the forward also keeps the share of the result that
+    comes from edges on the negative side of the LeakyReLU; the backward then gets grad_attn_row from the
+    destination rows alone (kernels.gat_rowstat_full) and the column pass writes no per-edge array.  Other
+    shapes go through the extension-module calls of the reference signature."""
+
     @staticmethod
     def forward(ctx, attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, permute, negative_slope, in_feat,
                 attn_drop):
+        attn_drop = float(attn_drop)
+        ctx.negative_slope = negative_slope
+        ctx.attn_drop = attn_drop
+        ctx.neg = in_feat.is_cuda and in_feat.dim() == 3 and kernels.gat_fast_shape(in_feat.shape[1], in_feat.shape[2])
+        if ctx.neg:
+            edge_mask = fused_gat.make_edge_mask(col_ind.numel(), in_feat.shape[1], attn_drop, in_feat.device)
+            out_feat, edge_max, edge_sum, out_neg, a_neg = kernels.gat_forward(
+                attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop,
+                edge_mask if attn_drop > 0.0 else None, neg=True)
+            ctx.save_for_backward(col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, in_feat, attn_row,
+                                  attn_col, out_feat, out_neg, a_neg)
+            return out_feat
         out_feat, edge_max, edge_sum, edge_mask = fused_gat.gat_forward(
             attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop)
         # the forward output is saved too: the backward's per-row term is <grad_out, out>
         ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, in_feat,
                               attn_row, attn_col, out_feat)
-        ctx.negative_slope = negative_slope
-        ctx.attn_drop = attn_drop
         return out_feat
 
     @staticmethod
     def backward(ctx, grad_out):
+        grad_out = grad_out.contiguous()
+        if ctx.neg:
+            (col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, in_feat, attn_row, attn_col, out_feat,
+             out_neg, a_neg) = ctx.saved_tensors
+            pack, grad_attn_row, _ = kernels.gat_rowstat_full(attn_row, edge_max, edge_sum, out_feat, grad_out,
+                                                              ctx.negative_slope, out_neg=out_neg, a_neg=a_neg)
+            masked = ctx.attn_drop > 0.0
+            grad_feat, _, grad_attn_col = kernels.gat_backward_cols(
+                None, col_ptr, row_ind, permute if masked else None, pack, edge_mask if masked else None, in_feat,
+                attn_col, grad_out, ctx.negative_slope, ctx.attn_drop, row_grad=False)
+            return grad_attn_row, grad_attn_col, None, None, None, None, None, None, grad_feat, None
         (row_ptr, col_ind, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, in_feat, attn_row, attn_col,
          out_feat) = ctx.saved_tensors
-        grad_out = grad_out.contiguous()
         grad_feat, grad_attn_row, grad_attn_col = fused_gat.gat_backward(
             ctx.negative_slope, ctx.attn_drop, row_ptr, col_ind, col_ptr, row_ind, permute, edge_max, edge_sum,
             edge_mask, in_feat, attn_row, attn_col, grad_out, out_feat)
@@ -59,10 +84,11 @@ class FusedGATLayerFunction(torch.autograd.Function):
         attn_row, attn_col = kernels.gat_logits_forward(h, attn_l, attn_r)
         attn_drop = float(attn_drop)
         edge_mask = fused_gat.make_edge_mask(col_ind.numel(), h.shape[1], attn_drop, h.device)
-        out_feat, edge_max, edge_sum = kernels.gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h,
-                                                           attn_drop, edge_mask if attn_drop > 0.0 else None, True, bias)
-        saved = [row_ptr, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
-                 attn_l, attn_r]
+        out_feat, edge_max, edge_sum, out_neg, a_neg = kernels.gat_forward(
+            attn_row, attn_col, row_ptr, col_ind, negative_slope, h, attn_drop,
+            edge_mask if attn_drop > 0.0 else None, True, bias, neg=True)
+        saved = [col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
+                 out_neg, a_neg, attn_l, attn_r]
         if bias is not None:
             saved.append(bias)
         ctx.save_for_backward(*saved)
@@ -73,19 +99,20 @@ class FusedGATLayerFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out):
-        (row_ptr, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
-         attn_l, attn_r) = ctx.saved_tensors[:13]
+        (col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
+         out_neg, a_neg, attn_l, attn_r) = ctx.saved_tensors[:14]
         grad_out = grad_out.contiguous()
-        mask = edge_mask if ctx.attn_drop > 0.0 else None
-        grad_bias = None
-        if ctx.has_bias:
-            bias = ctx.saved_tensors[13]
-            pack, grad_bias = kernels.gat_rowstat_bias(attn_row, edge_max, edge_sum, out_feat, grad_out, bias)
+        masked = ctx.attn_drop > 0.0
+        bias = ctx.saved_tensors[14] if ctx.has_bias else None
+        # pack, grad_attn_row and the bias gradient all come out of one pass over the destination rows
+        pack, grad_attn_row, grad_bias = kernels.gat_rowstat_full(attn_row, edge_max, edge_sum, out_feat, grad_out,
+                                                                  ctx.negative_slope, bias=bias, out_neg=out_neg,
+                                                                  a_neg=a_neg)
+        if grad_bias is not None:
             grad_bias = grad_bias.view_as(bias)
-        else:
-            pack = kernels.gat_rowstat(attn_row, edge_max, edge_sum, out_feat, grad_out)
-        grad_h, grad_attn_row, grad_attn_col = kernels.gat_backward_cols(
-            row_ptr, col_ptr, row_ind, permute, pack, mask, h, attn_col, grad_out, ctx.negative_slope, ctx.attn_drop)
+        grad_h, _, grad_attn_col = kernels.gat_backward_cols(
+            None, col_ptr, row_ind, permute if masked else None, pack, edge_mask if masked else None, h, attn_col,
+            grad_out, ctx.negative_slope, ctx.attn_drop, row_grad=False)
         grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_h)
         return (grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None, None, None, None, None,
                 grad_bias)

@@ -13,9 +13,12 @@ from .. import kernels
 
 class ProjectFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, feat, weight):
+    def forward(ctx, feat, weight, out=None):
         ctx.save_for_backward(feat, weight)
-        return kernels.project_forward(feat, weight, w_kn=True)
+        res = kernels.project_forward(feat, weight, w_kn=True, out=out)
+        if out is not None:
+            ctx.mark_dirty(out)          # the caller's buffer is the result
+        return res
 
     @staticmethod
     def backward(ctx, grad_out):
@@ -24,13 +27,31 @@ class ProjectFunction(torch.autograd.Function):
         grad_weight = None
         if ctx.needs_input_grad[1]:
             grad_weight = kernels.project_wgrad(feat, grad_out.contiguous(), w_kn=True)
-        return grad_feat, grad_weight
+        return grad_feat, grad_weight, None
 
 
-def project(feat, weight):
-    """feat [M,K] @ weight [K,N] -> [M,N]."""
+def project(feat, weight, out=None):
+    """feat [M,K] @ weight [K,N] -> [M,N].  `out` (a contiguous float32 [M,N] tensor without autograd history,
+    e.g. a detached view of a persistent buffer) receives the result when given."""
     if (feat.is_cuda and feat.dtype == torch.float32 and weight.dtype == torch.float32 and feat.dim() == 2
             and feat.is_contiguous() and weight.is_contiguous()
             and kernels.project_supported(feat.shape[0], weight.shape[1], feat.shape[1])):
-        return ProjectFunction.apply(feat, weight)
-    return torch.matmul(feat, weight)
+        return ProjectFunction.apply(feat, weight, out)
+    res = torch.matmul(feat, weight)
+    if out is None:
+        return res
+    return _CopyInto.apply(res, out)
+
+
+class _CopyInto(torch.autograd.Function):
+    """out <- src with the gradient passed through (library-GEMM path of project(out=...))."""
+
+    @staticmethod
+    def forward(ctx, src, out):
+        out.copy_(src)
+        ctx.mark_dirty(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None

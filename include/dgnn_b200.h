@@ -75,14 +75,21 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f,
  * first != 0 starts from an empty state, last != 0 normalises and writes out / edge_max /
  * edge_sum (they may be NULL otherwise).  first = last = 1 is dgnn_gat_forward.  `bias`
  * (NULL or [h*f]) is added to the normalised output by the last call: the bias add of the
- * layer (dgNN/layers/gatconv_layer.py:86-87) as a kernel epilogue.  No counterpart in the
- * reference, which is single-GPU. */
+ * layer (dgNN/layers/gatconv_layer.py:86-87) as a kernel epilogue.
+ * out_neg [n_rows,h,f] and a_neg [n_rows,h] (both NULL or both given; float4 layout only, see
+ * dgnn_gat_fast_shape) receive the share of the result that comes from edges whose score lies on the
+ * negative side of the LeakyReLU: out_neg = sum_{e: leaky_e < 0} keep_e alpha_e/(1-p) in_feat[c_e],
+ * a_neg = sum_{e: leaky_e < 0} alpha_e.  dgnn_gat_rowstat_full turns them into grad_attn_row, which
+ * the reference obtains from a per-edge array (fused_backward_kernel, fused_gatconv_kernel.cu:931-957).
+ * The staged form has no counterpart in the reference, which is single-GPU. */
+int dgnn_gat_fast_shape(int h, int f);   /* 1 when (h, f) uses the float4 layout: f = 4*2^k, h*f <= 1024 */
 size_t dgnn_gat_forward_state_bytes(int64_t n_rows, int h, int f);
 int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f,
                             const void* row_ptr, int idx_bits, const int32_t* col_ind,
                             const float* attn_row, const float* attn_col, const float* in_feat,
                             float negative_slope, float attn_drop, const float* edge_mask,
                             const float* bias, float* out, float* edge_max, float* edge_sum,
+                            float* out_neg, float* a_neg,
                             float* state, int first, int last,
                             void* workspace, size_t workspace_bytes, void* stream);
 
@@ -104,6 +111,22 @@ int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f,
                           float* pack, float* grad_bias,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* Everything the backward needs from the destination rows in one pass over grad_out, out (and out_neg):
+ * pack as above (S uses out - bias when bias is given, and grad_bias [h*f] = sum_r grad_out[r,:] is
+ * produced in a fixed order); with out_neg / a_neg (from dgnn_gat_forward_staged)
+ *   grad_attn_row[r,h] = (1 - slope) * (S[r,h] * a_neg[r,h] - <grad_out[r,h,:], out_neg[r,h,:]>),
+ * equal to the reference's sum over the row's edges of d_e (fused_gatconv_kernel.cu:931-957) without
+ * the per-edge array, its scattered write and its row reduction; grad_copy (NULL or [n_rows,h,f])
+ * receives a copy of grad_out (on the sharded path: the buffer that other ranks read).  bias/grad_bias,
+ * out_neg/a_neg/grad_attn_row are each all NULL or all given.  Float4 layout only.  The workspace
+ * (dgnn_gat_rowstat_bias_workspace_bytes) is needed only with a bias. */
+int dgnn_gat_rowstat_full(int64_t n_rows, int h, int f,
+                          const float* attn_row, const float* edge_max, const float* edge_sum,
+                          const float* out, const float* grad_out, const float* bias,
+                          const float* out_neg, const float* a_neg, float negative_slope,
+                          float* pack, float* grad_attn_row, float* grad_bias, float* grad_copy,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 /* Column pass of the backward over the CSC form of an [n_rows x n_cols] block:
  *   grad_feat[c,h,:]   = sum_{e in col c} keep*alpha/(1-p) * grad_out[row_e,h,:]
  *   g_e                = keep/(1-p) * <grad_out[row_e,h,:], in_feat[c,h,:]>
@@ -114,8 +137,12 @@ int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f,
  * (fused_gatconv_kernel.cu:712-763, 814-890, 892-968); no float atomics.
  * in_feat / attn_col / grad_feat / grad_attn_col have n_cols rows; pack and
  * grad_out have n_rows rows; permute[j] is the CSR position of CSC entry j and
- * row_ptr is the CSR index pointer of the same block. */
+ * row_ptr is the CSR index pointer of the same block.
+ * grad_attn_row may be NULL (the caller takes it from dgnn_gat_rowstat_full): the per-edge array is
+ * then neither written nor reduced, row_ptr and permute may be NULL, an edge_mask is indexed by CSC
+ * position, and the smaller workspace of dgnn_gat_backward_cols_workspace_bytes(.., 0) suffices. */
 size_t dgnn_gat_backward_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f);
+size_t dgnn_gat_backward_cols_workspace_bytes(int64_t nnz, int h, int f, int with_grad_attn_row);
 int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f,
                            const void* row_ptr, const void* col_ptr, int idx_bits,
                            const int32_t* row_ind, const int32_t* permute,
@@ -129,7 +156,7 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
  * edges of one row block (its CSC / CSR arrays, pack and grad_out of that block) and the
  * per-column accumulators (dgnn_gat_backward_state_bytes) are carried in `state`;
  * grad_feat / grad_attn_col are written by the last call, grad_attn_row (of the block's
- * rows) by every call.  first = last = 1 is dgnn_gat_backward_cols. */
+ * rows, unless NULL) by every call.  first = last = 1 is dgnn_gat_backward_cols. */
 size_t dgnn_gat_backward_state_bytes(int64_t n_cols, int h, int f);
 int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f,
                                   const void* row_ptr, const void* col_ptr, int idx_bits,
@@ -195,6 +222,31 @@ int dgnn_project_status(const void* workspace, void* stream, int* status_out);
 /* Uniform floats in (0,1] from a counter-based Philox4x32-10 stream; stands in
  * for the cuRAND fill of edge_mask (fused_gatconv_kernel.cu:333-341). */
 int dgnn_uniform_fill(uint64_t seed, uint64_t offset, int64_t n, float* out, void* stream);
+
+/* The same stream addressed by edge: out[i*h + j] = element edge_id[i]*h + j of the stream of
+ * dgnn_uniform_fill(seed, offset).  With edge_id[i] = position of the edge in the CSR of the whole
+ * graph, every rank of a sharded layer draws the mask value of an edge that the single-GPU layer
+ * draws, in whatever order its own graph pieces hold the edges (forward: destination owner, CSR
+ * order; backward: source owner, CSC order).  No counterpart in the reference, which is single-GPU. */
+int dgnn_uniform_fill_edges(uint64_t seed, uint64_t offset, int64_t nnz, int h,
+                            const int32_t* edge_id, float* out, void* stream);
+
+/* ---- halo exchange of the row-block sharded layer (no counterpart in the reference) ----------
+ * dst_a[i,:] = src_a[rank_i][idx_i,:] (and the same for tensor b when row_bytes_b > 0) for
+ * i < n_rows, where codes[i] = (rank_i << dgnn_halo_rank_shift()) | idx_i names a row of the block
+ * that rank_i owns.  src_a / src_b are HOST arrays of n_ranks device pointers to the owners'
+ * buffers ([src_rows, row_bytes] each): this GPU's own memory or peer mappings of other GPUs'
+ * memory (read with plain loads over NVLink; no TMA, no multicast).  Row sizes are multiples of 16
+ * bytes, all pointers 16-byte aligned, n_ranks <= dgnn_halo_max_ranks(), src_rows <= 2^shift.  A code
+ * that names a rank or row out of range is skipped (never dereferenced) and *status (device int,
+ * may be NULL) becomes 1.  max_ctas > 0 bounds the grid so that the fetch can run beside other
+ * kernels. */
+int dgnn_halo_max_ranks(void);
+int dgnn_halo_rank_shift(void);
+int dgnn_halo_pull(int64_t n_rows, const int32_t* codes, int n_ranks, int64_t src_rows,
+                   const void* const* src_a, void* dst_a, int row_bytes_a,
+                   const void* const* src_b, void* dst_b, int row_bytes_b,
+                   int max_ctas, int32_t* status, void* stream);
 
 /* ---- multi-head SDDMM / transpose -----------------------------------------
  * out[e,h] = <a[row_e,h,:], b[col_e,h,:]>; replaces mhsddmm.mhsddmm

@@ -83,6 +83,28 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, slope, in_feat, attn_drop=
     return out, edge_max, edge_sum
 
 
+def gat_forward_negative_side(attn_row, attn_col, row_ptr, col_ind, slope, in_feat, attn_drop=0.0, edge_mask=None):
+    """The share of gat_forward's result carried by edges whose LeakyReLU output is negative (the edges
+    whose gradient fused_backward_kernel scales by the slope, fused_gatconv_kernel.cu:953-954):
+      out_neg[r,h,:] = sum_{e: leaky_e < 0} keep_e alpha_e / (1 - p) in_feat[col_e,h,:]
+      a_neg[r,h]     = sum_{e: leaky_e < 0} alpha_e.
+    With S = <grad_out, out> the row gradient of gat_backward equals
+      grad_attn_row = (1 - slope) * (S * a_neg - <grad_out, out_neg>),
+    which is how the CUDA library obtains it (checked against gat_backward in the tests)."""
+    rows = edge_rows(row_ptr)
+    cols = col_ind.long()
+    n, h = attn_row.shape
+    leaky, _, _, alpha = gat_edge_softmax(attn_row, attn_col, row_ptr, col_ind, slope)
+    neg = (leaky < 0).to(alpha.dtype)
+    w = alpha * neg
+    a_neg = torch.zeros((n, h), dtype=alpha.dtype).index_add_(0, rows, w)
+    if edge_mask is not None:
+        w = w * (edge_mask > attn_drop).to(w.dtype)
+    w = w / (1.0 - attn_drop)
+    out_neg = torch.zeros((n, h, in_feat.shape[2]), dtype=in_feat.dtype).index_add_(0, rows, w[:, :, None] * in_feat[cols])
+    return out_neg, a_neg
+
+
 def gat_backward(slope, attn_drop, row_ptr, col_ind, edge_max, edge_sum, edge_mask,
                  in_feat, attn_row, attn_col, grad_out, s_row=None):
     """mhspmm_backward_kernel + mhsddmm + fused_backward_kernel

@@ -50,3 +50,63 @@ def scipy_csc(row_ptr, col_ind, n_cols=None):
     csc = csr.tocsc()
     return (torch.from_numpy(csc.indptr.astype(np.int64)), torch.from_numpy(csc.indices.astype(np.int64)),
             torch.from_numpy(csc.data.astype(np.int64)))
+
+
+def free_port():
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_entry(worker, rank, world, port, args, q, done):
+    """Child process: run worker(rank, world, port, *args) and report its result or its traceback; then stay
+    until the parent has read the results (tensors travel as shared-memory handles served by this process)."""
+    import traceback
+    try:
+        q.put((rank, "ok", worker(rank, world, port, *args)))
+    except BaseException:
+        q.put((rank, "error", traceback.format_exc()))
+    done.wait(timeout=600)
+
+
+def run_ranks(worker, world, args=(), timeout=300, expect_errors=False):
+    """Spawn `world` processes running worker(rank, world, port, *args) and return their results by rank.
+    A rank that raises makes the call fail at once with its traceback (or, with expect_errors, is returned
+    as ("error", traceback)); whatever happens, every child that is still alive afterwards is terminated
+    and then killed, so no process stays behind blocked in a collective."""
+    import queue as _queue
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    done = ctx.Event()
+    port = free_port()
+    procs = [ctx.Process(target=_rank_entry, args=(worker, r, world, port, tuple(args), q, done), daemon=True)
+             for r in range(world)]
+    results = {}
+    try:
+        for p in procs:
+            p.start()
+        while len(results) < world:
+            try:
+                rank, status, payload = q.get(timeout=timeout)
+            except _queue.Empty:
+                raise AssertionError(f"ranks {sorted(set(range(world)) - set(results))} gave no result within {timeout} s")
+            if status == "error" and not expect_errors:
+                raise AssertionError(f"rank {rank} failed:\n{payload}")
+            results[rank] = payload if status == "ok" else ("error", payload)
+        done.set()
+        for p in procs:
+            p.join(timeout=30)
+    finally:
+        done.set()
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    return [results[r] for r in range(world)]

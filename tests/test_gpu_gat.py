@@ -50,6 +50,23 @@ def _fwd_bwd_check(cuda, rp, ci, h, f, seed, slope=0.2, p=0.0):
     out2, a, b = kernels.gat_forward(d(ar), d(ac), d(rp), d(ci), slope, d(x), p, d(mask), save_stats=False)
     assert a is None and b is None
     assert_equal(out2, out, "inference out")
+    if not kernels.gat_fast_shape(h, f):
+        return
+    # negative-side outputs and the row gradient derived from them (no per-edge array, no permutation)
+    on_ref, an_ref = orc.gat_forward_negative_side(ar, ac, rp, ci, slope, x, p, mask)
+    out3, emax3, esum3, out_neg, a_neg = kernels.gat_forward(d(ar), d(ac), d(rp), d(ci), slope, d(x), p, d(mask), neg=True)
+    assert_equal(out3, out, "out with negative-side outputs")
+    assert_equal(emax3, emax, "edge_max with negative-side outputs")
+    assert_equal(esum3, esum, "edge_sum with negative-side outputs")
+    assert_close(out_neg, on_ref, "out_neg")
+    assert_close(a_neg, an_ref, "a_neg")
+    pack, gr2, _ = kernels.gat_rowstat_full(d(ar), emax, esum, out, d(g), slope, out_neg=out_neg, a_neg=a_neg)
+    gf2, none_row, gc2 = kernels.gat_backward_cols(None, d(cp.to(rp.dtype)), d(ri.int()), d(pm.int()) if p > 0 else None,
+                                                   pack, d(mask), d(x), d(ac), d(g), slope, p, row_grad=False)
+    assert none_row is None
+    assert_equal(gf2, gf, "grad_feat without the per-edge array")
+    assert_equal(gc2, gc, "grad_attn_col without the per-edge array")
+    assert_close(gr2, gr_ref, "grad_attn_row from the negative-side outputs", atol=2e-5)
 
 
 @pytest.mark.parametrize("h,f", SHAPES)
@@ -210,45 +227,3 @@ def test_layer_fused_path_equals_composed_path(cuda, residual):
     for k, p in layer.named_parameters():
         scale = max(1.0, float(p.grad.abs().max()))
         assert_close(got[k], p.grad, f"grad {k}", atol=1e-4 * scale)
-
-
-@pytest.mark.parametrize("stages", [1, 2, 5])
-def test_staged_sweeps_equal_single_sweep(cuda, stages):
-    """The state-carrying staged forward / backward column pass (used by the pipelined multi-GPU
-    path) over `stages` column / row blocks gives the same results as one sweep."""
-    from dgnn_b200 import dist as gdist
-    rp, ci = _case(**GRAPHS["long_rows"])
-    n, h, f = rp.numel() - 1, 8, 32
-    ar, ac, x, g = [t.to(cuda) for t in gat_inputs(rp, n, h, f, 17)]
-    rp, ci = rp.to(cuda), ci.to(cuda)
-    cp, ri, pm = kernels.csr2csc(rp, ci)
-    out, emax, esum = kernels.gat_forward(ar, ac, rp, ci, 0.2, x)
-    gf, gr, gc = kernels.gat_backward(0.2, 0.0, rp, cp, ri, pm, emax, esum, None, x, out, ar, ac, g)
-
-    shard = gdist.build_pipe_shard(rp, ci, 0, 1, stages=stages, seed=1)     # one rank: the buffers are slices of the local arrays
-    real = shard.local_ids >= 0
-    idx = shard.local_ids[real]
-    ar_l, ac_l, x_l, g_l = [gdist.scatter_rows(t, shard) for t in (ar, ac, x, g)]
-    sl = shard.slice
-    state = kernels.gat_forward_state(shard.blk, h, f, cuda)
-    res = None
-    for p in range(stages):
-        ptr, col = shard.fwd[p]
-        res = kernels.gat_forward_staged(ar_l, ac_l[p * sl:(p + 1) * sl], ptr, col, 0.2, x_l[p * sl:(p + 1) * sl],
-                                         state, p == 0, p == stages - 1)
-    out_s, emax_s, esum_s = res
-    assert_close(out_s[real], out[idx], "staged out")
-    assert_equal(emax_s[real], emax[idx], "staged edge_max")
-    assert_close(esum_s[real], esum[idx], "staged edge_sum")
-    pack = kernels.gat_rowstat(ar_l, emax_s, esum_s, out_s, g_l)
-    bstate = kernels.gat_backward_state(shard.blk, h, f, cuda)
-    parts = []
-    for p in range(stages):
-        rptr, cptr, rind, perm = shard.bwd[p]
-        part, gf_s, gc_s = kernels.gat_backward_cols_staged(rptr, cptr, rind, perm, pack[p * sl:(p + 1) * sl], x_l, ac_l,
-                                                            g_l[p * sl:(p + 1) * sl], 0.2, bstate, p == 0, p == stages - 1)
-        parts.append(part)
-    gr_s = torch.cat(parts, 0)
-    assert_close(gf_s[real], gf[idx], "staged grad_feat")
-    assert_close(gc_s[real], gc[idx], "staged grad_attn_col", atol=2e-5)
-    assert_close(gr_s[real], gr[idx], "staged grad_attn_row", atol=2e-5)
