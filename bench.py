@@ -49,7 +49,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--stages", type=int, default=3,
                     help="sweeps per pass of the sharded layer: stage 0 = own nodes, the others one halo chunk each")
-    ap.add_argument("--pull-ctas", type=int, default=48, help="grid bound of the halo fetch kernel (0: unbounded)")
+    ap.add_argument("--halo-mode", default="dma", choices=["dma", "pull"],
+                    help="dma: owners pack, peers copy with the copy engines; pull: a kernel loads the rows from peer memory")
+    ap.add_argument("--pull-ctas", type=int, default=48, help="grid bound of the halo fetch kernel in pull mode (0: unbounded)")
     ap.add_argument("--gather-fallback", action="store_true",
                     help="halo rows through all-gathers instead of peer loads from symmetric memory")
     return ap.parse_args()
@@ -304,7 +306,7 @@ def run_ours(args, rank, world, local):
         import torch.distributed as dist
         del cp, ri, pm
         shard = gdist.build_halo_shard(rp, ci, rank, world, stages=args.stages, seed=7)
-        transport = gdist.GatherTransport(shard) if args.gather_fallback else gdist.make_transport(shard, None, args.pull_ctas)
+        transport = gdist.GatherTransport(shard) if args.gather_fallback else gdist.make_transport(shard, None, args.halo_mode, args.pull_ctas)
         layer = gdist.ShardedGATConv(IN, F, H, shard, negative_slope=SLOPE, transport=transport).to(dev).train()
         with torch.no_grad():
             layer.W.copy_(W); layer.attn_l.copy_(al); layer.attn_r.copy_(ar_)
@@ -450,7 +452,8 @@ def run_ours(args, rank, world, local):
     if timer.mean_ms("bwd_cols") and timer.mean_ms("bwd_stat"):      # the layer calls the two halves of the backward itself
         bwd_ms = timer.mean_ms("bwd_stat") + timer.mean_ms("bwd_cols")
     sharded = (f", node blocks over {world} GPUs, {args.stages} sweeps per pass, halo rows by "
-               + ("all-gathers" if args.gather_fallback else "peer loads from symmetric memory")) if world > 1 else ""
+               + ("all-gathers" if args.gather_fallback else ("packed send buffers in symmetric memory copied by the copy engines"
+                                                         if args.halo_mode == "dma" else "peer loads from symmetric memory"))) if world > 1 else ""
     line = {
         "metric": "GAT layer fwd+bwd edges/sec", "value": nnz / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,

@@ -60,6 +60,8 @@ SIGNATURES = {
     "dgnn_project_wgrad_workspace_bytes": (c_sz, [c_int]),
     "dgnn_project_wgrad": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_int, c_p, c_sz, c_p]),
     "dgnn_project_status": (c_int, [c_p, c_p, c_p]),
+    "dgnn_project_sticky_status": (c_int, [c_p, c_p, c_p, c_int]),
+    "dgnn_project_set_test_knobs": (c_int, [c_i64, c_int]),
     "dgnn_uniform_fill": (c_int, [c_u64, c_u64, c_i64, c_p, c_p]),
     "dgnn_uniform_fill_edges": (c_int, [c_u64, c_u64, c_i64, c_int, c_p, c_p, c_p]),
     "dgnn_halo_max_ranks": (c_int, []),
@@ -83,6 +85,10 @@ SIGNATURES = {
     "dgnn_csr2csc_static_max_cols": (c_i64, []),
     "dgnn_csr2csc_static": (c_int, [c_i64, c_i64, c_i64, c_p, c_int, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_coo2csr": (c_int, [c_i64, c_i64, c_p, c_p, c_int, c_p]),
+    "dgnn_coo_sort_workspace_bytes": (c_sz, [c_i64, c_i64]),
+    "dgnn_coo_sort": (c_int, [c_i64, c_i64, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
+    "dgnn_knn_max_k": (c_int, []),
+    "dgnn_knn_graph": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_p, c_p]),
 }
 
 

@@ -137,7 +137,9 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 //   slot_stride (floats per slot), MIN_BLOCKS, HAS_PARTIALS, struct State,
 //   skip_empty (rows without edges need no work), init(State&, row, lane) = empty state,
 //   resume(State&, row, lane) = fold in a state carried from an earlier call (once per row),
-//   range(State&, row, e0, e1, lane), combine(State&, lane) = fold the sub-groups' states after range,
+//   ring_bytes() = shared memory per warp for an operator that stages its gathered rows there (0: none),
+//   range(State&, row, e0, e1, lane, ring) with ring = the warp's staging area,
+//   combine(State&, lane) = fold the sub-groups' states after range,
 //   finalize(State&, row, lane), store_partial(State&, float* p, lane),
 //   merge_partial(State&, const float* p, lane)
 // ---------------------------------------------------------------------------
@@ -149,7 +151,9 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 // batch's index pointers arrive in one coalesced load.
 template <class Op>
 __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op, unsigned long long* next_row, const int batch) {
+  extern __shared__ float4 dgnn_smem4[];
   const int lane = threadIdx.x & 31;
+  float4* ring = dgnn_smem4 + (size_t)(threadIdx.x >> 5) * (op.ring_bytes() / 16);
   for (;;) {
     unsigned long long t = 0;
     if (lane == 0) t = atomicAdd(next_row, (unsigned long long)batch);
@@ -166,7 +170,7 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const
       typename Op::State st;
       op.init(st, r, lane);
       op.resume(st, r, lane);
-      op.range(st, r, lb, hb, lane);
+      op.range(st, r, lb, hb, lane, ring);
       op.combine(st, lane);
       op.finalize(st, r, lane);
     }
@@ -177,7 +181,9 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const
 // length, no counter and no chunk / merge kernels -- launch latency is all that matters there.
 template <class Op>
 __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows_small(const Op op) {
+  extern __shared__ float4 dgnn_smem4[];
   const int lane = threadIdx.x & 31;
+  float4* ring = dgnn_smem4 + (size_t)(threadIdx.x >> 5) * (op.ring_bytes() / 16);
   const i64 r = (i64)blockIdx.x * DGNN_ROW_WARPS + (threadIdx.x >> 5);
   if (r >= op.n_rows) return;
   const i64 lb = ldp(op.indptr, op.idx_bits, r);
@@ -186,7 +192,7 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows_small
   typename Op::State st;
   op.init(st, r, lane);
   op.resume(st, r, lane);
-  op.range(st, r, lb, hb, lane);
+  op.range(st, r, lb, hb, lane, ring);
   op.combine(st, lane);
   op.finalize(st, r, lane);
 }
@@ -196,10 +202,12 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows_small
 // states are folded in edge order through shared memory and warp 0 writes the
 // chunk's partial state.
 template <class Op>
-__global__ void __launch_bounds__(DGNN_CHUNK_WARPS * 32) k_chunks(const Op op) {
-  extern __shared__ float4 dgnn_smem4[];
+__global__ void __launch_bounds__(DGNN_CHUNK_WARPS * 32, Op::MIN_BLOCKS) k_chunks(const Op op) {
+  extern __shared__ float4 dgnn_smem4[];   // [partial states of warps 1.. | staging areas of the warps]
   float* smem = reinterpret_cast<float*>(dgnn_smem4);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t part4 = Op::HAS_PARTIALS ? ((size_t)(DGNN_CHUNK_WARPS - 1) * op.slot_stride + 3) / 4 : 0;
+  float4* ring = dgnn_smem4 + part4 + (size_t)warp * (op.ring_bytes() / 16);
   const i64 w = blockIdx.x;
   const i64 j = w >> 1;
   const int slot = (int)(w & 1);
@@ -217,7 +225,7 @@ __global__ void __launch_bounds__(DGNN_CHUNK_WARPS * 32) k_chunks(const Op op) {
   const i64 w1 = (w0 + per < e1) ? w0 + per : e1;
   typename Op::State st;
   op.init(st, r, lane);
-  if (w0 < w1) op.range(st, r, w0, w1, lane);
+  if (w0 < w1) op.range(st, r, w0, w1, lane, ring);
   if (!Op::HAS_PARTIALS) return;
   op.combine(st, lane);
   if (warp > 0) op.store_partial(st, smem + (i64)(warp - 1) * op.slot_stride, lane);
@@ -256,31 +264,50 @@ static inline i64 dgnn_num_chunks(i64 nnz) { return (nnz + DGNN_SEG - 1) / DGNN_
 
 // Launch the row / chunk / merge trio for one operator.  `counter` points at 8
 // zero-able bytes of workspace (the row counter of k_rows).
+// kernels whose dynamic shared memory exceeds the 48 KB default need the limit raised once per launch site
+template <class K>
+static inline cudaError_t dgnn_allow_smem(K kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
 template <class Op>
 static inline int dgnn_launch_trio(const Op& op, unsigned long long* counter, cudaStream_t s) {
   if (op.n_rows <= 0) return DGNN_OK;
+  const size_t ring = (size_t)op.ring_bytes();          // staging area per warp (0 for operators that gather into registers)
+  const size_t row_smem = ring * DGNN_ROW_WARPS;
+  cudaError_t e;
   if (op.nnz <= DGNN_SMALL_NNZ) {
-    k_rows_small<Op><<<dgnn_grid(op.n_rows, DGNN_ROW_WARPS), DGNN_ROW_THREADS, 0, s>>>(op);
+    if ((e = dgnn_allow_smem(k_rows_small<Op>, row_smem)) != cudaSuccess) return (int)e;
+    k_rows_small<Op><<<dgnn_grid(op.n_rows, DGNN_ROW_WARPS), DGNN_ROW_THREADS, row_smem, s>>>(op);
     cudaError_t e0 = cudaGetLastError();
     return e0 == cudaSuccess ? DGNN_OK : (int)e0;
   }
-  cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned long long), s);
+  e = cudaMemsetAsync(counter, 0, sizeof(unsigned long long), s);
   if (e != cudaSuccess) return (int)e;
   {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const i64 pool = (i64)sms * Op::MIN_BLOCKS;     // resident CTAs: one wave, rows are drawn dynamically
+    int per_sm = Op::MIN_BLOCKS;                         // resident CTAs per SM: registers, or the staging areas
+    if (row_smem > 0) {
+      const int fit = (int)((227 * 1024) / (row_smem + 1024));
+      if (fit < per_sm) per_sm = fit < 1 ? 1 : fit;
+    }
+    const i64 pool = (i64)sms * per_sm;                  // one wave, rows are drawn dynamically
     const i64 need = (op.n_rows + DGNN_ROW_WARPS - 1) / DGNN_ROW_WARPS;
     // rows per draw: about 64 edges' worth, one row once the average row has 32 edges or more
     const i64 avg = op.nnz / op.n_rows;
     int batch = avg >= 32 ? 1 : (int)(64 / (avg > 2 ? avg : 2));
     if (batch > 31) batch = 31;  // the batch's pointers plus one fit the 32 lanes
-    k_rows<Op><<<(unsigned)(need < pool ? need : pool), DGNN_ROW_THREADS, 0, s>>>(op, counter, batch);
+    if ((e = dgnn_allow_smem(k_rows<Op>, row_smem)) != cudaSuccess) return (int)e;
+    k_rows<Op><<<(unsigned)(need < pool ? need : pool), DGNN_ROW_THREADS, row_smem, s>>>(op, counter, batch);
   }
   if (op.nnz > DGNN_SEG) {
     const i64 nc = dgnn_num_chunks(op.nnz);
-    const size_t smem = Op::HAS_PARTIALS ? (size_t)(DGNN_CHUNK_WARPS - 1) * op.slot_stride * sizeof(float) : 0;
+    const size_t part = Op::HAS_PARTIALS ? (((size_t)(DGNN_CHUNK_WARPS - 1) * op.slot_stride + 3) / 4) * 16 : 0;
+    const size_t smem = part + ring * DGNN_CHUNK_WARPS;
+    if ((e = dgnn_allow_smem(k_chunks<Op>, smem)) != cudaSuccess) return (int)e;
     k_chunks<Op><<<(unsigned)(2 * nc), DGNN_CHUNK_WARPS * 32, smem, s>>>(op);
     if (Op::HAS_PARTIALS) k_merge<Op><<<dgnn_grid(nc, DGNN_WARPS), DGNN_THREADS, 0, s>>>(op);
   }

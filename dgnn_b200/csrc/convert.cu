@@ -6,8 +6,10 @@
 // histogram per tile -> exclusive scan over (digit, tile) -> stable scatter;
 // ranks inside a tile come from warp match_any votes taken in index order, so
 // entries of one column keep their CSR order exactly as the reference's
-// cuSPARSE conversion (and scipy's tocsc) produce.  col_ptr is the exclusive
-// scan of the column histogram.  Only integer atomics (commutative) are used.
+// cuSPARSE conversion (and scipy's tocsc) produce.  The last pass also writes
+// the sorted column ids, and col_ptr[c] is the first position whose id is >= c
+// (a binary search per column: no per-column histogram, no global atomics).
+// Only shared-memory integer atomics (commutative) are used.
 #include "common.cuh"
 #include <mutex>
 
@@ -114,16 +116,26 @@ int exclusive_scan(unsigned* data, i64 n, unsigned* scratch, cudaStream_t s) {
   return DGNN_OK;
 }
 
-// ---- column histogram -> col_ptr ------------------------------------------
-__global__ void k_col_hist(i64 nnz, const int* col_ind, unsigned* hist) {
-  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < nnz) atomicAdd(hist + __ldg(col_ind + t), 1u);
+// ---- col_ptr from the sorted column ids -------------------------------------
+__global__ void k_col_ptr(i64 n_cols, i64 nnz, const unsigned* sorted_keys, void* out, int bits) {
+  const i64 c = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c > n_cols) return;
+  i64 lo = 0, hi = nnz;  // first position whose column id is >= c
+  while (lo < hi) {
+    const i64 mid = (lo + hi) >> 1;
+    if ((i64)__ldg(sorted_keys + mid) < c) lo = mid + 1; else hi = mid;
+  }
+  if (bits == 64) reinterpret_cast<i64*>(out)[c] = lo;
+  else reinterpret_cast<int*>(out)[c] = (int)lo;
 }
-__global__ void k_write_ptr(i64 n_plus_1, const unsigned* scanned, void* out, int bits) {
-  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n_plus_1) return;
-  if (bits == 64) reinterpret_cast<i64*>(out)[t] = (i64)scanned[t];
-  else reinterpret_cast<int*>(out)[t] = (int)scanned[t];
+
+// row of the first entry of every run of RS_WARP_ITEMS consecutive CSR positions (the items one warp of the
+// first pass owns): the warps then look their rows up between two neighbouring entries of this table
+// instead of searching the whole index pointer
+__global__ void k_warp_rows(i64 nnz, i64 n_rows, const void* row_ptr, int idx_bits, int* wrow, int items) {
+  const i64 w = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  const i64 pos = w * items;
+  if (pos < nnz) wrow[w] = (int)find_row(row_ptr, idx_bits, n_rows, pos);
 }
 
 // ---- radix passes -----------------------------------------------------------
@@ -151,13 +163,13 @@ k_radix_hist(const unsigned* keys, i64 n, int shift, unsigned* tile_hist, i64 nt
 // the output, so a warp's store covers a few runs of consecutive addresses instead
 // of 32 scattered words.
 // FIRST: keys are the CSR column ids, payload (position,row) is generated here.
-// LAST: keys are not written.
-template <bool FIRST, bool LAST>
+// TWO: a second payload (the row id) travels with the first; a plain (key, value) sort carries one.
+template <bool FIRST, bool TWO>
 __global__ void __launch_bounds__(RS_THREADS, 2)
 k_radix_scatter(const unsigned* __restrict__ keys_in, const int* __restrict__ pos_in, const int* __restrict__ row_in,
                 unsigned* __restrict__ keys_out, int* __restrict__ pos_out, int* __restrict__ row_out, i64 n, int shift,
                 const unsigned* __restrict__ tile_off, i64 ntiles, const void* __restrict__ row_ptr, int idx_bits,
-                i64 n_rows) {
+                i64 n_rows, const int* __restrict__ wrow) {
   __shared__ unsigned cnt[RS_WARPS][RADIX];  // per-warp digit counts, then per-warp start inside the sorted tile
   __shared__ unsigned gbase[RADIX];          // start of the digit's run in the output minus its start in the tile
   __shared__ unsigned buf[RS_TILE];          // exchange buffer
@@ -231,7 +243,7 @@ k_radix_scatter(const unsigned* __restrict__ keys_in, const int* __restrict__ po
     if (i < n_tile) {
       const unsigned kk = buf[i];
       dst[k] = gbase[(kk >> shift) & (RADIX - 1)] + (unsigned)i;
-      if (!LAST) keys_out[dst[k]] = kk;
+      keys_out[dst[k]] = kk;
     }
   }
   __syncthreads();
@@ -247,13 +259,14 @@ k_radix_scatter(const unsigned* __restrict__ keys_in, const int* __restrict__ po
     const int i = k * RS_THREADS + tid;
     if (i < n_tile) pos_out[dst[k]] = (int)buf[i];
   }
+  if (!TWO) return;
   __syncthreads();
   // payload 2: row id (FIRST: looked up between the rows of the warp's first and last entry)
   i64 r_lo = 0, r_hi = 0;
   if (FIRST && wbase < n) {
-    const i64 last = (wbase + RS_WARP_ITEMS <= n ? wbase + RS_WARP_ITEMS : n) - 1;
-    r_lo = find_row(row_ptr, idx_bits, n_rows, wbase);
-    r_hi = find_row(row_ptr, idx_bits, n_rows, last);
+    const i64 gw = wbase / RS_WARP_ITEMS;
+    r_lo = __ldg(wrow + gw);
+    r_hi = wbase + RS_WARP_ITEMS < n ? (i64)__ldg(wrow + gw + 1) : n_rows - 1;   // row of the next run's first entry bounds this run's rows
   }
 #pragma unroll
   for (int t = 0; t < RS_IPT; ++t) {
@@ -293,7 +306,7 @@ __global__ void k_coo2csr(i64 nnz, i64 m, const int* row_ind, void* row_ptr, int
 }
 
 struct C2CLayout {
-  size_t col_hist, tile_hist, scan_scratch, keys[2], pos[2], row[2], total;
+  size_t tile_hist, scan_scratch, wrow, keys[2], pos[2], row[2], total;
   i64 ntiles;
   int passes;
 };
@@ -304,16 +317,17 @@ inline C2CLayout c2c_layout(i64 n_cols, i64 nnz) {
   L.passes = (bits + 7) / 8;
   L.ntiles = cdiv(nnz > 0 ? nnz : 1, RS_TILE);
   const i64 hist_items = (i64)RADIX * L.ntiles;
-  const i64 scan_items = hist_items > n_cols + 1 ? hist_items : n_cols + 1;
   size_t off = 0;
-  L.col_hist = off;     off += up256((size_t)(n_cols + 1) * 4);
   L.tile_hist = off;    off += up256((size_t)hist_items * 4);
-  L.scan_scratch = off; off += up256((size_t)scan_scratch_items(scan_items) * 4);
+  L.scan_scratch = off; off += up256((size_t)scan_scratch_items(hist_items) * 4);
+  L.wrow = off;         off += up256((size_t)(cdiv(nnz > 0 ? nnz : 1, RS_WARP_ITEMS) + 1) * 4);
   for (int i = 0; i < 2; ++i) {
-    const bool need = L.passes > i + 1;  // passes-1 intermediate buffers, at most 2 alive
-    L.keys[i] = off; off += need ? up256((size_t)nnz * 4) : 0;
-    L.pos[i] = off;  off += need ? up256((size_t)nnz * 4) : 0;
-    L.row[i] = off;  off += need ? up256((size_t)nnz * 4) : 0;
+    // pass p writes slot p & 1: the keys of every pass (the last pass's sorted ids give col_ptr), the
+    // payload of every pass but the last (that one goes to permute / row_ind)
+    const bool need_keys = L.passes > i, need_payload = L.passes > i + 1;
+    L.keys[i] = off; off += need_keys ? up256((size_t)nnz * 4) : 0;
+    L.pos[i] = off;  off += need_payload ? up256((size_t)nnz * 4) : 0;
+    L.row[i] = off;  off += need_payload ? up256((size_t)nnz * 4) : 0;
   }
   L.total = off + 256;
   return L;
@@ -326,16 +340,12 @@ int dgnn_csr2csc_impl(i64 n_rows, i64 n_cols, i64 nnz, const void* row_ptr, int 
                       const int32_t* col_ind, void* col_ptr, int32_t* row_ind, int32_t* permute,
                       char* wsb, cudaStream_t s) {
   const C2CLayout L = c2c_layout(n_cols, nnz);
-  unsigned* col_hist = reinterpret_cast<unsigned*>(wsb + L.col_hist);
   unsigned* tile_hist = reinterpret_cast<unsigned*>(wsb + L.tile_hist);
   unsigned* scratch = reinterpret_cast<unsigned*>(wsb + L.scan_scratch);
-  cudaError_t e = cudaMemsetAsync(col_hist, 0, (size_t)(n_cols + 1) * 4, s);
-  if (e != cudaSuccess) return (int)e;
-  if (nnz > 0) k_col_hist<<<dgnn_grid(nnz, 256), 256, 0, s>>>(nnz, col_ind, col_hist);
-  int rc = exclusive_scan(col_hist, n_cols + 1, scratch, s);
-  if (rc) return rc;
-  k_write_ptr<<<dgnn_grid(n_cols + 1, 256), 256, 0, s>>>(n_cols + 1, col_hist, col_ptr, idx_bits);
+  int* wrow = reinterpret_cast<int*>(wsb + L.wrow);
+  const unsigned* sorted = nullptr;
   if (nnz > 0) {
+    k_warp_rows<<<dgnn_grid(cdiv(nnz, RS_WARP_ITEMS), 256), 256, 0, s>>>(nnz, n_rows, row_ptr, idx_bits, wrow, RS_WARP_ITEMS);
     const unsigned* kin = reinterpret_cast<const unsigned*>(col_ind);
     const int* pin = nullptr;
     const int* rin = nullptr;
@@ -343,26 +353,78 @@ int dgnn_csr2csc_impl(i64 n_rows, i64 n_cols, i64 nnz, const void* row_ptr, int 
     for (int p = 0; p < L.passes; ++p) {
       const bool first = p == 0, last = p == L.passes - 1;
       const int shift = 8 * p;
-      unsigned* kout = last ? nullptr : reinterpret_cast<unsigned*>(wsb + L.keys[p & 1]);
+      unsigned* kout = reinterpret_cast<unsigned*>(wsb + L.keys[p & 1]);
       int* pout = last ? permute : reinterpret_cast<int*>(wsb + L.pos[p & 1]);
       int* rout = last ? row_ind : reinterpret_cast<int*>(wsb + L.row[p & 1]);
       k_radix_hist<<<grid, HIST_THREADS, 0, s>>>(kin, nnz, shift, tile_hist, L.ntiles);
-      rc = exclusive_scan(tile_hist, (i64)RADIX * L.ntiles, scratch, s);
+      int rc = exclusive_scan(tile_hist, (i64)RADIX * L.ntiles, scratch, s);
       if (rc) return rc;
-#define RS_ARGS kin, pin, rin, kout, pout, rout, nnz, shift, tile_hist, L.ntiles, row_ptr, idx_bits, n_rows
-      if (first && last) k_radix_scatter<true, true><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
-      else if (first) k_radix_scatter<true, false><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
-      else if (last) k_radix_scatter<false, true><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
-      else k_radix_scatter<false, false><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
+#define RS_ARGS kin, pin, rin, kout, pout, rout, nnz, shift, tile_hist, L.ntiles, row_ptr, idx_bits, n_rows, wrow
+      if (first) k_radix_scatter<true, true><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
+      else k_radix_scatter<false, true><<<grid, RS_THREADS, 0, s>>>(RS_ARGS);
 #undef RS_ARGS
       kin = kout; pin = pout; rin = rout;
     }
+    sorted = kin;
   }
-  e = cudaGetLastError();
+  k_col_ptr<<<dgnn_grid(n_cols + 1, 256), 256, 0, s>>>(n_cols, nnz, sorted, col_ptr, idx_bits);
+  cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
 
 size_t dgnn_csr2csc_scratch_bytes(i64 n_cols, i64 nnz) { return c2c_layout(n_cols, nnz).total; }
+
+// ---------------------------------------------------------------------------
+// Stable sort of (key, value) pairs by the low key_bits bits of the key with the same radix passes; two of
+// them in a row (by source, then by destination) order an edge list by (destination, source).
+// ---------------------------------------------------------------------------
+namespace {
+struct PairLayout {
+  size_t tile_hist, scan_scratch, keys, vals, total;
+  i64 ntiles;
+  int passes;
+};
+inline PairLayout pair_layout(i64 n, int key_bits) {
+  PairLayout L;
+  L.passes = (key_bits + 7) / 8;
+  if (L.passes < 1) L.passes = 1;
+  L.ntiles = cdiv(n > 0 ? n : 1, RS_TILE);
+  const i64 hist_items = (i64)RADIX * L.ntiles;
+  size_t off = 0;
+  L.tile_hist = off;    off += up256((size_t)hist_items * 4);
+  L.scan_scratch = off; off += up256((size_t)scan_scratch_items(hist_items) * 4);
+  L.keys = off;         off += up256((size_t)n * 4);      // one ping-pong partner: the output arrays are the other
+  L.vals = off;         off += up256((size_t)n * 4);
+  L.total = off + 256;
+  return L;
+}
+
+// passes alternate between (tmp) and (out); the last one lands in out
+int sort_pairs(i64 n, int key_bits, const unsigned* keys_in, const int* vals_in, unsigned* keys_out, int* vals_out,
+               char* wsb, cudaStream_t s) {
+  const PairLayout L = pair_layout(n, key_bits);
+  unsigned* tile_hist = reinterpret_cast<unsigned*>(wsb + L.tile_hist);
+  unsigned* scratch = reinterpret_cast<unsigned*>(wsb + L.scan_scratch);
+  unsigned* ktmp = reinterpret_cast<unsigned*>(wsb + L.keys);
+  int* vtmp = reinterpret_cast<int*>(wsb + L.vals);
+  const unsigned* kin = keys_in;
+  const int* vin = vals_in;
+  const unsigned grid = (unsigned)L.ntiles;
+  for (int p = 0; p < L.passes; ++p) {
+    const bool to_out = ((L.passes - 1 - p) & 1) == 0;
+    unsigned* kout = to_out ? keys_out : ktmp;
+    int* vout = to_out ? vals_out : vtmp;
+    k_radix_hist<<<grid, HIST_THREADS, 0, s>>>(kin, n, 8 * p, tile_hist, L.ntiles);
+    int rc = exclusive_scan(tile_hist, (i64)RADIX * L.ntiles, scratch, s);
+    if (rc) return rc;
+    k_radix_scatter<false, false><<<grid, RS_THREADS, 0, s>>>(kin, vin, nullptr, kout, vout, nullptr, n, 8 * p, tile_hist,
+                                                               L.ntiles, nullptr, 32, 0, nullptr);
+    kin = kout; vin = vout;
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+}  // namespace
 
 // ---------------------------------------------------------------------------
 // Allocation-free variant: the scratch of the conversion lives in a fixed array
@@ -418,6 +480,34 @@ int dgnn_csr2csc(int64_t n_rows, int64_t n_cols, int64_t nnz, const void* row_pt
                            reinterpret_cast<cudaStream_t>(stream));
 }
 
+size_t dgnn_coo_sort_workspace_bytes(int64_t nnz, int64_t n_nodes) {
+  if (nnz < 0 || n_nodes < 0) return 256;
+  int bits = 1;
+  while (((i64)1 << bits) < n_nodes) ++bits;
+  return pair_layout(nnz, bits).total + 2 * up256((size_t)nnz * 4);
+}
+
+int dgnn_coo_sort(int64_t nnz, int64_t n_nodes, const int32_t* dst, const int32_t* src, int32_t* dst_sorted,
+                  int32_t* src_sorted, void* workspace, size_t workspace_bytes, void* stream) {
+  if (nnz < 0 || n_nodes < 0) return DGNN_ERR_SHAPE;
+  if (nnz > 0x7fffffffLL || n_nodes > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;
+  if (nnz == 0) return DGNN_OK;
+  if (!dst || !src || !dst_sorted || !src_sorted) return DGNN_ERR_NULL;
+  if (!workspace || workspace_bytes < dgnn_coo_sort_workspace_bytes(nnz, n_nodes)) return DGNN_ERR_WORKSPACE;
+  int bits = 1;
+  while (((i64)1 << bits) < n_nodes) ++bits;
+  char* wsb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  const PairLayout L = pair_layout(nnz, bits);
+  unsigned* mid_src = reinterpret_cast<unsigned*>(wsb + L.total);
+  int* mid_dst = reinterpret_cast<int*>(wsb + L.total + up256((size_t)nnz * 4));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // by source (destination rides along), then stably by destination (source rides along)
+  int rc = sort_pairs(nnz, bits, reinterpret_cast<const unsigned*>(src), dst, mid_src, mid_dst, wsb, s);
+  if (rc) return rc;
+  return sort_pairs(nnz, bits, reinterpret_cast<const unsigned*>(mid_dst), reinterpret_cast<const int*>(mid_src),
+                    reinterpret_cast<unsigned*>(dst_sorted), src_sorted, wsb, s);
+}
+
 int dgnn_coo2csr(int64_t nnz, int64_t m, const int32_t* row_ind, void* row_ptr, int idx_bits, void* stream) {
   if (nnz < 0 || m < 0) return DGNN_ERR_SHAPE;
   if (idx_bits != 32 && idx_bits != 64) return DGNN_ERR_IDX_BITS;
@@ -442,8 +532,9 @@ int dgnn_csr2csc_static(int64_t n_rows, int64_t n_cols, int64_t nnz, const void*
   char* scratch = nullptr;
   const int rc = static_scratch_for_current_device(&scratch);
   if (rc) return rc;
-  // every region of the scratch that is read is written first by this call (the column
-  // histogram is cleared, the rest is overwritten), so stale contents of the previous call do no harm
+  // every region of the scratch that is read is written first by this call (tile histograms, row
+  // table and the ping-pong buffers are all overwritten before use), so stale contents of the previous
+  // call do no harm and nothing needs clearing
   return dgnn_csr2csc_impl(n_rows, n_cols, nnz, row_ptr, idx_bits, col_ind, col_ptr, row_ind, permute, scratch,
                            reinterpret_cast<cudaStream_t>(stream));
 }

@@ -173,7 +173,8 @@ struct GatFwdOp {
     }
   }
 
-  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+  __host__ __device__ __forceinline__ int ring_bytes() const { return 0; }   // gathers go straight into registers
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     constexpr int STEP = Unroll<VPL>::U * EPW;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
@@ -499,7 +500,8 @@ struct GatBwdOp {
     }
   }
 
-  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+  __host__ __device__ __forceinline__ int ring_bytes() const { return 0; }   // gathers go straight into registers
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     constexpr int STEP = Unroll<VPL>::U * EPW;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
@@ -719,10 +721,10 @@ int launch_bwd_op(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const 
   return dgnn_launch_trio(op, counter, s);
 }
 
-template <int VPL, bool MASK, bool FULL, int LPR, class... A>
+template <int VPL, bool MASK, bool FULL, int LPR, bool EDGE, class... A>
 int launch_bwd(const FastShape& fs, A... a) {
   if constexpr (VPL > 1) {
-    if (same_head_layout(fs)) return launch_bwd_op<GatBwdOpSH<VPL, MASK, FULL>>(fs, a...);
+    if (same_head_layout(fs)) return launch_bwd_op<GatBwdOpSH<VPL, MASK, FULL, EDGE>>(fs, a...);
   }
   return launch_bwd_op<GatBwdOp<VPL, MASK, FULL, LPR>>(fs, a...);
 }
@@ -986,12 +988,14 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
   if (n_cols > 0) {
     if (fs.ok && aligned16(in_feat) && aligned16(grad_out) && aligned16(grad_feat)) {
       int rc;
-#define CALL_BWD(V, M, FW, L)                                                                           \
-  launch_bwd<V, M, FW, L>(fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat,    \
-                   attn_col, grad_out, negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, \
-                   col_part, counter, state, first, last, s)
+#define BWD_ARGS                                                                                          \
+  fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat, attn_col, grad_out,   \
+      negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, col_part, counter, state, first, last, s
+#define CALL_BWD(V, M, FW, L) \
+  (edge ? launch_bwd<V, M, FW, L, true>(BWD_ARGS) : launch_bwd<V, M, FW, L, false>(BWD_ARGS))
       auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_BWD) };
 #undef CALL_BWD
+#undef BWD_ARGS
       rc = run();
       if (rc) return rc;
     } else {

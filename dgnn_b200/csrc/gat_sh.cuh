@@ -160,7 +160,8 @@ struct GatFwdOpSH {
     }
   }
 
-  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+  __host__ __device__ __forceinline__ int ring_bytes() const { return 0; }   // gathers go straight into registers
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
@@ -239,9 +240,11 @@ struct GatFwdOpSH {
 };
 
 // ------------------------------------------------------------ backward cols
-template <int VPL, bool MASK, bool FULL>
+// EDGE: the per-edge term d_e is written to grad_edge (CSR position through `permute`); without it -- the row
+// gradient then comes from the row statistics -- neither array is touched unless a dropout mask needs the position
+template <int VPL, bool MASK, bool FULL, bool EDGE>
 struct GatBwdOpSH {
-  static constexpr int MIN_BLOCKS = VPL <= 2 ? 4 : (VPL == 4 ? 3 : 2);
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? (EDGE || MASK ? 4 : 5) : (VPL == 4 ? 3 : 2);
   static constexpr bool HAS_PARTIALS = true;
   static constexpr int U = VPL <= 2 ? 4 : 2;
   i64 n_rows, nnz;      // "rows" of the CSC form = source columns
@@ -291,7 +294,7 @@ struct GatBwdOpSH {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       r[u] = __shfl_sync(DGNN_FULL, my_r, (k + u) & 31);
-      pp[u] = __shfl_sync(DGNN_FULL, my_p, (k + u) & 31);
+      pp[u] = (EDGE || MASK) ? __shfl_sync(DGNN_FULL, my_p, (k + u) & 31) : 0;
     }
     float4 pk[U], g4[U][VPL];
     bool keep[U];
@@ -325,17 +328,19 @@ struct GatBwdOpSH {
         const float w = alpha * kp;
 #pragma unroll
         for (int v = 0; v < VPL; ++v) fma4(st.acc[v], w, g4[u][v]);
-        if (grad_edge && st.lm.lead) grad_edge[(i64)pp[u] * H + st.lm.hd] = de;
+        if (EDGE && st.lm.lead) grad_edge[(i64)pp[u] * H + st.lm.hd] = de;
       }
     }
   }
 
-  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+  __host__ __device__ __forceinline__ int ring_bytes() const { return 0; }   // gathers go straight into registers
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
       const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
       // without a permutation the mask (if any) is laid out in CSC order: the position is the index
-      const int my_p = lane < cnt ? (permute ? __ldg(permute + base + lane) : (int)(base + lane)) : 0;
+      int my_p = 0;
+      if (EDGE || MASK) my_p = lane < cnt ? (permute ? __ldg(permute + base + lane) : (int)(base + lane)) : 0;
       int k = 0;
       for (; k + U <= cnt; k += U) batch<true>(st, my_r, my_p, k, cnt);
       if (k < cnt) batch<false>(st, my_r, my_p, k, cnt);

@@ -21,6 +21,7 @@
 //
 // Every wait on an mbarrier is bounded: when a wait runs out the CTA raises a flag,
 // all roles leave their loops, tensor memory is freed and a status word is written.
+#include <atomic>
 #include <cuda.h>  // CUtensorMap and its enums; the encode function is looked up at run time, nothing links to libcuda
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -43,7 +44,7 @@ constexpr int PJ_WARP_TMA = 4, PJ_WARP_MMA = 5, PJ_WARP_CONV0 = 6;
 constexpr int PJ_THREADS = (PJ_WARP_CONV0 + PJ_CONV_WARPS) * 32;  // 448
 constexpr int PJ_TMEM_COLS = 2 * PJ_BN;
 constexpr size_t PJ_SMEM = (size_t)(2 * PJ_MAX_KB + 2 * PJ_STAGES) * PJ_TILE_BYTES + 2 * PJ_OUT_BYTES + 1024;  // + alignment slack
-constexpr i64 PJ_TIMEOUT = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
+constexpr i64 PJ_TIMEOUT = 4000000000LL;  // clock cycles (~2 s) before a wait gives up (dgnn_project_set_test_knobs overrides it)
 
 // tcgen05 instruction descriptor: fp32 accumulate, tf32 A and B, both K-major, M = 128 (columns of out), N = 128 (rows of x)
 constexpr uint32_t PJ_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(PJ_BN >> 3) << 17) | ((uint32_t)(PJ_BM >> 4) << 24);
@@ -74,7 +75,12 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
 // is nothing but try_wait (which parks the thread for a while by itself); the clock and the give-up flag
 // are looked at once per 64 failed tries, so waiting warps leave the issue slots and the memory pipe to
 // the warps that have work.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int who) {
+struct PjKnobs {
+  i64 wait_limit;         // clock cycles before a wait gives up
+  int skip_first_arrive;  // test only: the converter warps never announce their first stage, so the MMA thread's wait runs out
+};
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int who, i64 limit = PJ_TIMEOUT) {
 #pragma unroll 1
   for (int spin = 0; spin < 64; ++spin)
     if (mbar_try(bar, parity)) return true;
@@ -84,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (int spin = 0; spin < 64; ++spin)
       if (mbar_try(bar, parity)) return true;
     if (*give_up) return false;
-    if (clock64() - t0 > PJ_TIMEOUT) {
+    if (clock64() - t0 > limit) {
       *give_up = who;
       return false;
     }
@@ -158,7 +164,7 @@ struct PjBars {  // mbarriers of one CTA
 
 __global__ void __launch_bounds__(PJ_THREADS, 1)
 k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_out, const float* __restrict__ x,
-          const i64 m, const int n, const int k, const i64 ntiles, const int groups, int* __restrict__ status) {
+          const i64 m, const int n, const int k, const i64 ntiles, const int groups, int* __restrict__ status, const PjKnobs knobs) {
   extern __shared__ unsigned char pj_smem_raw[];
   __shared__ PjBars bars;
   __shared__ uint32_t tmem_slot;
@@ -210,16 +216,16 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     }
   } else if (warp == PJ_WARP_MMA) {
     if (lane == 0) {
-      bool ok = mbar_wait(smem_u32(&bars.wfull), 0, give_up, 2);
+      bool ok = mbar_wait(smem_u32(&bars.wfull), 0, give_up, 2, knobs.wait_limit);
       uint32_t it = 0, j = 0;
       for (i64 tile = first; ok && tile < ntiles; tile += stride, ++j) {
         const uint32_t a = j & 1u;
-        if (!(ok = mbar_wait(smem_u32(&bars.tempty[a]), ((j >> 1) & 1u) ^ 1u, give_up, 3))) break;
+        if (!(ok = mbar_wait(smem_u32(&bars.tempty[a]), ((j >> 1) & 1u) ^ 1u, give_up, 3, knobs.wait_limit))) break;
         tc_fence_after();
         const uint32_t d = tmem + a * PJ_BN;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t s = it % PJ_STAGES, ph = (it / PJ_STAGES) & 1u;
-          if (!(ok = mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4))) break;
+          if (!(ok = mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4, knobs.wait_limit))) break;
           tc_fence_after();
           const uint64_t a_hi = umma_desc(ring + s * 2 * PJ_TILE_BYTES), a_lo = umma_desc(ring + s * 2 * PJ_TILE_BYTES + PJ_TILE_BYTES);
           const uint64_t b_hi = umma_desc(w_hi + kb * PJ_TILE_BYTES), b_lo = umma_desc(w_lo + kb * PJ_TILE_BYTES);
@@ -267,7 +273,7 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         ++it;
         // one thread waits for the stage, the hardware barrier tells the others (and keeps the eight warps
         // on the same number of barriers whatever the outcome)
-        if (ct == 0) conv_ok_s = mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5) ? 1 : 0;
+        if (ct == 0) conv_ok_s = mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5, knobs.wait_limit) ? 1 : 0;
         conv_sync();
         if (!(ok = conv_ok_s != 0)) break;
         unsigned char* hi = ring_ptr + (size_t)s * 2 * PJ_TILE_BYTES + soff;
@@ -286,7 +292,7 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         // the eight warps meet at the hardware barrier and one thread arrives: 256 arrivals on one mbarrier
         // word serialise, and a per-warp arrival behind __syncwarp measured several times slower than this
         conv_sync();
-        if (ct == 0) mbar_arrive(smem_u32(&bars.conv[s]));
+        if (ct == 0 && !(knobs.skip_first_arrive && it == 1)) mbar_arrive(smem_u32(&bars.conv[s]));   // it was advanced above
         fetch(tile + stride, kb);
       }
     }
@@ -298,7 +304,7 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int cw = warp * 32 + lane;  // warp w reads lanes 32w .. 32w+31
     for (i64 tile = first; tile < ntiles; tile += stride, ++j) {
       const uint32_t a = j & 1u;
-      if (tid == 0) epi_ok_s = mbar_wait(smem_u32(&bars.tfull[a]), (j >> 1) & 1u, give_up, 6) ? 1 : 0;
+      if (tid == 0) epi_ok_s = mbar_wait(smem_u32(&bars.tfull[a]), (j >> 1) & 1u, give_up, 6, knobs.wait_limit) ? 1 : 0;
       epi_sync();
       if (!epi_ok_s) break;
       tc_fence_after();
@@ -329,7 +335,10 @@ k_project(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PJ_TMEM_COLS) : "memory");
   }
-  if (tid == 0 && give_up_s != 0) atomicMax(status, give_up_s);
+  if (tid == 0 && give_up_s != 0) {
+    atomicMax(status, give_up_s);       // this call
+    atomicMax(status + 1, give_up_s);   // sticky: only the owner of the workspace clears it
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -367,18 +376,25 @@ __device__ __forceinline__ void umma_tf32_mn(uint32_t d_tmem, uint64_t adesc, ui
       : "memory");
 }
 
+// The tensor core adds each product into the fp32 accumulator with truncation, so the error of a chain of
+// accumulations grows with its length (measured: 2.3e-4 of the largest entry after the 32 k rows one CTA sums
+// at 2.4 M rows, against 3e-6 for a library SGEMM).  The accumulator is therefore drained every WG_DRAIN steps
+// (1024 rows) into the CTA's fp32 partial sums, which are added with round-to-nearest.
+constexpr int WG_DRAIN = 32;
+
 struct WgBars {
-  unsigned long long conv[WG_STAGES], empty[WG_STAGES], done;
+  unsigned long long conv[WG_STAGES], empty[WG_STAGES], done, drained;
 };
 
 __global__ void __launch_bounds__(PJ_THREADS, 1)
 k_project_wgrad(const float* __restrict__ x, const float* __restrict__ g, float* __restrict__ partial, const i64 m,
-                const int n, const int k, const i64 nsteps, const int groups, int* __restrict__ status) {
+                const int n, const int k, const i64 nsteps, const int groups, int* __restrict__ status, const PjKnobs knobs) {
   extern __shared__ unsigned char pj_smem_raw[];
   __shared__ WgBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int give_up_s;
   __shared__ int conv_ok_s;
+  __shared__ int epi_ok_s[PJ_EPI_WARPS];
   volatile int* give_up = &give_up_s;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -394,6 +410,7 @@ k_project_wgrad(const float* __restrict__ x, const float* __restrict__ g, float*
       mbar_init(smem_u32(&bars.empty[s]), 1);
     }
     mbar_init(smem_u32(&bars.done), 1);
+    mbar_init(smem_u32(&bars.drained), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == PJ_WARP_MMA) {
@@ -411,20 +428,25 @@ k_project_wgrad(const float* __restrict__ x, const float* __restrict__ g, float*
       bool ok = true;
       for (i64 t = first; ok && t < nsteps; t += stride, ++it) {
         const uint32_t s = it % WG_STAGES, ph = (it / WG_STAGES) & 1u;
-        if (!(ok = mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4))) break;
+        const uint32_t in_grp = it % WG_DRAIN, grp = it / WG_DRAIN;
+        if (in_grp == 0 && grp > 0) {   // the accumulator of the previous group must have been drained
+          if (!(ok = mbar_wait(smem_u32(&bars.drained), (grp - 1) & 1u, give_up, 7, knobs.wait_limit))) break;
+          tc_fence_after();
+        }
+        if (!(ok = mbar_wait(smem_u32(&bars.conv[s]), ph, give_up, 4, knobs.wait_limit))) break;
         tc_fence_after();
         const uint32_t st = ring + s * WG_STAGE_BYTES;
 #pragma unroll
         for (int q = 0; q < WG_ROWS / 8; ++q) {  // eight rows (1024 bytes) of every chunk per MMA
           const uint64_t g_hi = umma_desc_mn(st + q * 1024), g_lo = umma_desc_mn(st + WG_PART_BYTES + q * 1024);
           const uint64_t x_hi = umma_desc_mn(st + 2 * WG_PART_BYTES + q * 1024), x_lo = umma_desc_mn(st + 3 * WG_PART_BYTES + q * 1024);
-          umma_tf32_mn(tmem, g_lo, x_hi, (it | (uint32_t)q) != 0);
+          umma_tf32_mn(tmem, g_lo, x_hi, (in_grp | (uint32_t)q) != 0);
           umma_tf32_mn(tmem, g_hi, x_lo, 1u);
           umma_tf32_mn(tmem, g_hi, x_hi, 1u);
         }
         umma_commit(smem_u32(&bars.empty[s]));
+        if (in_grp == WG_DRAIN - 1 || t + stride >= nsteps) umma_commit(smem_u32(&bars.done));
       }
-      if (ok) umma_commit(smem_u32(&bars.done));
     }
   } else if (warp >= PJ_WARP_CONV0) {
     // thread -> 16-byte piece p of row r of every chunk; the same piece of the next step is requested as
@@ -457,7 +479,7 @@ k_project_wgrad(const float* __restrict__ x, const float* __restrict__ g, float*
     bool ok = true;
     for (i64 t = first; ok && t < nsteps; t += stride, ++it) {
       const uint32_t s = it % WG_STAGES, ph = (it / WG_STAGES) & 1u;
-      if (ct == 0) conv_ok_s = mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5) ? 1 : 0;
+      if (ct == 0) conv_ok_s = mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u, give_up, 5, knobs.wait_limit) ? 1 : 0;
       conv_sync();
       if (!(ok = conv_ok_s != 0)) break;
       unsigned char* st = ring_ptr + (size_t)s * WG_STAGE_BYTES + soff;
@@ -468,26 +490,43 @@ k_project_wgrad(const float* __restrict__ x, const float* __restrict__ g, float*
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       conv_sync();
-      if (ct == 0) mbar_arrive(smem_u32(&bars.conv[s]));
+      if (ct == 0 && !(knobs.skip_first_arrive && it == 0)) mbar_arrive(smem_u32(&bars.conv[s]));
       fetch(t + stride);
     }
   } else if (warp < PJ_EPI_WARPS) {
-    // after the last MMA: accumulator lane = column n of the group, accumulator column = k
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait(smem_u32(&bars.done), 0, give_up, 6);
-    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-    if (ok) {
+    // after every group of WG_DRAIN steps: accumulator lane = column n of the group, accumulator column = k;
+    // the first group's values are stored, the later ones added to the CTA's partial sums
+    const i64 my_steps = first < nsteps ? (nsteps - first + stride - 1) / stride : 0;
+    const i64 my_groups = (my_steps + WG_DRAIN - 1) / WG_DRAIN;
+    float* dst = partial + ((size_t)blockIdx.x * PJ_BN + warp * 32 + lane) * PJ_BN;
+    for (i64 gidx = 0; gidx < my_groups; ++gidx) {
+      // all four warps must take the same way out: one of them may see the barrier complete while another
+      // sees the give-up flag of a different role first
+      if (lane == 0) epi_ok_s[warp] = mbar_wait(smem_u32(&bars.done), (uint32_t)(gidx & 1), give_up, 6, knobs.wait_limit) ? 1 : 0;
+      epi_sync();
+      const bool ok = (epi_ok_s[0] & epi_ok_s[1] & epi_ok_s[2] & epi_ok_s[3]) != 0;
+      epi_sync();
+      if (!ok) break;
       tc_fence_after();
-      float* dst = partial + ((size_t)blockIdx.x * PJ_BN + warp * 32 + lane) * PJ_BN;
 #pragma unroll 1
       for (int c = 0; c < PJ_BN; c += 32) {
         uint32_t rr[32];
         tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c, rr);
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<float4*>(dst + c + 4 * q) = make_float4(__uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]),
-                                                                   __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3]));
+        for (int q = 0; q < 8; ++q) {
+          float4 v = make_float4(__uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]),
+                                 __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3]));
+          float4* pd = reinterpret_cast<float4*>(dst + c + 4 * q);
+          if (gidx > 0) {
+            const float4 o = *pd;
+            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+          }
+          *pd = v;
+        }
       }
+      tc_fence_before();
+      epi_sync();
+      if (tid == 0) mbar_arrive(smem_u32(&bars.drained));
     }
   }
 
@@ -497,7 +536,10 @@ k_project_wgrad(const float* __restrict__ x, const float* __restrict__ g, float*
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PJ_BN) : "memory");
   }
-  if (tid == 0 && give_up_s != 0) atomicMax(status, give_up_s);
+  if (tid == 0 && give_up_s != 0) {
+    atomicMax(status, give_up_s);       // this call
+    atomicMax(status + 1, give_up_s);   // sticky: only the owner of the workspace clears it
+  }
 }
 
 // grad_w = sum of the partials of one column group, in CTA order; written [k,n] (w_kn) or [n,k]
@@ -543,7 +585,11 @@ int make_map(CUtensorMap* map, const float* ptr, i64 rows, i64 cols, int box_row
   return r == CUDA_SUCCESS ? DGNN_OK : (int)cudaErrorInvalidValue;
 }
 
-constexpr size_t PJ_WS_HEADER = 256;  // status word
+constexpr size_t PJ_WS_HEADER = 256;  // status word of the last call, then the sticky status word
+
+std::atomic<long long> g_wait_limit{PJ_TIMEOUT};
+std::atomic<int> g_skip_first_arrive{0};
+inline PjKnobs current_knobs() { return PjKnobs{g_wait_limit.load(), g_skip_first_arrive.load()}; }
 
 }  // namespace
 
@@ -590,7 +636,7 @@ int dgnn_project_forward(int64_t m, int n, int k, const float* x, const float* w
   i64 per_group = sms / groups > 0 ? sms / groups : 1;
   if (per_group > ntiles) per_group = ntiles;
   const unsigned grid = (unsigned)(per_group * groups);
-  k_project<<<grid, PJ_THREADS, PJ_SMEM, s>>>(map_w, map_out, x, m, n, k, ntiles, groups, status);
+  k_project<<<grid, PJ_THREADS, PJ_SMEM, s>>>(map_w, map_out, x, m, n, k, ntiles, groups, status, current_knobs());
   e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
@@ -599,8 +645,9 @@ size_t dgnn_project_wgrad_workspace_bytes(int n) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  (void)n;
-  return PJ_WS_HEADER + (size_t)sms * PJ_BN * PJ_BN * sizeof(float);
+  const int groups = n > 0 ? n / PJ_BN : 1;
+  const int ctas = groups > sms ? groups : sms;   // the grid is (CTAs per group) x groups: never fewer than one CTA per group
+  return PJ_WS_HEADER + (size_t)ctas * PJ_BN * PJ_BN * sizeof(float);
 }
 
 int dgnn_project_wgrad(int64_t m, int n, int k, const float* x, const float* grad_out, float* grad_w, int w_kn,
@@ -629,7 +676,7 @@ int dgnn_project_wgrad(int64_t m, int n, int k, const float* x, const float* gra
   i64 per_group = sms / groups > 0 ? sms / groups : 1;
   if (per_group > nsteps) per_group = nsteps;  // every CTA gets at least one step, so every partial is written
   const unsigned grid = (unsigned)(per_group * groups);
-  k_project_wgrad<<<grid, PJ_THREADS, WG_SMEM, s>>>(x, grad_out, partial, m, n, k, nsteps, groups, status);
+  k_project_wgrad<<<grid, PJ_THREADS, WG_SMEM, s>>>(x, grad_out, partial, m, n, k, nsteps, groups, status, current_knobs());
   k_wgrad_reduce<<<(n * k + 255) / 256, 256, 0, s>>>(partial, (int)per_group, groups, n, k, w_kn, grad_w);
   e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
@@ -644,6 +691,31 @@ int dgnn_project_status(const void* workspace, void* stream, int* status_out) {
   if (e != cudaSuccess) return (int)e;
   e = cudaStreamSynchronize(s);
   return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+/* The second word of the workspace is never cleared by the calls: a caller that keeps one workspace for many
+ * calls (and zeroed its first 8 bytes once) reads here whether ANY call since then gave up.  clear != 0 zeroes
+ * it after reading.  Synchronises the stream. */
+int dgnn_project_sticky_status(void* workspace, void* stream, int* status_out, int clear) {
+  if (!workspace || !status_out) return DGNN_ERR_NULL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* word = static_cast<int*>(workspace) + 1;
+  cudaError_t e = cudaMemcpyAsync(status_out, word, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess && clear) e = cudaMemsetAsync(word, 0, sizeof(int), s);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaStreamSynchronize(s);
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+/* Test knobs of the projection kernels (process-wide): wait_limit_cycles > 0 replaces the ~2 s limit of every
+ * bounded wait, 0 restores it; skip_first_arrive != 0 makes the converter warps withhold the announcement of
+ * their first stage, so that the MMA thread's wait runs out -- the way a test exercises the give-up path (all
+ * roles leave, tensor memory is freed, the status words are set, the call returns) without hanging anything. */
+int dgnn_project_set_test_knobs(int64_t wait_limit_cycles, int skip_first_arrive) {
+  if (wait_limit_cycles < 0) return DGNN_ERR_VALUE;
+  g_wait_limit.store(wait_limit_cycles > 0 ? wait_limit_cycles : PJ_TIMEOUT);
+  g_skip_first_arrive.store(skip_first_arrive ? 1 : 0);
+  return DGNN_OK;
 }
 
 

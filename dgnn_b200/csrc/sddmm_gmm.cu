@@ -56,7 +56,8 @@ struct SddmmOp {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) st.a[v] = st.lm.act[v] ? ld4(a + r * hf4 + st.lm.q[v]) : zero4();
   }
-  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+  __host__ __device__ __forceinline__ int ring_bytes() const { return 0; }   // gathers go straight into registers
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     constexpr int U = VPL <= 2 ? 4 : 2;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
@@ -188,7 +189,8 @@ struct GmmOp {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) st.acc[v] = zero4();
   }
-  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane) const {
+  __host__ __device__ __forceinline__ int ring_bytes() const { return 0; }   // gathers go straight into registers
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     constexpr int U = VPL <= 2 ? 4 : 2;
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);

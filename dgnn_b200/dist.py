@@ -191,6 +191,50 @@ def _decode(codes):
     return c >> HALO_SHIFT, c & ((1 << HALO_SHIFT) - 1)
 
 
+@dataclass
+class SendPlan:
+    """Who sends what to whom for one direction, derived from every rank's halo row list.
+
+    The owner of a row packs it into its send buffer; the buffer is laid out chunk-major, then by
+    requester, then in the requester's halo order, so that what rank g needs from owner s for chunk c is
+    ONE contiguous range on both sides: send_off[s][c][g] in s's send buffer, recv rows in g's halo."""
+    pack_idx: torch.Tensor      # [total_send] int32: rows of this rank's block in send-buffer order
+    cap_send: int               # rows of the largest send buffer over all ranks
+    recv: list                  # per chunk: [(owner, first halo row, rows, offset in the owner's send buffer)]
+
+
+def build_send_plan(me, world, chunks, codes_all, chunk_off_all) -> SendPlan:
+    """codes_all[g] / chunk_off_all[g]: HaloSide.codes and .chunk_off of every rank g (what g fetches)."""
+    dev = codes_all[me].device
+    cnt = torch.zeros(world, chunks, world, dtype=torch.long)          # cnt[g][c][s]: rows g needs from s in chunk c
+    mine = []                                                          # rows of my block, per (c, g)
+    for g in range(world):
+        owner, loc = _decode(codes_all[g])
+        for c in range(chunks):
+            lo, hi = int(chunk_off_all[g][c]), int(chunk_off_all[g][c + 1])
+            o = owner[lo:hi]
+            if hi > lo:
+                cnt[g, c] = torch.bincount(o, minlength=world).cpu()
+            mine.append((c, g, loc[lo:hi][o == me]))
+    # send_off[s][c][g]: chunk-major, then requester
+    per_sc = cnt.permute(2, 1, 0).contiguous()                         # [s][c][g]
+    flat = per_sc.reshape(world, -1)
+    send_off = (torch.cumsum(flat, 1) - flat).reshape(world, chunks, world)
+    mine.sort(key=lambda t: (t[0], t[1]))
+    pack_idx = torch.cat([t[2] for t in mine]).to(torch.int32).contiguous() if mine else torch.zeros(0, dtype=torch.int32, device=dev)
+    recv = []
+    for c in range(chunks):
+        row = int(chunk_off_all[me][c])
+        lst = []
+        for s_ in range(world):                                        # halo rows of a chunk are sorted by owner
+            k = int(cnt[me, c, s_])
+            if k and s_ != me:
+                lst.append((s_, row, k, int(send_off[s_, c, me])))
+            row += k
+        recv.append(lst)
+    return SendPlan(pack_idx, int(flat.sum(1).max()), recv)
+
+
 class GatherTransport:
     """Fallback that needs nothing but torch.distributed collectives (gloo on CPU, NCCL without symmetric
     memory): the own blocks are all-gathered and the halo rows picked out of the result."""
@@ -202,7 +246,7 @@ class GatherTransport:
     def empty(self, tag, rows, tail, device):
         return torch.empty((rows,) + tuple(tail), dtype=torch.float32, device=device)
 
-    def barrier(self):
+    def publish(self, side, bufs, tags):
         pass
 
     def start_pulls(self, side, bufs, tags):
@@ -216,58 +260,125 @@ class GatherTransport:
         return [_Done() for _ in range(sh.chunks)]
 
 
-class PullTransport:
-    """Halo rows fetched out of the owners' buffers by kernels.halo_pull on a side stream (CUDA), chunk by
-    chunk.  Sub-classes say where the owners' buffers are: `SymmetricTransport` (one process per GPU,
-    torch.distributed symmetric memory: every rank maps every other rank's buffer over NVLink) and
-    `LocalTransport` (all ranks emulated in one process on one device, for tests)."""
+class PeerTransport:
+    """Halo rows taken out of the owners' memory, chunk by chunk, on a side stream.  Two modes:
 
-    def __init__(self, shard, pull_ctas=0):
-        self.shard = shard
+    "dma"   the owner packs the rows each peer needs into a send buffer (kernels.halo_pull with itself as
+            the only owner), a barrier follows, and every rank copies its contiguous ranges out of the
+            peers' send buffers with plain device-to-device copies -- copy engines, no SM taken from the
+            sweeps they run beside;
+    "pull"  no packing: kernels.halo_pull reads the rows straight out of the owners' [own | halo] buffers
+            with plain loads (over NVLink when the owner is another GPU).
+
+    Sub-classes say where the peers' buffers are: `SymmetricTransport` (one process per GPU, torch.distributed
+    symmetric memory) and `LocalTransport` (all ranks emulated in one process on one device, for tests)."""
+
+    def __init__(self, shard, mode="dma", pull_ctas=0):
+        if mode not in ("dma", "pull"):
+            raise ValueError("mode must be 'dma' or 'pull'")
+        self.shard, self.mode = shard, mode
         self.pull_ctas = int(pull_ctas)
         self.stream = None
         self.status = None
+        self.plans = None           # (forward SendPlan, backward SendPlan) in dma mode
+        self.send = {}              # tag -> this rank's send buffer
 
-    # -- to be provided --
-    def owners(self, tag):
+    # -- provided by the sub-class --
+    def peer_buffers(self, tag):
+        """The buffer registered under `tag` on every rank (own tensor or peer mapping)."""
+        raise NotImplementedError
+
+    def shared_empty(self, tag, rows, tail, device):
+        """A buffer that the other ranks can read; collective (same order on every rank)."""
         raise NotImplementedError
 
     def barrier(self):
         raise NotImplementedError
 
     # -- shared --
+    def empty(self, tag, rows, tail, device):
+        if self.mode == "pull":                                   # peers read the [own | halo] buffers themselves
+            return self.shared_empty(tag, rows, tail, device)
+        return torch.empty((rows,) + tuple(tail), dtype=torch.float32, device=device)
+
+    def _plan(self, side):
+        return self.plans[0] if side is self.shard.fwd else self.plans[1]
+
+    def publish(self, side, bufs, tags):
+        """Own rows are written: make them available to the peers (pack in dma mode), then the barrier."""
+        sh = self.shard
+        if self.mode == "dma" and sh.world > 1:
+            plan = self._plan(side)
+            sends = []
+            for buf, tag in zip(bufs, tags):
+                if tag not in self.send:
+                    self.send[tag] = self.shared_empty(tag + ".send", max(plan.cap_send, 1), buf.shape[1:], buf.device)
+                sends.append(self.send[tag])
+            k = plan.pack_idx.numel()
+            if k:
+                if bufs[0].is_cuda:
+                    own = [[b[:sh.blk]] for b in bufs]
+                    kernels.halo_pull(plan.pack_idx, own[0], sends[0][:k], own[1] if len(bufs) > 1 else None,
+                                      sends[1][:k] if len(bufs) > 1 else None, status=self._status(bufs[0].device))
+                else:
+                    for b, sbuf in zip(bufs, sends):
+                        sbuf[:k] = b[:sh.blk][plan.pack_idx.long()]
+        self.barrier()
+
+    def _status(self, dev):
+        if self.status is None:
+            self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        return self.status
+
     def start_pulls(self, side, bufs, tags):
         sh = self.shard
-        if side.n_halo == 0:
+        if side.n_halo == 0 or sh.world == 1:
             return [_Done() for _ in range(sh.chunks)]
-        srcs = [self.owners(t) for t in tags]
-        if not bufs[0].is_cuda:                                   # emulation on the CPU: plain indexing
-            owner, loc = _decode(side.codes)
-            for buf, src in zip(bufs, srcs):
-                stacked = torch.stack([s[:sh.blk] for s in src], 0)
-                buf[sh.blk: sh.blk + side.n_halo] = stacked[owner, loc]
+        cuda = bufs[0].is_cuda
+        if self.mode == "dma":
+            srcs = [self.peer_buffers(t + ".send") for t in tags]
+        else:
+            srcs = [[s_[:sh.blk] for s_ in self.peer_buffers(t)] for t in tags]
+        if not cuda:                                              # emulation on the CPU
+            self._fetch_chunks(side, bufs, srcs, range(sh.chunks))
             return [_Done() for _ in range(sh.chunks)]
         dev = bufs[0].device
         if self.stream is None:
             self.stream = torch.cuda.Stream(device=dev, priority=-1)
-            self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._status(dev)
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(dev))
         works = []
-        own_views = [[s[:sh.blk] for s in src] for src in srcs]
         with torch.cuda.stream(self.stream):
             self.stream.wait_event(ready)
             for c in range(sh.chunks):
-                lo, hi = side.chunk_off[c], side.chunk_off[c + 1]
-                if hi > lo:
-                    dsts = [b[sh.blk + lo: sh.blk + hi] for b in bufs]
-                    kernels.halo_pull(side.codes[lo:hi], own_views[0], dsts[0],
-                                      own_views[1] if len(bufs) > 1 else None, dsts[1] if len(bufs) > 1 else None,
-                                      max_ctas=self.pull_ctas, status=self.status)
+                self._fetch_chunks(side, bufs, srcs, [c])
                 ev = torch.cuda.Event()
                 ev.record(self.stream)
                 works.append(_StreamEvent(ev))
         return works
+
+    def _fetch_chunks(self, side, bufs, srcs, chunks):
+        sh = self.shard
+        for c in chunks:
+            if self.mode == "dma":
+                lst = self._plan(side).recv[c]
+                lst = lst[sh.rank % max(len(lst), 1):] + lst[:sh.rank % max(len(lst), 1)]   # ranks start at different owners
+                for owner, row, k, off in lst:
+                    for buf, src in zip(bufs, srcs):
+                        buf[sh.blk + row: sh.blk + row + k].copy_(src[owner][off: off + k], non_blocking=True)
+                continue
+            lo, hi = side.chunk_off[c], side.chunk_off[c + 1]
+            if hi <= lo:
+                continue
+            if bufs[0].is_cuda:
+                dsts = [b[sh.blk + lo: sh.blk + hi] for b in bufs]
+                kernels.halo_pull(side.codes[lo:hi], srcs[0], dsts[0], srcs[1] if len(bufs) > 1 else None,
+                                  dsts[1] if len(bufs) > 1 else None, max_ctas=self.pull_ctas, status=self.status)
+            else:
+                owner, loc = _decode(side.codes[lo:hi])
+                for buf, src in zip(bufs, srcs):
+                    buf[sh.blk + lo: sh.blk + hi] = torch.stack(list(src), 0)[owner, loc]
 
     def check(self):
         """Raise if a fetch met a row code outside its owner's block (synchronises)."""
@@ -275,48 +386,77 @@ class PullTransport:
             raise RuntimeError("dgnn_b200: a halo fetch skipped rows whose code lies outside the owner's block")
 
 
-class LocalTransport(PullTransport):
-    """All ranks in one process on one device: `registry[rank][tag]` holds every emulated rank's buffer.  The
-    caller runs the phases of all ranks in lockstep (prepare on every rank, then sweep on every rank), which is
-    what the barrier stands for."""
+class LocalTransport(PeerTransport):
+    """All ranks in one process on one device: `registry[rank][tag]` holds every emulated rank's buffers.  The
+    caller runs the phases of all ranks in lockstep (prepare + publish on every rank, then sweep on every
+    rank), which is what the barrier stands for.  Create one per rank with LocalTransport.for_all(shards)."""
 
-    def __init__(self, shard, registry, pull_ctas=0):
-        super().__init__(shard, pull_ctas)
+    def __init__(self, shard, registry, mode="dma", pull_ctas=0):
+        super().__init__(shard, mode, pull_ctas)
         self.registry = registry
-        self.caps = None            # set by the caller: (max forward halo, max backward halo) over all ranks
+        self.caps = None
 
-    def empty(self, tag, rows, tail, device):
+    @classmethod
+    def for_all(cls, shards, mode="dma", pull_ctas=0):
+        registry = {}
+        caps = (max(s.fwd.n_halo for s in shards), max(s.bwd.n_halo for s in shards))
+        world, chunks = shards[0].world, shards[0].chunks
+        out = []
+        for s in shards:
+            t = cls(s, registry, mode, pull_ctas)
+            t.caps = caps
+            if mode == "dma":
+                t.plans = tuple(build_send_plan(s.rank, world, chunks, [getattr(x, d).codes for x in shards],
+                                                [getattr(x, d).chunk_off for x in shards]) for d in ("fwd", "bwd"))
+            out.append(t)
+        return out
+
+    def shared_empty(self, tag, rows, tail, device):
         buf = torch.empty((rows,) + tuple(tail), dtype=torch.float32, device=device)
         self.registry.setdefault(self.shard.rank, {})[tag] = buf
         return buf
 
-    def owners(self, tag):
+    def peer_buffers(self, tag):
         return [self.registry[r][tag] for r in range(self.shard.world)]
 
     def barrier(self):
         pass
 
 
-class SymmetricTransport(PullTransport):
-    """One process per GPU.  The buffers live in torch.distributed's symmetric memory, so the producing kernels
-    write where the peers read; the barrier is a one-element NCCL all-reduce on the compute stream.  Two barriers
-    per training step (one per pass) also keep a rank from overwriting rows that a peer is still fetching: a
-    rank's writes of pass k+1 come after its barrier of pass k, which every peer enters only after its own sweeps
-    -- and therefore its fetches -- of the pass before.  No multicast object is created."""
+class SymmetricTransport(PeerTransport):
+    """One process per GPU.  The buffers that peers read live in torch.distributed's symmetric memory (every
+    rank maps every other rank's buffer over NVLink); the barrier is a one-element NCCL all-reduce on the compute
+    stream.  Two barriers per training step (one per pass) also keep a rank from overwriting rows that a peer is
+    still fetching: a rank's writes of pass k+1 come after its barrier of pass k, which every peer enters only
+    after its own sweeps -- and therefore its fetches -- of the pass before.  No multicast object is created."""
 
-    def __init__(self, shard, group=None, pull_ctas=0):
+    def __init__(self, shard, group=None, mode="dma", pull_ctas=0):
         import os
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads only
-        super().__init__(shard, pull_ctas)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer reads only
+        super().__init__(shard, mode, pull_ctas)
         self.group = group if group is not None else dist.group.WORLD
         dev = shard.local_ids.device
+        world, chunks = shard.world, shard.chunks
         caps = torch.tensor([shard.fwd.n_halo, shard.bwd.n_halo], dtype=torch.int64, device=dev)
         dist.all_reduce(caps, op=dist.ReduceOp.MAX, group=self.group)     # symmetric buffers have one size on all ranks
         self.caps = (int(caps[0]), int(caps[1]))
         self.flag = torch.zeros(1, dtype=torch.float32, device=dev)
         self.peers = {}
+        if mode == "dma":
+            plans = []
+            for side, cap in ((shard.fwd, self.caps[0]), (shard.bwd, self.caps[1])):
+                # every rank learns every rank's halo row list (what it fetches, in which order)
+                mine = torch.full((max(cap, 1),), -1, dtype=torch.int32, device=dev)
+                mine[:side.n_halo] = side.codes
+                codes = torch.empty((world, max(cap, 1)), dtype=torch.int32, device=dev)
+                dist.all_gather_into_tensor(codes, mine, group=self.group)
+                offs = torch.empty((world, chunks + 1), dtype=torch.int64, device=dev)
+                dist.all_gather_into_tensor(offs, torch.tensor(side.chunk_off, dtype=torch.int64, device=dev), group=self.group)
+                offs = offs.tolist()
+                plans.append(build_send_plan(shard.rank, world, chunks, [codes[g, :offs[g][-1]] for g in range(world)], offs))
+            self.plans = tuple(plans)
 
-    def empty(self, tag, rows, tail, device):
+    def shared_empty(self, tag, rows, tail, device):
         import torch.distributed._symmetric_memory as symm
         shape = (rows,) + tuple(tail)
         buf = symm.empty(shape, dtype=torch.float32, device=device)
@@ -325,19 +465,19 @@ class SymmetricTransport(PullTransport):
                            for q in range(self.shard.world)]
         return buf
 
-    def owners(self, tag):
+    def peer_buffers(self, tag):
         return self.peers[tag]
 
     def barrier(self):
         dist.all_reduce(self.flag, group=self.group)
 
 
-def make_transport(shard, group=None, pull_ctas=0):
+def make_transport(shard, group=None, mode="dma", pull_ctas=0):
     """SymmetricTransport on CUDA ranks when symmetric memory works on this platform, else GatherTransport."""
     if shard.world > 1 and shard.local_ids.is_cuda and dist.is_initialized() and dist.get_backend(group) == "nccl":
         try:
-            t = SymmetricTransport(shard, group, pull_ctas)
-            t.empty("probe", 16, (4,), shard.local_ids.device)             # collective probe: all ranks fail together
+            t = SymmetricTransport(shard, group, mode, pull_ctas)
+            t.shared_empty("probe", 16, (4,), shard.local_ids.device)      # collective probe: all ranks fail together
             return t
         except Exception as exc:
             import warnings
@@ -467,7 +607,7 @@ class HaloGATFunction(torch.autograd.Function):
             attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_l=b, attn_r=c)
         else:
             attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_row=b.contiguous(), attn_col=c.contiguous())
-        hc.transport.barrier()
+        hc.transport.publish(hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2])
         out, edge_max, edge_sum, out_neg, a_neg = halo_forward_sweep(hc, attn_row, bias, attn_drop, seed, train=True)
         ctx.save_for_backward(attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c,
                               bias if bias is not None else out.new_empty(0))
@@ -483,7 +623,7 @@ class HaloGATFunction(torch.autograd.Function):
         attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c, bias = ctx.saved_tensors
         grad_row, grad_bias = halo_backward_prepare(hc, attn_row, edge_max, edge_sum, out, out_neg, a_neg,
                                                     grad_out.contiguous(), bias if ctx.has_bias else None)
-        hc.transport.barrier()
+        hc.transport.publish(hc.shard.bwd, [hc.G, hc.PK], hc.tags[2:4])
         grad_feat, grad_col = halo_backward_sweep(hc, ctx.attn_drop, ctx.seed)
         if grad_bias is not None:
             grad_bias = grad_bias.view_as(bias)
@@ -518,7 +658,7 @@ class ShardedGATConv(torch.nn.Module):
     sees the same mask for an edge; it needs build_halo_shard(edge_ids=True)."""
 
     def __init__(self, in_feats, out_feats, num_heads, shard, feat_drop=0., attn_drop=0., negative_slope=0.2,
-                 residual=False, activation=None, bias=True, group=None, transport=None, seed=0, pull_ctas=0):
+                 residual=False, activation=None, bias=True, group=None, transport=None, seed=0):
         super().__init__()
         from .layers.gatconv_layer import GATConv
         proto = GATConv(in_feats, out_feats, num_heads, feat_drop, attn_drop, negative_slope, residual, activation, bias)
@@ -535,7 +675,7 @@ class ShardedGATConv(torch.nn.Module):
         else:
             self.register_buffer("res_fc", None)
         self.shard, self.group = shard, group
-        self.transport = transport if transport is not None else make_transport(shard, group, pull_ctas)
+        self.transport = transport if transport is not None else make_transport(shard, group)
         self.hc = None
         self.seed, self.step = int(seed), 0
 
@@ -559,7 +699,7 @@ class ShardedGATConv(torch.nn.Module):
         else:
             with torch.no_grad():
                 attn_row = halo_forward_prepare(hc, h=h.contiguous(), attn_l=self.attn_l, attn_r=self.attn_r)
-                hc.transport.barrier()
+                hc.transport.publish(hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2])
                 rst = halo_forward_sweep(hc, attn_row, self.bias if fuse_bias else None, train=False)[0]
         if self.res_fc is not None:
             rst = rst + self.res_fc(h).view(-1, heads, width)       # as in the reference: applied to the projected features

@@ -21,33 +21,28 @@ class Graph(NamedTuple):
 
 
 def build_graph(src, dst, num_nodes, ptr_dtype=torch.int32, add_self_loops=False) -> Graph:
-    """Edge list (src[e] -> dst[e], any order, duplicates kept) -> CSR + CSC + permute.
-    The sort by (dst, src) is a torch sort of one 64-bit key per edge; the row pointer
-    comes from dgnn_coo2csr and the CSC form from dgnn_csr2csc."""
+    """Edge list (src[e] -> dst[e], any order, duplicates kept) -> CSR + CSC + permute, all by this library's
+    kernels: dgnn_coo_sort orders the edges by (dst, src), dgnn_coo2csr gives the row pointer and dgnn_csr2csc the
+    CSC form."""
     if not (src.is_cuda and dst.is_cuda):
         raise RuntimeError("dgnn_b200: build_graph works on CUDA tensors (there is no CPU path)")
-    src, dst = src.long(), dst.long()
+    if num_nodes >= 2**31:
+        raise RuntimeError("dgnn_b200: node ids are int32")
+    src, dst = src.to(torch.int32), dst.to(torch.int32)
     if add_self_loops:
         keep = src != dst
-        loops = torch.arange(num_nodes, device=src.device)
+        loops = torch.arange(num_nodes, device=src.device, dtype=torch.int32)
         src, dst = torch.cat([src[keep], loops]), torch.cat([dst[keep], loops])
-    key, _ = torch.sort(dst * num_nodes + src)
-    rows = torch.div(key, num_nodes, rounding_mode="floor")
-    col_ind = (key - rows * num_nodes).to(torch.int32)
-    row_ptr = kernels.coo2csr(rows.to(torch.int32), num_nodes, ptr_dtype)
+    rows, col_ind = kernels.coo_sort(dst, src, num_nodes)
+    row_ptr = kernels.coo2csr(rows, num_nodes, ptr_dtype)
     col_ptr, row_ind, permute = kernels.csr2csc(row_ptr, col_ind)
     return Graph(row_ptr, col_ind, col_ptr, row_ind, permute)
 
 
-def knn_graph(points, k, chunk=8):
+def knn_graph(points, k):
     """points [B,P,D] (one cloud per batch entry) -> src_ind [B*P*k] int32 with global ids;
-    neighbours of point i are src_ind[i*k:(i+1)*k], the point itself included (distance 0).
-    Brute force per cloud (cdist + topk), `chunk` clouds at a time."""
-    b, p, _ = points.shape
-    out = []
-    for s in range(0, b, chunk):
-        x = points[s: s + chunk]
-        idx = torch.cdist(x, x).topk(k, dim=2, largest=False).indices
-        idx = idx + (torch.arange(s, s + x.shape[0], device=points.device) * p)[:, None, None]
-        out.append(idx.reshape(-1))
-    return torch.cat(out).to(torch.int32)
+    neighbours of point i are src_ind[i*k:(i+1)*k] in ascending distance, the point itself first (distance 0),
+    ties to the smaller index (dgnn_knn_graph)."""
+    if not points.is_cuda:
+        raise RuntimeError("dgnn_b200: knn_graph works on CUDA tensors (there is no CPU path)")
+    return kernels.knn_graph(points.float().contiguous(), k)

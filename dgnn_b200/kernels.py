@@ -343,6 +343,43 @@ def halo_pull(codes, src_a, dst_a, src_b=None, dst_b=None, max_ctas=0, status=No
 
 
 # ------------------------------------------------------- dense projection
+# One workspace per (device, stream), kept for the life of the process: calls on a stream are ordered, so they can
+# share it, and its second word collects the status of every call (dgnn_project_sticky_status), which
+# project_check() reads at a point where the caller synchronises anyway.
+_PROJECT_WS = {}
+_PROJECT_RETIRED = []
+
+
+def _project_ws(nbytes, dev):
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)
+    ws = _PROJECT_WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _PROJECT_RETIRED.append((key, ws))          # its status word stays readable
+        ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
+        ws[:8].zero_()
+        _PROJECT_WS[key] = ws
+    return ws
+
+
+def project_check(device=None):
+    """Raise if any tensor-core projection call on `device` (default: every device) gave up in one of its bounded
+    waits since the last check; its result was then invalid.  Synchronises the streams that ran projections."""
+    import ctypes
+    bad = []
+    for key, ws in list(_PROJECT_WS.items()) + list(_PROJECT_RETIRED):
+        if device is not None and torch.device(device).index not in (None, key[0]):
+            continue
+        st = ctypes.c_int(0)
+        with torch.cuda.device(key[0]):
+            check(lib().dgnn_project_sticky_status(_p(ws), ctypes.c_void_p(key[1]), ctypes.byref(st), 1), "project_sticky_status")
+        if st.value != 0:
+            bad.append((key[0], st.value))
+    if bad:
+        raise RuntimeError("dgnn_b200: a projection kernel gave up in a bounded wait (device, wait id): "
+                           f"{bad}; results of the projections since the last check are invalid")
+
+
 def project_supported(m, n, k) -> bool:
     """Shapes the tensor-core projection handles (n % 128 == 0, k % 4 == 0, k <= 128)."""
     return bool(lib().dgnn_project_supported(int(m), int(n), int(k)))
@@ -366,7 +403,7 @@ def project_forward(x, w, w_kn=False, check_status=False, out=None):
         if out is None:
             out = torch.empty((m, n), dtype=torch.float32, device=dev)
         nbytes = lib().dgnn_project_workspace_bytes(n)
-        ws = _workspace(nbytes, dev)
+        ws = _project_ws(nbytes, dev)
         check(lib().dgnn_project_forward(m, n, k, _p(x), _p(w), int(bool(w_kn)), _p(out), _p(ws), nbytes, _stream(dev)),
               "project_forward")
         if check_status:
@@ -391,7 +428,7 @@ def project_wgrad(x, grad_out, w_kn=False, check_status=False):
     with device_guard(dev):
         grad_w = torch.empty((k, n) if w_kn else (n, k), dtype=torch.float32, device=dev)
         nbytes = lib().dgnn_project_wgrad_workspace_bytes(n)
-        ws = _workspace(nbytes, dev)
+        ws = _project_ws(nbytes, dev)
         check(lib().dgnn_project_wgrad(m, n, k, _p(x), _p(grad_out), _p(grad_w), int(bool(w_kn)), _p(ws), nbytes,
                                        _stream(dev)), "project_wgrad")
         if check_status:
@@ -566,6 +603,36 @@ def coo2csr(row_ind, m, dtype=torch.int32):
         row_ptr = torch.empty(int(m) + 1, dtype=dtype, device=dev)
         check(lib().dgnn_coo2csr(row_ind.numel(), int(m), _p(row_ind), _p(row_ptr), bits, _stream(dev)), "coo2csr")
     return row_ptr
+
+
+def coo_sort(dst, src, n_nodes):
+    """Edge list (int32 ids, any order, duplicates kept) sorted by (dst, src): returns (dst_sorted, src_sorted)."""
+    dst = _cuda_i32(dst, "dst")
+    src = _cuda_i32(src, "src")
+    if dst.numel() != src.numel():
+        raise RuntimeError("dgnn_b200: coo_sort needs one source per destination")
+    nnz = dst.numel()
+    dev = dst.device
+    with device_guard(dev):
+        d_out = torch.empty(nnz, dtype=torch.int32, device=dev)
+        s_out = torch.empty(nnz, dtype=torch.int32, device=dev)
+        ws = _workspace(lib().dgnn_coo_sort_workspace_bytes(nnz, int(n_nodes)), dev)
+        check(lib().dgnn_coo_sort(nnz, int(n_nodes), _p(dst), _p(src), _p(d_out), _p(s_out), _p(ws), ws.numel(),
+                                  _stream(dev)), "coo_sort")
+    return d_out, s_out
+
+
+def knn_graph(points, k):
+    """points [B,P,D] -> src_ind [B*P*k] int32 with global ids (cloud*P + neighbour), the point itself first."""
+    points = _cuda_f32(points, "points")
+    if points.dim() != 3:
+        raise RuntimeError("dgnn_b200: knn_graph needs points [B,P,D]")
+    b, p, d = points.shape
+    dev = points.device
+    with device_guard(dev):
+        out = torch.empty(b * p * int(k), dtype=torch.int32, device=dev)
+        check(lib().dgnn_knn_graph(b, p, d, int(k), _p(points), _p(out), _stream(dev)), "knn_graph")
+    return out
 
 
 # ------------------------------------------------ staged (block-by-block) GAT

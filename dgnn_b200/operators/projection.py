@@ -12,8 +12,12 @@ from .. import kernels
 
 
 class ProjectFunction(torch.autograd.Function):
+    """`out` comes first: when it is a view, autograd treats the first input of a function that marks an
+    input dirty as the tensor written in place (the convention of the built-in in-place operators) and routes
+    the other inputs' gradients by position."""
+
     @staticmethod
-    def forward(ctx, feat, weight, out=None):
+    def forward(ctx, out, feat, weight):
         ctx.save_for_backward(feat, weight)
         res = kernels.project_forward(feat, weight, w_kn=True, out=out)
         if out is not None:
@@ -23,11 +27,11 @@ class ProjectFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         feat, weight = ctx.saved_tensors
-        grad_feat = grad_out @ weight.t() if ctx.needs_input_grad[0] else None
+        grad_feat = grad_out @ weight.t() if ctx.needs_input_grad[1] else None
         grad_weight = None
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[2]:
             grad_weight = kernels.project_wgrad(feat, grad_out.contiguous(), w_kn=True)
-        return grad_feat, grad_weight, None
+        return None, grad_feat, grad_weight
 
 
 def project(feat, weight, out=None):
@@ -36,22 +40,22 @@ def project(feat, weight, out=None):
     if (feat.is_cuda and feat.dtype == torch.float32 and weight.dtype == torch.float32 and feat.dim() == 2
             and feat.is_contiguous() and weight.is_contiguous()
             and kernels.project_supported(feat.shape[0], weight.shape[1], feat.shape[1])):
-        return ProjectFunction.apply(feat, weight, out)
+        return ProjectFunction.apply(out, feat, weight)
     res = torch.matmul(feat, weight)
     if out is None:
         return res
-    return _CopyInto.apply(res, out)
+    return _CopyInto.apply(out, res)
 
 
 class _CopyInto(torch.autograd.Function):
     """out <- src with the gradient passed through (library-GEMM path of project(out=...))."""
 
     @staticmethod
-    def forward(ctx, src, out):
+    def forward(ctx, out, src):
         out.copy_(src)
         ctx.mark_dirty(out)
         return out
 
     @staticmethod
     def backward(ctx, grad):
-        return grad, None
+        return None, grad

@@ -218,6 +218,15 @@ size_t dgnn_project_wgrad_workspace_bytes(int n);
 int dgnn_project_wgrad(int64_t m, int n, int k, const float* x, const float* grad_out, float* grad_w, int w_kn,
                        void* workspace, size_t workspace_bytes, void* stream);
 int dgnn_project_status(const void* workspace, void* stream, int* status_out);
+/* The second word of a projection workspace is set like the first but never cleared by the calls: a caller
+ * that keeps one workspace for many calls (and zeroed its first 8 bytes once) learns here whether any call
+ * since then gave up in a wait; clear != 0 zeroes the word after reading.  Synchronises the stream. */
+int dgnn_project_sticky_status(void* workspace, void* stream, int* status_out, int clear);
+/* Test knobs of the projection kernels (process-wide): wait_limit_cycles > 0 replaces the ~2 s limit of every
+ * bounded wait (0 restores it); skip_first_arrive != 0 makes the producer warps withhold the announcement of
+ * their first stage, so that the consumer's wait runs out.  A test uses both to run the give-up path (all
+ * roles leave, tensor memory is freed, the status words are set, the call returns) without hanging the GPU. */
+int dgnn_project_set_test_knobs(int64_t wait_limit_cycles, int skip_first_arrive);
 
 /* Uniform floats in (0,1] from a counter-based Philox4x32-10 stream; stands in
  * for the cuRAND fill of edge_mask (fused_gatconv_kernel.cu:333-341). */
@@ -327,6 +336,12 @@ int dgnn_csr2csc(int64_t n_rows, int64_t n_cols, int64_t nnz,
  * DGNN_ERR_STATIC_LIMIT.  The call neither allocates nor frees.  The first call
  * on each device looks up the array's device address (cudaGetSymbolAddress) with
  * that device current; make that first call before any stream capture begins.
+ * With CUDA's default lazy module loading the array itself is only set up on a
+ * device when this library's code is first used there, so that first call can
+ * still take the 32 MiB from the device: make one warm-up call per device at
+ * start-up, before the host application claims the memory (or run with
+ * CUDA_MODULE_LOADING=EAGER).  The address is remembered per device ordinal for
+ * the life of the process: do not call cudaDeviceReset between calls.
  * All calls on a device share the one array: calls that may overlap on the GPU
  * (different streams, different threads) race and must be serialised by the caller. */
 int64_t dgnn_csr2csc_static_max_nnz(void);
@@ -334,6 +349,25 @@ int64_t dgnn_csr2csc_static_max_cols(void);
 int dgnn_csr2csc_static(int64_t n_rows, int64_t n_cols, int64_t nnz,
                         const void* row_ptr, int idx_bits, const int32_t* col_ind,
                         void* col_ptr, int32_t* row_ind, int32_t* permute, void* stream);
+/* ---- graph preparation on the device (the step in front of the operators) ---------------------
+ * dgnn_coo_sort orders an edge list by (destination, source), duplicates kept: two stable radix sorts of
+ * (key, value) pairs with the passes of dgnn_csr2csc -- by source with the destination riding along, then by
+ * destination.  Followed by dgnn_coo2csr and dgnn_csr2csc it yields every array the operators take from an
+ * edge list in any order; it stands where the scipy recipe of the reference's training scripts stands
+ * (dgNN/script/train/train_gatconv.py:78-94: csr_matrix(...), tocsc()).  Node ids are int32 below n_nodes. */
+size_t dgnn_coo_sort_workspace_bytes(int64_t nnz, int64_t n_nodes);
+int dgnn_coo_sort(int64_t nnz, int64_t n_nodes, const int32_t* dst, const int32_t* src,
+                  int32_t* dst_sorted, int32_t* src_sorted,
+                  void* workspace, size_t workspace_bytes, void* stream);
+/* k nearest neighbours inside every cloud of points [n_clouds, n_points, dim] (squared Euclidean distance,
+ * the point itself included, ascending distance, ties to the smaller index): src_ind[(c*n_points + i)*k + j] =
+ * c*n_points + (j-th neighbour of point i of cloud c), the regular graph dgnn_edgeconv_forward takes.  Stands
+ * where DGL's KNNGraph stands in the reference's point-cloud script (dgNN/script/train/train_edgeconv.py:49).
+ * Distances are accumulated with separately rounded multiplies and adds, so the result is reproducible bit for
+ * bit.  k <= dgnn_knn_max_k() (32) and k <= n_points. */
+int dgnn_knn_max_k(void);
+int dgnn_knn_graph(int64_t n_clouds, int64_t n_points, int dim, int k, const float* points,
+                   int32_t* src_ind, void* stream);
 /* row_ptr[i] = number of entries with row id < i, for sorted COO row ids;
  * replaces format_conversion.coo2csr (convert.cpp:32-35, convert_kernel.cu:44-59) */
 int dgnn_coo2csr(int64_t nnz, int64_t m, const int32_t* row_ind,

@@ -260,6 +260,31 @@ def coo2csr(row_ind, m):
     return torch.from_numpy(np.searchsorted(ri, np.arange(m + 1), side="left").astype(np.int64))
 
 
+def coo_sort(dst, src):
+    """Edge list ordered by (dst, src), duplicates kept: what scipy's csr_matrix((data, (row, col))) followed by
+    sort_indices() gives the reference's scripts (script/train/train_gatconv.py:78-82)."""
+    d, s_ = dst.long().numpy(), src.long().numpy()
+    order = np.lexsort((s_, d))
+    return torch.from_numpy(d[order]), torch.from_numpy(s_[order])
+
+
+def knn_graph(points, k):
+    """k nearest neighbours inside every cloud of points [B,P,D] (the graph the reference builds with DGL's
+    KNNGraph, script/train/train_edgeconv.py:49): squared distances accumulated dimension by dimension in fp32
+    with separately rounded multiply and add, the point itself included, ascending distance, ties to the smaller
+    index.  Returns src_ind [B*P*k] int64 with global ids cloud*P + neighbour."""
+    x = points.detach().cpu().numpy().astype(np.float32)
+    b, p, dim = x.shape
+    out = np.empty((b, p, k), dtype=np.int64)
+    for c in range(b):
+        d2 = np.zeros((p, p), dtype=np.float32)
+        for dd in range(dim):
+            diff = (x[c, :, None, dd] - x[c, None, :, dd]).astype(np.float32)
+            d2 = (d2 + (diff * diff).astype(np.float32)).astype(np.float32)
+        out[c] = np.argsort(d2, axis=1, kind="stable")[:, :k] + c * p
+    return torch.from_numpy(out.reshape(-1))
+
+
 # ----------------------------------------------------------------------------
 # whole layers (dgNN/layers/*.py) -- used for the CPU baseline timing
 # ----------------------------------------------------------------------------

@@ -73,3 +73,16 @@ def test_cpu_tensors_are_rejected():
     from dgnn_b200 import kernels
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         kernels.mhtranspose(torch.zeros(3, dtype=torch.int32), torch.zeros(3, 2))
+
+
+def test_wgrad_workspace_covers_one_cta_per_column_group():
+    """dgnn_project_wgrad launches (CTAs per group) x groups CTAs, never fewer than one per 128-column group, and
+    every CTA writes a 128 x 128 fp32 partial: the workspace query must cover groups > SM count as well (the SM
+    count is read from the device, 148 when there is none)."""
+    from dgnn_b200 import _C
+    lib = _C.lib()
+    small = lib.dgnn_project_wgrad_workspace_bytes(256)
+    for groups in (1, 2, 148, 149, 400):
+        got = lib.dgnn_project_wgrad_workspace_bytes(128 * groups)
+        assert got >= 256 + groups * 128 * 128 * 4
+        assert got >= small

@@ -167,24 +167,25 @@ def test_sharded_gat_gloo_equals_single(world, stages, p):
     _check_ranks(results, ref, GRAPH["n"])
 
 
-@pytest.mark.parametrize("world,stages", [(1, 1), (2, 2), (4, 3)])
-def test_all_ranks_emulated_in_one_process(world, stages):
-    """LocalTransport: every rank's buffers in one registry, phases run in lockstep; the halo rows are picked out
-    of the owners' buffers by their codes (the path that the CUDA fetch kernel takes on a GPU)."""
+@pytest.mark.parametrize("mode", ["dma", "pull"])
+@pytest.mark.parametrize("world,stages", [(1, 1), (2, 2), (4, 3), (3, 1)])
+def test_all_ranks_emulated_in_one_process(world, stages, mode):
+    """LocalTransport: every rank's buffers in one registry, phases run in lockstep.  "dma": owners pack what each
+    peer needs into send buffers and the peers copy their contiguous ranges (the send plan); "pull": the halo rows
+    are picked out of the owners' buffers by their codes."""
     h, f = 2, 4
     rp, ci, (ar, ac, x, g), ref = _reference(h, f)
-    registry = {}
     shards = [gdist.build_halo_shard(rp, ci, r, world, stages=stages, seed=9, csr2csc=orc.csr2csc) for r in range(world)]
-    caps = (max(s.fwd.n_halo for s in shards), max(s.bwd.n_halo for s in shards))
-    ctxs = []
-    for s in shards:
-        t = gdist.LocalTransport(s, registry)
-        t.caps = caps
-        ctxs.append(gdist.HaloContext(s, t, h, f, 0.2, backend=OracleBackend))
+    ctxs = [gdist.HaloContext(s, t, h, f, 0.2, backend=OracleBackend)
+            for s, t in zip(shards, gdist.LocalTransport.for_all(shards, mode))]
     loc = [[s.scatter_rows(t) for t in (ar, ac, x, g)] for s in shards]
     rows = [gdist.halo_forward_prepare(c, h=l[2], attn_row=l[0], attn_col=l[1]) for c, l in zip(ctxs, loc)]
+    for c in ctxs:
+        c.transport.publish(c.shard.fwd, [c.X, c.AC], c.tags[0:2])
     fwd = [gdist.halo_forward_sweep(c, r) for c, r in zip(ctxs, rows)]
     grow = [gdist.halo_backward_prepare(c, r, o[1], o[2], o[0], o[3], o[4], l[3])[0] for c, r, o, l in zip(ctxs, rows, fwd, loc)]
+    for c in ctxs:
+        c.transport.publish(c.shard.bwd, [c.G, c.PK], c.tags[2:4])
     bwd = [gdist.halo_backward_sweep(c) for c in ctxs]
     results = [(s.local_ids, o[0], (gr, b[1], b[0])) for s, o, gr, b in zip(shards, fwd, grow, bwd)]
     _check_ranks(results, ref, GRAPH["n"])

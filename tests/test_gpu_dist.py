@@ -27,26 +27,25 @@ def _single_gpu(rp, ci, ar, ac, x, g, p=0.0, seed=0):
     return out, gf, gr, gc
 
 
-@pytest.mark.parametrize("world,stages,p", [(1, 1, 0.0), (2, 1, 0.0), (2, 2, 0.0), (4, 3, 0.0), (3, 4, 0.3), (8, 3, 0.0)])
-def test_emulated_ranks_equal_single_gpu(cuda, world, stages, p):
+@pytest.mark.parametrize("world,stages,p,mode", [(1, 1, 0.0, "dma"), (2, 1, 0.0, "dma"), (2, 2, 0.0, "pull"), (4, 3, 0.0, "dma"),
+                                                 (3, 4, 0.3, "dma"), (3, 4, 0.3, "pull"), (8, 3, 0.0, "dma"), (8, 3, 0.0, "pull")])
+def test_emulated_ranks_equal_single_gpu(cuda, world, stages, p, mode):
     from dgnn_b200 import dist as gdist
     from dgnn_b200 import kernels, synth
     n, e, h, f = 20_000, 600_000, 8, 32
     rp, ci = synth.rmat_graph(n, e, seed=9, device=cuda, ptr_dtype=torch.int64)
     ar, ac, x, g = [t.to(cuda) for t in gat_inputs(rp, n, h, f, 17)]
     out, gf, gr, gc = _single_gpu(rp, ci, ar, ac, x, g, p, seed=123)
-    registry = {}
     shards = [gdist.build_halo_shard(rp, ci, r, world, stages=stages, seed=5, edge_ids=p > 0) for r in range(world)]
-    caps = (max(s.fwd.n_halo for s in shards), max(s.bwd.n_halo for s in shards))
-    ctxs = []
-    for s in shards:
-        t = gdist.LocalTransport(s, registry, pull_ctas=8)
-        t.caps = caps
-        ctxs.append(gdist.HaloContext(s, t, h, f, 0.2))
+    ctxs = [gdist.HaloContext(s, t, h, f, 0.2) for s, t in zip(shards, gdist.LocalTransport.for_all(shards, mode, pull_ctas=8))]
     loc = [[s.scatter_rows(t) for t in (ar, ac, x, g)] for s in shards]
     rows = [gdist.halo_forward_prepare(c, h=l[2], attn_row=l[0], attn_col=l[1]) for c, l in zip(ctxs, loc)]
+    for c in ctxs:
+        c.transport.publish(c.shard.fwd, [c.X, c.AC], c.tags[0:2])
     fwd = [gdist.halo_forward_sweep(c, r, None, p, 123) for c, r in zip(ctxs, rows)]
     grow = [gdist.halo_backward_prepare(c, r, o[1], o[2], o[0], o[3], o[4], l[3])[0] for c, r, o, l in zip(ctxs, rows, fwd, loc)]
+    for c in ctxs:
+        c.transport.publish(c.shard.bwd, [c.G, c.PK], c.tags[2:4])
     bwd = [gdist.halo_backward_sweep(c, p, 123) for c in ctxs]
     torch.cuda.synchronize()
     seen = []
@@ -151,8 +150,11 @@ def _layer_worker(rank, world, port, n, e, in_feats, heads, width, stages):
                 layer.transport.check()
             err = lambda a, b: float(((a - b).abs() / (1e-5 + 1e-4 * b.abs())).max())
             rel = lambda a, b: float((a - b).abs().max() / (b.abs().max() + 1e-12))
+            ref_params = dict(ref.named_parameters())
             report[name] = dict(out=err(out.detach()[real], ref_out.detach()[ids]),
-                                grads={k: rel(p.grad, dict(ref.named_parameters())[k].grad) for k, p in layer.named_parameters()})
+                                missing=[k for k, p in layer.named_parameters() if (p.grad is None) != (ref_params[k].grad is None)],
+                                grads={k: rel(p.grad, ref_params[k].grad) for k, p in layer.named_parameters()
+                                       if ref_params[k].grad is not None and p.grad is not None})
             # evaluation path: no statistics, no autograd
             layer.eval(); ref.eval()
             with torch.no_grad():
@@ -174,5 +176,6 @@ def test_sharded_layer_equals_single_gpu_layer(cuda):
             assert rep[name + "_transport"] == "SymmetricTransport", (rank, rep[name + "_transport"])
             r = rep[name]
             # outputs to 1e-4 relative / 1e-5 absolute; parameter gradients (sums over 50 k rows) within 1e-4 of their largest entry
+            assert not r["missing"], (rank, name, r["missing"])
             assert r["out"] <= 1.0 and r["eval"] <= 1.0, (rank, name, r)
             assert all(v <= 1e-4 for v in r["grads"].values()), (rank, name, r)

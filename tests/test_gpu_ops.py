@@ -229,5 +229,37 @@ def test_build_graph_and_knn_on_device(cuda):
     gl = graph.build_graph(src.to(cuda), dst.to(cuda), n, add_self_loops=True)
     deg = (gl.row_ptr[1:] - gl.row_ptr[:-1])
     assert int(deg.min()) >= 1
-    x = synth.unit_sphere_clouds(5, 128, seed=1, device=cuda)
-    assert_equal(graph.knn_graph(x, 8, chunk=2), synth.knn_src_ind(x, 8), "kNN src_ind")
+
+
+@pytest.mark.parametrize("n,e", [(1, 5), (300, 1), (70_000, 400_000), (5_000_000, 3_000_000)])
+def test_coo_sort_bit_exact(cuda, n, e):
+    """1, 3 (17-bit ids) and 3 (23-bit ids) radix passes per key; duplicates and empty rows included."""
+    g = torch.Generator().manual_seed(n + e)
+    src = torch.randint(0, n, (e,), generator=g, dtype=torch.int32)
+    dst = torch.randint(0, n, (e,), generator=g, dtype=torch.int32)
+    d_ref, s_ref = orc.coo_sort(dst, src)
+    d_out, s_out = kernels.coo_sort(dst.to(cuda), src.to(cuda), n)
+    assert_equal(d_out, d_ref, "sorted destinations")
+    assert_equal(s_out, s_ref, "sorted sources")
+
+
+@pytest.mark.parametrize("b,p,dim,k", [(5, 128, 3, 8), (2, 300, 3, 20), (3, 77, 64, 20), (1, 40, 5, 32), (2, 2048, 3, 20)])
+def test_knn_graph_bit_exact(cuda, b, p, dim, k):
+    g = torch.Generator().manual_seed(b * p + k)
+    x = torch.randn(b, p, dim, generator=g)
+    x[0, 3] = x[0, 1]                                   # an exact duplicate: ties go to the smaller index
+    from dgnn_b200 import graph
+    got = graph.knn_graph(x.to(cuda), k)
+    assert_equal(got, orc.knn_graph(x, k), "kNN src_ind")
+    first = got.view(b, p, k)[:, :, 0].cpu()
+    self_ids = (torch.arange(b)[:, None] * p + torch.arange(p)[None, :])
+    assert bool((first == self_ids)[0, [0, 1, 2, 4]].all()) and int(first[0, 3]) == 1    # itself first, except the duplicate
+
+
+def test_knn_feeds_edgeconv_like_the_brute_force_graph(cuda):
+    """On clouds without near-ties the kernel's graph equals the cdist + topk graph of the test harness."""
+    x = synth.unit_sphere_clouds(4, 256, seed=1, device=cuda)
+    from dgnn_b200 import graph
+    a = graph.knn_graph(x, 8).view(4, 256, 8).sort(dim=2).values
+    b_ = synth.knn_src_ind(x, 8).view(4, 256, 8).sort(dim=2).values
+    assert float((a == b_).float().mean()) > 0.999

@@ -119,3 +119,58 @@ def test_projection_function_gradients():
     assert torch.allclose(out.double(), xd @ wd, rtol=1e-5, atol=1e-4)
     assert torch.allclose(w.grad.double(), wd.grad, rtol=1e-4, atol=1e-3)
     assert torch.allclose(x.grad.double(), xd.grad, rtol=1e-4, atol=1e-3)
+
+
+def test_wgrad_accuracy_does_not_degrade_with_rows():
+    """The weight gradient sums over all rows; the tensor core's accumulator truncates, so the kernel drains it
+    every 1024 rows.  At 1.2 M rows the result must stay at the level of the fp32 library GEMM (it was 40 x worse
+    with one accumulation chain per CTA)."""
+    from dgnn_b200 import kernels
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1)
+    m = 1_200_000
+    x = torch.randn(m, 100, device=dev, generator=g)
+    go = torch.randn(m, 256, device=dev, generator=g)
+    ref = x.double().t() @ go.double()
+    got = kernels.project_wgrad(x, go, w_kn=True, check_status=True)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        lib32 = x.t() @ go
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    e_mine = float((got.double() - ref).abs().max() / ref.abs().max())
+    e_lib = float((lib32.double() - ref).abs().max() / ref.abs().max())
+    assert e_mine <= max(4.0 * e_lib, 1e-5), (e_mine, e_lib)
+    kernels.project_check()
+
+
+@pytest.mark.parametrize("which", ["forward", "wgrad"])
+def test_a_wait_that_runs_out_sets_the_status_and_returns(which):
+    """The producer warps withhold their first announcement and the wait limit is a millisecond: the consumer's
+    wait runs out (and with it the waits of the roles behind it), every role leaves its loop, tensor memory is
+    freed, the call returns and the status names the highest-numbered wait that gave up.  Nothing hangs and the
+    next call works."""
+    from dgnn_b200 import _C, kernels
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(2)
+    x = torch.randn(4096, 100, device=dev, generator=g)
+    w = torch.randn(100, 256, device=dev, generator=g)
+    go = torch.randn(4096, 256, device=dev, generator=g)
+    kernels.project_check()                                   # clean slate
+    assert _C.lib().dgnn_project_set_test_knobs(2_000_000, 1) == 0
+    try:
+        with pytest.raises(RuntimeError, match="gave up in wait [1-9]"):
+            if which == "forward":
+                kernels.project_forward(x, w, w_kn=True, check_status=True)
+            else:
+                kernels.project_wgrad(x, go, w_kn=True, check_status=True)
+        torch.cuda.synchronize()
+    finally:
+        assert _C.lib().dgnn_project_set_test_knobs(0, 0) == 0
+    with pytest.raises(RuntimeError, match="gave up in a bounded wait"):
+        kernels.project_check()                               # the sticky word remembers it ...
+    kernels.project_check()                                   # ... once
+    out = kernels.project_forward(x, w, w_kn=True, check_status=True)
+    assert torch.allclose(out, x @ w, rtol=1e-4, atol=1e-4)
+    kernels.project_check()

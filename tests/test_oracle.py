@@ -137,3 +137,17 @@ def test_chunked_cpu_step_equals_unchunked():
     part = orc.gat_fused_step_cpu(ar, ac, row_ptr, col_ind, 0.2, x, g, chunk_rows=13)
     for a, b, name in zip(full, part, ("out", "grad_feat", "grad_row", "grad_col")):
         assert_close(a, b, name)
+
+
+def test_knn_and_coo_sort_oracles():
+    """kNN against a float64 brute force on points without near-ties; the edge sort against python's sorted()."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(3, 50, 4, generator=g)
+    got = orc.knn_graph(x, 6).view(3, 50, 6)
+    d = torch.cdist(x.double(), x.double())
+    ref = d.argsort(dim=2, stable=True)[:, :, :6] + (torch.arange(3) * 50)[:, None, None]
+    assert torch.equal(got, ref)
+    dst = torch.randint(0, 20, (300,), generator=g)
+    src = torch.randint(0, 20, (300,), generator=g)
+    d_s, s_s = orc.coo_sort(dst, src)
+    assert list(zip(d_s.tolist(), s_s.tolist())) == sorted(zip(dst.tolist(), src.tolist()))
