@@ -47,11 +47,13 @@ def parse():
     ap.add_argument("--cpu-sample-edges", type=int, default=2_000_000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--stages", type=int, default=3,
-                    help="sweeps per pass of the sharded layer: stage 0 = own nodes, the others one halo chunk each")
+    ap.add_argument("--stages", type=int, default=0,
+                    help="sweeps per pass of the sharded layer: stage 0 = own nodes, the others one halo chunk each (0: 2 on two GPUs, else 3)")
     ap.add_argument("--halo-mode", default="dma", choices=["dma", "pull"],
                     help="dma: owners pack, peers copy with the copy engines; pull: a kernel loads the rows from peer memory")
     ap.add_argument("--pull-ctas", type=int, default=48, help="grid bound of the halo fetch kernel in pull mode (0: unbounded)")
+    ap.add_argument("--overlap-publish", type=int, default=0,
+                    help="1: packing of the send buffers and the barrier run on the side stream beside the first sweep")
     ap.add_argument("--gather-fallback", action="store_true",
                     help="halo rows through all-gathers instead of peer loads from symmetric memory")
     return ap.parse_args()
@@ -305,8 +307,12 @@ def run_ours(args, rank, world, local):
     else:
         import torch.distributed as dist
         del cp, ri, pm
+        if args.stages <= 0:
+            args.stages = 2 if world == 2 else 3
         shard = gdist.build_halo_shard(rp, ci, rank, world, stages=args.stages, seed=7)
         transport = gdist.GatherTransport(shard) if args.gather_fallback else gdist.make_transport(shard, None, args.halo_mode, args.pull_ctas)
+        if hasattr(transport, "overlap_publish"):
+            transport.overlap_publish = bool(args.overlap_publish)
         layer = gdist.ShardedGATConv(IN, F, H, shard, negative_slope=SLOPE, transport=transport).to(dev).train()
         with torch.no_grad():
             layer.W.copy_(W); layer.attn_l.copy_(al); layer.attn_r.copy_(ar_)

@@ -187,18 +187,30 @@ def suite_micro(iters, edges, degrees, heads, cap_gb):
         for h in heads:
             tensor_gb = n * h * f * 4 / 1e9
             cfg = cfg0 + f", {h} heads x {f}"
-            if tensor_gb > cap_gb or h * f > 1024:
-                print(json.dumps({"op": "skipped", "config": cfg, "reason": f"one [N,H,F] tensor is {tensor_gb:.1f} GB (cap {cap_gb} GB)"}), flush=True)
+            # peak use: two [N,H,F] tensors (SDDMM operands; then input and output of the forward), the [E,H] SDDMM
+            # result and the long-row partials; what does not fit the free device memory is reported, not tried
+            free_gb = torch.cuda.mem_get_info(dev)[0] / 1e9
+            need_gb = 2 * tensor_gb + edges * h * 4 / 1e9 + 2 * (edges / 1024) * 2 * (2 * h * f + 3 * h) * 4 / 1e9 + 2.0
+            limit_gb = min(free_gb, cap_gb) if cap_gb > 0 else free_gb
+            if h * f > 1024:
+                print(json.dumps({"op": "skipped", "config": cfg, "reason": "heads x width above 1024 floats per row: outside the float4 layout of the kernels"}), flush=True)
+                continue
+            if need_gb > limit_gb:
+                print(json.dumps({"op": "skipped", "config": cfg,
+                                  "reason": f"needs {need_gb:.0f} GB (two [N,H,F] tensors of {tensor_gb:.1f} GB, the [E,H] result, partials) "
+                                            f"but {limit_gb:.0f} GB are available on one GPU"}), flush=True)
                 continue
             a = torch.randn(n, h, f, device=dev)
             b = torch.randn(n, h, f, device=dev)
-            ar, ac = torch.randn(n, h, device=dev), torch.randn(n, h, device=dev)
             it = max(3, iters // 4)
             sd_b = (n + 1) * 8 + 4 * edges + 4 * edges * h * f + 4 * n * h * f + 4 * edges * h
             report("mhsddmm", cfg, timed(lambda: kernels.mhsddmm(rp, ci, a, b), it, False), sd_b)
+            del a
+            torch.cuda.empty_cache()
+            ar, ac = torch.randn(n, h, device=dev), torch.randn(n, h, device=dev)
             fb, _ = gat_bytes(n, edges, h, f, 8)
             report("edge_softmax+spmm (gat_forward)", cfg, timed(lambda: kernels.gat_forward(ar, ac, rp, ci, 0.2, b), it, False), fb)
-            del a, b, ar, ac
+            del b, ar, ac
             torch.cuda.empty_cache()
         del rp, ci
         torch.cuda.empty_cache()
@@ -234,7 +246,7 @@ def main():
     ap.add_argument("--micro-edges", type=int, default=256_000_000)
     ap.add_argument("--micro-degrees", default="4,16,64,128")
     ap.add_argument("--micro-heads", default="1,4,8,16")
-    ap.add_argument("--cap-gb", type=float, default=35.0)
+    ap.add_argument("--cap-gb", type=float, default=0.0, help="memory cap for one configuration (0: the free device memory)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("bench_ops.py needs a CUDA device: there is no CPU path")

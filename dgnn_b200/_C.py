@@ -30,13 +30,15 @@ SIGNATURES = {
     "dgnn_version": (c_int, []),
     "dgnn_status_string": (ctypes.c_char_p, [c_int]),
     "dgnn_seg_chunk": (c_i64, []),
+    "dgnn_check_ptr": (c_int, [c_i64, c_i64, c_p, c_int, c_p, c_p]),
+    "dgnn_check_index": (c_int, [c_i64, c_p, c_i64, c_p, c_p]),
     "dgnn_gat_forward_workspace_bytes": (c_sz, [c_i64, c_i64, c_int, c_int]),
     "dgnn_gat_forward": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
                                  c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_forward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
     "dgnn_gat_fast_shape": (c_int, [c_int, c_int]),
     "dgnn_gat_forward_staged": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
-                                        c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
+                                        c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_p, c_sz, c_p]),
     "dgnn_gat_rowstat_full": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_f, c_p, c_p,
                                       c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_backward_cols_workspace_bytes": (c_sz, [c_i64, c_int, c_int, c_int]),
@@ -44,7 +46,8 @@ SIGNATURES = {
     "dgnn_gat_rowstat_bias": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_backward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
     "dgnn_gat_backward_cols_staged": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p,
-                                              c_p, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]),
+                                              c_p, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_p, c_sz,
+                                              c_p]),
     "dgnn_gat_rowstat": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_gat_backward_workspace_bytes": (c_sz, [c_i64, c_i64, c_i64, c_int, c_int]),
     "dgnn_gat_backward_cols": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p,

@@ -136,13 +136,42 @@ __device__ __forceinline__ void head_reduce(float (&p)[VPL], int f4_shift) {
 // Op must provide: n_rows, nnz, indptr, idx_bits, ws (float* partial slots),
 //   slot_stride (floats per slot), MIN_BLOCKS, HAS_PARTIALS, struct State,
 //   skip_empty (rows without edges need no work), init(State&, row, lane) = empty state,
-//   resume(State&, row, lane) = fold in a state carried from an earlier call (once per row),
+//   STAGED (bool; true: members first, last, stage, stage_mask -- see dgnn_row_role),
+//   resume(State&, row, lane, first) = unless first, fold in a state carried from an earlier call (once per row),
 //   ring_bytes() = shared memory per warp for an operator that stages its gathered rows there (0: none),
 //   range(State&, row, e0, e1, lane, ring) with ring = the warp's staging area,
 //   combine(State&, lane) = fold the sub-groups' states after range,
-//   finalize(State&, row, lane), store_partial(State&, float* p, lane),
+//   finalize(State&, row, lane, last) = write the row's result (last) or its state, store_partial(State&, float* p, lane),
 //   merge_partial(State&, const float* p, lane)
 // ---------------------------------------------------------------------------
+// The part a row plays in this launch.  Plain operators: the whole row, once (first = last = true).  Staged
+// sweeps (Op::STAGED) carry a per-row state between launches: either every row takes part in every stage
+// (op.first / op.last mark the ends), or -- with op.stage_mask -- bit p of stage_mask[r] says whether row r has
+// entries in stage p: the row starts fresh in its first such stage, is written out in its last one and is not
+// touched (no state read or written) in any other; rows without entries anywhere are written by stage 0.
+template <class Op>
+__device__ __forceinline__ bool dgnn_row_role(const Op& op, i64 r, bool& first, bool& last) {
+  if constexpr (Op::STAGED) {
+    if (op.stage_mask == nullptr) {
+      first = op.first != 0;
+      last = op.last != 0;
+      return true;
+    }
+    const unsigned m = op.stage_mask[r];
+    const int p = op.stage;
+    if (m == 0) {
+      first = last = true;
+      return p == 0;
+    }
+    first = (m & ((1u << p) - 1u)) == 0;
+    last = (m >> (p + 1)) == 0;
+    return ((m >> p) & 1u) != 0;
+  } else {
+    first = last = true;
+    return true;
+  }
+}
+
 // Short rows: every warp of a fixed pool draws the next `batch` rows (1..31) from a
 // counter.  Rows come out in id order, so whatever skew the ids carry (R-MAT: low
 // ids are the heavy ones) is spread over all warps and the tail consists of a few
@@ -167,12 +196,14 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const
       const i64 hb = __shfl_sync(DGNN_FULL, mine, i + 1);
       if (hb - lb > DGNN_SEG) continue;  // long row: chunk + merge kernels own it
       if (op.skip_empty && hb == lb) continue;  // middle stage of a staged sweep: the carried state stays as it is
+      bool first, last;
+      if (!dgnn_row_role(op, r, first, last)) continue;
       typename Op::State st;
       op.init(st, r, lane);
-      op.resume(st, r, lane);
+      op.resume(st, r, lane, first);
       op.range(st, r, lb, hb, lane, ring);
       op.combine(st, lane);
-      op.finalize(st, r, lane);
+      op.finalize(st, r, lane, last);
     }
   }
 }
@@ -189,12 +220,14 @@ __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows_small
   const i64 lb = ldp(op.indptr, op.idx_bits, r);
   const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
   if (op.skip_empty && hb == lb) return;
+  bool first, last;
+  if (!dgnn_row_role(op, r, first, last)) return;
   typename Op::State st;
   op.init(st, r, lane);
-  op.resume(st, r, lane);
+  op.resume(st, r, lane, first);
   op.range(st, r, lb, hb, lane, ring);
   op.combine(st, lane);
-  op.finalize(st, r, lane);
+  op.finalize(st, r, lane, last);
 }
 
 // Long rows: one CTA of DGNN_CHUNK_WARPS warps per (chunk, slot).  The piece of the
@@ -248,12 +281,14 @@ __global__ void __launch_bounds__(DGNN_THREADS) k_merge(const Op op) {
   const i64 lb = ldp(op.indptr, op.idx_bits, r);
   const i64 hb = ldp(op.indptr, op.idx_bits, r + 1);
   if (hb - lb <= DGNN_SEG || lb < cs) return;  // the long row that begins in this chunk
+  bool first, last;
+  if (!dgnn_row_role(op, r, first, last)) return;   // a row this long has entries in this stage; kept for symmetry
   typename Op::State st;
   op.init(st, r, lane);
-  op.resume(st, r, lane);
+  op.resume(st, r, lane, first);
   op.merge_partial(st, op.ws + (2 * j + 1) * op.slot_stride, lane);
   for (i64 jj = j + 1; jj * DGNN_SEG < hb; ++jj) op.merge_partial(st, op.ws + (2 * jj) * op.slot_stride, lane);
-  op.finalize(st, r, lane);
+  op.finalize(st, r, lane, last);
 }
 
 static inline unsigned dgnn_grid(i64 items, int per_block) {

@@ -45,6 +45,9 @@ struct GatFwdOp {
   // carried in `state` (one slot per row) between calls; first / last mark the ends
   float* state;
   int first, last, skip_empty;
+  static constexpr bool STAGED = true;
+  const unsigned char* stage_mask;   // per row: bit p set = the row has entries in stage p (NULL: every row in every stage)
+  int stage;
   const float4* bias;   // optional [H*F] added to the normalised output (layer epilogue)
   // NEG: the share of the result that comes from edges on the negative side of the LeakyReLU
   float4* out_neg;      // [n_rows, H*F], normalised like out (no bias)
@@ -68,8 +71,8 @@ struct GatFwdOp {
       if (NEG) { st.zn[v] = 0.f; st.accn[v] = zero4(); }
     }
   }
-  __device__ __forceinline__ void resume(State& st, i64 r, int lane) const {
-    if (!first && st.lm.sg == 0) merge_partial(st, state + r * slot_stride, lane);
+  __device__ __forceinline__ void resume(State& st, i64 r, int lane, bool first_) const {
+    if (!first_ && st.lm.sg == 0) merge_partial(st, state + r * slot_stride, lane);
   }
   // fold the (max, sum, accumulator) of the sub-groups; afterwards every sub-group holds the row's state
   __device__ __forceinline__ void combine(State& st, int) const {
@@ -185,8 +188,8 @@ struct GatFwdOp {
     }
   }
 
-  __device__ __forceinline__ void finalize(State& st, i64 r, int lane) const {
-    if (!last) { store_partial(st, state + r * slot_stride, lane); return; }
+  __device__ __forceinline__ void finalize(State& st, i64 r, int lane, bool last_) const {
+    if (!last_) { store_partial(st, state + r * slot_stride, lane); return; }
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.act[v]) continue;
@@ -329,31 +332,49 @@ k_gat_rowstat_full(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_r
     b4[v] = (bias && lm.act[v]) ? ld4(bias + lm.q[v]) : zero4();
     gsum[v] = zero4();
   }
+  // two rows per warp and step: all their loads are issued before the first reduction
+  constexpr int RS_ROWS = 2;
   const i64 stride = (i64)gridDim.x * DGNN_WARPS;
-  for (i64 r = (i64)blockIdx.x * DGNN_WARPS + warp; r < n_rows; r += stride) {
-    float s[VPL], t[VPL];
+  for (i64 r0 = (i64)blockIdx.x * DGNN_WARPS + warp; r0 < n_rows; r0 += stride * RS_ROWS) {
+    float4 g[RS_ROWS][VPL], o[RS_ROWS][VPL], on[RS_ROWS][VPL];
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      s[v] = 0.f;
-      t[v] = 0.f;
-      if (lm.act[v]) {
-        const float4 g = ld4(grad + r * hf4 + lm.q[v]);
-        float4 o = ld4(out + r * hf4 + lm.q[v]);
-        o.x -= b4[v].x; o.y -= b4[v].y; o.z -= b4[v].z; o.w -= b4[v].w;
-        s[v] = dot4(g, o);
-        if (out_neg) t[v] = dot4(g, ld4(out_neg + r * hf4 + lm.q[v]));
-        if (grad_copy) grad_copy[r * hf4 + lm.q[v]] = g;
-        add4(gsum[v], g);
+    for (int k = 0; k < RS_ROWS; ++k) {
+      const i64 r = r0 + k * stride;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        const bool ok = lm.act[v] && r < n_rows;
+        g[k][v] = ok ? ld4(grad + r * hf4 + lm.q[v]) : zero4();
+        o[k][v] = ok ? ld4(out + r * hf4 + lm.q[v]) : zero4();
+        on[k][v] = (ok && out_neg) ? ld4(out_neg + r * hf4 + lm.q[v]) : zero4();
       }
     }
-    head_reduce<VPL>(s, f4_shift);
-    if (out_neg) head_reduce<VPL>(t, f4_shift);
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      if (lm.lead[v]) {
-        const i64 i = r * H + lm.hd[v];
-        pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), 1.f / __ldg(edge_sum + i), s[v]);
-        if (out_neg) grad_attn_row[i] = one_minus_slope * (s[v] * __ldg(a_neg + i) - t[v]);
+    for (int k = 0; k < RS_ROWS; ++k) {
+      const i64 r = r0 + k * stride;
+      if (r >= n_rows) break;            // uniform per warp
+      float s[VPL], t[VPL];
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        s[v] = 0.f;
+        t[v] = 0.f;
+        if (lm.act[v]) {
+          float4 ob = o[k][v];
+          ob.x -= b4[v].x; ob.y -= b4[v].y; ob.z -= b4[v].z; ob.w -= b4[v].w;
+          s[v] = dot4(g[k][v], ob);
+          if (out_neg) t[v] = dot4(g[k][v], on[k][v]);
+          if (grad_copy) grad_copy[r * hf4 + lm.q[v]] = g[k][v];
+          add4(gsum[v], g[k][v]);
+        }
+      }
+      head_reduce<VPL>(s, f4_shift);
+      if (out_neg) head_reduce<VPL>(t, f4_shift);
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        if (lm.lead[v]) {
+          const i64 i = r * H + lm.hd[v];
+          pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), 1.f / __ldg(edge_sum + i), s[v]);
+          if (out_neg) grad_attn_row[i] = one_minus_slope * (s[v] * __ldg(a_neg + i) - t[v]);
+        }
       }
     }
   }
@@ -414,6 +435,9 @@ struct GatBwdOp {
   i64 slot_stride;
   float* state;      // staged sweep over row blocks: (grad_feat, grad_attn_col) accumulators per column
   int first, last, skip_empty;
+  static constexpr bool STAGED = true;
+  const unsigned char* stage_mask;   // per row: bit p set = the row has entries in stage p (NULL: every row in every stage)
+  int stage;
 
   struct State {
     LaneMap<VPL, LPR> lm;
@@ -431,8 +455,8 @@ struct GatBwdOp {
       st.gc[v] = 0.f;
     }
   }
-  __device__ __forceinline__ void resume(State& st, i64 c, int lane) const {
-    if (!first && st.lm.sg == 0) merge_partial(st, state + c * slot_stride, lane);
+  __device__ __forceinline__ void resume(State& st, i64 c, int lane, bool first_) const {
+    if (!first_ && st.lm.sg == 0) merge_partial(st, state + c * slot_stride, lane);
   }
   // sum the sub-groups' accumulators (lower sub-group first, so all partners agree bit for bit)
   __device__ __forceinline__ void combine(State& st, int) const {
@@ -514,8 +538,8 @@ struct GatBwdOp {
     }
   }
 
-  __device__ __forceinline__ void finalize(State& st, i64 c, int lane) const {
-    if (!last) { store_partial(st, state + c * slot_stride, lane); return; }
+  __device__ __forceinline__ void finalize(State& st, i64 c, int lane, bool last_) const {
+    if (!last_) { store_partial(st, state + c * slot_stride, lane); return; }
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       if (!st.lm.wr[v]) continue;
@@ -674,7 +698,7 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
                   const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
                   float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
                   void* ws, float* state, int first, int last, const float* bias, float* out_neg, float* a_neg,
-                  cudaStream_t s) {
+                  const unsigned char* stage_mask, int stage, cudaStream_t s) {
   Op op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -684,7 +708,8 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
   op.out = reinterpret_cast<float4*>(out); op.edge_max = edge_max; op.edge_sum = edge_sum;
   op.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + DGNN_WS_HEADER);
   op.slot_stride = fwd_slot_stride(h, f, out_neg != nullptr);
-  op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last) ? 1 : 0;
+  op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last && !stage_mask) ? 1 : 0;
+  op.stage_mask = stage_mask; op.stage = stage;
   op.bias = reinterpret_cast<const float4*>(bias);
   op.out_neg = reinterpret_cast<float4*>(out_neg); op.a_neg = a_neg;
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
@@ -707,7 +732,7 @@ int launch_bwd_op(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const 
                   const int* row_ind, const int* permute, const float* pack, const float* mask,
                   const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
                   float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, unsigned long long* counter,
-                  float* state, int first, int last, cudaStream_t s) {
+                  float* state, int first, int last, const unsigned char* stage_mask, int stage, cudaStream_t s) {
   Op op;
   op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -717,7 +742,8 @@ int launch_bwd_op(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const 
   op.slope = slope; op.drop_p = drop; op.inv_keep = (float)(1.0 / (1.0 - (double)drop));
   op.grad_feat = reinterpret_cast<float4*>(grad_feat); op.grad_attn_col = grad_attn_col;
   op.grad_edge = grad_edge; op.ws = ws; op.slot_stride = bwd_slot_stride(h, f);
-  op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last) ? 1 : 0;
+  op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last && !stage_mask) ? 1 : 0;
+  op.stage_mask = stage_mask; op.stage = stage;
   return dgnn_launch_trio(op, counter, s);
 }
 
@@ -799,7 +825,7 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_
                      size_t workspace_bytes, void* stream) {
   return dgnn_gat_forward_staged(n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,
                                  negative_slope, attn_drop, edge_mask, nullptr, out, edge_max, edge_sum, nullptr,
-                                 nullptr, nullptr, 1, 1, workspace, workspace_bytes, stream);
+                                 nullptr, nullptr, 1, 1, nullptr, 0, workspace, workspace_bytes, stream);
 }
 
 int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
@@ -807,15 +833,19 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
                             const float* in_feat, float negative_slope, float attn_drop,
                             const float* edge_mask, const float* bias, float* out, float* edge_max,
                             float* edge_sum, float* out_neg, float* a_neg, float* state, int first, int last,
+                            const uint8_t* stage_mask, int stage,
                             void* workspace, size_t workspace_bytes, void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
   const bool staged = !(first && last);
+  if (stage_mask && (stage < 0 || stage > 7)) return DGNN_ERR_VALUE;
+  // with a stage mask rows are written out in whatever stage is their last: the outputs are needed in every stage
+  const bool need_out = last || stage_mask != nullptr;
   if (staged && (!state || !aligned16(state))) return state ? DGNN_ERR_ALIGN : DGNN_ERR_NULL;
   if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
   if ((out_neg == nullptr) != (a_neg == nullptr)) return DGNN_ERR_NULL;
   if (n_rows == 0) return DGNN_OK;
-  if (!row_ptr || !attn_row || (last && !out) || (nnz > 0 && (!col_ind || !attn_col || !in_feat))) return DGNN_ERR_NULL;
+  if (!row_ptr || !attn_row || (need_out && !out) || (nnz > 0 && (!col_ind || !attn_col || !in_feat))) return DGNN_ERR_NULL;
   if ((edge_max == nullptr) != (edge_sum == nullptr)) return DGNN_ERR_NULL;
   if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
   const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
@@ -827,7 +857,7 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
     if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
 #define FWD_ARGS                                                                                             \
   fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, negative_slope, attn_drop, \
-      mask, out, edge_max, edge_sum, workspace, state, first, last, bias, out_neg, a_neg, s
+      mask, out, edge_max, edge_sum, workspace, state, first, last, bias, out_neg, a_neg, stage_mask, stage, s
 #define CALL_FWD(V, M, FW, L) \
   (out_neg ? launch_fwd<V, M, FW, L, true>(FWD_ARGS) : launch_fwd<V, M, FW, L, false>(FWD_ARGS))
     DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_FWD)
@@ -835,7 +865,7 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
 #undef FWD_ARGS
   }
   // staged sweeps, the bias epilogue and the negative-side outputs exist only for the float4 layout
-  if (staged || bias || out_neg) return DGNN_ERR_SHAPE;
+  if (staged || bias || out_neg || stage_mask) return DGNN_ERR_SHAPE;
   k_gat_fwd_generic<<<dgnn_grid(n_rows * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
       n_rows, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, mask, negative_slope,
       attn_drop, (float)(1.0 / (1.0 - (double)attn_drop)), out, edge_max, edge_sum);
@@ -950,7 +980,7 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
                            float* grad_attn_col, void* workspace, size_t workspace_bytes, void* stream) {
   return dgnn_gat_backward_cols_staged(n_rows, n_cols, nnz, h, f, row_ptr, col_ptr, idx_bits, row_ind, permute, pack,
                                        edge_mask, in_feat, attn_col, grad_out, negative_slope, attn_drop, grad_feat,
-                                       grad_attn_row, grad_attn_col, nullptr, 1, 1, workspace, workspace_bytes, stream);
+                                       grad_attn_row, grad_attn_col, nullptr, 1, 1, nullptr, 0, workspace, workspace_bytes, stream);
 }
 
 int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f, const void* row_ptr,
@@ -958,11 +988,13 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
                                   const int32_t* permute, const float* pack, const float* edge_mask,
                                   const float* in_feat, const float* attn_col, const float* grad_out,
                                   float negative_slope, float attn_drop, float* grad_feat, float* grad_attn_row,
-                                  float* grad_attn_col, float* state, int first, int last, void* workspace,
-                                  size_t workspace_bytes, void* stream) {
+                                  float* grad_attn_col, float* state, int first, int last, const uint8_t* stage_mask,
+                                  int stage, void* workspace, size_t workspace_bytes, void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
   const bool staged = !(first && last);
+  if (stage_mask && (stage < 0 || stage > 7)) return DGNN_ERR_VALUE;
+  const bool need_out = last || stage_mask != nullptr;   // with a stage mask columns are written out in their own last stage
   if (staged && (!state || !aligned16(state))) return state ? DGNN_ERR_ALIGN : DGNN_ERR_NULL;
   st = check_common(n_cols, nnz, h, f, idx_bits);
   if (st) return st;
@@ -970,7 +1002,7 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
   if (!(attn_drop >= 0.f && attn_drop < 1.f)) return DGNN_ERR_VALUE;
   const bool edge = grad_attn_row != nullptr;   // the per-edge term and its row reduction are wanted
   if (!col_ptr || (edge && !row_ptr)) return DGNN_ERR_NULL;
-  if (n_cols > 0 && (!in_feat || !attn_col || (last && (!grad_feat || !grad_attn_col)))) return DGNN_ERR_NULL;
+  if (n_cols > 0 && (!in_feat || !attn_col || (need_out && (!grad_feat || !grad_attn_col)))) return DGNN_ERR_NULL;
   if (n_rows > 0 && (!pack || !grad_out)) return DGNN_ERR_NULL;
   if (nnz > 0 && (!row_ind || (edge && !permute))) return DGNN_ERR_NULL;
   if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
@@ -990,7 +1022,8 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
       int rc;
 #define BWD_ARGS                                                                                          \
   fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat, attn_col, grad_out,   \
-      negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, col_part, counter, state, first, last, s
+      negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, col_part, counter, state, first, last, stage_mask, \
+      stage, s
 #define CALL_BWD(V, M, FW, L) \
   (edge ? launch_bwd<V, M, FW, L, true>(BWD_ARGS) : launch_bwd<V, M, FW, L, false>(BWD_ARGS))
       auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_BWD) };
@@ -999,7 +1032,7 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
       rc = run();
       if (rc) return rc;
     } else {
-      if (staged) return DGNN_ERR_SHAPE;
+      if (staged || stage_mask) return DGNN_ERR_SHAPE;
       k_gat_bwd_cols_generic<<<dgnn_grid(n_cols * h, DGNN_WARPS), DGNN_THREADS, 0, s>>>(
           n_cols, h, f, col_ptr, idx_bits, row_ind, permute, reinterpret_cast<const float4*>(pack), mask,
           in_feat, attn_col, grad_out, negative_slope, attn_drop,

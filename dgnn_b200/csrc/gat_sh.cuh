@@ -12,6 +12,14 @@
 #pragma once
 #include "common.cuh"
 
+// resident CTAs per SM asked of the compiler for the 2-vectors-per-lane kernels (it caps the registers per thread)
+#ifndef DGNN_SH_FWD_BLOCKS
+#define DGNN_SH_FWD_BLOCKS 5
+#endif
+#ifndef DGNN_SH_BWD_BLOCKS
+#define DGNN_SH_BWD_BLOCKS 5
+#endif
+
 template <int VPL> struct Log2;
 template <> struct Log2<2> { static constexpr int v = 1; };
 template <> struct Log2<4> { static constexpr int v = 2; };
@@ -52,7 +60,7 @@ __device__ __forceinline__ void lanes_reduce(float (&d)[U], int lph_shift) {
 // the LeakyReLU (out_neg, a_neg); the backward derives grad_attn_row from it without a per-edge array.
 template <int VPL, bool MASK, bool FULL, bool NEG>
 struct GatFwdOpSH {
-  static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 2);
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? DGNN_SH_FWD_BLOCKS : (VPL == 4 ? 4 : 2);
   static constexpr bool HAS_PARTIALS = true;
   static constexpr int U = VPL <= 2 ? 4 : 2;
   i64 n_rows, nnz;
@@ -72,6 +80,9 @@ struct GatFwdOpSH {
   i64 slot_stride;
   float* state;
   int first, last, skip_empty;
+  static constexpr bool STAGED = true;
+  const unsigned char* stage_mask;   // per row: bit p set = the row has entries in stage p (NULL: every row in every stage)
+  int stage;
   const float4* bias;
   float4* out_neg;
   float* a_neg;
@@ -96,8 +107,8 @@ struct GatFwdOpSH {
       for (int v = 0; v < VPL; ++v) st.accn[v] = zero4();
     }
   }
-  __device__ __forceinline__ void resume(State& st, i64 r, int lane) const {
-    if (!first) merge_partial(st, state + r * slot_stride, lane);
+  __device__ __forceinline__ void resume(State& st, i64 r, int lane, bool first_) const {
+    if (!first_) merge_partial(st, state + r * slot_stride, lane);
   }
   __device__ __forceinline__ void combine(State&, int) const {}
 
@@ -171,8 +182,8 @@ struct GatFwdOpSH {
     }
   }
 
-  __device__ __forceinline__ void finalize(State& st, i64 r, int lane) const {
-    if (!last) { store_partial(st, state + r * slot_stride, lane); return; }
+  __device__ __forceinline__ void finalize(State& st, i64 r, int lane, bool last_) const {
+    if (!last_) { store_partial(st, state + r * slot_stride, lane); return; }
     if (!st.lm.act) return;
     const float sc = st.z > 0.f ? inv_keep / st.z : 0.f;
 #pragma unroll
@@ -244,7 +255,7 @@ struct GatFwdOpSH {
 // gradient then comes from the row statistics -- neither array is touched unless a dropout mask needs the position
 template <int VPL, bool MASK, bool FULL, bool EDGE>
 struct GatBwdOpSH {
-  static constexpr int MIN_BLOCKS = VPL <= 2 ? (EDGE || MASK ? 4 : 5) : (VPL == 4 ? 3 : 2);
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? (EDGE || MASK ? 4 : DGNN_SH_BWD_BLOCKS) : (VPL == 4 ? 3 : 2);
   static constexpr bool HAS_PARTIALS = true;
   static constexpr int U = VPL <= 2 ? 4 : 2;
   i64 n_rows, nnz;      // "rows" of the CSC form = source columns
@@ -266,6 +277,9 @@ struct GatBwdOpSH {
   i64 slot_stride;
   float* state;
   int first, last, skip_empty;
+  static constexpr bool STAGED = true;
+  const unsigned char* stage_mask;   // per row: bit p set = the row has entries in stage p (NULL: every row in every stage)
+  int stage;
 
   struct State {
     HeadLanes<VPL> lm;
@@ -283,8 +297,8 @@ struct GatBwdOpSH {
       st.acc[v] = zero4();
     }
   }
-  __device__ __forceinline__ void resume(State& st, i64 c, int lane) const {
-    if (!first) merge_partial(st, state + c * slot_stride, lane);
+  __device__ __forceinline__ void resume(State& st, i64 c, int lane, bool first_) const {
+    if (!first_) merge_partial(st, state + c * slot_stride, lane);
   }
   __device__ __forceinline__ void combine(State&, int) const {}
 
@@ -347,8 +361,8 @@ struct GatBwdOpSH {
     }
   }
 
-  __device__ __forceinline__ void finalize(State& st, i64 c, int lane) const {
-    if (!last) { store_partial(st, state + c * slot_stride, lane); return; }
+  __device__ __forceinline__ void finalize(State& st, i64 c, int lane, bool last_) const {
+    if (!last_) { store_partial(st, state + c * slot_stride, lane); return; }
     if (!st.lm.act) return;
 #pragma unroll
     for (int v = 0; v < VPL; ++v) grad_feat[c * hf4 + st.lm.q[v]] = st.acc[v];

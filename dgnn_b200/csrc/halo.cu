@@ -29,35 +29,45 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) {
   return v;
 }
 
-// one tensor: dst[i, :] = src[rank_i][idx_i, :], rows of `vpr` float4 vectors
+// One tensor: dst[i, :] = src[rank_i][idx_i, :], rows of `vpr` float4 vectors.  A group of G = min(32, next power
+// of two >= vpr) lanes owns a row (a whole warp for rows of 512 bytes or more, several rows per warp for short
+// ones), so the row's code is read once per group and no division by the row length is needed; every group
+// works on HALO_UNROLL rows at a time with all their loads issued before the first store.
 __device__ __forceinline__ void pull_tensor(i64 n_rows, const int* codes, int n_ranks, i64 src_rows, const HaloPtrs& src,
                                             float4* dst, int vpr, int* status) {
-  const i64 total = n_rows * vpr;
-  const i64 step = (i64)gridDim.x * HALO_THREADS * HALO_UNROLL;
-  for (i64 base = (i64)blockIdx.x * HALO_THREADS * HALO_UNROLL + threadIdx.x; base < total; base += step) {
-    float4 v[HALO_UNROLL];
-    bool ok[HALO_UNROLL];
+  int g = 1;
+  while (g < vpr && g < 32) g <<= 1;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (g - 1);                        // lane inside its group
+  const i64 groups_per_cta = (HALO_THREADS / 32) * (32 / g);
+  const i64 group = (i64)blockIdx.x * groups_per_cta + (threadIdx.x >> 5) * (32 / g) + lane / g;
+  const i64 step = (i64)gridDim.x * groups_per_cta;
+  for (i64 row0 = group; row0 < n_rows; row0 += step * HALO_UNROLL) {
+    const float4* from[HALO_UNROLL];
 #pragma unroll
     for (int k = 0; k < HALO_UNROLL; ++k) {
-      const i64 e = base + (i64)k * HALO_THREADS;
-      ok[k] = e < total;
-      if (ok[k]) {
-        const i64 row = e / vpr;
-        const int q = (int)(e - row * vpr);
+      const i64 row = row0 + (i64)k * step;
+      from[k] = nullptr;
+      if (row < n_rows) {
         const unsigned code = (unsigned)__ldg(codes + row);
         const int rk = (int)(code >> HALO_SHIFT);
         const i64 idx = (i64)(code & ((1u << HALO_SHIFT) - 1));
-        if (rk >= n_ranks || idx >= src_rows) {   // never dereference an address outside an owner's block
-          ok[k] = false;
-          if (status) atomicMax(status, 1);
+        if (rk >= n_ranks || idx >= src_rows) {          // never dereference an address outside an owner's block
+          if (status && sub == 0) atomicMax(status, 1);
         } else {
-          v[k] = ld_stream(src.p[rk] + idx * vpr + q);
+          from[k] = src.p[rk] + idx * vpr;
         }
       }
     }
+    for (int q = sub; q < vpr; q += g) {
+      float4 v[HALO_UNROLL];
 #pragma unroll
-    for (int k = 0; k < HALO_UNROLL; ++k)
-      if (ok[k]) dst[base + (i64)k * HALO_THREADS] = v[k];
+      for (int k = 0; k < HALO_UNROLL; ++k)
+        if (from[k]) v[k] = ld_stream(from[k] + q);
+#pragma unroll
+      for (int k = 0; k < HALO_UNROLL; ++k)
+        if (from[k]) dst[(row0 + (i64)k * step) * vpr + q] = v[k];
+    }
   }
 }
 
@@ -121,8 +131,10 @@ int dgnn_halo_pull(int64_t n_rows, const int32_t* codes, int n_ranks, int64_t sr
   }
   if ((reinterpret_cast<uintptr_t>(dst_a) & 15) || (reinterpret_cast<uintptr_t>(dst_b) & 15)) return DGNN_ERR_ALIGN;
   const int vpr_a = row_bytes_a / 16, vpr_b = row_bytes_b / 16;
-  const i64 total = n_rows * (vpr_a > vpr_b ? vpr_a : vpr_b);
-  i64 ctas = (total + (i64)HALO_THREADS * HALO_UNROLL - 1) / ((i64)HALO_THREADS * HALO_UNROLL);
+  // one warp (or part of one) per row of the wider tensor, HALO_UNROLL rows per group and step
+  const int wide = vpr_a > vpr_b ? vpr_a : vpr_b;
+  const i64 groups_per_cta = (HALO_THREADS / 32) * (wide >= 32 ? 1 : 32 / (wide <= 1 ? 1 : wide <= 2 ? 2 : wide <= 4 ? 4 : wide <= 8 ? 8 : wide <= 16 ? 16 : 32));
+  i64 ctas = (n_rows + groups_per_cta * HALO_UNROLL - 1) / (groups_per_cta * HALO_UNROLL);
   if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
   if (ctas < 1) ctas = 1;
   k_halo_pull<<<(unsigned)ctas, HALO_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(

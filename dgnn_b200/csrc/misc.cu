@@ -31,11 +31,54 @@ __global__ void k_uniform(uint64_t seed, uint64_t offset, i64 n, float* out) {
   }
 }
 
+// ---- guard mode: validation of the index arrays a caller hands over ------------------------------------
+// report[0] = first kind of defect seen (0 none; 1 ptr[0] != 0; 2 ptr decreases; 3 ptr[n] != nnz; 4 index out of
+// range), report[1] = smallest position at which a defect of any kind was seen (atomicMin), report[2] = its value
+__device__ __forceinline__ void guard_note(int* report, int kind, i64 pos, i64 value) {
+  atomicCAS(report, 0, kind);
+  const int p = pos > 0x7fffffffLL ? 0x7fffffff : (int)pos;
+  if (atomicMin(report + 1, p) > p) report[2] = (int)value;
+}
+
+__global__ void k_check_ptr(i64 n, i64 nnz, const void* ptr, int bits, int* report) {
+  const i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > n) return;
+  const i64 v = ldp(ptr, bits, i);
+  if (i == 0 && v != 0) guard_note(report, 1, 0, v);
+  if (i == n && v != nnz) guard_note(report, 3, n, v);
+  if (i < n && ldp(ptr, bits, i + 1) < v) guard_note(report, 2, i, v);
+}
+
+__global__ void k_check_index(i64 n, const int* idx, i64 limit, int* report) {
+  const i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int v = __ldg(idx + i);
+  if (v < 0 || (i64)v >= limit) guard_note(report, 4, i, v);
+}
+
 }  // namespace
 
 extern "C" {
 
-int dgnn_version(void) { return 100; }
+int dgnn_version(void) { return 110; }
+
+int dgnn_check_ptr(int64_t n, int64_t nnz, const void* ptr, int idx_bits, int32_t* report, void* stream) {
+  if (n < 0 || nnz < 0) return DGNN_ERR_SHAPE;
+  if (idx_bits != 32 && idx_bits != 64) return DGNN_ERR_IDX_BITS;
+  if (!ptr || !report) return DGNN_ERR_NULL;
+  k_check_ptr<<<dgnn_grid(n + 1, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(n, nnz, ptr, idx_bits, report);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+int dgnn_check_index(int64_t n, const int32_t* idx, int64_t limit, int32_t* report, void* stream) {
+  if (n < 0 || limit < 0) return DGNN_ERR_SHAPE;
+  if (n == 0) return DGNN_OK;
+  if (!idx || !report) return DGNN_ERR_NULL;
+  k_check_index<<<dgnn_grid(n, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(n, idx, limit, report);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
 
 int64_t dgnn_seg_chunk(void) { return DGNN_SEG; }
 

@@ -90,9 +90,10 @@ struct SddmmOp {
       }
     }
   }
-  __device__ __forceinline__ void resume(State&, i64, int) const {}
+  static constexpr bool STAGED = false;
+  __device__ __forceinline__ void resume(State&, i64, int, bool) const {}
   __device__ __forceinline__ void combine(State&, int) const {}
-  __device__ __forceinline__ void finalize(State&, i64, int) const {}
+  __device__ __forceinline__ void finalize(State&, i64, int, bool) const {}
   __device__ __forceinline__ void store_partial(State&, float*, int) const {}
   __device__ __forceinline__ void merge_partial(State&, const float*, int) const {}
 };
@@ -217,7 +218,8 @@ struct GmmOp {
       }
     }
   }
-  __device__ __forceinline__ void resume(State&, i64, int) const {}
+  static constexpr bool STAGED = false;
+  __device__ __forceinline__ void resume(State&, i64, int, bool) const {}
   __device__ __forceinline__ void combine(State& st, int) const {
 #pragma unroll
     for (int off = LPR; off < 32; off <<= 1) {
@@ -232,7 +234,7 @@ struct GmmOp {
       st.acc[0] = a;
     }
   }
-  __device__ __forceinline__ void finalize(State& st, i64 r, int) const {
+  __device__ __forceinline__ void finalize(State& st, i64 r, int, bool) const {
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
       if (st.lm.wr[v]) out[r * hf4 + st.lm.q[v]] = st.acc[v];

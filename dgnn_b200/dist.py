@@ -51,6 +51,7 @@ class HaloSide:
     ptr: list                         # per stage: index pointer [blk+1] int32
     ind: list                         # per stage: buffer row of every entry, int32
     edge_id: list | None = None       # per stage: position of the entry in the CSR of the whole graph (int32)
+    stage_mask: torch.Tensor = None   # [blk] uint8: bit p = the segment has entries in stage p
 
 
 @dataclass
@@ -116,17 +117,23 @@ def _build_side(ptr, ind, edge_pos, local_ids, inv, rank, blk, n_pad, stages, wa
         buf[rem] = blk + place[hidx]
         if stages > 1:
             stage[rem] = 1 + u_chunk[hidx]
+    if stages > 8:
+        raise ValueError("dgnn_b200: at most 8 stages (one bit per stage in the per-row stage mask)")
     ptrs, inds, ids = [], [], []
+    smask = torch.zeros(blk, dtype=torch.long, device=dev)
     eid = pos if edge_pos is None else edge_pos[pos].long()
     for p in range(stages):
         m = stage == p
+        cnt = torch.bincount(seg[m], minlength=blk)
+        smask |= (cnt > 0).long() << p
         sp = torch.zeros(blk + 1, dtype=torch.long, device=dev)
-        torch.cumsum(torch.bincount(seg[m], minlength=blk), 0, out=sp[1:])
+        torch.cumsum(cnt, 0, out=sp[1:])
         ptrs.append(sp.to(torch.int32))
         inds.append(buf[m].to(torch.int32).contiguous())
         if want_ids:
             ids.append(eid[m].to(torch.int32).contiguous())
-    return HaloSide(int(uniq.numel()), codes, chunk_off, ptrs, inds, ids if want_ids else None)
+    return HaloSide(int(uniq.numel()), codes, chunk_off, ptrs, inds, ids if want_ids else None,
+                    smask.to(torch.uint8).contiguous())
 
 
 def build_halo_shard(row_ptr, col_ind, rank, world, stages=3, seed=0, csr2csc=None, edge_ids=False,
@@ -278,6 +285,9 @@ class PeerTransport:
             raise ValueError("mode must be 'dma' or 'pull'")
         self.shard, self.mode = shard, mode
         self.pull_ctas = int(pull_ctas)
+        # True: packing and the barrier run on the side stream, beside the sweep over the own nodes (stage 0), instead
+        # of in front of it on the compute stream
+        self.overlap_publish = False
         self.stream = None
         self.status = None
         self.plans = None           # (forward SendPlan, backward SendPlan) in dma mode
@@ -307,6 +317,23 @@ class PeerTransport:
     def publish(self, side, bufs, tags):
         """Own rows are written: make them available to the peers (pack in dma mode), then the barrier."""
         sh = self.shard
+        cuda = bufs[0].is_cuda
+        if cuda and self.overlap_publish and sh.world > 1:
+            dev = bufs[0].device
+            if self.stream is None:
+                self.stream = torch.cuda.Stream(device=dev, priority=-1)
+            written = torch.cuda.Event()
+            written.record(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(self.stream):
+                self.stream.wait_event(written)
+                self._pack(side, bufs, tags)
+                self.barrier()
+            return
+        self._pack(side, bufs, tags)
+        self.barrier()
+
+    def _pack(self, side, bufs, tags):
+        sh = self.shard
         if self.mode == "dma" and sh.world > 1:
             plan = self._plan(side)
             sends = []
@@ -323,7 +350,6 @@ class PeerTransport:
                 else:
                     for b, sbuf in zip(bufs, sends):
                         sbuf[:k] = b[:sh.blk][plan.pack_idx.long()]
-        self.barrier()
 
     def _status(self, dev):
         if self.status is None:
@@ -350,7 +376,8 @@ class PeerTransport:
         ready.record(torch.cuda.current_stream(dev))
         works = []
         with torch.cuda.stream(self.stream):
-            self.stream.wait_event(ready)
+            if not self.overlap_publish:
+                self.stream.wait_event(ready)              # the barrier ran on the compute stream
             for c in range(sh.chunks):
                 self._fetch_chunks(side, bufs, srcs, [c])
                 ev = torch.cuda.Event()
@@ -548,9 +575,10 @@ def halo_forward_sweep(ctx: HaloContext, attn_row, bias=None, attn_drop=0.0, see
             _timed_wait(ctx, works[waited], "fwd", waited)
             waited += 1
         last = p == sh.stages - 1
+        # rows are finished in the last stage in which they have edges (stage_mask), so the bias goes to every stage
         res = be.gat_forward_staged(attn_row, ctx.AC, sh.fwd.ptr[p], sh.fwd.ind[p], ctx.slope, ctx.X, state, p == 0, last,
-                                    bias=bias if last else None, attn_drop=attn_drop, edge_mask=masks[p], neg=train,
-                                    save_stats=train)
+                                    bias=bias, attn_drop=attn_drop, edge_mask=masks[p], neg=train,
+                                    save_stats=train, stage_mask=sh.fwd.stage_mask, stage=p, outs=res)
     if train:
         return res
     return res[0], None, None, None, None
@@ -573,15 +601,17 @@ def halo_backward_sweep(ctx: HaloContext, attn_drop=0.0, seed=0):
     masks = _masks(ctx, sh.bwd, attn_drop, seed)
     state = be.gat_backward_state(sh.blk, ctx.h, ctx.f, ctx.X.device)
     waited = 0
-    grad_feat = grad_col = None
+    outs = None
     for p in range(sh.stages):
         while waited < sh.chunks and sh.chunk_stage(waited) <= p:
             _timed_wait(ctx, works[waited], "bwd", waited)
             waited += 1
         _, grad_feat, grad_col = be.gat_backward_cols_staged(
             None, sh.bwd.ptr[p], sh.bwd.ind[p], None, ctx.PK, ctx.X[:sh.blk], ctx.AC[:sh.blk], ctx.G, ctx.slope, state,
-            p == 0, p == sh.stages - 1, attn_drop=attn_drop, edge_mask=masks[p], row_grad=False)
-    return grad_feat, grad_col
+            p == 0, p == sh.stages - 1, attn_drop=attn_drop, edge_mask=masks[p], row_grad=False,
+            stage_mask=sh.bwd.stage_mask, stage=p, outs=outs)
+        outs = (grad_feat, grad_col)
+    return outs
 
 
 def _timed_wait(ctx, work, phase, chunk):

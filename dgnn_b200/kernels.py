@@ -11,6 +11,36 @@ from . import _C
 from ._C import _cuda_f32, _cuda_i32, _cuda_ptr, _p, _same_bits, _stream, _workspace, check, device_guard, lib
 
 
+# ------------------------------------------------------------- guard mode
+def guard_enabled() -> bool:
+    """DGNN_BOUNDS_CHECK=1: every wrapper validates the index arrays it is given (index pointers start at 0, do not
+    decrease and end at the entry count; ids lie inside the tensors they index) and raises before an operator kernel
+    is launched.  Each check synchronises: a switch for bringing a program up, not for production runs."""
+    import os
+    return os.environ.get("DGNN_BOUNDS_CHECK", "0") not in ("", "0")
+
+
+_GUARD_KINDS = {1: "the index pointer does not start at 0", 2: "the index pointer decreases",
+                3: "the index pointer does not end at the number of entries", 4: "an id lies outside the tensor it indexes"}
+
+
+def guard_check(what, ptr=None, nnz=None, index=None, limit=None):
+    """Validate an index pointer (`ptr` [n+1] against `nnz` entries) and / or an id array (`index` in [0, limit))."""
+    t = ptr if ptr is not None else index
+    dev = t.device
+    with device_guard(dev):
+        report = torch.tensor([0, 2**31 - 1, 0], dtype=torch.int32, device=dev)
+        if ptr is not None:
+            bits = 64 if ptr.dtype == torch.int64 else 32
+            check(lib().dgnn_check_ptr(ptr.numel() - 1, int(nnz), _p(ptr), bits, _p(report), _stream(dev)), "check_ptr")
+        if index is not None and index.numel():
+            check(lib().dgnn_check_index(index.numel(), _p(index), int(limit), _p(report), _stream(dev)), "check_index")
+        kind, pos, val = report.tolist()
+    if kind:
+        raise RuntimeError(f"dgnn_b200 guard: {what}: {_GUARD_KINDS.get(kind, kind)} (first at position {pos}, value {val}"
+                           + (f", limit {int(limit)}" if kind == 4 else "") + ")")
+
+
 def _dims3(t, name):
     if t.dim() != 3:
         raise RuntimeError(f"dgnn_b200: {name} must be [N,H,F], got shape {tuple(t.shape)}")
@@ -44,6 +74,8 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
         raise RuntimeError(f"dgnn_b200: attn_row must be [{n_rows},{h}], got {tuple(attn_row.shape)}")
     if attn_col.dim() != 2 or attn_col.shape[1] != h or attn_col.shape[0] != in_feat.shape[0]:
         raise RuntimeError("dgnn_b200: attn_col must be [n_src,H] with n_src = in_feat.shape[0]")
+    if guard_enabled():
+        guard_check("gat_forward", row_ptr, nnz, col_ind, in_feat.shape[0])
     if attn_drop > 0.0:
         if edge_mask is None:
             raise RuntimeError("dgnn_b200: attn_drop > 0 needs an edge_mask")
@@ -75,7 +107,7 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
                                                 _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
                                                 _p(edge_mask), _p(bias), _p(out), _p(edge_max), _p(edge_sum),
                                                 _p(out_neg), _p(a_neg), None,
-                                                1, 1, _p(ws), ws.numel(), _stream(dev)), "gat_forward(bias/neg)")
+                                                1, 1, None, 0, _p(ws), ws.numel(), _stream(dev)), "gat_forward(bias/neg)")
     if neg:
         return out, edge_max, edge_sum, out_neg, a_neg
     return out, edge_max, edge_sum
@@ -177,6 +209,12 @@ def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_fe
         raise RuntimeError("dgnn_b200: col_ptr length must be in_feat.shape[0] + 1")
     if grad_out.shape != (n_rows, h, f) or pack.shape != (n_rows, h, 4):
         raise RuntimeError("dgnn_b200: grad_out / pack must have one row per CSR row")
+    if guard_enabled():
+        guard_check("gat_backward_cols (CSC)", col_ptr, nnz, row_ind, n_rows)
+        if permute is not None:
+            guard_check("gat_backward_cols (permute)", index=permute, limit=nnz)
+        if row_ptr is not None:
+            guard_check("gat_backward_cols (CSR)", row_ptr, nnz)
     if attn_drop > 0.0:
         edge_mask = _cuda_f32(edge_mask, "edge_mask")
     else:
@@ -217,6 +255,9 @@ def gat_backward(negative_slope, attn_drop, row_ptr, col_ptr, row_ind, permute, 
         raise RuntimeError("dgnn_b200: gat_backward needs a square graph (row_ptr, col_ptr of length N+1)")
     if grad_out.shape != (n, h, f) or out.shape != (n, h, f):
         raise RuntimeError("dgnn_b200: grad_out / out must be [N,H,F]")
+    if guard_enabled():
+        guard_check("gat_backward (CSC)", col_ptr, nnz, row_ind, n)
+        guard_check("gat_backward (CSR, permute)", row_ptr, nnz, permute, nnz)
     if attn_drop > 0.0:
         edge_mask = _cuda_f32(edge_mask, "edge_mask")
     else:
@@ -453,6 +494,8 @@ def mhsddmm(row_ptr, col_ind, a, b):
         raise RuntimeError("dgnn_b200: mhsddmm operands must be [V,H,F] with V = len(rowptr) - 1 rows in `grad`")
     nnz = col_ind.numel()
     dev = b.device
+    if guard_enabled():
+        guard_check("mhsddmm", row_ptr, nnz, col_ind, b.shape[0])
     with device_guard(dev):
         out = torch.empty((nnz, h), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_mhsddmm_workspace_bytes(), dev)
@@ -471,6 +514,9 @@ def coo_sddmm(row_ind, col_ind, d1, d2):
         raise RuntimeError("dgnn_b200: coo_sddmm needs D1 [m,k], D2 [n,k] and two index arrays of equal length")
     nnz, k = row_ind.numel(), d1.shape[1]
     dev = d1.device
+    if guard_enabled():
+        guard_check("coo_sddmm (rows)", index=row_ind, limit=d1.shape[0])
+        guard_check("coo_sddmm (columns)", index=col_ind, limit=d2.shape[0])
     with device_guard(dev):
         out = torch.empty(nnz, dtype=torch.float32, device=dev)
         check(lib().dgnn_coo_sddmm(nnz, k, _p(row_ind), _p(col_ind), _p(d1), _p(d2), _p(out), _stream(dev)), "coo_sddmm")
@@ -485,6 +531,8 @@ def mhtranspose(permute, attention):
         raise RuntimeError("dgnn_b200: mhtranspose input must be [E,H]")
     nnz, h = permute.numel(), attention.shape[1]
     dev = attention.device
+    if guard_enabled():
+        guard_check("mhtranspose", index=permute, limit=attention.shape[0])
     with device_guard(dev):
         out = torch.empty((nnz, h), dtype=torch.float32, device=dev)
         check(lib().dgnn_mhtranspose(nnz, h, _p(permute), _p(attention), _p(out), _stream(dev)), "mhtranspose")
@@ -504,6 +552,8 @@ def gmm_forward(row_ptr, col_ind, node_feat, pseudo, mu, inv_sigma):
     dim = mu.shape[1]
     if mu.shape != (k, dim) or inv_sigma.shape != (k, dim) or pseudo.shape != (nnz, dim):
         raise RuntimeError("dgnn_b200: gmmconv needs mu, sigma [K,dim] and pseudo [E,dim]")
+    if guard_enabled():
+        guard_check("gmm_forward", row_ptr, nnz, col_ind, node_feat.shape[0])
     dev = node_feat.device
     with device_guard(dev):
         out = torch.empty((n_rows, k, f), dtype=torch.float32, device=dev)
@@ -556,6 +606,8 @@ def edgeconv_forward(k, src_ind, h_src, h_dst):
     m, f = h_src.shape
     if h_dst.shape != (m, f) or src_ind.numel() != m * int(k):
         raise RuntimeError("dgnn_b200: edgeconv needs h_src, h_dst [M,F] and src_ind [M*k]")
+    if guard_enabled():
+        guard_check("edgeconv_forward", index=src_ind, limit=m)
     dev = h_src.device
     with device_guard(dev):
         out = torch.empty((m, f), dtype=torch.float32, device=dev)
@@ -570,6 +622,8 @@ def edgeconv_backward(grad_out, max_idx):
     max_idx = _cuda_i32(max_idx, "max_idx")
     m, f = grad_out.shape
     dev = grad_out.device
+    if guard_enabled():
+        guard_check("edgeconv_backward", index=max_idx.reshape(-1), limit=m)
     with device_guard(dev):
         grad_src = torch.empty((m, f), dtype=torch.float32, device=dev)
         check(lib().dgnn_edgeconv_backward(m, f, _p(max_idx), _p(grad_out), _p(grad_src), _stream(dev)),
@@ -585,6 +639,8 @@ def csr2csc(row_ptr, col_ind, n_cols=None):
     n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
     n_cols = n_rows if n_cols is None else int(n_cols)
     dev = col_ind.device
+    if guard_enabled():
+        guard_check("csr2csc", row_ptr, nnz, col_ind, n_cols)
     with device_guard(dev):
         col_ptr = torch.empty(n_cols + 1, dtype=row_ptr.dtype, device=dev)
         row_ind = torch.empty(nnz, dtype=torch.int32, device=dev)
@@ -613,6 +669,9 @@ def coo_sort(dst, src, n_nodes):
         raise RuntimeError("dgnn_b200: coo_sort needs one source per destination")
     nnz = dst.numel()
     dev = dst.device
+    if guard_enabled():
+        guard_check("coo_sort (destinations)", index=dst, limit=n_nodes)
+        guard_check("coo_sort (sources)", index=src, limit=n_nodes)
     with device_guard(dev):
         d_out = torch.empty(nnz, dtype=torch.int32, device=dev)
         s_out = torch.empty(nnz, dtype=torch.int32, device=dev)
@@ -648,12 +707,15 @@ def gat_backward_state(n_cols, h, f, device):
 
 
 def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope, feat_blk, state, first, last, bias=None,
-                       attn_drop=0.0, edge_mask=None, neg=False, save_stats=True):
+                       attn_drop=0.0, edge_mask=None, neg=False, save_stats=True, stage_mask=None, stage=0, outs=None):
     """One stage of the forward over the edges whose source lies in one column block.
     Returns (out, edge_max, edge_sum[, out_neg, a_neg]) from the last stage, None before.  `bias` [H*F] is
-    added to the output by the last stage when given; `edge_mask` [nnz,H] (with attn_drop > 0) follows the
+    added to the output when a row is written out; `edge_mask` [nnz,H] (with attn_drop > 0) follows the
     order of this stage's col_ind; neg=True must be passed to every stage of a sweep that wants the
-    negative-side outputs (the carried state holds their accumulators)."""
+    negative-side outputs (the carried state holds their accumulators).
+    stage_mask [n_rows] uint8 (bit p = the row has edges in stage p) makes the stages sparse: a row is only
+    touched in its own stages and written out in its last one, so the outputs must exist from the first stage
+    on: the tuple is returned by every stage and has to be passed back in as `outs`."""
     attn_row = _cuda_f32(attn_row, "attn_row")
     attn_col_blk = _cuda_f32(attn_col_blk, "attn_col")
     feat_blk = _cuda_f32(feat_blk, "in_feat")
@@ -661,23 +723,33 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
     row_ptr, bits = _cuda_ptr(row_ptr, "row_ptr")
     _, h, f = _dims3(feat_blk, "in_feat")
     n_rows, nnz = row_ptr.numel() - 1, col_ind.numel()
+    if guard_enabled():
+        guard_check("gat_forward_staged", row_ptr, nnz, col_ind, min(feat_blk.shape[0], attn_col_blk.shape[0]))
     if attn_drop > 0.0:
         edge_mask = _cuda_f32(edge_mask, "edge_mask")
         if edge_mask.shape != (nnz, h):
             raise RuntimeError(f"dgnn_b200: edge_mask must be [{nnz},{h}]")
     else:
         edge_mask = None
+    if stage_mask is not None and not (stage_mask.is_cuda and stage_mask.dtype == torch.uint8 and stage_mask.numel() == n_rows
+                                       and stage_mask.is_contiguous()):
+        raise RuntimeError("dgnn_b200: stage_mask must be a contiguous uint8 CUDA tensor with one entry per row")
     dev = feat_blk.device
     with device_guard(dev):
         out = emax = esum = out_neg = a_neg = None
-        if last:
+        if outs is not None:
+            out, emax, esum, out_neg, a_neg = (tuple(outs) + (None, None))[:5]
+        elif last or stage_mask is not None:
             out = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
             if save_stats:
                 emax = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
                 esum = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
-        if neg:   # every stage gets the pointers: they select the kernel variant whose state carries the accumulators
-            out_neg = torch.empty((n_rows, h, f) if last else (1, h, f), dtype=torch.float32, device=dev)
-            a_neg = torch.empty((n_rows, h) if last else (1, h), dtype=torch.float32, device=dev)
+            if neg:
+                out_neg = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
+                a_neg = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
+        if neg and out_neg is None:   # every stage gets the pointers: they select the kernel variant whose state carries the accumulators
+            out_neg = torch.empty((1, h, f), dtype=torch.float32, device=dev)
+            a_neg = torch.empty((1, h), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f), dev)
         if bias is not None:
             bias = _cuda_f32(bias, "bias").reshape(h * f)
@@ -685,19 +757,21 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
                                             _p(attn_col_blk), _p(feat_blk), float(negative_slope), float(attn_drop),
                                             _p(edge_mask), _p(bias) if bias is not None else None,
                                             _p(out), _p(emax), _p(esum), _p(out_neg), _p(a_neg), _p(state),
-                                            int(bool(first)), int(bool(last)),
+                                            int(bool(first)), int(bool(last)), _p(stage_mask), int(stage),
                                             _p(ws), ws.numel(), _stream(dev)), "gat_forward_staged")
-    if not last:
+    if not last and stage_mask is None:
         return None
     return (out, emax, esum, out_neg, a_neg) if neg else (out, emax, esum)
 
 
 def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_feat, attn_col, grad_blk,
-                             negative_slope, state, first, last, attn_drop=0.0, edge_mask=None, row_grad=True):
+                             negative_slope, state, first, last, attn_drop=0.0, edge_mask=None, row_grad=True,
+                             stage_mask=None, stage=0, outs=None):
     """One stage of the backward column pass over the edges whose destination lies in one
     row block.  Returns (grad_attn_row of the block's rows or None, grad_feat or None, grad_attn_col or None).
     With row_grad=False (grad_attn_row comes from gat_rowstat_full) row_ptr and permute may be None and an
-    `edge_mask` [nnz,H] follows the order of this stage's row_ind."""
+    `edge_mask` [nnz,H] follows the order of this stage's row_ind.  stage_mask [n_cols] uint8 / stage / outs =
+    (grad_feat, grad_attn_col): sparse stages as in gat_forward_staged (every stage returns the outputs)."""
     in_feat = _cuda_f32(in_feat, "in_feat")
     attn_col = _cuda_f32(attn_col, "attn_col")
     grad_blk = _cuda_f32(grad_blk, "grad_out")
@@ -717,6 +791,10 @@ def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_fe
     if (grad_blk.shape != (n_rows, h, f) or pack_blk.shape != (n_rows, h, 4) or col_ptr.numel() - 1 != n_cols
             or (row_grad and row_ptr.numel() - 1 != n_rows)):
         raise RuntimeError("dgnn_b200: staged backward: block shapes do not match the sub-matrix")
+    if guard_enabled():
+        guard_check("gat_backward_cols_staged (CSC)", col_ptr, nnz, row_ind, n_rows)
+        if permute is not None:
+            guard_check("gat_backward_cols_staged (permute)", index=permute, limit=nnz)
     if attn_drop > 0.0:
         edge_mask = _cuda_f32(edge_mask, "edge_mask")
         if edge_mask.shape != (nnz, h):
@@ -726,7 +804,9 @@ def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_fe
     dev = in_feat.device
     with device_guard(dev):
         grad_feat = grad_col = None
-        if last:
+        if outs is not None:
+            grad_feat, grad_col = outs
+        elif last or stage_mask is not None:
             grad_feat = torch.empty((n_cols, h, f), dtype=torch.float32, device=dev)
             grad_col = torch.empty((n_cols, h), dtype=torch.float32, device=dev)
         grad_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if row_grad else None
@@ -735,6 +815,7 @@ def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_fe
                                                   _p(row_ind), _p(permute), _p(pack_blk), _p(edge_mask), _p(in_feat),
                                                   _p(attn_col), _p(grad_blk), float(negative_slope), float(attn_drop),
                                                   _p(grad_feat), _p(grad_row), _p(grad_col), _p(state),
-                                                  int(bool(first)), int(bool(last)), _p(ws), ws.numel(), _stream(dev)),
+                                                  int(bool(first)), int(bool(last)), _p(stage_mask), int(stage),
+                                                  _p(ws), ws.numel(), _stream(dev)),
               "gat_backward_cols_staged")
     return grad_row, grad_feat, grad_col

@@ -44,6 +44,15 @@ typedef enum dgnn_status {
 
 int dgnn_version(void);
 const char* dgnn_status_string(int status);
+/* Guard mode: validation of the index arrays a caller hands over, for use in front of the operators while a
+ * program is being brought up (the reference checks nothing: its asserts are compiled out, a bad index is an
+ * out-of-bounds access, dgNN/src/fused_gatconv/fused_gatconv.cpp:15-29).  report is a device int[3] that the
+ * caller sets to {0, INT_MAX, 0} beforehand: [0] = kind of the first defect noted (0 none; 1 ptr[0] != 0;
+ * 2 ptr decreases; 3 ptr[n] != nnz; 4 index outside [0, limit)), [1] = smallest position with a defect, [2] = the
+ * value found there.  Nothing but the checked arrays is read.  The Python wrappers run these checks on every
+ * call when DGNN_BOUNDS_CHECK=1 is set and raise before any operator kernel is launched. */
+int dgnn_check_ptr(int64_t n, int64_t nnz, const void* ptr, int idx_bits, int32_t* report, void* stream);
+int dgnn_check_index(int64_t n, const int32_t* idx, int64_t limit, int32_t* report, void* stream);
 /* edges per chunk used when rows longer than this are split across warps */
 int64_t dgnn_seg_chunk(void);
 
@@ -81,6 +90,11 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f,
  * negative side of the LeakyReLU: out_neg = sum_{e: leaky_e < 0} keep_e alpha_e/(1-p) in_feat[c_e],
  * a_neg = sum_{e: leaky_e < 0} alpha_e.  dgnn_gat_rowstat_full turns them into grad_attn_row, which
  * the reference obtains from a per-edge array (fused_backward_kernel, fused_gatconv_kernel.cu:931-957).
+ * stage_mask (NULL, or one byte per row; at most 8 stages) makes the stages sparse: bit p of stage_mask[r] says
+ * that row r has edges in stage `stage` = p.  A row then starts from an empty state in its first such stage, is
+ * normalised and written out in its last one, and is not touched -- no state read or written -- in any other
+ * stage; rows without edges in any stage are written by stage 0.  The output pointers must then be the same
+ * valid buffers in every stage.  Without a mask every row takes part in every stage (first / last mark the ends).
  * The staged form has no counterpart in the reference, which is single-GPU. */
 int dgnn_gat_fast_shape(int h, int f);   /* 1 when (h, f) uses the float4 layout: f = 4*2^k, h*f <= 1024 */
 size_t dgnn_gat_forward_state_bytes(int64_t n_rows, int h, int f);
@@ -91,6 +105,7 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f,
                             const float* bias, float* out, float* edge_max, float* edge_sum,
                             float* out_neg, float* a_neg,
                             float* state, int first, int last,
+                            const uint8_t* stage_mask, int stage,
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /* Row statistics for the backward pass: pack[r,h] = (attn_row, edge_max,
@@ -156,7 +171,8 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
  * edges of one row block (its CSC / CSR arrays, pack and grad_out of that block) and the
  * per-column accumulators (dgnn_gat_backward_state_bytes) are carried in `state`;
  * grad_feat / grad_attn_col are written by the last call, grad_attn_row (of the block's
- * rows, unless NULL) by every call.  first = last = 1 is dgnn_gat_backward_cols. */
+ * rows, unless NULL) by every call.  first = last = 1 is dgnn_gat_backward_cols.  stage_mask / stage: as for
+ * dgnn_gat_forward_staged, one byte per column. */
 size_t dgnn_gat_backward_state_bytes(int64_t n_cols, int h, int f);
 int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f,
                                   const void* row_ptr, const void* col_ptr, int idx_bits,
@@ -166,6 +182,7 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
                                   float negative_slope, float attn_drop,
                                   float* grad_feat, float* grad_attn_row, float* grad_attn_col,
                                   float* state, int first, int last,
+                                  const uint8_t* stage_mask, int stage,
                                   void* workspace, size_t workspace_bytes, void* stream);
 
 /* Whole backward on a square graph: replaces fused_gatconv.gat_backward

@@ -9,7 +9,9 @@ target architecture.  The modules need a GPU to run: on a GPU box the tests
 compare them with the oracle and with the new kernels, and
 tests/golden/make_golden.py records their outputs as fixtures.
 
-    python oracle/build_ref.py [/path/to/reference]
+    python oracle/build_ref.py /path/to/reference      (or DGNN_REFERENCE_ROOT=/path/to/reference)
+
+Without either, a checkout named `reference` beside this repository is used when it exists.
 """
 from __future__ import annotations
 
@@ -20,7 +22,7 @@ import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REF = os.environ.get("DGNN_REFERENCE_ROOT", "/root/reference")
+DEFAULT_REF = os.environ.get("DGNN_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 EXTENSIONS = {
     "fused_gatconv": ["dgNN/src/fused_gatconv/fused_gatconv.cpp", "dgNN/src/fused_gatconv/fused_gatconv_kernel.cu"],

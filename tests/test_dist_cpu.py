@@ -34,7 +34,8 @@ class OracleBackend:
 
     @staticmethod
     def gat_forward_staged(attn_row, attn_col_buf, row_ptr, col_ind, slope, feat_buf, state, first, last, bias=None,
-                           attn_drop=0.0, edge_mask=None, neg=False, save_stats=True):
+                           attn_drop=0.0, edge_mask=None, neg=False, save_stats=True, stage_mask=None, stage=0, outs=None):
+        # every row takes part in every stage here (the per-row stage mask only saves work on the GPU)
         n, h = attn_row.shape
         rows = orc.edge_rows(row_ptr)
         cols = col_ind.long()
@@ -87,7 +88,8 @@ class OracleBackend:
 
     @staticmethod
     def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_buf, in_feat, attn_col, grad_buf, slope,
-                                 state, first, last, attn_drop=0.0, edge_mask=None, row_grad=True):
+                                 state, first, last, attn_drop=0.0, edge_mask=None, row_grad=True, stage_mask=None, stage=0,
+                                 outs=None):
         assert not row_grad and row_ptr is None and permute is None
         cols = orc.edge_rows(col_ptr)                     # local column of every CSC entry
         rows = row_ind.long()                             # buffer row of its destination
@@ -213,6 +215,7 @@ def test_halo_shard_invariants(world, stages, relabel):
             for p in range(s.stages):
                 ptr, ind, eid = side.ptr[p].long(), side.ind[p].long(), side.edge_id[p].long()
                 assert ptr[0] == 0 and ptr[-1] == ind.numel() == eid.numel()
+                assert torch.equal(((side.stage_mask.long() >> p) & 1).bool(), (ptr[1:] - ptr[:-1]) > 0)   # bit p = has entries in stage p
                 seg = orc.edge_rows(ptr)
                 far = buf_orig[ind]                                    # original id of the far end of every entry
                 near = s.local_ids[seg]

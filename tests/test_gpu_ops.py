@@ -263,3 +263,40 @@ def test_knn_feeds_edgeconv_like_the_brute_force_graph(cuda):
     a = graph.knn_graph(x, 8).view(4, 256, 8).sort(dim=2).values
     b_ = synth.knn_src_ind(x, 8).view(4, 256, 8).sort(dim=2).values
     assert float((a == b_).float().mean()) > 0.999
+
+
+def test_guard_mode_validates_index_arrays(cuda, monkeypatch):
+    """DGNN_BOUNDS_CHECK=1: valid inputs pass through every wrapper, an id outside the tensor it indexes or a broken
+    index pointer raises before any operator kernel is launched (nothing is read out of bounds)."""
+    monkeypatch.setenv("DGNN_BOUNDS_CHECK", "1")
+    assert kernels.guard_enabled()
+    rp, ci = synth.random_graph(200, 5, seed=8)
+    n, h, f = rp.numel() - 1, 4, 8
+    g = torch.Generator().manual_seed(0)
+    ar, ac = torch.randn(n, h, generator=g).to(cuda), torch.randn(n, h, generator=g).to(cuda)
+    x, go = torch.randn(n, h, f, generator=g).to(cuda), torch.randn(n, h, f, generator=g).to(cuda)
+    rp_d, ci_d = rp.to(cuda), ci.to(cuda)
+    cp, ri, pm = kernels.csr2csc(rp_d, ci_d)
+    out, emax, esum = kernels.gat_forward(ar, ac, rp_d, ci_d, 0.2, x)
+    kernels.gat_backward(0.2, 0.0, rp_d, cp, ri, pm, emax, esum, None, x, out, ar, ac, go)
+    kernels.mhsddmm(rp_d, ci_d, x, x)
+    kernels.mhtranspose(pm, torch.randn(ci.numel(), h, device=cuda))
+    bad_col = ci_d.clone()
+    bad_col[17] = n                                            # one past the last source node
+    with pytest.raises(RuntimeError, match=r"guard: gat_forward: an id lies outside .*position 17, value 200"):
+        kernels.gat_forward(ar, ac, rp_d, bad_col, 0.2, x)
+    with pytest.raises(RuntimeError, match="guard: csr2csc"):
+        kernels.csr2csc(rp_d, bad_col)
+    bad_ptr = rp_d.clone()
+    bad_ptr[5] = bad_ptr[6] + 3                                # decreases between rows 5 and 6
+    with pytest.raises(RuntimeError, match="guard: mhsddmm: the index pointer decreases"):
+        kernels.mhsddmm(bad_ptr, ci_d, x, x)
+    short_ptr = rp_d.clone()
+    short_ptr[-1] -= 1
+    with pytest.raises(RuntimeError, match="guard: gat_forward: the index pointer"):
+        kernels.gat_forward(ar, ac, short_ptr, ci_d, 0.2, x)
+    with pytest.raises(RuntimeError, match="guard: edgeconv_forward"):
+        kernels.edgeconv_forward(2, torch.tensor([0, 1, 2, 3, -1, 0], dtype=torch.int32, device=cuda),
+                                 torch.zeros(3, 4, device=cuda), torch.zeros(3, 4, device=cuda))
+    monkeypatch.setenv("DGNN_BOUNDS_CHECK", "0")
+    assert not kernels.guard_enabled()
