@@ -326,11 +326,21 @@ def run_ours(args, rank, world, local):
         del rp, ci, owner_of
         torch.cuda.empty_cache()
 
+        timer.spans["step_forward"], timer.spans["step_loss_and_backward"], timer.spans["step_grad_allreduce"] = [], [], []
+
         def step(x_in):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timer.active else None
+            if ev: ev[0].record()
             out = layer(x_in)                                  # the same layer on this rank's node block
+            if ev: ev[1].record()
             loss = torch.dot(out.reshape(-1), cot.view(-1))
             loss.backward()
+            if ev: ev[2].record()
             layer.allreduce_grads()                            # replicated parameters: one flat all-reduce
+            if ev:
+                ev[3].record()
+                for k, name in enumerate(("step_forward", "step_loss_and_backward", "step_grad_allreduce")):
+                    timer.spans[name].append((ev[k], ev[k + 1]))
             return loss, out
 
         def sample_sum(out):
@@ -362,9 +372,11 @@ def run_ours(args, rank, world, local):
         hc.exposed_ms = []
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
+    host_t0 = time.perf_counter()
     for _ in range(args.steps):
         step(x)
         zero_grads()
+    host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps    # time the host needs to enqueue a step (no sync inside)
     e.record()
     sync_all()
     timer.active = False
@@ -469,6 +481,7 @@ def run_ours(args, rank, world, local):
                    "l2": "inputs (2.46 GB feature tensor per pass) exceed the 126 MB L2; no flush needed",
                    "csr2csc_ms": csr2csc_ms},
         "gpu_launches": timer.launches,
+        "host_enqueue_ms_per_step": host_ms,
         "clocks": clocks,
         "check": check,
     }

@@ -40,7 +40,8 @@ SIGNATURES = {
     "dgnn_gat_forward_staged": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
                                         c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_p, c_sz, c_p]),
     "dgnn_gat_rowstat_full": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_f, c_p, c_p,
-                                      c_p, c_p, c_p, c_sz, c_p]),
+                                      c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
+    "dgnn_gat_logits_forward_fan": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_gat_backward_cols_workspace_bytes": (c_sz, [c_i64, c_int, c_int, c_int]),
     "dgnn_gat_rowstat_bias_workspace_bytes": (c_sz, [c_int, c_int]),
     "dgnn_gat_rowstat_bias": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),

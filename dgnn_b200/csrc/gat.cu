@@ -316,12 +316,21 @@ k_gat_rowstat(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, c
 //    sum over the row's edges of alpha (g - S) (slope where the LeakyReLU is on its negative side) of the
 //    reference (fused_backward_kernel, fused_gatconv_kernel.cu:931-957) with no per-edge array;
 //  * grad_copy != NULL: grad is also written there (the buffer that the other ranks read on the sharded path).
+//  * fan.ptr != NULL: row r's grad and pack are also written to the send-buffer rows fan.pos[fan.ptr[r]..fan.ptr[r+1])
+//    (one per peer and chunk of the sharded layer that fetches the row), so no separate packing pass is needed.
+struct RowFan {
+  const int* ptr;
+  const int* pos;
+  float4* grad;   // [send rows, hf4]
+  float4* pack;   // [send rows, H]
+};
+
 template <int VPL>
 __global__ void __launch_bounds__(DGNN_THREADS)
 k_gat_rowstat_full(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_row, const float* edge_max,
                    const float* edge_sum, const float4* out, const float4* grad, const float4* bias,
                    const float4* out_neg, const float* a_neg, float one_minus_slope,
-                   float4* pack, float* grad_attn_row, float4* grad_copy, float4* part) {
+                   float4* pack, float* grad_attn_row, float4* grad_copy, float4* part, const RowFan fan) {
   extern __shared__ float4 rs_sm[];   // [DGNN_WARPS][hf4]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   LaneMap<VPL> lm;
@@ -337,6 +346,7 @@ k_gat_rowstat_full(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_r
   const i64 stride = (i64)gridDim.x * DGNN_WARPS;
   for (i64 r0 = (i64)blockIdx.x * DGNN_WARPS + warp; r0 < n_rows; r0 += stride * RS_ROWS) {
     float4 g[RS_ROWS][VPL], o[RS_ROWS][VPL], on[RS_ROWS][VPL];
+    float4 sc[RS_ROWS][VPL];   // per head (lead lanes): attn_row, edge_max, edge_sum, a_neg -- requested with the rows
 #pragma unroll
     for (int k = 0; k < RS_ROWS; ++k) {
       const i64 r = r0 + k * stride;
@@ -346,6 +356,11 @@ k_gat_rowstat_full(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_r
         g[k][v] = ok ? ld4(grad + r * hf4 + lm.q[v]) : zero4();
         o[k][v] = ok ? ld4(out + r * hf4 + lm.q[v]) : zero4();
         on[k][v] = (ok && out_neg) ? ld4(out_neg + r * hf4 + lm.q[v]) : zero4();
+        sc[k][v] = zero4();
+        if (lm.lead[v] && r < n_rows) {
+          const i64 i = r * H + lm.hd[v];
+          sc[k][v] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), __ldg(edge_sum + i), out_neg ? __ldg(a_neg + i) : 0.f);
+        }
       }
     }
 #pragma unroll
@@ -368,12 +383,27 @@ k_gat_rowstat_full(i64 n_rows, int H, int hf4, int f4_shift, const float* attn_r
       }
       head_reduce<VPL>(s, f4_shift);
       if (out_neg) head_reduce<VPL>(t, f4_shift);
+      float4 pk[VPL];
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
+        pk[v] = zero4();
         if (lm.lead[v]) {
           const i64 i = r * H + lm.hd[v];
-          pack[i] = make_float4(__ldg(attn_row + i), __ldg(edge_max + i), 1.f / __ldg(edge_sum + i), s[v]);
-          if (out_neg) grad_attn_row[i] = one_minus_slope * (s[v] * __ldg(a_neg + i) - t[v]);
+          pk[v] = make_float4(sc[k][v].x, sc[k][v].y, 1.f / sc[k][v].z, s[v]);
+          pack[i] = pk[v];
+          if (out_neg) grad_attn_row[i] = one_minus_slope * (s[v] * sc[k][v].w - t[v]);
+        }
+      }
+      if (fan.ptr) {
+        const int lo = __ldg(fan.ptr + r), hi = __ldg(fan.ptr + r + 1);
+        for (int j = lo; j < hi; ++j) {
+          const i64 p = __ldg(fan.pos + j);
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) {
+            if (!lm.act[v]) continue;
+            fan.grad[p * hf4 + lm.q[v]] = g[k][v];
+            if (lm.lead[v]) fan.pack[p * H + lm.hd[v]] = pk[v];
+          }
         }
       }
     }
@@ -909,9 +939,13 @@ size_t dgnn_gat_rowstat_bias_workspace_bytes(int h, int f) {
 int dgnn_gat_rowstat_full(int64_t n_rows, int h, int f, const float* attn_row, const float* edge_max,
                           const float* edge_sum, const float* out, const float* grad_out, const float* bias,
                           const float* out_neg, const float* a_neg, float negative_slope, float* pack,
-                          float* grad_attn_row, float* grad_bias, float* grad_copy, void* workspace,
+                          float* grad_attn_row, float* grad_bias, float* grad_copy, const int32_t* send_ptr,
+                          const int32_t* send_pos, float* send_grad, float* send_pack, void* workspace,
                           size_t workspace_bytes, void* stream) {
   if (n_rows < 0 || h <= 0 || f <= 0) return DGNN_ERR_SHAPE;
+  if (send_ptr && (!send_pos || !send_grad || !send_pack)) return DGNN_ERR_NULL;
+  if (send_ptr && (!aligned16(send_grad) || !aligned16(send_pack))) return DGNN_ERR_ALIGN;
+  const RowFan fan{send_ptr, send_pos, reinterpret_cast<float4*>(send_grad), reinterpret_cast<float4*>(send_pack)};
   if ((bias == nullptr) != (grad_bias == nullptr)) return DGNN_ERR_NULL;
   if ((out_neg == nullptr) != (a_neg == nullptr) || (out_neg == nullptr) != (grad_attn_row == nullptr)) return DGNN_ERR_NULL;
   if (n_rows > 0 && (!attn_row || !edge_max || !edge_sum || !out || !grad_out || !pack)) return DGNN_ERR_NULL;
@@ -940,7 +974,7 @@ int dgnn_gat_rowstat_full(int64_t n_rows, int h, int f, const float* attn_row, c
   const float oms = 1.f - negative_slope;
 #define ROWSTAT(V)                                                                                              \
   k_gat_rowstat_full<V><<<(unsigned)ctas, DGNN_THREADS, smem, s>>>(n_rows, h, fs.hf4, fs.f4_shift, attn_row,     \
-      edge_max, edge_sum, o4, g4, b4, n4, a_neg, oms, pk, grad_attn_row, gc4, part)
+      edge_max, edge_sum, o4, g4, b4, n4, a_neg, oms, pk, grad_attn_row, gc4, part, fan)
   switch (fs.vpl) {
     case 1: ROWSTAT(1); break;
     case 2: ROWSTAT(2); break;
@@ -958,7 +992,8 @@ int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f, const float* attn_row, c
                           float* pack, float* grad_bias, void* workspace, size_t workspace_bytes, void* stream) {
   if (!bias || !grad_bias) return DGNN_ERR_NULL;
   return dgnn_gat_rowstat_full(n_rows, h, f, attn_row, edge_max, edge_sum, out, grad_out, bias, nullptr, nullptr, 0.f,
-                               pack, nullptr, grad_bias, nullptr, workspace, workspace_bytes, stream);
+                               pack, nullptr, grad_bias, nullptr, nullptr, nullptr, nullptr, nullptr, workspace,
+                               workspace_bytes, stream);
 }
 
 size_t dgnn_gat_backward_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f) {

@@ -14,7 +14,7 @@
 
 // resident CTAs per SM asked of the compiler for the 2-vectors-per-lane kernels (it caps the registers per thread)
 #ifndef DGNN_SH_FWD_BLOCKS
-#define DGNN_SH_FWD_BLOCKS 5
+#define DGNN_SH_FWD_BLOCKS 6
 #endif
 #ifndef DGNN_SH_BWD_BLOCKS
 #define DGNN_SH_BWD_BLOCKS 5

@@ -35,10 +35,19 @@ inline Shape shape_of(int h, int f) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 
+// Fan-out of a rank's rows into its send buffer (sharded layer): row r is copied to the send-buffer rows
+// pos[ptr[r]] .. pos[ptr[r+1]-1], one per (peer, chunk) that fetches it.  ptr == NULL: no fan-out.
+struct LogitsFan {
+  const int* ptr;
+  const int* pos;
+  float4* feat;      // [send rows, hf4]
+  float* attn_col;   // [send rows, H]
+};
+
 template <int VPL>
 __global__ void __launch_bounds__(LG_THREADS)
 k_logits_fwd(i64 n, int H, int hf4, int f4_shift, const float4* feat, const float4* al, const float4* ar,
-             float* attn_row, float* attn_col) {
+             float* attn_row, float* attn_col, const LogitsFan fan) {
   const int lane = threadIdx.x & 31;
   LaneMap<VPL> lm;
   lm.init(lane, hf4, f4_shift);
@@ -76,6 +85,21 @@ k_logits_fwd(i64 n, int H, int hf4, int f4_shift, const float4* feat, const floa
         if (two) {
           attn_row[r2 * H + lm.hd[v]] = d[2][v];
           attn_col[r2 * H + lm.hd[v]] = d[3][v];
+        }
+      }
+    }
+    if (fan.ptr) {   // the row is in registers: write the copies its fetchers will read
+      for (int k = 0; k < (two ? 2 : 1); ++k) {
+        const i64 rr = k ? r2 : r;
+        const int lo = __ldg(fan.ptr + rr), hi = __ldg(fan.ptr + rr + 1);
+        for (int j = lo; j < hi; ++j) {
+          const i64 p = __ldg(fan.pos + j);
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) {
+            if (!lm.act[v]) continue;
+            fan.feat[p * hf4 + lm.q[v]] = k ? xb[v] : xa[v];
+            if (lm.lead[v]) fan.attn_col[p * H + lm.hd[v]] = k ? d[3][v] : d[1][v];
+          }
         }
       }
     }
@@ -150,9 +174,19 @@ extern "C" {
 
 int dgnn_gat_logits_forward(int64_t n, int h, int f, const float* feat, const float* attn_l, const float* attn_r,
                             float* attn_row, float* attn_col, void* stream) {
+  return dgnn_gat_logits_forward_fan(n, h, f, feat, attn_l, attn_r, attn_row, attn_col, nullptr, nullptr, nullptr, nullptr,
+                                     stream);
+}
+
+int dgnn_gat_logits_forward_fan(int64_t n, int h, int f, const float* feat, const float* attn_l, const float* attn_r,
+                                float* attn_row, float* attn_col, const int32_t* send_ptr, const int32_t* send_pos,
+                                float* send_feat, float* send_attn_col, void* stream) {
   if (n < 0 || h <= 0 || f <= 0) return DGNN_ERR_SHAPE;
   if (n == 0) return DGNN_OK;
   if (!feat || !attn_l || !attn_r || !attn_row || !attn_col) return DGNN_ERR_NULL;
+  if (send_ptr && (!send_pos || !send_feat || !send_attn_col)) return DGNN_ERR_NULL;
+  if (send_ptr && !aligned16(send_feat)) return DGNN_ERR_ALIGN;
+  const LogitsFan fan{send_ptr, send_pos, reinterpret_cast<float4*>(send_feat), send_attn_col};
   const Shape sp = shape_of(h, f);
   if (!sp.ok) return DGNN_ERR_SHAPE;   // callers fall back to separate tensor ops for other shapes
   if (!aligned16(feat) || !aligned16(attn_l) || !aligned16(attn_r)) return DGNN_ERR_ALIGN;
@@ -163,10 +197,10 @@ int dgnn_gat_logits_forward(int64_t n, int h, int f, const float* feat, const fl
   const float4* l = reinterpret_cast<const float4*>(attn_l);
   const float4* r = reinterpret_cast<const float4*>(attn_r);
   switch (sp.vpl) {
-    case 1: k_logits_fwd<1><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col); break;
-    case 2: k_logits_fwd<2><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col); break;
-    case 4: k_logits_fwd<4><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col); break;
-    default: k_logits_fwd<8><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col); break;
+    case 1: k_logits_fwd<1><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col, fan); break;
+    case 2: k_logits_fwd<2><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col, fan); break;
+    case 4: k_logits_fwd<4><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col, fan); break;
+    default: k_logits_fwd<8><<<grid, LG_THREADS, 0, s>>>(n, h, sp.hf4, sp.f4_shift, x, l, r, attn_row, attn_col, fan); break;
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;

@@ -208,10 +208,13 @@ class SendPlan:
     pack_idx: torch.Tensor      # [total_send] int32: rows of this rank's block in send-buffer order
     cap_send: int               # rows of the largest send buffer over all ranks
     recv: list                  # per chunk: [(owner, first halo row, rows, offset in the owner's send buffer)]
+    fan_ptr: torch.Tensor = None   # [blk+1] int32: the inverse of pack_idx -- own row r goes to the send-buffer rows
+    fan_pos: torch.Tensor = None   #   fan_pos[fan_ptr[r] : fan_ptr[r+1]] (kernels that produce the rows write them there)
 
 
-def build_send_plan(me, world, chunks, codes_all, chunk_off_all) -> SendPlan:
-    """codes_all[g] / chunk_off_all[g]: HaloSide.codes and .chunk_off of every rank g (what g fetches)."""
+def build_send_plan(me, world, chunks, codes_all, chunk_off_all, blk=None) -> SendPlan:
+    """codes_all[g] / chunk_off_all[g]: HaloSide.codes and .chunk_off of every rank g (what g fetches); blk = rows
+    per rank (for the inverse lists)."""
     dev = codes_all[me].device
     cnt = torch.zeros(world, chunks, world, dtype=torch.long)          # cnt[g][c][s]: rows g needs from s in chunk c
     mine = []                                                          # rows of my block, per (c, g)
@@ -239,7 +242,15 @@ def build_send_plan(me, world, chunks, codes_all, chunk_off_all) -> SendPlan:
                 lst.append((s_, row, k, int(send_off[s_, c, me])))
             row += k
         recv.append(lst)
-    return SendPlan(pack_idx, int(flat.sum(1).max()), recv)
+    plan = SendPlan(pack_idx, int(flat.sum(1).max()), recv)
+    if blk is not None:
+        rows = pack_idx.long()
+        order = torch.argsort(rows, stable=True)
+        ptr = torch.zeros(blk + 1, dtype=torch.long, device=dev)
+        if rows.numel():
+            torch.cumsum(torch.bincount(rows, minlength=blk), 0, out=ptr[1:])
+        plan.fan_ptr, plan.fan_pos = ptr.to(torch.int32).contiguous(), order.to(torch.int32).contiguous()
+    return plan
 
 
 class GatherTransport:
@@ -253,7 +264,10 @@ class GatherTransport:
     def empty(self, tag, rows, tail, device):
         return torch.empty((rows,) + tuple(tail), dtype=torch.float32, device=device)
 
-    def publish(self, side, bufs, tags):
+    def fan(self, side, bufs, tags):
+        return None
+
+    def publish(self, side, bufs, tags, packed=False):
         pass
 
     def start_pulls(self, side, bufs, tags):
@@ -314,10 +328,35 @@ class PeerTransport:
     def _plan(self, side):
         return self.plans[0] if side is self.shard.fwd else self.plans[1]
 
-    def publish(self, side, bufs, tags):
-        """Own rows are written: make them available to the peers (pack in dma mode), then the barrier."""
+    def fan(self, side, bufs, tags):
+        """For a kernel that produces the own rows of `bufs`: where each row goes in this rank's send buffers
+        (kernels._fan_args), so that it can write the copies itself; None when nothing is to be packed this way.
+        A caller that used it passes packed=True to publish()."""
+        sh = self.shard
+        if not (self.mode == "dma" and sh.world > 1 and bufs[0].is_cuda and len(bufs) == 2):
+            return None
+        plan = self._plan(side)
+        if plan.fan_ptr is None or plan.pack_idx.numel() == 0:
+            return None
+        sends = self._sends(plan, bufs, tags)
+        return dict(ptr=plan.fan_ptr, pos=plan.fan_pos, a=sends[0], b=sends[1])
+
+    def _sends(self, plan, bufs, tags):
+        out = []
+        for buf, tag in zip(bufs, tags):
+            if tag not in self.send:
+                self.send[tag] = self.shared_empty(tag + ".send", max(plan.cap_send, 1), buf.shape[1:], buf.device)
+            out.append(self.send[tag])
+        return out
+
+    def publish(self, side, bufs, tags, packed=False):
+        """Own rows are written: make them available to the peers (pack in dma mode unless the producing kernel
+        already did), then the barrier."""
         sh = self.shard
         cuda = bufs[0].is_cuda
+        if packed:
+            self.barrier()
+            return
         if cuda and self.overlap_publish and sh.world > 1:
             dev = bufs[0].device
             if self.stream is None:
@@ -336,11 +375,7 @@ class PeerTransport:
         sh = self.shard
         if self.mode == "dma" and sh.world > 1:
             plan = self._plan(side)
-            sends = []
-            for buf, tag in zip(bufs, tags):
-                if tag not in self.send:
-                    self.send[tag] = self.shared_empty(tag + ".send", max(plan.cap_send, 1), buf.shape[1:], buf.device)
-                sends.append(self.send[tag])
+            sends = self._sends(plan, bufs, tags)
             k = plan.pack_idx.numel()
             if k:
                 if bufs[0].is_cuda:
@@ -434,7 +469,7 @@ class LocalTransport(PeerTransport):
             t.caps = caps
             if mode == "dma":
                 t.plans = tuple(build_send_plan(s.rank, world, chunks, [getattr(x, d).codes for x in shards],
-                                                [getattr(x, d).chunk_off for x in shards]) for d in ("fwd", "bwd"))
+                                                [getattr(x, d).chunk_off for x in shards], s.blk) for d in ("fwd", "bwd"))
             out.append(t)
         return out
 
@@ -480,7 +515,8 @@ class SymmetricTransport(PeerTransport):
                 offs = torch.empty((world, chunks + 1), dtype=torch.int64, device=dev)
                 dist.all_gather_into_tensor(offs, torch.tensor(side.chunk_off, dtype=torch.int64, device=dev), group=self.group)
                 offs = offs.tolist()
-                plans.append(build_send_plan(shard.rank, world, chunks, [codes[g, :offs[g][-1]] for g in range(world)], offs))
+                plans.append(build_send_plan(shard.rank, world, chunks, [codes[g, :offs[g][-1]] for g in range(world)], offs,
+                                             shard.blk))
             self.plans = tuple(plans)
 
     def shared_empty(self, tag, rows, tail, device):
@@ -532,7 +568,9 @@ class HaloContext:
         self.PK = transport.empty(tag + ".pk", blk + cap_b, (heads, 4), dev)
         self.tags = (tag + ".x", tag + ".ac", tag + ".g", tag + ".pk")
         self.version = 0
-        self.exposed_ms = None        # set by measure_waits(): events around every wait for a halo chunk
+        self.fuse_pack = True         # the kernels that produce the own rows also write their copies into the send buffers
+        self.packed_fwd = self.packed_bwd = False
+        self.exposed_ms = None        # a list: _timed_wait appends event pairs around every wait for a halo chunk
 
     @property
     def h_own(self):
@@ -554,8 +592,12 @@ def halo_forward_prepare(ctx: HaloContext, h=None, attn_l=None, attn_r=None, att
     blk = ctx.shard.blk
     if h.data_ptr() != ctx.X.data_ptr():
         ctx.X[:blk].copy_(h)
+    ctx.packed_fwd = False
     if attn_l is not None:
-        attn_row, _ = ctx.backend.gat_logits_forward(ctx.X[:blk], attn_l, attn_r, out_col=ctx.AC[:blk])
+        fan = ctx.transport.fan(ctx.shard.fwd, [ctx.X, ctx.AC], ctx.tags[0:2]) if ctx.fuse_pack else None
+        kw = {"fan": fan} if fan is not None else {}
+        attn_row, _ = ctx.backend.gat_logits_forward(ctx.X[:blk], attn_l, attn_r, out_col=ctx.AC[:blk], **kw)
+        ctx.packed_fwd = fan is not None
     else:
         ctx.AC[:blk].copy_(attn_col)
     ctx.version += 1
@@ -587,9 +629,12 @@ def halo_forward_sweep(ctx: HaloContext, attn_row, bias=None, attn_drop=0.0, see
 def halo_backward_prepare(ctx: HaloContext, attn_row, edge_max, edge_sum, out, out_neg, a_neg, grad_out, bias=None):
     """Row statistics of the own rows into the backward buffers; returns (grad_attn_row, grad_bias)."""
     blk = ctx.shard.blk
+    fan = ctx.transport.fan(ctx.shard.bwd, [ctx.G, ctx.PK], ctx.tags[2:4]) if ctx.fuse_pack else None
+    kw = {"fan": fan} if fan is not None else {}
     _, grad_row, grad_bias = ctx.backend.gat_rowstat_full(attn_row, edge_max, edge_sum, out, grad_out, ctx.slope, bias=bias,
                                                           out_neg=out_neg, a_neg=a_neg, pack=ctx.PK[:blk],
-                                                          grad_copy=ctx.G[:blk])
+                                                          grad_copy=ctx.G[:blk], **kw)
+    ctx.packed_bwd = fan is not None
     return grad_row, grad_bias
 
 
@@ -637,7 +682,7 @@ class HaloGATFunction(torch.autograd.Function):
             attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_l=b, attn_r=c)
         else:
             attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_row=b.contiguous(), attn_col=c.contiguous())
-        hc.transport.publish(hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2])
+        hc.transport.publish(hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2], packed=hc.packed_fwd)
         out, edge_max, edge_sum, out_neg, a_neg = halo_forward_sweep(hc, attn_row, bias, attn_drop, seed, train=True)
         ctx.save_for_backward(attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c,
                               bias if bias is not None else out.new_empty(0))
@@ -653,7 +698,7 @@ class HaloGATFunction(torch.autograd.Function):
         attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c, bias = ctx.saved_tensors
         grad_row, grad_bias = halo_backward_prepare(hc, attn_row, edge_max, edge_sum, out, out_neg, a_neg,
                                                     grad_out.contiguous(), bias if ctx.has_bias else None)
-        hc.transport.publish(hc.shard.bwd, [hc.G, hc.PK], hc.tags[2:4])
+        hc.transport.publish(hc.shard.bwd, [hc.G, hc.PK], hc.tags[2:4], packed=hc.packed_bwd)
         grad_feat, grad_col = halo_backward_sweep(hc, ctx.attn_drop, ctx.seed)
         if grad_bias is not None:
             grad_bias = grad_bias.view_as(bias)
@@ -729,7 +774,7 @@ class ShardedGATConv(torch.nn.Module):
         else:
             with torch.no_grad():
                 attn_row = halo_forward_prepare(hc, h=h.contiguous(), attn_l=self.attn_l, attn_r=self.attn_r)
-                hc.transport.publish(hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2])
+                hc.transport.publish(hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2], packed=hc.packed_fwd)
                 rst = halo_forward_sweep(hc, attn_row, self.bias if fuse_bias else None, train=False)[0]
         if self.res_fc is not None:
             rst = rst + self.res_fc(h).view(-1, heads, width)       # as in the reference: applied to the projected features

@@ -113,12 +113,27 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
     return out, edge_max, edge_sum
 
 
+def _fan_args(fan, n_rows):
+    """(send_ptr, send_pos, send_a, send_b) of a fan-out, or four Nones.  fan = dict(ptr [n_rows+1] int32, pos int32,
+    a = send buffer of the wide tensor, b = send buffer of the narrow one)."""
+    if fan is None:
+        return None, None, None, None
+    ptr, pos = _cuda_i32(fan["ptr"], "fan ptr"), _cuda_i32(fan["pos"], "fan pos")
+    if ptr.numel() != n_rows + 1:
+        raise RuntimeError("dgnn_b200: the fan-out pointer must have one entry per row plus one")
+    for t in (fan["a"], fan["b"]):
+        if not (t.is_cuda and t.is_contiguous() and t.dtype == torch.float32):
+            raise RuntimeError("dgnn_b200: send buffers must be contiguous float32 CUDA tensors")
+    return ptr, pos, fan["a"], fan["b"]
+
+
 def gat_rowstat_full(attn_row, edge_max, edge_sum, out, grad_out, negative_slope, bias=None, out_neg=None,
-                     a_neg=None, pack=None, grad_copy=None):
+                     a_neg=None, pack=None, grad_copy=None, fan=None):
     """One pass over the destination rows for the backward: returns (pack [N,H,4], grad_attn_row [N,H]
     or None, grad_bias [H*F] or None).  grad_attn_row needs out_neg / a_neg of gat_forward(neg=True);
     grad_bias needs the bias that the forward added to `out`.  `pack` and `grad_copy` (a copy of
-    grad_out) are written into the given tensors when passed (buffers that other ranks read)."""
+    grad_out) are written into the given tensors when passed; `fan` (see _fan_args) additionally writes every
+    row's grad_out and pack to its places in the send buffers that other ranks read."""
     out = _cuda_f32(out, "out")
     grad_out = _cuda_f32(grad_out, "grad_out")
     n, h, f = _dims3(out, "out")
@@ -141,10 +156,12 @@ def gat_rowstat_full(attn_row, edge_max, edge_sum, out, grad_out, negative_slope
             out_neg = _cuda_f32(out_neg, "out_neg")
             a_neg = _cuda_f32(a_neg, "a_neg")
             grad_row = torch.empty((n, h), dtype=torch.float32, device=dev)
+        f_ptr, f_pos, f_a, f_b = _fan_args(fan, n)
         check(lib().dgnn_gat_rowstat_full(n, h, f, _p(_cuda_f32(attn_row, "attn_row")), _p(_cuda_f32(edge_max, "edge_max")),
                                           _p(_cuda_f32(edge_sum, "edge_sum")), _p(out), _p(grad_out), _p(bias),
                                           _p(out_neg), _p(a_neg), float(negative_slope), _p(pack), _p(grad_row),
-                                          _p(grad_bias), _p(grad_copy), _p(ws), ws.numel() if ws is not None else 0,
+                                          _p(grad_bias), _p(grad_copy), _p(f_ptr), _p(f_pos), _p(f_a), _p(f_b),
+                                          _p(ws), ws.numel() if ws is not None else 0,
                                           _stream(dev)), "gat_rowstat_full")
     return pack, grad_row, grad_bias
 
@@ -282,9 +299,10 @@ def logits_supported(h, f):
     return f % 4 == 0 and f4 > 0 and (f4 & (f4 - 1)) == 0 and h * f <= 1024
 
 
-def gat_logits_forward(feat, attn_l, attn_r, out_row=None, out_col=None):
+def gat_logits_forward(feat, attn_l, attn_r, out_row=None, out_col=None, fan=None):
     """attn_row, attn_col [N,H] from feat [N,H,F] and the attention vectors [.., H, F]; written into
-    out_row / out_col when given (contiguous float32 [N,H] on the same device)."""
+    out_row / out_col when given (contiguous float32 [N,H] on the same device).  `fan` (see _fan_args) also
+    writes every row of feat and attn_col to its places in the send buffers that other ranks read."""
     feat = _cuda_f32(feat, "feat")
     n, h, f = _dims3(feat, "feat")
     attn_l = _cuda_f32(attn_l, "attn_l").reshape(h, f)
@@ -296,8 +314,9 @@ def gat_logits_forward(feat, attn_l, attn_r, out_row=None, out_col=None):
     with device_guard(dev):
         attn_row = torch.empty((n, h), dtype=torch.float32, device=dev) if out_row is None else out_row
         attn_col = torch.empty((n, h), dtype=torch.float32, device=dev) if out_col is None else out_col
-        check(lib().dgnn_gat_logits_forward(n, h, f, _p(feat), _p(attn_l), _p(attn_r), _p(attn_row), _p(attn_col),
-                                            _stream(dev)), "gat_logits_forward")
+        f_ptr, f_pos, f_a, f_b = _fan_args(fan, n)
+        check(lib().dgnn_gat_logits_forward_fan(n, h, f, _p(feat), _p(attn_l), _p(attn_r), _p(attn_row), _p(attn_col),
+                                                _p(f_ptr), _p(f_pos), _p(f_a), _p(f_b), _stream(dev)), "gat_logits_forward")
     return attn_row, attn_col
 
 

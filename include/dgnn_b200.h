@@ -133,13 +133,17 @@ int dgnn_gat_rowstat_bias(int64_t n_rows, int h, int f,
  * equal to the reference's sum over the row's edges of d_e (fused_gatconv_kernel.cu:931-957) without
  * the per-edge array, its scattered write and its row reduction; grad_copy (NULL or [n_rows,h,f])
  * receives a copy of grad_out (on the sharded path: the buffer that other ranks read).  bias/grad_bias,
- * out_neg/a_neg/grad_attn_row are each all NULL or all given.  Float4 layout only.  The workspace
+ * out_neg/a_neg/grad_attn_row are each all NULL or all given.  send_ptr [n_rows+1] / send_pos (NULL, or both
+ * given with send_grad [send rows,h,f] and send_pack [send rows,h,4]) fan row r's grad_out and pack out to the
+ * send-buffer rows send_pos[send_ptr[r] .. send_ptr[r+1]) -- one per peer and chunk of the sharded layer that
+ * fetches the row -- so that no separate packing pass is needed.  Float4 layout only.  The workspace
  * (dgnn_gat_rowstat_bias_workspace_bytes) is needed only with a bias. */
 int dgnn_gat_rowstat_full(int64_t n_rows, int h, int f,
                           const float* attn_row, const float* edge_max, const float* edge_sum,
                           const float* out, const float* grad_out, const float* bias,
                           const float* out_neg, const float* a_neg, float negative_slope,
                           float* pack, float* grad_attn_row, float* grad_bias, float* grad_copy,
+                          const int32_t* send_ptr, const int32_t* send_pos, float* send_grad, float* send_pack,
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /* Column pass of the backward over the CSC form of an [n_rows x n_cols] block:
@@ -207,6 +211,13 @@ int dgnn_gat_backward(int64_t n, int64_t nnz, int h, int f,
 int dgnn_gat_logits_forward(int64_t n, int h, int f, const float* feat,
                             const float* attn_l, const float* attn_r,
                             float* attn_row, float* attn_col, void* stream);
+/* The same with a fan-out (see dgnn_gat_rowstat_full): feat[r] and attn_col[r] are also written to the
+ * send-buffer rows send_pos[send_ptr[r] .. send_ptr[r+1]) of send_feat [send rows,h,f] / send_attn_col [send rows,h]. */
+int dgnn_gat_logits_forward_fan(int64_t n, int h, int f, const float* feat,
+                                const float* attn_l, const float* attn_r,
+                                float* attn_row, float* attn_col,
+                                const int32_t* send_ptr, const int32_t* send_pos,
+                                float* send_feat, float* send_attn_col, void* stream);
 size_t dgnn_gat_logits_backward_workspace_bytes(int h, int f);
 int dgnn_gat_logits_backward(int64_t n, int h, int f, const float* feat,
                              const float* attn_l, const float* attn_r,
