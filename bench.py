@@ -54,9 +54,16 @@ def parse():
     ap.add_argument("--pull-ctas", type=int, default=48, help="grid bound of the halo fetch kernel in pull mode (0: unbounded)")
     ap.add_argument("--overlap-publish", type=int, default=0,
                     help="1: packing of the send buffers and the barrier run on the side stream beside the first sweep")
+    ap.add_argument("--l2-hot-mb", type=float, default=None,
+                    help="megabytes of the most referenced gathered rows the sweeps keep in the L2 (sets DGNN_L2_HOT_MB; 0: off)")
+    ap.add_argument("--l2-set-aside-mb", type=float, default=None,
+                    help="set aside this much of the L2 for lines loaded with the evict_last priority")
     ap.add_argument("--gather-fallback", action="store_true",
                     help="halo rows through all-gathers instead of peer loads from symmetric memory")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.l2_hot_mb is not None:
+        os.environ["DGNN_L2_HOT_MB"] = str(args.l2_hot_mb)
+    return args
 
 
 def algorithmic_bytes(n, e, h, f, ptr_bytes):
@@ -165,6 +172,7 @@ class PhaseTimer:
                                     ("gat_forward_staged", "fwd", 3),
                                     ("gat_backward_cols_staged", "bwd_cols", 3),
                                     ("halo_pull", "halo_pull", 1),
+                                    ("hot_rows", "hot_rows", 3),            # histogram, threshold, bit words
                                     ("project_forward", "project", 2),     # weight split, projection
                                     ("project_wgrad", "project_wgrad", 2),  # partial products, fixed-order sum
                                     ("gat_logits_forward", "logits_fwd", 1),
@@ -276,6 +284,9 @@ def run_ours(args, rank, world, local):
     W, al, ar_ = make_params(dev)
     timer = PhaseTimer()
     timer.wrap(kernels)
+    if args.l2_set_aside_mb is not None:
+        got = kernels.l2_set_aside(int(args.l2_set_aside_mb * 2**20), dev)
+        sys.stderr.write(f"L2 set aside for evict_last lines: {got / 2**20:.1f} MB\n")
 
     # csr2csc is part of the preparation of the backward pass: timed on its own
     torch.cuda.synchronize()
@@ -479,7 +490,8 @@ def run_ours(args, rank, world, local):
         "config": {"workload": f"GATConv layer fwd+bwd, R-MAT {n} nodes / {nnz} edges (a=0.57,b=c=0.19), in={IN}, {H} heads x {F}, "
                                f"int64 row_ptr" + sharded,
                    "l2": "inputs (2.46 GB feature tensor per pass) exceed the 126 MB L2; no flush needed",
-                   "csr2csc_ms": csr2csc_ms},
+                   "csr2csc_ms": csr2csc_ms,
+                   "l2_hot_mb": kernels.l2_hot_budget_bytes() / 2**20 if world == 1 else 0.0},
         "gpu_launches": timer.launches,
         "host_enqueue_ms_per_step": host_ms,
         "clocks": clocks,

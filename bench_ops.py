@@ -4,7 +4,7 @@ line per measurement: time, algorithmic bytes, achieved GB/s and the fraction of
 the measured HBM copy peak.  bench.py stays the headline benchmark; this script
 covers the remaining operators.
 
-    python bench_ops.py [--suite small|edgeconv|micro|project|all] [--iters 20]
+    python bench_ops.py [--suite small|edgeconv|micro|project|gather|all] [--iters 20]
 
 Timing: CUDA events around each call on the launching stream, 3 warm-up calls,
 an L2 flush (256 MB write) before every timed call of the small configurations.
@@ -216,6 +216,38 @@ def suite_micro(iters, edges, degrees, heads, cap_gb):
         torch.cuda.empty_cache()
 
 
+def suite_gather(iters, nodes, edges):
+    """What bounds the fused forward sweep at the headline shape (8 heads x 32, R-MAT): the same kernel on the same
+    graph with the source ids folded into a window of W rows, so that every gathered row comes out of the L2
+    (W x 1 KB <= 32 MB) -- the time that is left is the L2 -> SM delivery and the arithmetic, not HBM -- and with
+    the most referenced rows held in the L2 (hot rows + set-aside), which cuts DRAM reads but not the row bytes
+    that cross the L2 -> SM path."""
+    dev = torch.device("cuda")
+    h, f = 8, 32
+    rp, ci = synth.rmat_graph(nodes, edges, seed=4, device=dev, ptr_dtype=torch.int64)
+    x = torch.randn(nodes, h, f, device=dev)
+    ar, ac = torch.randn(nodes, h, device=dev), torch.randn(nodes, h, device=dev)
+    fb, _ = gat_bytes(nodes, edges, h, f, 8)
+    cfg0 = f"R-MAT {nodes} nodes / {edges} edges, {h} heads x {f}, forward with negative-side outputs"
+    it = max(3, iters // 2)
+    report("gat_forward", cfg0 + ", sources as generated", timed(lambda: kernels.gat_forward(ar, ac, rp, ci, 0.2, x, neg=True), it, False),
+           fb, gathered_row_bytes=4 * edges * h * f)
+    cp, _, _ = kernels.csr2csc(rp, ci)
+    hot = kernels.hot_rows(cp, 64 * 2**20 // (4 * h * (f + 1)))
+    aside = kernels.l2_set_aside(80 * 2**20)
+    report("gat_forward", cfg0 + f", 64 MB of the most referenced source rows loaded evict_last, {aside / 2**20:.0f} MB of L2 set aside",
+           timed(lambda: kernels.gat_forward(ar, ac, rp, ci, 0.2, x, neg=True, hot=hot), it, False), fb,
+           gathered_row_bytes=4 * edges * h * f)
+    kernels.l2_set_aside(0)
+    del cp, hot
+    for w in (8192, 32768):
+        folded = ci % w
+        report("gat_forward", cfg0 + f", source ids folded into {w} rows ({w * h * f * 4 / 2**20:.0f} MB: every gather is an L2 hit)",
+               timed(lambda: kernels.gat_forward(ar, ac, rp, folded, 0.2, x, neg=True), it, False), fb,
+               gathered_row_bytes=4 * edges * h * f)
+        del folded
+
+
 def suite_project(iters, rows):
     """The dense node projection of the bench configuration (in=100 -> 8 x 32) on the tensor cores, forward and
     weight gradient, beside the fp32 library GEMM (TF32 off) that torch.matmul runs for the same product."""
@@ -240,7 +272,7 @@ def suite_project(iters, rows):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--suite", default="all", choices=["small", "edgeconv", "micro", "project", "all"])
+    ap.add_argument("--suite", default="all", choices=["small", "edgeconv", "micro", "project", "gather", "all"])
     ap.add_argument("--project-rows", type=int, default=2_400_000)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--micro-edges", type=int, default=256_000_000)
@@ -256,6 +288,8 @@ def main():
         suite_edgeconv(args.iters)
     if args.suite in ("project", "all"):
         suite_project(args.iters, args.project_rows)
+    if args.suite in ("gather", "all"):
+        suite_gather(args.iters, 2_400_000, 120_000_000)
     if args.suite in ("micro", "all"):
         suite_micro(args.iters, args.micro_edges, [int(d) for d in args.micro_degrees.split(",")],
                     [int(h) for h in args.micro_heads.split(",")], args.cap_gb)

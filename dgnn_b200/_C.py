@@ -38,7 +38,7 @@ SIGNATURES = {
     "dgnn_gat_forward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
     "dgnn_gat_fast_shape": (c_int, [c_int, c_int]),
     "dgnn_gat_forward_staged": (c_int, [c_i64, c_i64, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p,
-                                        c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_p, c_sz, c_p]),
+                                        c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_rowstat_full": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_f, c_p, c_p,
                                       c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_logits_forward_fan": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p]),
@@ -47,8 +47,11 @@ SIGNATURES = {
     "dgnn_gat_rowstat_bias": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_backward_state_bytes": (c_sz, [c_i64, c_int, c_int]),
     "dgnn_gat_backward_cols_staged": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p,
-                                              c_p, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_p, c_sz,
+                                              c_p, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_p, c_p, c_sz,
                                               c_p]),
+    "dgnn_hot_rows_workspace_bytes": (c_sz, []),
+    "dgnn_l2_set_aside": (c_i64, [c_i64]),
+    "dgnn_hot_rows": (c_int, [c_i64, c_p, c_int, c_i64, c_p, c_p, c_sz, c_p]),
     "dgnn_gat_rowstat": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_gat_backward_workspace_bytes": (c_sz, [c_i64, c_i64, c_i64, c_int, c_int]),
     "dgnn_gat_backward_cols": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_p, c_p, c_int, c_p, c_p, c_p, c_p,

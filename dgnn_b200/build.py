@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdgnn_b200.so")
-SOURCES = ["gat.cu", "logits.cu", "sddmm_gmm.cu", "edgeconv.cu", "convert.cu", "project.cu", "halo.cu", "knn.cu", "misc.cu"]
+SOURCES = ["gat.cu", "logits.cu", "sddmm_gmm.cu", "edgeconv.cu", "convert.cu", "project.cu", "halo.cu", "knn.cu", "hot.cu", "misc.cu"]
 import glob
 HEADERS = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + [os.path.join(HERE, "..", "include", "dgnn_b200.h")]
 NVCC_FLAGS = [

@@ -43,6 +43,51 @@ __device__ __forceinline__ i64 find_row(const void* indptr, int bits, i64 n_rows
 }
 
 __device__ __forceinline__ float4 ld4(const float4* p) { return __ldg(p); }
+// Read-only load whose line is the last to leave the L2: for the rows of a gathered tensor that many edges
+// reference (the "hot" rows, see dgnn_hot_rows).  A feature tensor of gigabytes streams through the 126 MB L2;
+// with plain loads the often-referenced rows are evicted by rows that are read once.
+__device__ __forceinline__ unsigned long long l2_keep_policy() {
+  unsigned long long pol;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ float4 ld4_keep(const float4* p, unsigned long long pol) {
+  float4 v;
+  asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+      : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(pol));
+  return v;
+}
+__device__ __forceinline__ float ld1_keep(const float* p, unsigned long long pol) {
+  float v;
+  asm("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
+  return v;
+}
+#ifndef DGNN_STREAM_STORES
+#define DGNN_STREAM_STORES 1
+#endif
+#ifndef DGNN_STREAM_INDEX
+#define DGNN_STREAM_INDEX 1
+#endif
+// store of a result that this kernel does not read again: first in line to leave the L2
+__device__ __forceinline__ void st4_stream(float4* p, const float4& v) {
+#if DGNN_STREAM_STORES
+  __stcs(p, v);
+#else
+  *p = v;
+#endif
+}
+// an index array entry that is read once
+__device__ __forceinline__ int ld_index(const int* p) {
+#if DGNN_STREAM_INDEX
+  return __ldcs(p);
+#else
+  return __ldg(p);
+#endif
+}
+// the hot flag of a gathered row travels in the sign bit of its (non-negative int32) index
+__device__ __forceinline__ int dgnn_tag_hot(const unsigned* hot, int idx) {
+  return hot ? (idx | (int)(((__ldg(hot + (idx >> 5)) >> (idx & 31)) & 1u) << 31)) : idx;
+}
 __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
 __device__ __forceinline__ void fma4(float4& acc, float w, const float4& x) {
   acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);

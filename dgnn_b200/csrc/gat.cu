@@ -48,6 +48,7 @@ struct GatFwdOp {
   static constexpr bool STAGED = true;
   const unsigned char* stage_mask;   // per row: bit p set = the row has entries in stage p (NULL: every row in every stage)
   int stage;
+  const unsigned* hot;   // accepted for symmetry with the same-head operators; this layout loads every row plainly
   const float4* bias;   // optional [H*F] added to the normalised output (layer epilogue)
   // NEG: the share of the result that comes from edges on the negative side of the LeakyReLU
   float4* out_neg;      // [n_rows, H*F], normalised like out (no bias)
@@ -468,6 +469,7 @@ struct GatBwdOp {
   static constexpr bool STAGED = true;
   const unsigned char* stage_mask;   // per row: bit p set = the row has entries in stage p (NULL: every row in every stage)
   int stage;
+  const unsigned* hot;   // accepted for symmetry with the same-head operators; this layout loads every row plainly
 
   struct State {
     LaneMap<VPL, LPR> lm;
@@ -728,7 +730,7 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
                   const int* col_ind, const float* attn_row, const float* attn_col, const float* in_feat,
                   float slope, float drop, const float* mask, float* out, float* edge_max, float* edge_sum,
                   void* ws, float* state, int first, int last, const float* bias, float* out_neg, float* a_neg,
-                  const unsigned char* stage_mask, int stage, cudaStream_t s) {
+                  const unsigned char* stage_mask, int stage, const unsigned* hot, cudaStream_t s) {
   Op op;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -742,6 +744,7 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
   op.stage_mask = stage_mask; op.stage = stage;
   op.bias = reinterpret_cast<const float4*>(bias);
   op.out_neg = reinterpret_cast<float4*>(out_neg); op.a_neg = a_neg;
+  op.hot = hot;
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
 }
 
@@ -749,10 +752,16 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
 // layout (gat_sh.cuh); everything else the plain one.
 inline bool same_head_layout(const FastShape& fs) { return fs.vpl > 1 && (1 << fs.f4_shift) >= fs.vpl; }
 
+// use_hot selects the kernel variant with the second (evict_last) load path; it exists without a dropout mask only
 template <int VPL, bool MASK, bool FULL, int LPR, bool NEG, class... A>
-int launch_fwd(const FastShape& fs, A... a) {
+int launch_fwd(bool use_hot, const FastShape& fs, A... a) {
   if constexpr (VPL > 1) {
-    if (same_head_layout(fs)) return launch_fwd_op<GatFwdOpSH<VPL, MASK, FULL, NEG>>(fs, a...);
+    if (same_head_layout(fs)) {
+      if constexpr (!MASK && NEG) {
+        if (use_hot) return launch_fwd_op<GatFwdOpSH<VPL, MASK, FULL, NEG, true>>(fs, a...);
+      }
+      return launch_fwd_op<GatFwdOpSH<VPL, MASK, FULL, NEG>>(fs, a...);
+    }
   }
   return launch_fwd_op<GatFwdOp<VPL, MASK, FULL, LPR, NEG>>(fs, a...);
 }
@@ -762,7 +771,8 @@ int launch_bwd_op(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const 
                   const int* row_ind, const int* permute, const float* pack, const float* mask,
                   const float* in_feat, const float* attn_col, const float* grad_out, float slope, float drop,
                   float* grad_feat, float* grad_attn_col, float* grad_edge, float* ws, unsigned long long* counter,
-                  float* state, int first, int last, const unsigned char* stage_mask, int stage, cudaStream_t s) {
+                  float* state, int first, int last, const unsigned char* stage_mask, int stage, const unsigned* hot,
+                  cudaStream_t s) {
   Op op;
   op.n_rows = n_cols; op.nnz = nnz; op.indptr = col_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift;
@@ -774,13 +784,19 @@ int launch_bwd_op(const FastShape& fs, i64 n_cols, i64 nnz, int h, int f, const 
   op.grad_edge = grad_edge; op.ws = ws; op.slot_stride = bwd_slot_stride(h, f);
   op.state = state; op.first = first; op.last = last; op.skip_empty = (!first && !last && !stage_mask) ? 1 : 0;
   op.stage_mask = stage_mask; op.stage = stage;
+  op.hot = hot;
   return dgnn_launch_trio(op, counter, s);
 }
 
 template <int VPL, bool MASK, bool FULL, int LPR, bool EDGE, class... A>
-int launch_bwd(const FastShape& fs, A... a) {
+int launch_bwd(bool use_hot, const FastShape& fs, A... a) {
   if constexpr (VPL > 1) {
-    if (same_head_layout(fs)) return launch_bwd_op<GatBwdOpSH<VPL, MASK, FULL, EDGE>>(fs, a...);
+    if (same_head_layout(fs)) {
+      if constexpr (!MASK && !EDGE) {
+        if (use_hot) return launch_bwd_op<GatBwdOpSH<VPL, MASK, FULL, EDGE, true>>(fs, a...);
+      }
+      return launch_bwd_op<GatBwdOpSH<VPL, MASK, FULL, EDGE>>(fs, a...);
+    }
   }
   return launch_bwd_op<GatBwdOp<VPL, MASK, FULL, LPR>>(fs, a...);
 }
@@ -855,7 +871,7 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f, const void* row_
                      size_t workspace_bytes, void* stream) {
   return dgnn_gat_forward_staged(n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat,
                                  negative_slope, attn_drop, edge_mask, nullptr, out, edge_max, edge_sum, nullptr,
-                                 nullptr, nullptr, 1, 1, nullptr, 0, workspace, workspace_bytes, stream);
+                                 nullptr, nullptr, 1, 1, nullptr, 0, nullptr, workspace, workspace_bytes, stream);
 }
 
 int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr, int idx_bits,
@@ -863,7 +879,7 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
                             const float* in_feat, float negative_slope, float attn_drop,
                             const float* edge_mask, const float* bias, float* out, float* edge_max,
                             float* edge_sum, float* out_neg, float* a_neg, float* state, int first, int last,
-                            const uint8_t* stage_mask, int stage,
+                            const uint8_t* stage_mask, int stage, const uint32_t* hot_cols,
                             void* workspace, size_t workspace_bytes, void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
@@ -887,9 +903,10 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
     if (!aligned16(workspace)) return DGNN_ERR_ALIGN;
 #define FWD_ARGS                                                                                             \
   fs, n_rows, nnz, h, f, row_ptr, idx_bits, col_ind, attn_row, attn_col, in_feat, negative_slope, attn_drop, \
-      mask, out, edge_max, edge_sum, workspace, state, first, last, bias, out_neg, a_neg, stage_mask, stage, s
+      mask, out, edge_max, edge_sum, workspace, state, first, last, bias, out_neg, a_neg, stage_mask, stage, \
+      hot_cols, s
 #define CALL_FWD(V, M, FW, L) \
-  (out_neg ? launch_fwd<V, M, FW, L, true>(FWD_ARGS) : launch_fwd<V, M, FW, L, false>(FWD_ARGS))
+  (out_neg ? launch_fwd<V, M, FW, L, true>(hot_cols != nullptr, FWD_ARGS) : launch_fwd<V, M, FW, L, false>(false, FWD_ARGS))
     DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_FWD)
 #undef CALL_FWD
 #undef FWD_ARGS
@@ -1015,7 +1032,8 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
                            float* grad_attn_col, void* workspace, size_t workspace_bytes, void* stream) {
   return dgnn_gat_backward_cols_staged(n_rows, n_cols, nnz, h, f, row_ptr, col_ptr, idx_bits, row_ind, permute, pack,
                                        edge_mask, in_feat, attn_col, grad_out, negative_slope, attn_drop, grad_feat,
-                                       grad_attn_row, grad_attn_col, nullptr, 1, 1, nullptr, 0, workspace, workspace_bytes, stream);
+                                       grad_attn_row, grad_attn_col, nullptr, 1, 1, nullptr, 0, nullptr, workspace, workspace_bytes,
+                                       stream);
 }
 
 int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f, const void* row_ptr,
@@ -1024,7 +1042,8 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
                                   const float* in_feat, const float* attn_col, const float* grad_out,
                                   float negative_slope, float attn_drop, float* grad_feat, float* grad_attn_row,
                                   float* grad_attn_col, float* state, int first, int last, const uint8_t* stage_mask,
-                                  int stage, void* workspace, size_t workspace_bytes, void* stream) {
+                                  int stage, const uint32_t* hot_rows, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
   int st = check_common(n_rows, nnz, h, f, idx_bits);
   if (st) return st;
   const bool staged = !(first && last);
@@ -1058,9 +1077,9 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
 #define BWD_ARGS                                                                                          \
   fs, n_cols, nnz, h, f, col_ptr, idx_bits, row_ind, permute, pack, mask, in_feat, attn_col, grad_out,   \
       negative_slope, attn_drop, grad_feat, grad_attn_col, grad_edge, col_part, counter, state, first, last, stage_mask, \
-      stage, s
+      stage, hot_rows, s
 #define CALL_BWD(V, M, FW, L) \
-  (edge ? launch_bwd<V, M, FW, L, true>(BWD_ARGS) : launch_bwd<V, M, FW, L, false>(BWD_ARGS))
+  (edge ? launch_bwd<V, M, FW, L, true>(false, BWD_ARGS) : launch_bwd<V, M, FW, L, false>(hot_rows != nullptr, BWD_ARGS))
       auto run = [&]() -> int { DGNN_DISPATCH_VPL(fs.vpl, fs.lpr, mask != nullptr, fs.hf4 == fs.lpr * fs.vpl, CALL_BWD) };
 #undef CALL_BWD
 #undef BWD_ARGS

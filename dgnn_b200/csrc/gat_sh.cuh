@@ -58,7 +58,8 @@ __device__ __forceinline__ void lanes_reduce(float (&d)[U], int lph_shift) {
 // ------------------------------------------------------------------ forward
 // NEG: also accumulate the part of the row's result that comes from edges on the negative side of
 // the LeakyReLU (out_neg, a_neg); the backward derives grad_attn_row from it without a per-edge array.
-template <int VPL, bool MASK, bool FULL, bool NEG>
+// HOT: the kernel variant that honours the hot-column set (two load paths per edge); without it the set is ignored
+template <int VPL, bool MASK, bool FULL, bool NEG, bool HOT = false>
 struct GatFwdOpSH {
   static constexpr int MIN_BLOCKS = VPL <= 2 ? DGNN_SH_FWD_BLOCKS : (VPL == 4 ? 4 : 2);
   static constexpr bool HAS_PARTIALS = true;
@@ -86,6 +87,7 @@ struct GatFwdOpSH {
   const float4* bias;
   float4* out_neg;
   float* a_neg;
+  const unsigned* hot;   // NULL, or one bit per column: its in_feat / attn_col rows stay in the L2 (ld4_keep)
 
   struct State {
     HeadLanes<VPL> lm;
@@ -123,11 +125,20 @@ struct GatFwdOpSH {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act);
-      s[u] = ok ? __ldg(attn_col + (i64)c[u] * H + st.lm.hd) : 0.f;
+      const bool hot_u = HOT && c[u] < 0;                       // the same for every lane: a uniform branch
+      const i64 cc = c[u] & 0x7fffffff;
       keep[u] = ok;
       if (MASK) keep[u] = ok ? (__ldg(mask + (ebase + k + u) * H + st.lm.hd) > drop_p) : false;
+      if (hot_u) {
+        const unsigned long long pol = l2_keep_policy();   // made where it is used: no register held across the loop
+        s[u] = ok ? ld1_keep(attn_col + cc * H + st.lm.hd, pol) : 0.f;
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4(in_feat + (i64)c[u] * hf4 + st.lm.q[v]) : zero4();
+        for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4_keep(in_feat + cc * hf4 + st.lm.q[v], pol) : zero4();
+      } else {
+        s[u] = ok ? __ldg(attn_col + cc * H + st.lm.hd) : 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4(in_feat + cc * hf4 + st.lm.q[v]) : zero4();
+      }
     }
     float l[U];
     float bm = st.m;
@@ -175,7 +186,7 @@ struct GatFwdOpSH {
   __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
-      const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
+      const int my_c = lane < cnt ? dgnn_tag_hot(HOT ? hot : nullptr, ld_index(col_ind + base + lane)) : 0;
       int k = 0;
       for (; k + U <= cnt; k += U) batch<true>(st, my_c, base, k, cnt);
       if (k < cnt) batch<false>(st, my_c, base, k, cnt);
@@ -191,14 +202,14 @@ struct GatFwdOpSH {
       float4 a = st.acc[v];
       scale4(a, sc);
       if (bias) add4(a, __ldg(bias + st.lm.q[v]));
-      out[r * hf4 + st.lm.q[v]] = a;
+      st4_stream(out + r * hf4 + st.lm.q[v], a);
     }
     if (NEG) {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
         float4 a = st.accn[v];
         scale4(a, sc);
-        out_neg[r * hf4 + st.lm.q[v]] = a;
+        st4_stream(out_neg + r * hf4 + st.lm.q[v], a);
       }
     }
     if (st.lm.lead && edge_max) {
@@ -253,7 +264,7 @@ struct GatFwdOpSH {
 // ------------------------------------------------------------ backward cols
 // EDGE: the per-edge term d_e is written to grad_edge (CSR position through `permute`); without it -- the row
 // gradient then comes from the row statistics -- neither array is touched unless a dropout mask needs the position
-template <int VPL, bool MASK, bool FULL, bool EDGE>
+template <int VPL, bool MASK, bool FULL, bool EDGE, bool HOT = false>
 struct GatBwdOpSH {
   static constexpr int MIN_BLOCKS = VPL <= 2 ? (EDGE || MASK ? 4 : DGNN_SH_BWD_BLOCKS) : (VPL == 4 ? 3 : 2);
   static constexpr bool HAS_PARTIALS = true;
@@ -280,6 +291,7 @@ struct GatBwdOpSH {
   static constexpr bool STAGED = true;
   const unsigned char* stage_mask;   // per row: bit p set = the row has entries in stage p (NULL: every row in every stage)
   int stage;
+  const unsigned* hot;   // NULL, or one bit per destination row: its grad_out / pack rows stay in the L2 (ld4_keep)
 
   struct State {
     HeadLanes<VPL> lm;
@@ -316,11 +328,20 @@ struct GatBwdOpSH {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const bool ok = (ALL || k + u < cnt) && (FULL || st.lm.act);
-      pk[u] = ok ? ld4(pack + (i64)r[u] * H + st.lm.hd) : zero4();
+      const bool hot_u = HOT && r[u] < 0;                       // the same for every lane: a uniform branch
+      const i64 rr = r[u] & 0x7fffffff;
       keep[u] = ok;
       if (MASK) keep[u] = ok ? (__ldg(mask + (i64)pp[u] * H + st.lm.hd) > drop_p) : false;
+      if (hot_u) {
+        const unsigned long long pol = l2_keep_policy();   // made where it is used: no register held across the loop
+        pk[u] = ok ? ld4_keep(pack + rr * H + st.lm.hd, pol) : zero4();
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4(grad_out + (i64)r[u] * hf4 + st.lm.q[v]) : zero4();
+        for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4_keep(grad_out + rr * hf4 + st.lm.q[v], pol) : zero4();
+      } else {
+        pk[u] = ok ? ld4(pack + rr * H + st.lm.hd) : zero4();
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4(grad_out + rr * hf4 + st.lm.q[v]) : zero4();
+      }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -351,7 +372,7 @@ struct GatBwdOpSH {
   __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
     for (i64 base = e0; base < e1; base += 32) {
       const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
-      const int my_r = lane < cnt ? __ldg(row_ind + base + lane) : 0;
+      const int my_r = lane < cnt ? dgnn_tag_hot(HOT ? hot : nullptr, ld_index(row_ind + base + lane)) : 0;
       // without a permutation the mask (if any) is laid out in CSC order: the position is the index
       int my_p = 0;
       if (EDGE || MASK) my_p = lane < cnt ? (permute ? __ldg(permute + base + lane) : (int)(base + lane)) : 0;
@@ -365,7 +386,7 @@ struct GatBwdOpSH {
     if (!last_) { store_partial(st, state + c * slot_stride, lane); return; }
     if (!st.lm.act) return;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) grad_feat[c * hf4 + st.lm.q[v]] = st.acc[v];
+    for (int v = 0; v < VPL; ++v) st4_stream(grad_feat + c * hf4 + st.lm.q[v], st.acc[v]);
     if (st.lm.lead) grad_attn_col[c * H + st.lm.hd] = st.gc;
   }
 

@@ -5,6 +5,8 @@ returns torch tensors; nothing synchronises.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _C
@@ -54,14 +56,64 @@ def gat_fast_shape(h, f) -> bool:
     return bool(lib().dgnn_gat_fast_shape(int(h), int(f)))
 
 
+def _hot_arg(hot, n):
+    """Validate a hot-row bit set for a gather out of a tensor of n rows."""
+    if hot is None:
+        return None
+    if not (hot.is_cuda and hot.dtype == torch.int32 and hot.is_contiguous() and hot.numel() >= (n + 31) // 32):
+        raise RuntimeError("dgnn_b200: a hot-row set is a contiguous int32 CUDA tensor of ceil(n/32) words (hot_rows)")
+    return hot
+
+
+def hot_rows(indptr, max_hot):
+    """Bit set [ceil(n/32)] int32 of the rows whose segment of `indptr` [n+1] is among the longest: at most
+    max_hot rows, chosen by a length threshold (dgnn_hot_rows)."""
+    indptr, bits = _cuda_ptr(indptr, "indptr")
+    n = indptr.numel() - 1
+    dev = indptr.device
+    with device_guard(dev):
+        out = torch.empty(((n + 31) // 32,), dtype=torch.int32, device=dev)
+        ws = torch.empty((lib().dgnn_hot_rows_workspace_bytes(),), dtype=torch.uint8, device=dev)
+        check(lib().dgnn_hot_rows(n, _p(indptr), bits, int(max_hot), _p(out), _p(ws), ws.numel(), _stream(dev)),
+              "hot_rows")
+    return out
+
+
+def l2_set_aside(nbytes, device=None):
+    """Set aside part of the L2 of `device` for the hot rows (dgnn_l2_set_aside); returns the bytes in force."""
+    with device_guard(torch.device("cuda", torch.cuda.current_device()) if device is None else device):
+        got = lib().dgnn_l2_set_aside(int(nbytes))
+    if got < 0:
+        raise RuntimeError(f"dgnn_b200: l2_set_aside: CUDA error {-got}")
+    return got
+
+
+def l2_hot_budget_bytes():
+    """Bytes of often-referenced rows the sweeps try to keep in the L2 (DGNN_L2_HOT_MB; 0 = off, the default:
+    on a B200 the hint cuts the DRAM reads of the sweeps by a quarter at R-MAT 2.4 M / 120 M but not their time,
+    which the delivery of rows from the L2 to the SMs bounds)."""
+    return int(float(os.environ.get("DGNN_L2_HOT_MB", "0")) * 2**20)
+
+
+def l2_hot(indptr, row_bytes):
+    """The hot-row set of a gather of rows of `row_bytes` bytes addressed through `indptr`, or None when the whole
+    tensor is small enough for the L2's own replacement (twice the budget) or the budget is 0."""
+    n = indptr.numel() - 1
+    budget = l2_hot_budget_bytes()
+    if budget <= 0 or n * row_bytes <= 2 * budget:
+        return None
+    return hot_rows(indptr, budget // row_bytes)
+
+
 def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop=0.0,
-                edge_mask=None, save_stats=True, bias=None, neg=False):
+                edge_mask=None, save_stats=True, bias=None, neg=False, hot=None):
     """Fused GAT forward.  Returns (out, edge_max, edge_sum); the statistics are
     None when save_stats is False (inference).  `bias` [H*F] is added to the output
     inside the kernel when given.  With neg=True (float4 layout only) two more tensors
     follow: out_neg [N,H,F] and a_neg [N,H], the share of the result that comes from
     edges on the negative side of the LeakyReLU (gat_rowstat_full turns them into
-    grad_attn_row)."""
+    grad_attn_row).  `hot` (from l2_hot / hot_rows on the CSC column pointer) marks the
+    source rows that are kept in the L2."""
     attn_row = _cuda_f32(attn_row, "attn_row")
     attn_col = _cuda_f32(attn_col, "attn_col")
     in_feat = _cuda_f32(in_feat, "in_feat")
@@ -95,7 +147,8 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
         if neg:
             out_neg = torch.empty((n_rows, h, f), dtype=torch.float32, device=dev)
             a_neg = torch.empty((n_rows, h), dtype=torch.float32, device=dev)
-        if bias is None and not neg:
+        hot = _hot_arg(hot, in_feat.shape[0])
+        if bias is None and not neg and hot is None:
             check(lib().dgnn_gat_forward(n_rows, nnz, h, f, _p(row_ptr), bits, _p(col_ind), _p(attn_row),
                                          _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
                                          _p(edge_mask), _p(out), _p(edge_max), _p(edge_sum), _p(ws), ws.numel(),
@@ -107,7 +160,8 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, a
                                                 _p(attn_col), _p(in_feat), float(negative_slope), float(attn_drop),
                                                 _p(edge_mask), _p(bias), _p(out), _p(edge_max), _p(edge_sum),
                                                 _p(out_neg), _p(a_neg), None,
-                                                1, 1, None, 0, _p(ws), ws.numel(), _stream(dev)), "gat_forward(bias/neg)")
+                                                1, 1, None, 0, _p(hot), _p(ws), ws.numel(), _stream(dev)),
+                  "gat_forward(bias/neg)")
     if neg:
         return out, edge_max, edge_sum, out_neg, a_neg
     return out, edge_max, edge_sum
@@ -198,8 +252,9 @@ def gat_rowstat(attn_row, edge_max, edge_sum, out, grad_out):
 
 
 def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_feat, attn_col, grad_out,
-                      negative_slope, attn_drop=0.0, row_grad=True):
-    """Column pass of the backward on an [n_rows x n_cols] block (see the header).
+                      negative_slope, attn_drop=0.0, row_grad=True, hot=None):
+    """Column pass of the backward on an [n_rows x n_cols] block (see the header).  `hot` (from l2_hot / hot_rows
+    on the CSR row pointer) marks the destination rows whose grad_out / pack rows are kept in the L2.
     Returns (grad_feat [n_cols,H,F], grad_attn_row [n_rows,H], grad_attn_col [n_cols,H]).
     With row_grad=False grad_attn_row is None (it comes from gat_rowstat_full), the per-edge array is
     skipped, row_ptr / permute may be None and an edge_mask is indexed by CSC position."""
@@ -242,10 +297,12 @@ def gat_backward_cols(row_ptr, col_ptr, row_ind, permute, pack, edge_mask, in_fe
         grad_attn_row = torch.empty((n_rows, h), dtype=torch.float32, device=dev) if row_grad else None
         grad_attn_col = torch.empty((n_cols, h), dtype=torch.float32, device=dev)
         ws = _workspace(lib().dgnn_gat_backward_cols_workspace_bytes(nnz, h, f, int(row_grad)), dev)
-        check(lib().dgnn_gat_backward_cols(n_rows, n_cols, nnz, h, f, _p(row_ptr), _p(col_ptr), bits, _p(row_ind),
-                                           _p(permute), _p(pack), _p(edge_mask), _p(in_feat), _p(attn_col),
-                                           _p(grad_out), float(negative_slope), float(attn_drop), _p(grad_feat),
-                                           _p(grad_attn_row), _p(grad_attn_col), _p(ws), ws.numel(), _stream(dev)),
+        hot = _hot_arg(hot, n_rows)
+        check(lib().dgnn_gat_backward_cols_staged(n_rows, n_cols, nnz, h, f, _p(row_ptr), _p(col_ptr), bits,
+                                                  _p(row_ind), _p(permute), _p(pack), _p(edge_mask), _p(in_feat),
+                                                  _p(attn_col), _p(grad_out), float(negative_slope), float(attn_drop),
+                                                  _p(grad_feat), _p(grad_attn_row), _p(grad_attn_col), None, 1, 1,
+                                                  None, 0, _p(hot), _p(ws), ws.numel(), _stream(dev)),
               "gat_backward_cols")
     return grad_feat, grad_attn_row, grad_attn_col
 
@@ -726,7 +783,8 @@ def gat_backward_state(n_cols, h, f, device):
 
 
 def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope, feat_blk, state, first, last, bias=None,
-                       attn_drop=0.0, edge_mask=None, neg=False, save_stats=True, stage_mask=None, stage=0, outs=None):
+                       attn_drop=0.0, edge_mask=None, neg=False, save_stats=True, stage_mask=None, stage=0, outs=None,
+                       hot=None):
     """One stage of the forward over the edges whose source lies in one column block.
     Returns (out, edge_max, edge_sum[, out_neg, a_neg]) from the last stage, None before.  `bias` [H*F] is
     added to the output when a row is written out; `edge_mask` [nnz,H] (with attn_drop > 0) follows the
@@ -777,6 +835,7 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
                                             _p(edge_mask), _p(bias) if bias is not None else None,
                                             _p(out), _p(emax), _p(esum), _p(out_neg), _p(a_neg), _p(state),
                                             int(bool(first)), int(bool(last)), _p(stage_mask), int(stage),
+                                            _p(_hot_arg(hot, feat_blk.shape[0])),
                                             _p(ws), ws.numel(), _stream(dev)), "gat_forward_staged")
     if not last and stage_mask is None:
         return None
@@ -785,7 +844,7 @@ def gat_forward_staged(attn_row, attn_col_blk, row_ptr, col_ind, negative_slope,
 
 def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_feat, attn_col, grad_blk,
                              negative_slope, state, first, last, attn_drop=0.0, edge_mask=None, row_grad=True,
-                             stage_mask=None, stage=0, outs=None):
+                             stage_mask=None, stage=0, outs=None, hot=None):
     """One stage of the backward column pass over the edges whose destination lies in one
     row block.  Returns (grad_attn_row of the block's rows or None, grad_feat or None, grad_attn_col or None).
     With row_grad=False (grad_attn_row comes from gat_rowstat_full) row_ptr and permute may be None and an
@@ -835,6 +894,6 @@ def gat_backward_cols_staged(row_ptr, col_ptr, row_ind, permute, pack_blk, in_fe
                                                   _p(attn_col), _p(grad_blk), float(negative_slope), float(attn_drop),
                                                   _p(grad_feat), _p(grad_row), _p(grad_col), _p(state),
                                                   int(bool(first)), int(bool(last)), _p(stage_mask), int(stage),
-                                                  _p(ws), ws.numel(), _stream(dev)),
+                                                  _p(_hot_arg(hot, n_rows)), _p(ws), ws.numel(), _stream(dev)),
               "gat_backward_cols_staged")
     return grad_row, grad_feat, grad_col

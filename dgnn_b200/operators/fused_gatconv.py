@@ -16,6 +16,16 @@ def GATConvFuse_inference(attn_row, attn_col, row_ptr, col_ind, negative_slope, 
     return fused_gat.gat_inference(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat)
 
 
+def _hot_sources(col_ptr, feat):
+    """Source rows the forward keeps in the L2: the most referenced columns (a feature row and its logits)."""
+    return kernels.l2_hot(col_ptr, 4 * feat.shape[1] * (feat.shape[2] + 1))
+
+
+def _hot_destinations(row_ptr, grad_out):
+    """Destination rows the backward keeps in the L2: the longest rows (a grad_out row and its statistics)."""
+    return kernels.l2_hot(row_ptr, 4 * grad_out.shape[1] * (grad_out.shape[2] + 4))
+
+
 class FusedGATFunction(torch.autograd.Function):
     """On the float4 layout (kernels.gat_fast_shape) the forward also keeps the share of the result that
     comes from edges on the negative side of the LeakyReLU; the backward then gets grad_attn_row from the
@@ -33,9 +43,9 @@ class FusedGATFunction(torch.autograd.Function):
             edge_mask = fused_gat.make_edge_mask(col_ind.numel(), in_feat.shape[1], attn_drop, in_feat.device)
             out_feat, edge_max, edge_sum, out_neg, a_neg = kernels.gat_forward(
                 attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop,
-                edge_mask if attn_drop > 0.0 else None, neg=True)
+                edge_mask if attn_drop > 0.0 else None, neg=True, hot=_hot_sources(col_ptr, in_feat))
             ctx.save_for_backward(col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, in_feat, attn_row,
-                                  attn_col, out_feat, out_neg, a_neg)
+                                  attn_col, out_feat, out_neg, a_neg, row_ptr)
             return out_feat
         out_feat, edge_max, edge_sum, edge_mask = fused_gat.gat_forward(
             attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, attn_drop)
@@ -49,13 +59,14 @@ class FusedGATFunction(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         if ctx.neg:
             (col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, in_feat, attn_row, attn_col, out_feat,
-             out_neg, a_neg) = ctx.saved_tensors
+             out_neg, a_neg, row_ptr) = ctx.saved_tensors
             pack, grad_attn_row, _ = kernels.gat_rowstat_full(attn_row, edge_max, edge_sum, out_feat, grad_out,
                                                               ctx.negative_slope, out_neg=out_neg, a_neg=a_neg)
             masked = ctx.attn_drop > 0.0
             grad_feat, _, grad_attn_col = kernels.gat_backward_cols(
                 None, col_ptr, row_ind, permute if masked else None, pack, edge_mask if masked else None, in_feat,
-                attn_col, grad_out, ctx.negative_slope, ctx.attn_drop, row_grad=False)
+                attn_col, grad_out, ctx.negative_slope, ctx.attn_drop, row_grad=False,
+                hot=_hot_destinations(row_ptr, grad_out))
             return grad_attn_row, grad_attn_col, None, None, None, None, None, None, grad_feat, None
         (row_ptr, col_ind, col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, in_feat, attn_row, attn_col,
          out_feat) = ctx.saved_tensors
@@ -86,9 +97,9 @@ class FusedGATLayerFunction(torch.autograd.Function):
         edge_mask = fused_gat.make_edge_mask(col_ind.numel(), h.shape[1], attn_drop, h.device)
         out_feat, edge_max, edge_sum, out_neg, a_neg = kernels.gat_forward(
             attn_row, attn_col, row_ptr, col_ind, negative_slope, h, attn_drop,
-            edge_mask if attn_drop > 0.0 else None, True, bias, neg=True)
+            edge_mask if attn_drop > 0.0 else None, True, bias, neg=True, hot=_hot_sources(col_ptr, h))
         saved = [col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
-                 out_neg, a_neg, attn_l, attn_r]
+                 out_neg, a_neg, attn_l, attn_r, row_ptr]
         if bias is not None:
             saved.append(bias)
         ctx.save_for_backward(*saved)
@@ -100,10 +111,10 @@ class FusedGATLayerFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         (col_ptr, row_ind, permute, edge_max, edge_sum, edge_mask, h, attn_row, attn_col, out_feat,
-         out_neg, a_neg, attn_l, attn_r) = ctx.saved_tensors[:14]
+         out_neg, a_neg, attn_l, attn_r, row_ptr) = ctx.saved_tensors[:15]
         grad_out = grad_out.contiguous()
         masked = ctx.attn_drop > 0.0
-        bias = ctx.saved_tensors[14] if ctx.has_bias else None
+        bias = ctx.saved_tensors[15] if ctx.has_bias else None
         # pack, grad_attn_row and the bias gradient all come out of one pass over the destination rows
         pack, grad_attn_row, grad_bias = kernels.gat_rowstat_full(attn_row, edge_max, edge_sum, out_feat, grad_out,
                                                                   ctx.negative_slope, bias=bias, out_neg=out_neg,
@@ -112,7 +123,7 @@ class FusedGATLayerFunction(torch.autograd.Function):
             grad_bias = grad_bias.view_as(bias)
         grad_h, _, grad_attn_col = kernels.gat_backward_cols(
             None, col_ptr, row_ind, permute if masked else None, pack, edge_mask if masked else None, h, attn_col,
-            grad_out, ctx.negative_slope, ctx.attn_drop, row_grad=False)
+            grad_out, ctx.negative_slope, ctx.attn_drop, row_grad=False, hot=_hot_destinations(row_ptr, grad_out))
         grad_l, grad_r = kernels.gat_logits_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_h)
         return (grad_h, grad_l.view_as(attn_l), grad_r.view_as(attn_r), None, None, None, None, None, None, None,
                 grad_bias)

@@ -105,7 +105,7 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f,
                             const float* bias, float* out, float* edge_max, float* edge_sum,
                             float* out_neg, float* a_neg,
                             float* state, int first, int last,
-                            const uint8_t* stage_mask, int stage,
+                            const uint8_t* stage_mask, int stage, const uint32_t* hot_cols,
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /* Row statistics for the backward pass: pack[r,h] = (attn_row, edge_max,
@@ -176,7 +176,8 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
  * per-column accumulators (dgnn_gat_backward_state_bytes) are carried in `state`;
  * grad_feat / grad_attn_col are written by the last call, grad_attn_row (of the block's
  * rows, unless NULL) by every call.  first = last = 1 is dgnn_gat_backward_cols.  stage_mask / stage: as for
- * dgnn_gat_forward_staged, one byte per column. */
+ * dgnn_gat_forward_staged, one byte per column.  hot_rows: as hot_cols there, one bit per destination row (from
+ * dgnn_hot_rows on the CSR row pointer): the grad_out / pack rows that stay in the L2. */
 size_t dgnn_gat_backward_state_bytes(int64_t n_cols, int h, int f);
 int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f,
                                   const void* row_ptr, const void* col_ptr, int idx_bits,
@@ -186,7 +187,7 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
                                   float negative_slope, float attn_drop,
                                   float* grad_feat, float* grad_attn_row, float* grad_attn_col,
                                   float* state, int first, int last,
-                                  const uint8_t* stage_mask, int stage,
+                                  const uint8_t* stage_mask, int stage, const uint32_t* hot_rows,
                                   void* workspace, size_t workspace_bytes, void* stream);
 
 /* Whole backward on a square graph: replaces fused_gatconv.gat_backward
@@ -396,6 +397,21 @@ int dgnn_coo_sort(int64_t nnz, int64_t n_nodes, const int32_t* dst, const int32_
 int dgnn_knn_max_k(void);
 int dgnn_knn_graph(int64_t n_clouds, int64_t n_points, int dim, int k, const float* points,
                    int32_t* src_ind, void* stream);
+
+/* Rows of a gathered tensor that should stay in the L2 (no counterpart in the reference, whose kernels load every
+ * row alike, dgNN/src/fused_gatconv/fused_gatconv_kernel.cu:68-100).  indptr [n+1] gives every row's reference count
+ * -- the CSC column pointer for the forward gather of in_feat by source, the CSR row pointer for the backward
+ * gather of grad_out by destination.  hot_bits [ceil(n/32)] gets bit r & 31 of word r >> 5 set for the rows whose
+ * count is at least T, T >= 1 being the smallest threshold that marks at most max_hot rows (rows without
+ * references are never marked; counts of 4095 and more fall into one class).  Pass the result as hot_cols /
+ * hot_rows to the staged GAT sweeps. */
+size_t dgnn_hot_rows_workspace_bytes(void);
+/* Sets aside `bytes` of the L2 (clamped to the device's maximum) for lines loaded with the evict_last priority:
+ * cudaLimitPersistingL2CacheSize of the calling process's context on the current device; nothing outlasts the
+ * process.  Returns the size in force afterwards, or minus a CUDA error code. */
+int64_t dgnn_l2_set_aside(int64_t bytes);
+int dgnn_hot_rows(int64_t n, const void* indptr, int idx_bits, int64_t max_hot, uint32_t* hot_bits,
+                  void* workspace, size_t workspace_bytes, void* stream);
 /* row_ptr[i] = number of entries with row id < i, for sorted COO row ids;
  * replaces format_conversion.coo2csr (convert.cpp:32-35, convert_kernel.cu:44-59) */
 int dgnn_coo2csr(int64_t nnz, int64_t m, const int32_t* row_ind,

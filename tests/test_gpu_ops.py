@@ -300,3 +300,75 @@ def test_guard_mode_validates_index_arrays(cuda, monkeypatch):
                                  torch.zeros(3, 4, device=cuda), torch.zeros(3, 4, device=cuda))
     monkeypatch.setenv("DGNN_BOUNDS_CHECK", "0")
     assert not kernels.guard_enabled()
+
+
+def _hot_rows_expected(ptr, max_hot):
+    """numpy restatement of dgnn_hot_rows: counts clamp at 4095, threshold = smallest t >= 1 that marks <= max_hot rows."""
+    import numpy as np
+    d = np.minimum(np.diff(ptr.numpy().astype(np.int64)), 4095)
+    thr = 4096
+    for t in range(1, 4096):
+        if int((d >= t).sum()) <= max_hot:
+            thr = t
+            break
+    hot = np.diff(ptr.numpy().astype(np.int64)) >= thr
+    words = np.zeros((len(hot) + 31) // 32 * 32, dtype=bool)
+    words[:len(hot)] = hot
+    packed = (words.reshape(-1, 32).astype(np.uint64) << np.arange(32, dtype=np.uint64)).sum(axis=1).astype(np.uint32)
+    return torch.from_numpy(packed.view(np.int32).copy()), thr
+
+
+@pytest.mark.parametrize("ptr64", [False, True])
+@pytest.mark.parametrize("n,avg,max_hot", [(1, 3, 1), (33, 2, 0), (1000, 6, 50), (70_001, 9, 3000), (5000, 4, 10**9)])
+def test_hot_rows_bit_exact(cuda, n, avg, max_hot, ptr64):
+    rp, ci = synth.random_graph(n, avg, seed=n + max_hot, long_rows=((n // 2, 6000),) if n >= 1000 else ())
+    if ptr64:
+        rp = rp.long()
+    want, thr = _hot_rows_expected(rp, max_hot)
+    got = kernels.hot_rows(rp.to(cuda), max_hot)
+    assert_equal(got, want, f"hot-row words (threshold {thr})")
+    n_hot = sum(bin(int(w) & 0xffffffff).count("1") for w in got.cpu().tolist())
+    assert n_hot <= max(max_hot, 0) or thr == 4096
+
+
+def test_hot_rows_change_no_result(cuda, monkeypatch):
+    """Cache hints only: the sweeps with a hot-row set give the same bits as without, on the same-head layout
+    (8 heads x 32) and on a layout that ignores the set (4 x 8); the operator path picks a set up from
+    DGNN_L2_HOT_MB once the gathered tensor is larger than twice the budget."""
+    rp, ci = synth.random_graph(3000, 12, seed=5, long_rows=((7, 2500), (1500, 1100)))
+    n = rp.numel() - 1
+    rp_d, ci_d = rp.to(cuda), ci.to(cuda)
+    cp, ri, pm = kernels.csr2csc(rp_d, ci_d)
+    for h, f in ((8, 32), (4, 8)):
+        g = torch.Generator().manual_seed(h)
+        ar, ac = torch.randn(n, h, generator=g).to(cuda), torch.randn(n, h, generator=g).to(cuda)
+        x, go = torch.randn(n, h, f, generator=g).to(cuda), torch.randn(n, h, f, generator=g).to(cuda)
+        hot_c, hot_r = kernels.hot_rows(cp, 200), kernels.hot_rows(rp_d, 200)
+        assert int(hot_c.ne(0).sum()) > 0 and int(hot_r.ne(0).sum()) > 0
+        base = kernels.gat_forward(ar, ac, rp_d, ci_d, 0.2, x, neg=True)
+        hinted = kernels.gat_forward(ar, ac, rp_d, ci_d, 0.2, x, neg=True, hot=hot_c)
+        for a, b, name in zip(base, hinted, ("out", "edge_max", "edge_sum", "out_neg", "a_neg")):
+            assert_equal(b, a, f"forward {name} with hot rows ({h}x{f})")
+        pack, _, _ = kernels.gat_rowstat_full(ar, base[1], base[2], base[0], go, 0.2, out_neg=base[3], a_neg=base[4])
+        b0 = kernels.gat_backward_cols(None, cp, ri, None, pack, None, x, ac, go, 0.2, row_grad=False)
+        b1 = kernels.gat_backward_cols(None, cp, ri, None, pack, None, x, ac, go, 0.2, row_grad=False, hot=hot_r)
+        assert_equal(b1[0], b0[0], f"grad_feat with hot rows ({h}x{f})")
+        assert_equal(b1[2], b0[2], f"grad_attn_col with hot rows ({h}x{f})")
+    with pytest.raises(RuntimeError, match="hot-row set"):
+        kernels.gat_forward(ar, ac, rp_d, ci_d, 0.2, x, neg=True, hot=hot_c[:3])
+    # operator path: budget 0.25 MB against a 3.1 MB feature tensor -> a set is used; results unchanged
+    from dgnn_b200.operators import GATConvFuse
+    h, f = 8, 32
+    g = torch.Generator().manual_seed(3)
+    ar, ac = torch.randn(n, h, generator=g).to(cuda), torch.randn(n, h, generator=g).to(cuda)
+    x = torch.randn(n, h, f, generator=g).to(cuda)
+    outs = []
+    for mb in ("0", "0.25"):
+        monkeypatch.setenv("DGNN_L2_HOT_MB", mb)
+        assert (kernels.l2_hot(cp, 4 * h * (f + 1)) is None) == (mb == "0")
+        xr = x.clone().requires_grad_(True)
+        y = GATConvFuse(ar, ac, rp_d, ci_d, cp, ri, pm, 0.2, xr, 0.0)
+        y.square().sum().backward()
+        outs.append((y.detach(), xr.grad))
+    assert_equal(outs[1][0], outs[0][0], "operator output with hot rows")
+    assert_equal(outs[1][1], outs[0][1], "operator grad_feat with hot rows")
