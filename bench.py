@@ -28,12 +28,16 @@ if ROOT not in sys.path:
 
 H, F, IN = 8, 32, 100
 SLOPE = 0.2
-# DRAM bytes (read + write) per edge of the forward call and of the backward calls, from ncu's
-# dram__bytes_read.sum + dram__bytes_write.sum over the kernels of one call on the R-MAT 300 k-node /
-# 12 M-edge case (same average degree and skew; traffic grows in proportion to the edges), scaled to the
-# workload's edge count at run time.  None = not captured for the current kernels.
-TRAFFIC_FWD_BYTES_PER_EDGE = None
-TRAFFIC_BWD_BYTES_PER_EDGE = None
+# DRAM bytes (read + write) per edge of the forward call and of the backward calls: ncu's
+# dram__bytes_read.sum + dram__bytes_write.sum summed over the kernels of one call, captured at the full
+# workload (R-MAT 2.4 M nodes / 120 M edges; the three metrics take one pass, so nothing is saved or
+# restored around the capture): forward k_rows + k_chunks + k_merge 43.18 + 24.86 + 0.15 GB; backward
+# k_gat_rowstat_full + k_bias_grad_final + k_rows + k_chunks + k_merge 8.06 + 0.00 + 45.00 + 26.28 + 0.07 GB.
+# The share of gathered rows that the L2 serves depends on the graph's size (231 B per edge at 300 k nodes /
+# 12 M edges against 568 here), so the figure is only attached to runs of the captured workload.
+TRAFFIC_WORKLOAD = (2_400_000, 120_000_000)
+TRAFFIC_FWD_BYTES_PER_EDGE = 68.18e9 / 120e6
+TRAFFIC_BWD_BYTES_PER_EDGE = 79.42e9 / 120e6
 
 
 def parse():
@@ -337,20 +341,22 @@ def run_ours(args, rank, world, local):
         del rp, ci, owner_of
         torch.cuda.empty_cache()
 
-        timer.spans["step_forward"], timer.spans["step_loss_and_backward"], timer.spans["step_grad_allreduce"] = [], [], []
+        for name in ("step_forward", "step_loss", "step_backward", "step_grad_allreduce"):
+            timer.spans[name] = []
 
         def step(x_in):
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timer.active else None
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if timer.active else None
             if ev: ev[0].record()
             out = layer(x_in)                                  # the same layer on this rank's node block
             if ev: ev[1].record()
             loss = torch.dot(out.reshape(-1), cot.view(-1))
-            loss.backward()
             if ev: ev[2].record()
+            loss.backward()
+            if ev: ev[3].record()
             layer.allreduce_grads()                            # replicated parameters: one flat all-reduce
             if ev:
-                ev[3].record()
-                for k, name in enumerate(("step_forward", "step_loss_and_backward", "step_grad_allreduce")):
+                ev[4].record()
+                for k, name in enumerate(("step_forward", "step_loss", "step_backward", "step_grad_allreduce")):
                     timer.spans[name].append((ev[k], ev[k + 1]))
             return loss, out
 
@@ -401,7 +407,7 @@ def run_ours(args, rank, world, local):
     if hc is not None:
         exposed = {}
         for phase, chunk, a, b in hc.exposed_ms:
-            key = f"{phase}_wait_chunk{chunk}"
+            key = f"{phase}_{chunk}" if isinstance(chunk, str) else f"{phase}_wait_chunk{chunk}"
             exposed[key] = exposed.get(key, 0.0) + a.elapsed_time(b) / args.steps
         hc.exposed_ms = None
 
@@ -506,17 +512,19 @@ def run_ours(args, rank, world, local):
         ach_b = bwd_b / (bwd_ms * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "kernel": "dgnn_gat_rowstat_full + dgnn_gat_backward_cols: k_gat_rowstat_full + k_rows/k_chunks/k_merge<GatBwdOp>",
                             "achieved": ach_b, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_b / peak,
-                            "traffic": TRAFFIC_BWD_BYTES_PER_EDGE * nnz if TRAFFIC_BWD_BYTES_PER_EDGE else None,
+                            "traffic": TRAFFIC_BWD_BYTES_PER_EDGE * nnz if (n, nnz) == TRAFFIC_WORKLOAD else None,
                             "algorithmic_bytes": bwd_b, "ms": bwd_ms}
         ach = fwd_b / (fwd_ms * 1e-3) / 1e9
         line["roofline_fwd"] = {"bound": "hbm", "kernel": "dgnn_gat_forward_staged: k_rows/k_chunks/k_merge<GatFwdOp>",
                                 "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                                "traffic": TRAFFIC_FWD_BYTES_PER_EDGE * nnz if TRAFFIC_FWD_BYTES_PER_EDGE else None,
+                                "traffic": TRAFFIC_FWD_BYTES_PER_EDGE * nnz if (n, nnz) == TRAFFIC_WORKLOAD else None,
                                 "algorithmic_bytes": fwd_b, "ms": fwd_ms}
         tot = (fwd_b + bwd_b) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
         line["fused_op"] = {"ms": fwd_ms + bwd_ms, "edges_per_s": nnz / ((fwd_ms + bwd_ms) * 1e-3), "achieved_gbs": tot,
                             "frac_of_peak": tot / peak,
-                            "note": "algorithmic bytes count every gathered row in full; hub rows are served from L2, so this can exceed the DRAM copy peak"}
+                            "note": "algorithmic bytes count every gathered row in full; 48 % of the gathered rows are served from L2 "
+                                    "(traffic = DRAM bytes), so achieved can exceed the DRAM copy peak; ncu names the L1TEX data pipe "
+                                    "(76-80 % of peak) and instruction issue (66-72 %) as the binding units, not HBM (DRAM 4.5-4.9 TB/s)"}
     if world == 1 and not args.no_cpu_baseline:
         from dgnn_b200.operators.projection import project
         with torch.no_grad():

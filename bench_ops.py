@@ -275,6 +275,8 @@ def main():
     ap.add_argument("--suite", default="all", choices=["small", "edgeconv", "micro", "project", "gather", "all"])
     ap.add_argument("--project-rows", type=int, default=2_400_000)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--gather-nodes", type=int, default=2_400_000)
+    ap.add_argument("--gather-edges", type=int, default=120_000_000)
     ap.add_argument("--micro-edges", type=int, default=256_000_000)
     ap.add_argument("--micro-degrees", default="4,16,64,128")
     ap.add_argument("--micro-heads", default="1,4,8,16")
@@ -289,7 +291,7 @@ def main():
     if args.suite in ("project", "all"):
         suite_project(args.iters, args.project_rows)
     if args.suite in ("gather", "all"):
-        suite_gather(args.iters, 2_400_000, 120_000_000)
+        suite_gather(args.iters, args.gather_nodes, args.gather_edges)
     if args.suite in ("micro", "all"):
         suite_micro(args.iters, args.micro_edges, [int(d) for d in args.micro_degrees.split(",")],
                     [int(h) for h in args.micro_heads.split(",")], args.cap_gb)

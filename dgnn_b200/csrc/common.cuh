@@ -89,14 +89,45 @@ __device__ __forceinline__ int dgnn_tag_hot(const unsigned* hot, int idx) {
   return hot ? (idx | (int)(((__ldg(hot + (idx >> 5)) >> (idx & 31)) & 1u) << 31)) : idx;
 }
 __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+// Packed fp32 arithmetic (fma.rn.f32x2 / mul.rn.f32x2 of sm_100: two lanes per issued instruction, each rounded as
+// the scalar operation): the sweeps issue two fused multiply-adds per gathered float, and their issue slots are
+// as busy as the load pipe.
+#ifndef DGNN_FFMA2
+#define DGNN_FFMA2 1
+#endif
 __device__ __forceinline__ void fma4(float4& acc, float w, const float4& x) {
+#if DGNN_FFMA2
+  const float2 ww = make_float2(w, w);
+  const float2 lo = __ffma2_rn(ww, make_float2(x.x, x.y), make_float2(acc.x, acc.y));
+  const float2 hi = __ffma2_rn(ww, make_float2(x.z, x.w), make_float2(acc.z, acc.w));
+  acc = make_float4(lo.x, lo.y, hi.x, hi.y);
+#else
   acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
   acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+#endif
 }
-__device__ __forceinline__ void scale4(float4& a, float s) { a.x *= s; a.y *= s; a.z *= s; a.w *= s; }
+__device__ __forceinline__ void scale4(float4& a, float s) {
+#if DGNN_FFMA2
+  const float2 ss = make_float2(s, s);
+  const float2 lo = __fmul2_rn(ss, make_float2(a.x, a.y)), hi = __fmul2_rn(ss, make_float2(a.z, a.w));
+  a = make_float4(lo.x, lo.y, hi.x, hi.y);
+#else
+  a.x *= s; a.y *= s; a.z *= s; a.w *= s;
+#endif
+}
 __device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
 __device__ __forceinline__ float dot4(const float4& a, const float4& b) {
   return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
+}
+// t += (a.x*b.x + a.z*b.z, a.y*b.y + a.w*b.w): a dot product kept as two partial sums (t.x + t.y at the end)
+__device__ __forceinline__ void dot4_acc(float2& t, const float4& a, const float4& b) {
+#if DGNN_FFMA2
+  t = __ffma2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y), t);
+  t = __ffma2_rn(make_float2(a.z, a.w), make_float2(b.z, b.w), t);
+#else
+  t.x = fmaf(a.z, b.z, fmaf(a.x, b.x, t.x));
+  t.y = fmaf(a.w, b.w, fmaf(a.y, b.y, t.y));
+#endif
 }
 __device__ __forceinline__ float leaky(float x, float slope) { return x > 0.f ? x : x * slope; }
 // exp through the hardware ex2 unit: relative error ~2^-22 plus |x| * 2^-24 from the

@@ -345,9 +345,10 @@ struct GatBwdOpSH {
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      d[u] = 0.f;
+      float2 t = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) d[u] += dot4(g4[u][v], st.x[v]);
+      for (int v = 0; v < VPL; ++v) dot4_acc(t, g4[u][v], st.x[v]);
+      d[u] = t.x + t.y;
     }
     lanes_reduce<U>(d, st.lm.lph_shift);  // executed by all lanes, also for slots past cnt
     if (!FULL && !st.lm.act) return;

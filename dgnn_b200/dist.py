@@ -574,8 +574,25 @@ class HaloContext:
 
     @property
     def h_own(self):
-        """[blk, H, F] view of the feature buffer's own rows: let the projection write here."""
-        return self.X.detach()[:self.shard.blk]      # detached: writes through it leave no autograd history on the buffer
+        """[blk, H, F] tensor over the feature buffer's own rows: let the projection write here.  It shares the
+        buffer's storage without being a view of it in autograd's eyes: an in-place write through a view makes
+        autograd rebuild the gradient of the whole [own | halo] buffer in the backward (a zero fill and two copies
+        of gigabytes); a tensor set on the storage has no base."""
+        return self._own_rows((self.shard.blk,) + tuple(self.X.shape[1:]))
+
+    @property
+    def h_own_flat(self):
+        """The same rows as [blk, H*F] (the shape the projection writes)."""
+        return self._own_rows((self.shard.blk, self.h * self.f))
+
+    def _own_rows(self, shape):
+        X = self.X
+        own = X.new_empty(0)
+        stride = [1] * len(shape)
+        for d in range(len(shape) - 2, -1, -1):
+            stride[d] = stride[d + 1] * shape[d + 1]
+        own.set_(X.untyped_storage(), X.storage_offset(), shape, tuple(stride))
+        return own
 
 
 def _masks(ctx, side, attn_drop, seed):
@@ -672,6 +689,19 @@ def _timed_wait(ctx, work, phase, chunk):
     ctx.exposed_ms.append((phase, chunk, a, b))
 
 
+def _timed_publish(ctx, phase, side, bufs, tags, packed):
+    """transport.publish (packing, if it was not fused, and the barrier that makes the send buffers visible: the
+    point where a rank waits for the slowest peer); bracketed like the chunk waits when ctx.exposed_ms is set."""
+    if ctx.exposed_ms is None or not ctx.X.is_cuda:
+        ctx.transport.publish(side, bufs, tags, packed=packed)
+        return
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    ctx.transport.publish(side, bufs, tags, packed=packed)
+    b.record()
+    ctx.exposed_ms.append((phase, "publish_and_barrier", a, b))
+
+
 class HaloGATFunction(torch.autograd.Function):
     """Fused GAT on this rank's block.  Layer form (logits=True): inputs (h, attn_l, attn_r, bias); operator form:
     (in_feat, attn_row, attn_col, None).  Output [blk,H,F] in HaloShard.local_ids order."""
@@ -682,7 +712,7 @@ class HaloGATFunction(torch.autograd.Function):
             attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_l=b, attn_r=c)
         else:
             attn_row = halo_forward_prepare(hc, h=a.contiguous(), attn_row=b.contiguous(), attn_col=c.contiguous())
-        hc.transport.publish(hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2], packed=hc.packed_fwd)
+        _timed_publish(hc, "fwd", hc.shard.fwd, [hc.X, hc.AC], hc.tags[0:2], hc.packed_fwd)
         out, edge_max, edge_sum, out_neg, a_neg = halo_forward_sweep(hc, attn_row, bias, attn_drop, seed, train=True)
         ctx.save_for_backward(attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c,
                               bias if bias is not None else out.new_empty(0))
@@ -698,7 +728,7 @@ class HaloGATFunction(torch.autograd.Function):
         attn_row, edge_max, edge_sum, out, out_neg, a_neg, b, c, bias = ctx.saved_tensors
         grad_row, grad_bias = halo_backward_prepare(hc, attn_row, edge_max, edge_sum, out, out_neg, a_neg,
                                                     grad_out.contiguous(), bias if ctx.has_bias else None)
-        hc.transport.publish(hc.shard.bwd, [hc.G, hc.PK], hc.tags[2:4], packed=hc.packed_bwd)
+        _timed_publish(hc, "bwd", hc.shard.bwd, [hc.G, hc.PK], hc.tags[2:4], hc.packed_bwd)
         grad_feat, grad_col = halo_backward_sweep(hc, ctx.attn_drop, ctx.seed)
         if grad_bias is not None:
             grad_bias = grad_bias.view_as(bias)
@@ -764,7 +794,7 @@ class ShardedGATConv(torch.nn.Module):
         hc = self._context()
         heads, width = self.num_heads, self.out_feats
         plain = self.feat_drop.p == 0.0 or not self.training
-        h = project(feat, self.W, out=hc.h_own.view(self.shard.blk, heads * width) if plain else None)
+        h = project(feat, self.W, out=hc.h_own_flat if plain else None)
         h = self.feat_drop(h.view(-1, heads, width))
         fuse_bias = self.bias is not None and self.res_fc is None
         self.step += 1
