@@ -43,6 +43,10 @@ __device__ __forceinline__ i64 find_row(const void* indptr, int bits, i64 n_rows
 }
 
 __device__ __forceinline__ float4 ld4(const float4* p) { return __ldg(p); }
+// load of a gathered row (one per edge).  Through the L1 like any read-only load: the hub rows of a skewed graph are
+// re-read by the same SM often enough that caching at the L2 only (ld.global.cg: +2 % on the forward and backward
+// sweeps at R-MAT 2.4 M / 120 M) or L1::no_allocate (+11-14 %) is slower.
+__device__ __forceinline__ float4 ld4_gather(const float4* p) { return __ldg(p); }
 // Read-only load whose line is the last to leave the L2: for the rows of a gathered tensor that many edges
 // reference (the "hot" rows, see dgnn_hot_rows).  A feature tensor of gigabytes streams through the 126 MB L2;
 // with plain loads the often-referenced rows are evicted by rows that are read once.

@@ -137,7 +137,7 @@ struct GatFwdOpSH {
       } else {
         s[u] = ok ? __ldg(attn_col + cc * H + st.lm.hd) : 0.f;
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4(in_feat + cc * hf4 + st.lm.q[v]) : zero4();
+        for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4_gather(in_feat + cc * hf4 + st.lm.q[v]) : zero4();
       }
     }
     float l[U];
@@ -340,7 +340,7 @@ struct GatBwdOpSH {
       } else {
         pk[u] = ok ? ld4(pack + rr * H + st.lm.hd) : zero4();
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4(grad_out + rr * hf4 + st.lm.q[v]) : zero4();
+        for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4_gather(grad_out + rr * hf4 + st.lm.q[v]) : zero4();
       }
     }
 #pragma unroll
