@@ -94,10 +94,11 @@ __device__ __forceinline__ int dgnn_tag_hot(const unsigned* hot, int idx) {
 }
 __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
 // Packed fp32 arithmetic (fma.rn.f32x2 / mul.rn.f32x2 of sm_100: two lanes per issued instruction, each rounded as
-// the scalar operation): the sweeps issue two fused multiply-adds per gathered float, and their issue slots are
-// as busy as the load pipe.
+// the scalar operation, so the results are bit-identical).  Off: measured on the GAT sweeps it changes nothing (their
+// first limit is the L1TEX data pipe, not the issue rate), and the register pairs it needs cost the streaming
+// kernels occupancy (logits backward 62 -> 74 registers, 1.19 -> 1.64 ms at 2.4 M rows x 8 heads x 32).
 #ifndef DGNN_FFMA2
-#define DGNN_FFMA2 1
+#define DGNN_FFMA2 0
 #endif
 __device__ __forceinline__ void fma4(float4& acc, float w, const float4& x) {
 #if DGNN_FFMA2
