@@ -33,6 +33,8 @@ SLOPE = 0.2
 # workload (R-MAT 2.4 M nodes / 120 M edges; the three metrics take one pass, so nothing is saved or
 # restored around the capture): forward k_rows + k_chunks + k_merge 43.18 + 24.86 + 0.15 GB; backward
 # k_gat_rowstat_full + k_bias_grad_final + k_rows + k_chunks + k_merge 8.06 + 0.00 + 45.00 + 26.28 + 0.07 GB.
+# Captured on 2026-11-25 with the kernels of commit ea39e14 (the sweeps have since gained streaming stores of their
+# results, which changes no DRAM byte count); a kernel change that moves bytes needs a new capture.
 # The share of gathered rows that the L2 serves depends on the graph's size (231 B per edge at 300 k nodes /
 # 12 M edges against 568 here), so the figure is only attached to runs of the captured workload.
 TRAFFIC_WORKLOAD = (2_400_000, 120_000_000)
@@ -53,6 +55,10 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--stages", type=int, default=0,
                     help="sweeps per pass of the sharded layer: stage 0 = own nodes, the others one halo chunk each (0: 2 on two GPUs, else 3)")
+    ap.add_argument("--schedule", default="staged", choices=["staged", "rowsets"],
+                    help="staged: every sweep covers all rows and one slice of the sources (state carried between sweeps); "
+                         "rowsets: every sweep finishes a range of rows once the halo rows it references have arrived")
+    ap.add_argument("--fractions", default="", help="rowsets: cumulative shares of a rank's edges per sweep, e.g. 0.08,0.25,0.55,1")
     ap.add_argument("--halo-mode", default="dma", choices=["dma", "pull"],
                     help="dma: owners pack, peers copy with the copy engines; pull: a kernel loads the rows from peer memory")
     ap.add_argument("--pull-ctas", type=int, default=48, help="grid bound of the halo fetch kernel in pull mode (0: unbounded)")
@@ -324,7 +330,9 @@ def run_ours(args, rank, world, local):
         del cp, ri, pm
         if args.stages <= 0:
             args.stages = 2 if world == 2 else 3
-        shard = gdist.build_halo_shard(rp, ci, rank, world, stages=args.stages, seed=7)
+        fractions = tuple(float(v) for v in args.fractions.split(",")) if args.fractions else None
+        shard = gdist.build_halo_shard(rp, ci, rank, world, stages=args.stages, seed=7, schedule=args.schedule, fractions=fractions)
+        args.stages = shard.stages
         transport = gdist.GatherTransport(shard) if args.gather_fallback else gdist.make_transport(shard, None, args.halo_mode, args.pull_ctas)
         if hasattr(transport, "overlap_publish"):
             transport.overlap_publish = bool(args.overlap_publish)
@@ -486,7 +494,7 @@ def run_ours(args, rank, world, local):
     fwd_ms, bwd_ms = timer.mean_ms("fwd"), None
     if timer.mean_ms("bwd_cols") and timer.mean_ms("bwd_stat"):      # the layer calls the two halves of the backward itself
         bwd_ms = timer.mean_ms("bwd_stat") + timer.mean_ms("bwd_cols")
-    sharded = (f", node blocks over {world} GPUs, {args.stages} sweeps per pass, halo rows by "
+    sharded = (f", node blocks over {world} GPUs, {args.stages} sweeps per pass ({args.schedule}), halo rows by "
                + ("all-gathers" if args.gather_fallback else ("packed send buffers in symmetric memory copied by the copy engines"
                                                          if args.halo_mode == "dma" else "peer loads from symmetric memory"))) if world > 1 else ""
     line = {

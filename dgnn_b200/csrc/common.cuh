@@ -259,32 +259,48 @@ __device__ __forceinline__ bool dgnn_row_role(const Op& op, i64 r, bool& first, 
 // rows.  The batch grows as the average row gets shorter, which keeps the rate of
 // atomics on the one counter far below what the memory system serialises, and the
 // batch's index pointers arrive in one coalesced load.
+// Rows of more than DGNN_HEAVY entries are drawn first (pass 0, from next_row[0], 31 rows per draw of which the
+// light ones are skipped at once), all others afterwards (pass 1, next_row[1]); a warp goes on to pass 1 as soon as
+// pass 0 has no rows left, there is no barrier in between.  A row is one warp's work from its first entry to its last
+// (about 0.4 us per entry in the GAT sweeps), so the last rows to be drawn decide how long the grid idles at its end:
+// with the heavy rows out of the way that is a row of at most DGNN_HEAVY entries instead of one of up to DGNN_SEG.
+#ifndef DGNN_HEAVY_ROWS
+#define DGNN_HEAVY_ROWS 128
+#endif
+constexpr int DGNN_HEAVY = DGNN_HEAVY_ROWS;
 template <class Op>
 __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op, unsigned long long* next_row, const int batch) {
   extern __shared__ float4 dgnn_smem4[];
   const int lane = threadIdx.x & 31;
   float4* ring = dgnn_smem4 + (size_t)(threadIdx.x >> 5) * (op.ring_bytes() / 16);
-  for (;;) {
-    unsigned long long t = 0;
-    if (lane == 0) t = atomicAdd(next_row, (unsigned long long)batch);
-    const i64 r0 = (i64)__shfl_sync(DGNN_FULL, t, 0);
-    if (r0 >= op.n_rows) break;
-    const int cnt = (int)((op.n_rows - r0 < batch) ? op.n_rows - r0 : batch);
-    const i64 mine = lane <= cnt ? ldp(op.indptr, op.idx_bits, r0 + lane) : 0;
-    for (int i = 0; i < cnt; ++i) {
-      const i64 r = r0 + i;
-      const i64 lb = __shfl_sync(DGNN_FULL, mine, i);
-      const i64 hb = __shfl_sync(DGNN_FULL, mine, i + 1);
-      if (hb - lb > DGNN_SEG) continue;  // long row: chunk + merge kernels own it
-      if (op.skip_empty && hb == lb) continue;  // middle stage of a staged sweep: the carried state stays as it is
-      bool first, last;
-      if (!dgnn_row_role(op, r, first, last)) continue;
-      typename Op::State st;
-      op.init(st, r, lane);
-      op.resume(st, r, lane, first);
-      op.range(st, r, lb, hb, lane, ring);
-      op.combine(st, lane);
-      op.finalize(st, r, lane, last);
+  for (int pass = 0; pass < 2; ++pass) {
+    const int draw = pass == 0 ? 31 : batch;
+    for (;;) {
+      unsigned long long t = 0;
+      if (lane == 0) t = atomicAdd(next_row + pass, (unsigned long long)draw);
+      const i64 r0 = (i64)__shfl_sync(DGNN_FULL, t, 0);
+      if (r0 >= op.n_rows) break;
+      const int cnt = (int)((op.n_rows - r0 < draw) ? op.n_rows - r0 : draw);
+      const i64 mine = lane <= cnt ? ldp(op.indptr, op.idx_bits, r0 + lane) : 0;
+      const i64 len = __shfl_down_sync(DGNN_FULL, mine, 1) - mine;   // lane i < cnt: length of row r0 + i
+      // long rows belong to the chunk + merge kernels; empty rows of a middle stage keep their carried state
+      const bool take = lane < cnt && len <= DGNN_SEG && ((len > DGNN_HEAVY) == (pass == 0)) && !(op.skip_empty && len == 0);
+      unsigned todo = __ballot_sync(DGNN_FULL, take);
+      while (todo) {
+        const int i = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const i64 r = r0 + i;
+        const i64 lb = __shfl_sync(DGNN_FULL, mine, i);
+        const i64 hb = __shfl_sync(DGNN_FULL, mine, i + 1);
+        bool first, last;
+        if (!dgnn_row_role(op, r, first, last)) continue;
+        typename Op::State st;
+        op.init(st, r, lane);
+        op.resume(st, r, lane, first);
+        op.range(st, r, lb, hb, lane, ring);
+        op.combine(st, lane);
+        op.finalize(st, r, lane, last);
+      }
     }
   }
 }
@@ -378,8 +394,8 @@ static inline unsigned dgnn_grid(i64 items, int per_block) {
 }
 static inline i64 dgnn_num_chunks(i64 nnz) { return (nnz + DGNN_SEG - 1) / DGNN_SEG; }
 
-// Launch the row / chunk / merge trio for one operator.  `counter` points at 8
-// zero-able bytes of workspace (the row counter of k_rows).
+// Launch the row / chunk / merge trio for one operator.  `counter` points at 16
+// zero-able bytes of workspace (the two row counters of k_rows).
 // kernels whose dynamic shared memory exceeds the 48 KB default need the limit raised once per launch site
 template <class K>
 static inline cudaError_t dgnn_allow_smem(K kernel, size_t bytes) {
@@ -399,7 +415,7 @@ static inline int dgnn_launch_trio(const Op& op, unsigned long long* counter, cu
     cudaError_t e0 = cudaGetLastError();
     return e0 == cudaSuccess ? DGNN_OK : (int)e0;
   }
-  e = cudaMemsetAsync(counter, 0, sizeof(unsigned long long), s);
+  e = cudaMemsetAsync(counter, 0, 2 * sizeof(unsigned long long), s);
   if (e != cudaSuccess) return (int)e;
   {
     int dev = 0, sms = 148;

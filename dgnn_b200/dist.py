@@ -52,6 +52,7 @@ class HaloSide:
     ind: list                         # per stage: buffer row of every entry, int32
     edge_id: list | None = None       # per stage: position of the entry in the CSR of the whole graph (int32)
     stage_mask: torch.Tensor = None   # [blk] uint8: bit p = the segment has entries in stage p
+    bounds: list | None = None        # "rowsets" schedule: stage p holds ALL entries of the segments bounds[p]:bounds[p+1]
 
 
 @dataclass
@@ -64,13 +65,21 @@ class HaloShard:
     local_ids: torch.Tensor           # original node id of every local row (-1 for padding)
     fwd: HaloSide = None
     bwd: HaloSide = None
+    schedule: str = "staged"          # "staged": every sweep covers all segments and one slice of the far ends, the
+                                      # per-segment state is carried between sweeps.  "rowsets": every sweep finishes
+                                      # a range of segments (all their entries); halo chunk p = the halo rows that
+                                      # ranges 0..p reference first.  No carried state; the first sweep waits for chunk 0
 
     @property
     def chunks(self):
+        if self.schedule == "rowsets":
+            return self.stages
         return max(self.stages - 1, 1)
 
     def chunk_stage(self, c):
-        """The stage that needs halo chunk c."""
+        """The first stage that needs halo chunk c."""
+        if self.schedule == "rowsets":
+            return c
         return c + 1 if self.stages > 1 else 0
 
     def scatter_rows(self, x_global):
@@ -93,14 +102,36 @@ def _expand_segments(ptr, ids):
     return pos, seg
 
 
-def _build_side(ptr, ind, edge_pos, local_ids, inv, rank, blk, n_pad, stages, want_ids) -> HaloSide:
+def _set_bounds(seg, blk, fractions):
+    """Segment ranges whose entry counts follow the cumulative `fractions` (the last one is 1)."""
+    cnt = torch.bincount(seg, minlength=blk)
+    cum = torch.cumsum(cnt, 0)
+    total = int(cum[-1]) if blk else 0
+    bounds = [0]
+    for fr in fractions[:-1]:
+        r = int(torch.searchsorted(cum, torch.tensor(int(fr * total), device=cum.device), right=True))
+        bounds.append(min(max(r, bounds[-1]), blk))
+    bounds.append(blk)
+    return bounds, cnt
+
+
+def _build_side(ptr, ind, edge_pos, local_ids, inv, rank, blk, n_pad, stages, want_ids, fractions=None) -> HaloSide:
     dev = ind.device
-    chunks = max(stages - 1, 1)
+    rowsets = fractions is not None
+    chunks = stages if rowsets else max(stages - 1, 1)
     pos, seg = _expand_segments(ptr, local_ids)
     other = inv[ind[pos].long()]                                   # relabelled id of the far end
     own = (other // blk) == rank
     uniq = torch.unique(other[~own])                               # ascending = (owner, row in block)
-    u_chunk = ((uniq % blk) * chunks) // blk                       # position slice inside the owner's block
+    if rowsets:
+        bounds, seg_cnt = _set_bounds(seg, blk, fractions)
+        set_of_seg = torch.bucketize(torch.arange(blk, device=dev), torch.tensor(bounds[1:-1], device=dev), right=True)
+        set_of_entry = set_of_seg[seg]
+        u_chunk = torch.full((uniq.numel(),), chunks, dtype=torch.long, device=dev)
+        if uniq.numel():                                           # chunk = the first set that references the row
+            u_chunk.scatter_reduce_(0, torch.searchsorted(uniq, other[~own]), set_of_entry[~own], reduce="amin")
+    else:
+        u_chunk = ((uniq % blk) * chunks) // blk                   # position slice inside the owner's block
     order = torch.argsort(u_chunk * n_pad + uniq)                  # chunk-major, then owner, then row
     place = torch.empty_like(order)
     place[order] = torch.arange(order.numel(), device=dev)         # halo row of uniq[i]
@@ -115,8 +146,21 @@ def _build_side(ptr, ind, edge_pos, local_ids, inv, rank, blk, n_pad, stages, wa
         rem = ~own
         hidx = torch.searchsorted(uniq, other[rem])
         buf[rem] = blk + place[hidx]
-        if stages > 1:
+        if stages > 1 and not rowsets:
             stage[rem] = 1 + u_chunk[hidx]
+    if rowsets:
+        eid = pos if edge_pos is None else edge_pos[pos].long()
+        ptrs, inds, ids = [], [], []
+        for p_ in range(stages):
+            r0, r1 = bounds[p_], bounds[p_ + 1]
+            sp = torch.zeros(r1 - r0 + 1, dtype=torch.long, device=dev)
+            torch.cumsum(seg_cnt[r0:r1], 0, out=sp[1:])
+            m = set_of_entry == p_                                 # a contiguous run: entries are grouped by segment
+            ptrs.append(sp.to(torch.int32))
+            inds.append(buf[m].to(torch.int32).contiguous())
+            if want_ids:
+                ids.append(eid[m].to(torch.int32).contiguous())
+        return HaloSide(int(uniq.numel()), codes, chunk_off, ptrs, inds, ids if want_ids else None, None, bounds)
     if stages > 8:
         raise ValueError("dgnn_b200: at most 8 stages (one bit per stage in the per-row stage mask)")
     ptrs, inds, ids = [], [], []
@@ -136,13 +180,30 @@ def _build_side(ptr, ind, edge_pos, local_ids, inv, rank, blk, n_pad, stages, wa
                     smask.to(torch.uint8).contiguous())
 
 
+ROWSET_FRACTIONS = (0.08, 0.25, 0.55, 1.0)
+
+
 def build_halo_shard(row_ptr, col_ind, rank, world, stages=3, seed=0, csr2csc=None, edge_ids=False,
-                     relabel=True) -> HaloShard:
+                     relabel=True, schedule="staged", fractions=None) -> HaloShard:
     """Cut rank's pieces out of the global CSR (rows = destinations).  Every rank calls this with the same
     graph, seed and options.  `edge_ids` keeps, for every local entry, its position in the global CSR (needed
     for attention dropout: the mask of an edge is a function of that position, the same on the rank that
     holds the edge in its forward piece and on the rank that holds it in its backward piece).
-    relabel=False keeps the node order (contiguous equal blocks)."""
+    relabel=False keeps the node order (contiguous equal blocks).
+    schedule="rowsets": sweep p finishes the rows (columns in the backward) of one range completely -- `fractions`
+    = cumulative shares of the rank's entries per range, default ROWSET_FRACTIONS, `stages` is their number -- and
+    needs the halo rows that ranges 0..p reference; nothing is carried between sweeps."""
+    if schedule not in ("staged", "rowsets"):
+        raise ValueError("dgnn_b200: schedule is 'staged' or 'rowsets'")
+    if schedule == "rowsets":
+        fractions = tuple(fractions) if fractions is not None else ROWSET_FRACTIONS
+        if world == 1:
+            fractions = (1.0,)
+        if not fractions or abs(fractions[-1] - 1.0) > 1e-9 or any(b < a for a, b in zip(fractions, fractions[1:])):
+            raise ValueError("dgnn_b200: fractions are cumulative shares ending in 1")
+        stages = len(fractions)
+    else:
+        fractions = None
     if world > HALO_MAX_RANKS:
         raise ValueError(f"dgnn_b200: at most {HALO_MAX_RANKS} ranks")
     csr2csc = csr2csc or kernels.csr2csc
@@ -167,11 +228,11 @@ def build_halo_shard(row_ptr, col_ind, rank, world, stages=3, seed=0, csr2csc=No
     real = order >= 0
     inv[order[real]] = torch.arange(n_pad, device=dev)[real]
     local_ids = order[rank * blk: (rank + 1) * blk].contiguous()
-    shard = HaloShard(rank, world, int(stages), n, blk, local_ids)
-    shard.fwd = _build_side(rp, col_ind, None, local_ids, inv, rank, blk, n_pad, stages, edge_ids)
+    shard = HaloShard(rank, world, int(stages), n, blk, local_ids, schedule=schedule)
+    shard.fwd = _build_side(rp, col_ind, None, local_ids, inv, rank, blk, n_pad, stages, edge_ids, fractions)
     col_ptr, row_ind, permute = csr2csc(row_ptr, col_ind)
     shard.bwd = _build_side(col_ptr.long(), row_ind, permute if edge_ids else None, local_ids, inv, rank, blk, n_pad,
-                            stages, edge_ids)
+                            stages, edge_ids, fractions)
     return shard
 
 
@@ -627,6 +688,8 @@ def halo_forward_sweep(ctx: HaloContext, attn_row, bias=None, attn_drop=0.0, see
     sh, be = ctx.shard, ctx.backend
     works = ctx.transport.start_pulls(sh.fwd, [ctx.X, ctx.AC], ctx.tags[0:2])
     masks = _masks(ctx, sh.fwd, attn_drop, seed)
+    if sh.schedule == "rowsets":
+        return _forward_rowsets(ctx, works, masks, attn_row, bias, attn_drop, train)
     state = be.gat_forward_state(sh.blk, ctx.h, ctx.f, ctx.X.device)
     waited, res = 0, None
     for p in range(sh.stages):
@@ -641,6 +704,49 @@ def halo_forward_sweep(ctx: HaloContext, attn_row, bias=None, attn_drop=0.0, see
     if train:
         return res
     return res[0], None, None, None, None
+
+
+def _forward_rowsets(ctx, works, masks, attn_row, bias, attn_drop, train):
+    """Sweep p finishes the rows bounds[p]:bounds[p+1] (all their edges) once halo chunks 0..p are there."""
+    sh, be = ctx.shard, ctx.backend
+    dev, blk, h, f = ctx.X.device, sh.blk, ctx.h, ctx.f
+    out = torch.empty((blk, h, f), dtype=torch.float32, device=dev)
+    stats = [torch.empty((blk, h), dtype=torch.float32, device=dev) for _ in range(2)] if train else [None, None]
+    out_neg = torch.empty((blk, h, f), dtype=torch.float32, device=dev) if train else None
+    a_neg = torch.empty((blk, h), dtype=torch.float32, device=dev) if train else None
+    waited = 0
+    for p in range(sh.stages):
+        while waited < sh.chunks and sh.chunk_stage(waited) <= p:
+            _timed_wait(ctx, works[waited], "fwd", waited)
+            waited += 1
+        r0, r1 = sh.fwd.bounds[p], sh.fwd.bounds[p + 1]
+        if r1 == r0:
+            continue
+        cut = lambda t: None if t is None else t[r0:r1]
+        be.gat_forward_staged(attn_row[r0:r1], ctx.AC, sh.fwd.ptr[p], sh.fwd.ind[p], ctx.slope, ctx.X, None, True, True,
+                              bias=bias, attn_drop=attn_drop, edge_mask=masks[p], neg=train, save_stats=train,
+                              outs=(out[r0:r1], cut(stats[0]), cut(stats[1]), cut(out_neg), cut(a_neg)))
+    return out, stats[0], stats[1], out_neg, a_neg
+
+
+def _backward_rowsets(ctx, works, masks, attn_drop):
+    """Sweep p finishes the source columns bounds[p]:bounds[p+1] once halo chunks 0..p of grad_out / pack are there."""
+    sh, be = ctx.shard, ctx.backend
+    dev, blk, h, f = ctx.X.device, sh.blk, ctx.h, ctx.f
+    grad_feat = torch.empty((blk, h, f), dtype=torch.float32, device=dev)
+    grad_col = torch.empty((blk, h), dtype=torch.float32, device=dev)
+    waited = 0
+    for p in range(sh.stages):
+        while waited < sh.chunks and sh.chunk_stage(waited) <= p:
+            _timed_wait(ctx, works[waited], "bwd", waited)
+            waited += 1
+        c0, c1 = sh.bwd.bounds[p], sh.bwd.bounds[p + 1]
+        if c1 == c0:
+            continue
+        be.gat_backward_cols_staged(None, sh.bwd.ptr[p], sh.bwd.ind[p], None, ctx.PK, ctx.X[c0:c1], ctx.AC[c0:c1], ctx.G,
+                                    ctx.slope, None, True, True, attn_drop=attn_drop, edge_mask=masks[p], row_grad=False,
+                                    outs=(grad_feat[c0:c1], grad_col[c0:c1]))
+    return grad_feat, grad_col
 
 
 def halo_backward_prepare(ctx: HaloContext, attn_row, edge_max, edge_sum, out, out_neg, a_neg, grad_out, bias=None):
@@ -661,6 +767,8 @@ def halo_backward_sweep(ctx: HaloContext, attn_drop=0.0, seed=0):
     sh, be = ctx.shard, ctx.backend
     works = ctx.transport.start_pulls(sh.bwd, [ctx.G, ctx.PK], ctx.tags[2:4])
     masks = _masks(ctx, sh.bwd, attn_drop, seed)
+    if sh.schedule == "rowsets":
+        return _backward_rowsets(ctx, works, masks, attn_drop)
     state = be.gat_backward_state(sh.blk, ctx.h, ctx.f, ctx.X.device)
     waited = 0
     outs = None

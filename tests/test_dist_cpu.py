@@ -36,6 +36,7 @@ class OracleBackend:
     def gat_forward_staged(attn_row, attn_col_buf, row_ptr, col_ind, slope, feat_buf, state, first, last, bias=None,
                            attn_drop=0.0, edge_mask=None, neg=False, save_stats=True, stage_mask=None, stage=0, outs=None):
         # every row takes part in every stage here (the per-row stage mask only saves work on the GPU)
+        state = {} if state is None else state            # a single complete sweep (first = last) carries nothing
         n, h = attn_row.shape
         rows = orc.edge_rows(row_ptr)
         cols = col_ind.long()
@@ -69,8 +70,14 @@ class OracleBackend:
         if bias is not None:
             out = out + bias.view(1, h, -1)
         if not neg:
-            return out, (state["m"] if save_stats else None), (z if save_stats else None)
-        return out, state["m"], z, state["accn"] * inv[:, :, None], state["zn"] * inv
+            res = (out, (state["m"] if save_stats else None), (z if save_stats else None))
+        else:
+            res = (out, state["m"], z, state["accn"] * inv[:, :, None], state["zn"] * inv)
+        if outs is not None:                              # like the kernels: results land in the caller's tensors
+            for dst, src in zip(outs, res):
+                if dst is not None and src is not None:
+                    dst.copy_(src)
+        return res
 
     @staticmethod
     def gat_rowstat_full(attn_row, edge_max, edge_sum, out, grad_out, slope, bias=None, out_neg=None, a_neg=None,
@@ -102,10 +109,13 @@ class OracleBackend:
         d = torch.where(leaky < 0, d * slope, d)
         gf = torch.zeros_like(in_feat).index_add_(0, cols, (alpha * keep)[:, :, None] * grad_buf[rows])
         gc = torch.zeros_like(attn_col).index_add_(0, cols, d)
+        state = {} if state is None else state
         if first:
             state["gf"], state["gc"] = gf, gc
         else:
             state["gf"], state["gc"] = state["gf"] + gf, state["gc"] + gc
+        if last and outs is not None and outs[0] is not None:
+            outs[0].copy_(state["gf"]); outs[1].copy_(state["gc"])
         return None, (state["gf"] if last else None), (state["gc"] if last else None)
 
 
@@ -135,7 +145,7 @@ def _check_ranks(results, ref, n):
     assert torch.equal(torch.sort(torch.cat(seen)).values, torch.arange(n))     # every node owned exactly once
 
 
-def _gloo_worker(rank, world, port, h, f, stages, p):
+def _gloo_worker(rank, world, port, h, f, stages, p, schedule="staged"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
@@ -146,7 +156,8 @@ def _gloo_worker(rank, world, port, h, f, stages, p):
             mask = torch.rand(ci.numel(), h, generator=torch.Generator().manual_seed(77))
             OracleBackend.global_mask = mask
         ar, ac, x, g = gat_inputs(rp, rp.numel() - 1, h, f, seed=5)
-        shard = gdist.build_halo_shard(rp, ci, rank, world, stages=stages, seed=3, csr2csc=orc.csr2csc, edge_ids=p > 0)
+        shard = gdist.build_halo_shard(rp, ci, rank, world, stages=stages, seed=3, csr2csc=orc.csr2csc, edge_ids=p > 0,
+                                       schedule=schedule, fractions=(0.1, 0.5, 1.0) if schedule == "rowsets" else None)
         hc = gdist.HaloContext(shard, gdist.GatherTransport(shard), h, f, 0.2, backend=OracleBackend)
         loc = [shard.scatter_rows(t).requires_grad_() for t in (ar, ac, x)]
         out = gdist.sharded_gat(*loc, hc, attn_drop=p, seed=1)
@@ -157,27 +168,29 @@ def _gloo_worker(rank, world, port, h, f, stages, p):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,stages,p", [(2, 1, 0.0), (2, 3, 0.0), (3, 2, 0.0), (2, 2, 0.4)])
-def test_sharded_gat_gloo_equals_single(world, stages, p):
+@pytest.mark.parametrize("world,stages,p,schedule", [(2, 1, 0.0, "staged"), (2, 3, 0.0, "staged"), (3, 2, 0.0, "staged"),
+                                                     (2, 2, 0.4, "staged"), (2, 3, 0.0, "rowsets"), (3, 3, 0.4, "rowsets")])
+def test_sharded_gat_gloo_equals_single(world, stages, p, schedule):
     h, f = 2, 4
     mask = torch.rand(0)
     rp, ci, _, _ = _reference(h, f)
     if p > 0:
         mask = torch.rand(ci.numel(), h, generator=torch.Generator().manual_seed(77))
     _, _, _, ref = _reference(h, f, p, mask if p > 0 else None)
-    results = run_ranks(_gloo_worker, world, (h, f, stages, p), timeout=240)
+    results = run_ranks(_gloo_worker, world, (h, f, stages, p, schedule), timeout=240)
     _check_ranks(results, ref, GRAPH["n"])
 
 
 @pytest.mark.parametrize("mode", ["dma", "pull"])
-@pytest.mark.parametrize("world,stages", [(1, 1), (2, 2), (4, 3), (3, 1)])
+@pytest.mark.parametrize("world,stages", [(1, 1), (2, 2), (4, 3), (3, 1), (1, 0), (2, 0), (4, 0)])
 def test_all_ranks_emulated_in_one_process(world, stages, mode):
     """LocalTransport: every rank's buffers in one registry, phases run in lockstep.  "dma": owners pack what each
     peer needs into send buffers and the peers copy their contiguous ranges (the send plan); "pull": the halo rows
     are picked out of the owners' buffers by their codes."""
     h, f = 2, 4
     rp, ci, (ar, ac, x, g), ref = _reference(h, f)
-    shards = [gdist.build_halo_shard(rp, ci, r, world, stages=stages, seed=9, csr2csc=orc.csr2csc) for r in range(world)]
+    kw = dict(schedule="rowsets", fractions=(0.05, 0.3, 0.3, 1.0)) if stages == 0 else dict(stages=stages)   # 0: row sets (one empty)
+    shards = [gdist.build_halo_shard(rp, ci, r, world, seed=9, csr2csc=orc.csr2csc, **kw) for r in range(world)]
     ctxs = [gdist.HaloContext(s, t, h, f, 0.2, backend=OracleBackend)
             for s, t in zip(shards, gdist.LocalTransport.for_all(shards, mode))]
     loc = [[s.scatter_rows(t) for t in (ar, ac, x, g)] for s in shards]
@@ -193,14 +206,15 @@ def test_all_ranks_emulated_in_one_process(world, stages, mode):
     _check_ranks(results, ref, GRAPH["n"])
 
 
-@pytest.mark.parametrize("world,stages,relabel", [(1, 1, True), (3, 1, True), (4, 3, True), (2, 2, False)])
+@pytest.mark.parametrize("world,stages,relabel", [(1, 1, True), (3, 1, True), (4, 3, True), (2, 2, False), (3, 0, True)])
 def test_halo_shard_invariants(world, stages, relabel):
     rp, ci = synth.random_graph(200, 5, seed=4, long_rows=[(7, 300)])
     n, nnz = rp.numel() - 1, ci.numel()
     cp, ri, pm = orc.csr2csc(rp, ci)
     owned, fwd_ids, bwd_ids = [], [], []
-    shards = [gdist.build_halo_shard(rp, ci, r, world, stages=stages, seed=1, csr2csc=orc.csr2csc, edge_ids=True,
-                                     relabel=relabel) for r in range(world)]
+    kw = dict(schedule="rowsets", fractions=(0.1, 0.4, 1.0)) if stages == 0 else dict(stages=stages)   # 0: row sets
+    shards = [gdist.build_halo_shard(rp, ci, r, world, seed=1, csr2csc=orc.csr2csc, edge_ids=True, relabel=relabel, **kw)
+              for r in range(world)]
     for s in shards:
         owned.append(s.local_ids[s.local_ids >= 0])
         for side, glob_ptr, glob_ind in ((s.fwd, rp.long(), ci.long()), (s.bwd, cp, ri)):
@@ -215,18 +229,25 @@ def test_halo_shard_invariants(world, stages, relabel):
             for p in range(s.stages):
                 ptr, ind, eid = side.ptr[p].long(), side.ind[p].long(), side.edge_id[p].long()
                 assert ptr[0] == 0 and ptr[-1] == ind.numel() == eid.numel()
-                assert torch.equal(((side.stage_mask.long() >> p) & 1).bool(), (ptr[1:] - ptr[:-1]) > 0)   # bit p = has entries in stage p
                 seg = orc.edge_rows(ptr)
+                if s.schedule == "rowsets":                            # stage p = all entries of segments bounds[p]:bounds[p+1]
+                    assert ptr.numel() - 1 == side.bounds[p + 1] - side.bounds[p] and side.stage_mask is None
+                    assert bool((ind < s.blk + side.chunk_off[p + 1]).all())      # only own rows and chunks 0..p
+                    new = ind[ind >= s.blk + side.chunk_off[p]]                   # chunk p: first referenced by this set
+                    assert new.unique().numel() == side.chunk_off[p + 1] - side.chunk_off[p]
+                    seg = seg + side.bounds[p]
+                else:
+                    assert torch.equal(((side.stage_mask.long() >> p) & 1).bool(), (ptr[1:] - ptr[:-1]) > 0)   # bit p = has entries in stage p
                 far = buf_orig[ind]                                    # original id of the far end of every entry
                 near = s.local_ids[seg]
                 if side is s.fwd:
                     assert torch.equal(far, ci.long()[eid]) and torch.equal(near, orc.edge_rows(rp)[eid])
-                    assert bool(((ind < s.blk) == (p == 0)).all()) or s.stages == 1
+                    assert bool(((ind < s.blk) == (p == 0)).all()) or s.stages == 1 or s.schedule == "rowsets"
                     fwd_ids.append(eid)
                 else:
                     assert torch.equal(far, orc.edge_rows(rp)[eid]) and torch.equal(near, ci.long()[eid])
                     bwd_ids.append(eid)
-                if s.stages > 1 and p > 0:                             # stage p holds exactly halo chunk p-1
+                if s.schedule == "staged" and s.stages > 1 and p > 0:  # stage p holds exactly halo chunk p-1
                     lo, hi = s.blk + side.chunk_off[p - 1], s.blk + side.chunk_off[p]
                     assert bool(((ind >= lo) & (ind < hi)).all())
     assert torch.equal(torch.sort(torch.cat(owned)).values, torch.arange(n))

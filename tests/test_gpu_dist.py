@@ -28,8 +28,10 @@ def _single_gpu(rp, ci, ar, ac, x, g, p=0.0, seed=0):
 
 
 @pytest.mark.parametrize("world,stages,p,mode", [(1, 1, 0.0, "dma"), (2, 1, 0.0, "dma"), (2, 2, 0.0, "pull"), (4, 3, 0.0, "dma"),
-                                                 (3, 4, 0.3, "dma"), (3, 4, 0.3, "pull"), (8, 3, 0.0, "dma"), (8, 3, 0.0, "pull")])
+                                                 (3, 4, 0.3, "dma"), (3, 4, 0.3, "pull"), (8, 3, 0.0, "dma"), (8, 3, 0.0, "pull"),
+                                                 (2, 0, 0.0, "dma"), (4, 0, 0.3, "dma"), (8, 0, 0.0, "pull")])
 def test_emulated_ranks_equal_single_gpu(cuda, world, stages, p, mode):
+    """stages = 0: the row-set schedule (every sweep finishes a range of rows; four ranges)."""
     from dgnn_b200 import dist as gdist
     from dgnn_b200 import kernels, synth
     n, e, h, f = 20_000, 600_000, 8, 32
@@ -39,7 +41,8 @@ def test_emulated_ranks_equal_single_gpu(cuda, world, stages, p, mode):
     al, ar_ = torch.randn(1, h, f, generator=gen).to(cuda), torch.randn(1, h, f, generator=gen).to(cuda)
     ar, ac = kernels.gat_logits_forward(x, al, ar_)        # the layer form: logits from the features
     out, gf, gr, gc = _single_gpu(rp, ci, ar, ac, x, g, p, seed=123)
-    shards = [gdist.build_halo_shard(rp, ci, r, world, stages=stages, seed=5, edge_ids=p > 0) for r in range(world)]
+    kw = dict(schedule="rowsets") if stages == 0 else dict(stages=stages)
+    shards = [gdist.build_halo_shard(rp, ci, r, world, seed=5, edge_ids=p > 0, **kw) for r in range(world)]
     ctxs = [gdist.HaloContext(s, t, h, f, 0.2) for s, t in zip(shards, gdist.LocalTransport.for_all(shards, mode, pull_ctas=8))]
     loc = [[s.scatter_rows(t) for t in (x, g)] for s in shards]
     # phases in lockstep: own rows (the logits kernel and the row-statistics kernel also write the send buffers), then the sweeps
@@ -132,7 +135,7 @@ def _layer_worker(rank, world, port, n, e, in_feats, heads, width, stages):
         cot = torch.randn(n, heads, width, device=dev, generator=g)
         report = {}
         for name, kw in (("plain", {}), ("residual_relu", dict(residual=True, activation=torch.relu)),
-                         ("attn_drop", dict(attn_drop=0.3))):
+                         ("attn_drop", dict(attn_drop=0.3)), ("rowsets", {}), ("rowsets_attn_drop", dict(attn_drop=0.3))):
             torch.manual_seed(11)
             # the residual branch of the reference is applied to the projected features: identity when in_feats == H*F
             feat = feat_wide if "residual" in kw else feat_in
@@ -140,7 +143,8 @@ def _layer_worker(rank, world, port, n, e, in_feats, heads, width, stages):
             ref = GATConv(in_feats, width, heads, **kw).to(dev).train()
             with torch.no_grad():
                 ref.bias.uniform_(-1.0, 1.0)
-            shard = gdist.build_halo_shard(rp, ci, rank, world, stages=stages, seed=5, edge_ids="attn_drop" in kw)
+            sched = dict(schedule="rowsets") if name.startswith("rowsets") else dict(stages=stages)
+            shard = gdist.build_halo_shard(rp, ci, rank, world, seed=5, edge_ids="attn_drop" in kw, **sched)
             layer = gdist.ShardedGATConv(in_feats, width, heads, shard, seed=42, **kw).to(dev).train()
             layer.load_state_dict(ref.state_dict())
             report[name + "_transport"] = type(layer.transport).__name__
@@ -190,7 +194,7 @@ def test_sharded_layer_equals_single_gpu_layer(cuda):
         pytest.skip("needs at least 2 GPUs")
     reports = run_ranks(_layer_worker, world, (50_000, 2_000_000, 100, 8, 32, 3), timeout=600)
     for rank, rep in enumerate(reports):
-        for name in ("plain", "residual_relu", "attn_drop"):
+        for name in ("plain", "residual_relu", "attn_drop", "rowsets", "rowsets_attn_drop"):
             assert rep[name + "_transport"] == "SymmetricTransport", (rank, rep[name + "_transport"])
             r = rep[name]
             # outputs to 1e-4 relative / 1e-5 absolute; parameter gradients (sums over 50 k rows) within 1e-4 of their largest entry
