@@ -146,6 +146,8 @@ def suite_edgeconv(iters):
         report("edgeconv_forward", cfg, timed(lambda: kernels.edgeconv_forward(k, src, hs, hd), iters, True),
                4 * m * k + 4 * m * k * f + 12 * m * f, compulsory_bytes=4 * m * k + 16 * m * f)
         report("edgeconv_backward", cfg, timed(lambda: kernels.edgeconv_backward(go, idx), iters, True), 20 * m * f)
+        report("edgeconv_backward_ordered (csr2csc of the kNN graph + gather, reproducible)", cfg,
+               timed(lambda: kernels.edgeconv_backward_ordered(k, src, go, idx), iters, True), 20 * m * f)
 
 
 def check_csc(rp, ci, cp, ri, pm, n):

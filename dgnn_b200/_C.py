@@ -86,6 +86,7 @@ SIGNATURES = {
     "dgnn_gaussian_bp": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_edgeconv_forward": (c_int, [c_i64, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_edgeconv_backward": (c_int, [c_i64, c_int, c_p, c_p, c_p, c_p]),
+    "dgnn_edgeconv_backward_ordered": (c_int, [c_i64, c_int, c_p, c_p, c_p, c_p, c_p, c_p]),
     "dgnn_csr2csc_workspace_bytes": (c_sz, [c_i64, c_i64, c_i64]),
     "dgnn_csr2csc": (c_int, [c_i64, c_i64, c_i64, c_p, c_int, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
     "dgnn_csr2csc_static_max_nnz": (c_i64, []),

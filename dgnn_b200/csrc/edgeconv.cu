@@ -71,6 +71,28 @@ __global__ void k_edgeconv_bwd(i64 total, int f, const int* max_idx, const float
   atomicAdd(grad_src + (i64)id * f + (t % f), __ldg(grad_out + t));
 }
 
+// Reproducible backward: one thread per (source point s, feature j).  The in-edges of s come from the CSC form of the
+// neighbour graph (destinations ascending); destination i contributes grad_out[i, j] when it selected s for feature j,
+// added in ascending i.  A destination that lists s more than once (adjacent after the sort) is counted once, as in
+// the forward, which keeps the first of equal sums.  No atomics: the sum has one fixed order.
+__global__ void k_edgeconv_bwd_ordered(i64 m, int f, const int* col_ptr, const int* row_ind, const int* max_idx,
+                                       const float* grad_out, float* grad_src) {
+  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= m * f) return;
+  const i64 s = t / f;
+  const int j = (int)(t - s * f);
+  const int e0 = __ldg(col_ptr + s), e1 = __ldg(col_ptr + s + 1);
+  float acc = 0.f;
+  int prev = -1;
+  for (int e = e0; e < e1; ++e) {
+    const int i = __ldg(row_ind + e);
+    if (i == prev) continue;
+    prev = i;
+    if (__ldg(max_idx + (i64)i * f + j) == (int)s) acc += __ldg(grad_out + (i64)i * f + j);
+  }
+  grad_src[t] = acc;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -105,6 +127,18 @@ int dgnn_edgeconv_backward(int64_t m, int f, const int32_t* max_idx, const float
   if (e != cudaSuccess) return (int)e;
   k_edgeconv_bwd<<<dgnn_grid(m * f, 256), 256, 0, s>>>(m * f, f, max_idx, grad_out, grad_src);
   e = cudaGetLastError();
+  return e == cudaSuccess ? DGNN_OK : (int)e;
+}
+
+int dgnn_edgeconv_backward_ordered(int64_t m, int f, const int32_t* col_ptr, const int32_t* row_ind,
+                                   const int32_t* max_idx, const float* grad_out, float* grad_src, void* stream) {
+  if (m < 0 || f <= 0) return DGNN_ERR_SHAPE;
+  if (m > 0x7fffffffLL) return DGNN_ERR_OVERFLOW;
+  if (m == 0) return DGNN_OK;
+  if (!col_ptr || !max_idx || !grad_out || !grad_src) return DGNN_ERR_NULL;   // row_ind may be NULL for a graph without edges
+  k_edgeconv_bwd_ordered<<<dgnn_grid(m * f, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      m, f, col_ptr, row_ind, max_idx, grad_out, grad_src);
+  cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DGNN_OK : (int)e;
 }
 

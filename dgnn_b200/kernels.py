@@ -707,6 +707,26 @@ def edgeconv_backward(grad_out, max_idx):
     return grad_src
 
 
+def edgeconv_backward_ordered(k, src_ind, grad_out, max_idx):
+    """edgeconv_backward with a fixed summation order (bit-reproducible): the in-edges of every source point come
+    from the CSC form of the regular neighbour graph (k entries per destination), built here by csr2csc."""
+    grad_out = _cuda_f32(grad_out, "grad_out")
+    max_idx = _cuda_i32(max_idx, "max_idx")
+    src_ind = _cuda_i32(src_ind, "src_ind")
+    m, f = grad_out.shape
+    if src_ind.numel() != m * int(k):
+        raise RuntimeError("dgnn_b200: src_ind must hold k entries per destination point")
+    dev = grad_out.device
+    with device_guard(dev):
+        row_ptr = torch.arange(0, m * int(k) + 1, max(int(k), 1), dtype=torch.int32, device=dev)[: m + 1] if k > 0 \
+            else torch.zeros(m + 1, dtype=torch.int32, device=dev)
+        col_ptr, row_ind, _ = csr2csc(row_ptr, src_ind, n_cols=m)
+        grad_src = torch.empty((m, f), dtype=torch.float32, device=dev)
+        check(lib().dgnn_edgeconv_backward_ordered(m, f, _p(col_ptr), _p(row_ind), _p(max_idx), _p(grad_out),
+                                                   _p(grad_src), _stream(dev)), "edgeconv_backward_ordered")
+    return grad_src
+
+
 # -------------------------------------------------------------- conversion
 def csr2csc(row_ptr, col_ind, n_cols=None):
     """Returns (col_ptr [same width as row_ptr], row_ind int32, permute int32)."""

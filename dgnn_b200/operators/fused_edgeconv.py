@@ -12,12 +12,17 @@ class FusedEdgeConvFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, k, src_ind, h_src, h_dst):
         out_feat, max_idx = kernels.edgeconv_forward(k, src_ind, h_src, h_dst)  # max_idx stays int32
-        ctx.save_for_backward(max_idx)
+        ctx.save_for_backward(max_idx, src_ind)
+        ctx.k = int(k)
         return out_feat
 
     @staticmethod
     def backward(ctx, grad_out):
-        max_idx = ctx.saved_tensors[0]
+        max_idx, src_ind = ctx.saved_tensors
         grad_out = grad_out.contiguous()
-        grad_src = kernels.edgeconv_backward(grad_out, max_idx)
+        if torch.are_deterministic_algorithms_enabled():
+            # torch.use_deterministic_algorithms(True): the gather over the transposed graph instead of the scatter-add
+            grad_src = kernels.edgeconv_backward_ordered(ctx.k, src_ind, grad_out, max_idx)
+        else:
+            grad_src = kernels.edgeconv_backward(grad_out, max_idx)
         return None, None, grad_src, grad_out

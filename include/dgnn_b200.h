@@ -341,6 +341,13 @@ int dgnn_edgeconv_forward(int64_t m, int f, int k, const int32_t* src_ind,
  * the zero fill is ordered before the scatter. */
 int dgnn_edgeconv_backward(int64_t m, int f, const int32_t* max_idx,
                            const float* grad_out, float* grad_src, void* stream);
+/* The same gradient with a fixed summation order (bit-reproducible; the scatter-add above is not): col_ptr [m+1]
+ * / row_ind = the CSC form of the neighbour graph (dgnn_csr2csc of row_ptr = 0, k, 2k, ... and src_ind), int32.
+ * grad_src[s, j] = sum over the destinations i of s's in-edges, ascending, with max_idx[i, j] == s, of
+ * grad_out[i, j]; a destination that lists s twice counts once.  No counterpart in the reference, whose backward
+ * races (fused_edgeconv_kernel.cu:76-100). */
+int dgnn_edgeconv_backward_ordered(int64_t m, int f, const int32_t* col_ptr, const int32_t* row_ind,
+                                   const int32_t* max_idx, const float* grad_out, float* grad_src, void* stream);
 
 /* ---- format conversion ----------------------------------------------------
  * Stable counting sort of CSR entries by column: col_ptr [n_cols+1] (width

@@ -137,6 +137,37 @@ def test_edgeconv(cuda, m, k, f):
     assert_close(a.grad, orc.edgeconv_backward(go, i_ref), "h_src grad"); assert_equal(b.grad, go, "h_dst grad")
 
 
+@pytest.mark.parametrize("m,k,f", [(300, 20, 64), (1000, 5, 12), (64, 1, 4), (2048, 20, 128)])
+def test_edgeconv_backward_ordered_is_reproducible(cuda, m, k, f):
+    """The gather over the transposed neighbour graph: same gradient as the scatter-add, one fixed summation order
+    (ascending destination, which is also the order of the CPU oracle: bit-equal to it), repeated neighbours in a
+    list counted once, and chosen by the operator under torch.use_deterministic_algorithms(True)."""
+    g = torch.Generator().manual_seed(m + k)
+    src = torch.randint(0, max(m // 8, 1), (m * k,), generator=g, dtype=torch.int32)   # few sources: many ties and repeats
+    hs, hd, go = (torch.randn(m, f, generator=g) for _ in range(3))
+    hs[: m // 16] = 0.5                                                              # equal sums: the first neighbour wins
+    _, i_ref = orc.edgeconv_forward(k, src, hs, hd)
+    want = orc.edgeconv_backward(go, i_ref)
+    _, idx = kernels.edgeconv_forward(k, src.to(cuda), hs.to(cuda), hd.to(cuda))
+    got = kernels.edgeconv_backward_ordered(k, src.to(cuda), go.to(cuda), idx)
+    assert_close(got, want, "ordered grad_src")
+    assert_close(kernels.edgeconv_backward(go.to(cuda), idx), want, "scatter-add grad_src")
+    for _ in range(3):
+        assert_equal(kernels.edgeconv_backward_ordered(k, src.to(cuda), go.to(cuda), idx), got, "repeat of the ordered backward")
+    seq = torch.zeros(m, f)
+    flat = i_ref.long()
+    for i in range(m):                                   # sequential fp32 adds in ascending destination order
+        seq[flat[i], torch.arange(f)] += go[i]
+    assert_equal(got, seq, "ordered grad_src against sequential fp32 adds")
+    a = hs.to(cuda).requires_grad_(); b = hd.to(cuda).requires_grad_()
+    torch.use_deterministic_algorithms(True)
+    try:
+        EdgeConvFuse(k, src.to(cuda), a, b).backward(go.to(cuda))
+    finally:
+        torch.use_deterministic_algorithms(False)
+    assert_equal(a.grad, got, "h_src grad under deterministic algorithms")
+
+
 def test_edgeconv_ties_pick_first_neighbour(cuda):
     hs = torch.zeros(4, 8); hd = torch.zeros(4, 8)
     src = torch.tensor([3, 1, 2, 0, 1, 1, 2, 3], dtype=torch.int32)
