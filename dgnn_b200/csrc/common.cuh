@@ -47,6 +47,17 @@ __device__ __forceinline__ float4 ld4(const float4* p) { return __ldg(p); }
 // re-read by the same SM often enough that caching at the L2 only (ld.global.cg: +2 % on the forward and backward
 // sweeps at R-MAT 2.4 M / 120 M) or L1::no_allocate (+11-14 %) is slower.
 __device__ __forceinline__ float4 ld4_gather(const float4* p) { return __ldg(p); }
+// 32 contiguous bytes per lane in one instruction (the 256-bit global loads and stores of sm_100); p must be
+// 32-byte aligned.  A warp then fetches a 1 KB row with one request instead of two: on the GAT sweeps, whose first
+// limit is the L1TEX data pipe, that is 5-6 % of the forward and the backward sweep.
+__device__ __forceinline__ void ld8_gather(const float4* p, float4& a, float4& b) {
+  asm("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(p));
+}
+__device__ __forceinline__ void st8(float4* p, const float4& a, const float4& b) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               :: "l"(p), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y), "f"(b.z), "f"(b.w) : "memory");
+}
 // Read-only load whose line is the last to leave the L2: for the rows of a gathered tensor that many edges
 // reference (the "hot" rows, see dgnn_hot_rows).  A feature tensor of gigabytes streams through the 126 MB L2;
 // with plain loads the often-referenced rows are evicted by rows that are read once.
@@ -60,6 +71,10 @@ __device__ __forceinline__ float4 ld4_keep(const float4* p, unsigned long long p
   asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(pol));
   return v;
+}
+__device__ __forceinline__ void ld8_keep(const float4* p, float4& a, float4& b, unsigned long long pol) {
+  asm("ld.global.nc.L2::cache_hint.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8], %9;"
+      : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(p), "l"(pol));
 }
 __device__ __forceinline__ float ld1_keep(const float* p, unsigned long long pol) {
   float v;

@@ -703,9 +703,10 @@ inline i64 up4(i64 x) { return (x + 3) & ~i64(3); }
 struct FastShape {
   bool ok;
   int hf4, f4_shift, vpl, lpr;
+  bool wide_ok = true;   // the row tensors of this call are 32-byte aligned (the same-head layout uses 256-bit accesses)
 };
 inline FastShape fast_shape(int h, int f) {
-  FastShape s{false, 0, 0, 0, 32};
+  FastShape s{false, 0, 0, 0, 32, true};
   if (f % 4) return s;
   const int sh = ilog2_exact(f / 4);
   if (sh < 0) return s;
@@ -750,7 +751,8 @@ int launch_fwd_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, int f, const 
 
 // Rows of more than 32 vectors whose heads hold at least VPL vectors use the same-head lane
 // layout (gat_sh.cuh); everything else the plain one.
-inline bool same_head_layout(const FastShape& fs) { return fs.vpl > 1 && (1 << fs.f4_shift) >= fs.vpl; }
+inline bool same_head_layout(const FastShape& fs) { return fs.wide_ok && fs.vpl > 1 && (1 << fs.f4_shift) >= fs.vpl; }
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }
 
 // use_hot selects the kernel variant with the second (evict_last) load path; it exists without a dropout mask only
 template <int VPL, bool MASK, bool FULL, int LPR, bool NEG, class... A>
@@ -896,7 +898,8 @@ int dgnn_gat_forward_staged(int64_t n_rows, int64_t nnz, int h, int f, const voi
   if (attn_drop > 0.f && !edge_mask) return DGNN_ERR_NULL;
   const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const FastShape fs = fast_shape(h, f);
+  FastShape fs = fast_shape(h, f);
+  fs.wide_ok = aligned32(in_feat);   // the gathered tensor; results check their own alignment when they are stored
   if (fs.ok && aligned16(in_feat) && aligned16(out) && aligned16(bias) && aligned16(out_neg)) {
     if (!workspace || workspace_bytes < dgnn_gat_forward_workspace_bytes(n_rows, nnz, h, f))
       return DGNN_ERR_WORKSPACE;
@@ -1070,7 +1073,8 @@ int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, i
   unsigned long long* counter = reinterpret_cast<unsigned long long*>(wsb + L.counter);
   const float* mask = attn_drop > 0.f ? edge_mask : nullptr;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const FastShape fs = fast_shape(h, f);
+  FastShape fs = fast_shape(h, f);
+  fs.wide_ok = aligned32(in_feat) && aligned32(grad_out);
   if (n_cols > 0) {
     if (fs.ok && aligned16(in_feat) && aligned16(grad_out) && aligned16(grad_feat)) {
       int rc;

@@ -16,6 +16,12 @@
 #ifndef DGNN_SH_FWD_BLOCKS
 #define DGNN_SH_FWD_BLOCKS 6
 #endif
+// 1: a lane's vectors come in neighbouring pairs (32 contiguous bytes) that are loaded and stored by one 256-bit
+// instruction each; the tensors the same-head operators touch that way must then be 32-byte aligned (the launcher
+// falls back to the plain layout otherwise).  0: vectors j, j + LPH, ... and 128-bit accesses.
+#ifndef DGNN_LD256
+#define DGNN_LD256 1
+#endif
 #ifndef DGNN_SH_BWD_BLOCKS
 #define DGNN_SH_BWD_BLOCKS 5
 #endif
@@ -39,7 +45,9 @@ struct HeadLanes {
     hd = act ? hl : 0;
     lead = act && j == 0;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) q[v] = (hd << f4_shift) + (v << lph_shift) + j;
+    for (int v = 0; v < VPL; ++v)
+      q[v] = DGNN_LD256 ? (hd << f4_shift) + ((v >> 1) << (lph_shift + 1)) + 2 * j + (v & 1)   // pairs (2j, 2j+1), then + 2*LPH
+                        : (hd << f4_shift) + (v << lph_shift) + j;
   }
 };
 
@@ -53,6 +61,39 @@ __device__ __forceinline__ void lanes_reduce(float (&d)[U], int lph_shift) {
       for (int u = 0; u < U; ++u) d[u] += __shfl_xor_sync(DGNN_FULL, d[u], 1 << s);
     }
   }
+}
+
+// the lane's VPL vectors of one gathered row (zero when !ok); KEEP: with the L2 evict_last policy `pol`
+template <bool KEEP, int VPL>
+__device__ __forceinline__ void load_row(float4 (&x)[VPL], const float4* row, const HeadLanes<VPL>& lm, bool ok,
+                                         unsigned long long pol) {
+#if DGNN_LD256
+#pragma unroll
+  for (int v = 0; v < VPL; v += 2) {
+    if (!ok) { x[v] = zero4(); x[v + 1] = zero4(); }
+    else if (KEEP) ld8_keep(row + lm.q[v], x[v], x[v + 1], pol);
+    else ld8_gather(row + lm.q[v], x[v], x[v + 1]);
+  }
+#else
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) x[v] = !ok ? zero4() : (KEEP ? ld4_keep(row + lm.q[v], pol) : ld4_gather(row + lm.q[v]));
+#endif
+}
+// the lane's vectors of one result row
+template <int VPL>
+__device__ __forceinline__ void store_row(float4* row, const HeadLanes<VPL>& lm, const float4 (&a)[VPL]) {
+#if DGNN_LD256
+  if ((reinterpret_cast<uintptr_t>(row) & 31) == 0) {      // once per row; the same answer for every row of a tensor
+#pragma unroll
+    for (int v = 0; v < VPL; v += 2) st8(row + lm.q[v], a[v], a[v + 1]);
+  } else {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) row[lm.q[v]] = a[v];
+  }
+#else
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) st4_stream(row + lm.q[v], a[v]);
+#endif
 }
 
 // ------------------------------------------------------------------ forward
@@ -132,12 +173,10 @@ struct GatFwdOpSH {
       if (hot_u) {
         const unsigned long long pol = l2_keep_policy();   // made where it is used: no register held across the loop
         s[u] = ok ? ld1_keep(attn_col + cc * H + st.lm.hd, pol) : 0.f;
-#pragma unroll
-        for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4_keep(in_feat + cc * hf4 + st.lm.q[v], pol) : zero4();
+        load_row<true>(x[u], in_feat + cc * hf4, st.lm, ok, pol);
       } else {
         s[u] = ok ? __ldg(attn_col + cc * H + st.lm.hd) : 0.f;
-#pragma unroll
-        for (int v = 0; v < VPL; ++v) x[u][v] = ok ? ld4_gather(in_feat + cc * hf4 + st.lm.q[v]) : zero4();
+        load_row<false>(x[u], in_feat + cc * hf4, st.lm, ok, 0ull);
       }
     }
     float l[U];
@@ -197,20 +236,21 @@ struct GatFwdOpSH {
     if (!last_) { store_partial(st, state + r * slot_stride, lane); return; }
     if (!st.lm.act) return;
     const float sc = st.z > 0.f ? inv_keep / st.z : 0.f;
+    float4 res[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      float4 a = st.acc[v];
-      scale4(a, sc);
-      if (bias) add4(a, __ldg(bias + st.lm.q[v]));
-      st4_stream(out + r * hf4 + st.lm.q[v], a);
+      res[v] = st.acc[v];
+      scale4(res[v], sc);
+      if (bias) add4(res[v], __ldg(bias + st.lm.q[v]));
     }
+    store_row<VPL>(out + r * hf4, st.lm, res);
     if (NEG) {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
-        float4 a = st.accn[v];
-        scale4(a, sc);
-        st4_stream(out_neg + r * hf4 + st.lm.q[v], a);
+        res[v] = st.accn[v];
+        scale4(res[v], sc);
       }
+      store_row<VPL>(out_neg + r * hf4, st.lm, res);
     }
     if (st.lm.lead && edge_max) {
       edge_max[r * H + st.lm.hd] = st.m;
@@ -303,11 +343,9 @@ struct GatBwdOpSH {
     st.lm.init(lane, H, f4_shift);
     st.ac = st.lm.act ? __ldg(attn_col + c * H + st.lm.hd) : 0.f;
     st.gc = 0.f;
+    load_row<false>(st.x, in_feat + c * hf4, st.lm, st.lm.act, 0ull);
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      st.x[v] = st.lm.act ? ld4(in_feat + c * hf4 + st.lm.q[v]) : zero4();
-      st.acc[v] = zero4();
-    }
+    for (int v = 0; v < VPL; ++v) st.acc[v] = zero4();
   }
   __device__ __forceinline__ void resume(State& st, i64 c, int lane, bool first_) const {
     if (!first_) merge_partial(st, state + c * slot_stride, lane);
@@ -335,12 +373,10 @@ struct GatBwdOpSH {
       if (hot_u) {
         const unsigned long long pol = l2_keep_policy();   // made where it is used: no register held across the loop
         pk[u] = ok ? ld4_keep(pack + rr * H + st.lm.hd, pol) : zero4();
-#pragma unroll
-        for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4_keep(grad_out + rr * hf4 + st.lm.q[v], pol) : zero4();
+        load_row<true>(g4[u], grad_out + rr * hf4, st.lm, ok, pol);
       } else {
         pk[u] = ok ? ld4(pack + rr * H + st.lm.hd) : zero4();
-#pragma unroll
-        for (int v = 0; v < VPL; ++v) g4[u][v] = ok ? ld4_gather(grad_out + rr * hf4 + st.lm.q[v]) : zero4();
+        load_row<false>(g4[u], grad_out + rr * hf4, st.lm, ok, 0ull);
       }
     }
 #pragma unroll
@@ -386,8 +422,7 @@ struct GatBwdOpSH {
   __device__ __forceinline__ void finalize(State& st, i64 c, int lane, bool last_) const {
     if (!last_) { store_partial(st, state + c * slot_stride, lane); return; }
     if (!st.lm.act) return;
-#pragma unroll
-    for (int v = 0; v < VPL; ++v) st4_stream(grad_feat + c * hf4 + st.lm.q[v], st.acc[v]);
+    store_row<VPL>(grad_feat + c * hf4, st.lm, st.acc);
     if (st.lm.lead) grad_attn_col[c * H + st.lm.hd] = st.gc;
   }
 

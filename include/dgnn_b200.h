@@ -95,6 +95,10 @@ int dgnn_gat_forward(int64_t n_rows, int64_t nnz, int h, int f,
  * normalised and written out in its last one, and is not touched -- no state read or written -- in any other
  * stage; rows without edges in any stage are written by stage 0.  The output pointers must then be the same
  * valid buffers in every stage.  Without a mask every row takes part in every stage (first / last mark the ends).
+ * Shapes whose heads hold two or more float4 vectors per lane (e.g. 8 heads x 32) gather in_feat with 256-bit loads
+ * when it is 32-byte aligned and with 128-bit loads in another lane layout otherwise; the carried state differs
+ * between the two, so every stage of one sweep must pass an in_feat of the same alignment class (any row of a
+ * 32-byte aligned tensor is: rows are multiples of 32 bytes there).
  * The staged form has no counterpart in the reference, which is single-GPU. */
 int dgnn_gat_fast_shape(int h, int f);   /* 1 when (h, f) uses the float4 layout: f = 4*2^k, h*f <= 1024 */
 size_t dgnn_gat_forward_state_bytes(int64_t n_rows, int h, int f);

@@ -227,3 +227,33 @@ def test_layer_fused_path_equals_composed_path(cuda, residual):
     for k, p in layer.named_parameters():
         scale = max(1.0, float(p.grad.abs().max()))
         assert_close(got[k], p.grad, f"grad {k}", atol=1e-4 * scale)
+
+
+@pytest.mark.parametrize("h,f", [(8, 32), (8, 64), (16, 64)])
+def test_rows_that_are_only_16_byte_aligned(cuda, h, f):
+    """The same-head layout gathers with 256-bit loads and needs 32-byte aligned rows; tensors that start 16 bytes
+    into an allocation take the other lane layout (128-bit accesses) and give the same results."""
+    rp, ci = synth.random_graph(1500, 9, seed=3, long_rows=((5, 2100),))
+    n = rp.numel() - 1
+    rp_d, ci_d = rp.to(cuda), ci.to(cuda)
+    cp, ri, pm = kernels.csr2csc(rp_d, ci_d)
+    g = torch.Generator().manual_seed(h + f)
+    ar, ac = torch.randn(n, h, generator=g).to(cuda), torch.randn(n, h, generator=g).to(cuda)
+    x, go = torch.randn(n, h, f, generator=g).to(cuda), torch.randn(n, h, f, generator=g).to(cuda)
+
+    def shifted(t):                                        # a copy that starts 16 bytes into its allocation
+        buf = torch.empty(t.numel() + 4, dtype=t.dtype, device=t.device)
+        v = buf[4:].view(t.shape)
+        v.copy_(t)
+        assert v.data_ptr() % 32 == 16
+        return v
+
+    base = kernels.gat_forward(ar, ac, rp_d, ci_d, 0.2, x, neg=True)
+    off = kernels.gat_forward(ar, ac, rp_d, ci_d, 0.2, shifted(x), neg=True)
+    for a, b, name in zip(base, off, ("out", "edge_max", "edge_sum", "out_neg", "a_neg")):
+        assert_close(b, a, f"forward {name}, in_feat 16-byte aligned", rtol=1e-5, atol=1e-6)
+    pack, _, _ = kernels.gat_rowstat_full(ar, base[1], base[2], base[0], go, 0.2, out_neg=base[3], a_neg=base[4])
+    b0 = kernels.gat_backward_cols(None, cp, ri, None, pack, None, x, ac, go, 0.2, row_grad=False)
+    b1 = kernels.gat_backward_cols(None, cp, ri, None, pack, None, shifted(x), ac, shifted(go), 0.2, row_grad=False)
+    assert_close(b1[0], b0[0], "grad_feat, 16-byte aligned inputs", rtol=1e-4, atol=1e-5)
+    assert_close(b1[2], b0[2], "grad_attn_col, 16-byte aligned inputs", rtol=1e-4, atol=2e-5)
