@@ -274,48 +274,68 @@ __device__ __forceinline__ bool dgnn_row_role(const Op& op, i64 r, bool& first, 
 // rows.  The batch grows as the average row gets shorter, which keeps the rate of
 // atomics on the one counter far below what the memory system serialises, and the
 // batch's index pointers arrive in one coalesced load.
-// Rows of more than DGNN_HEAVY entries are drawn first (pass 0, from next_row[0], 31 rows per draw of which the
-// light ones are skipped at once), all others afterwards (pass 1, next_row[1]); a warp goes on to pass 1 as soon as
-// pass 0 has no rows left, there is no barrier in between.  A row is one warp's work from its first entry to its last
-// (about 0.4 us per entry in the GAT sweeps), so the last rows to be drawn decide how long the grid idles at its end:
-// with the heavy rows out of the way that is a row of at most DGNN_HEAVY entries instead of one of up to DGNN_SEG.
+// Rows of more than DGNN_HEAVY entries are handled first (pass 0), all others afterwards (pass 1); a warp goes on to
+// pass 1 as soon as pass 0 has no draws left, there is no barrier in between.  A row is one warp's work from its
+// first entry to its last (about 0.4 us per entry in the GAT sweeps), so the last rows to be drawn decide how long
+// the grid idles at its end: with the heavy rows out of the way that is a row of at most DGNN_HEAVY entries instead
+// of one of up to DGNN_SEG.  A draw of pass 0 looks at 31 rows spread evenly over the whole id range (row b, b + nb,
+// b + 2 nb, ...: where heavy rows cluster at some ids, as the low ids of an R-MAT graph, consecutive rows would give
+// one warp dozens of them) and handles the heavy ones; pass 1 draws `batch` consecutive rows and skips the heavy ones.
 #ifndef DGNN_HEAVY_ROWS
 #define DGNN_HEAVY_ROWS 128
 #endif
 constexpr int DGNN_HEAVY = DGNN_HEAVY_ROWS;
+
+template <class Op>
+__device__ __forceinline__ void dgnn_one_row(const Op& op, i64 r, i64 lb, i64 hb, int lane, float4* ring) {
+  bool first, last;
+  if (!dgnn_row_role(op, r, first, last)) return;
+  typename Op::State st;
+  op.init(st, r, lane);
+  op.resume(st, r, lane, first);
+  op.range(st, r, lb, hb, lane, ring);
+  op.combine(st, lane);
+  op.finalize(st, r, lane, last);
+}
+
 template <class Op>
 __global__ void __launch_bounds__(DGNN_ROW_THREADS, Op::MIN_BLOCKS) k_rows(const Op op, unsigned long long* next_row, const int batch) {
   extern __shared__ float4 dgnn_smem4[];
   const int lane = threadIdx.x & 31;
   float4* ring = dgnn_smem4 + (size_t)(threadIdx.x >> 5) * (op.ring_bytes() / 16);
-  for (int pass = 0; pass < 2; ++pass) {
-    const int draw = pass == 0 ? 31 : batch;
-    for (;;) {
-      unsigned long long t = 0;
-      if (lane == 0) t = atomicAdd(next_row + pass, (unsigned long long)draw);
-      const i64 r0 = (i64)__shfl_sync(DGNN_FULL, t, 0);
-      if (r0 >= op.n_rows) break;
-      const int cnt = (int)((op.n_rows - r0 < draw) ? op.n_rows - r0 : draw);
-      const i64 mine = lane <= cnt ? ldp(op.indptr, op.idx_bits, r0 + lane) : 0;
-      const i64 len = __shfl_down_sync(DGNN_FULL, mine, 1) - mine;   // lane i < cnt: length of row r0 + i
-      // long rows belong to the chunk + merge kernels; empty rows of a middle stage keep their carried state
-      const bool take = lane < cnt && len <= DGNN_SEG && ((len > DGNN_HEAVY) == (pass == 0)) && !(op.skip_empty && len == 0);
-      unsigned todo = __ballot_sync(DGNN_FULL, take);
-      while (todo) {
-        const int i = __ffs(todo) - 1;
-        todo &= todo - 1;
-        const i64 r = r0 + i;
-        const i64 lb = __shfl_sync(DGNN_FULL, mine, i);
-        const i64 hb = __shfl_sync(DGNN_FULL, mine, i + 1);
-        bool first, last;
-        if (!dgnn_row_role(op, r, first, last)) continue;
-        typename Op::State st;
-        op.init(st, r, lane);
-        op.resume(st, r, lane, first);
-        op.range(st, r, lb, hb, lane, ring);
-        op.combine(st, lane);
-        op.finalize(st, r, lane, last);
-      }
+  // pass 0: heavy rows, 31 strided rows per draw
+  const i64 nb = (op.n_rows + 30) / 31;
+  for (;;) {
+    unsigned long long t = 0;
+    if (lane == 0) t = atomicAdd(next_row, 1ull);
+    const i64 b = (i64)__shfl_sync(DGNN_FULL, t, 0);
+    if (b >= nb) break;
+    const i64 mine_r = b + (i64)lane * nb;
+    const bool valid = lane < 31 && mine_r < op.n_rows;
+    const i64 lo = valid ? ldp(op.indptr, op.idx_bits, mine_r) : 0;
+    const i64 hi = valid ? ldp(op.indptr, op.idx_bits, mine_r + 1) : 0;
+    unsigned todo = __ballot_sync(DGNN_FULL, valid && hi - lo > DGNN_HEAVY && hi - lo <= DGNN_SEG);
+    while (todo) {
+      const int i = __ffs(todo) - 1;
+      todo &= todo - 1;
+      dgnn_one_row(op, b + (i64)i * nb, __shfl_sync(DGNN_FULL, lo, i), __shfl_sync(DGNN_FULL, hi, i), lane, ring);
+    }
+  }
+  // pass 1: everything else, `batch` consecutive rows per draw
+  for (;;) {
+    unsigned long long t = 0;
+    if (lane == 0) t = atomicAdd(next_row + 1, (unsigned long long)batch);
+    const i64 r0 = (i64)__shfl_sync(DGNN_FULL, t, 0);
+    if (r0 >= op.n_rows) break;
+    const int cnt = (int)((op.n_rows - r0 < batch) ? op.n_rows - r0 : batch);
+    const i64 mine = lane <= cnt ? ldp(op.indptr, op.idx_bits, r0 + lane) : 0;
+    const i64 len = __shfl_down_sync(DGNN_FULL, mine, 1) - mine;   // lane i < cnt: length of row r0 + i
+    // long rows belong to the chunk + merge kernels; empty rows of a middle stage keep their carried state
+    unsigned todo = __ballot_sync(DGNN_FULL, lane < cnt && len <= DGNN_HEAVY && !(op.skip_empty && len == 0));
+    while (todo) {
+      const int i = __ffs(todo) - 1;
+      todo &= todo - 1;
+      dgnn_one_row(op, r0 + i, __shfl_sync(DGNN_FULL, mine, i), __shfl_sync(DGNN_FULL, mine, i + 1), lane, ring);
     }
   }
 }
