@@ -531,8 +531,8 @@ def run_ours(args, rank, world, local):
         line["fused_op"] = {"ms": fwd_ms + bwd_ms, "edges_per_s": nnz / ((fwd_ms + bwd_ms) * 1e-3), "achieved_gbs": tot,
                             "frac_of_peak": tot / peak,
                             "note": "algorithmic bytes count every gathered row in full; 48 % of the gathered rows are served from L2 "
-                                    "(traffic = DRAM bytes), so achieved can exceed the DRAM copy peak; ncu names the L1TEX data pipe "
-                                    "(76-80 % of peak) and instruction issue (66-72 %) as the binding units, not HBM (DRAM 4.5-4.9 TB/s)"}
+                                    "(traffic = DRAM bytes), so achieved can exceed the DRAM copy peak; DRAM runs at 4.5-5.2 TB/s during the sweeps, "
+                                    "whose busiest units under ncu are the issue slots (66-74 %) and the L1TEX data pipe (50-56 %)"}
     if world == 1 and not args.no_cpu_baseline:
         from dgnn_b200.operators.projection import project
         with torch.no_grad():
