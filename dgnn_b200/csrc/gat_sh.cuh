@@ -23,7 +23,7 @@
 #define DGNN_LD256 1
 #endif
 #ifndef DGNN_SH_BWD_BLOCKS
-#define DGNN_SH_BWD_BLOCKS 5
+#define DGNN_SH_BWD_BLOCKS 6
 #endif
 
 template <int VPL> struct Log2;
