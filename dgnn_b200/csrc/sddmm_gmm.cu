@@ -4,6 +4,7 @@
 // long-row splitting as the GAT kernels (common.cuh): the row operand stays in
 // registers, each edge gathers one contiguous H*F row of the column operand.
 #include "common.cuh"
+#include "gat_sh.cuh"   // HeadLanes, lanes_reduce, load_row: the same-head lane layout with 256-bit gathers
 
 namespace {
 
@@ -13,9 +14,10 @@ inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 struct FastShape {
   bool ok;
   int hf4, f4_shift, vpl, lpr;
+  bool same_head = false;   // set per call: heads of at least vpl vectors and 32-byte aligned operands
 };
 inline FastShape fast_shape(int h, int f) {
-  FastShape s{false, 0, 0, 0, 32};
+  FastShape s{false, 0, 0, 0, 32, false};
   if (f % 4) return s;
   const int sh = ilog2_exact(f / 4);
   if (sh < 0) return s;
@@ -87,6 +89,70 @@ struct SddmmOp {
               if (st.lm.lead[v]) out[(base + slot[u]) * H + st.lm.hd[v]] = d[u][v];
           }
         }
+      }
+    }
+  }
+  static constexpr bool STAGED = false;
+  __device__ __forceinline__ void resume(State&, i64, int, bool) const {}
+  __device__ __forceinline__ void combine(State&, int) const {}
+  __device__ __forceinline__ void finalize(State&, i64, int, bool) const {}
+  __device__ __forceinline__ void store_partial(State&, float*, int) const {}
+  __device__ __forceinline__ void merge_partial(State&, const float*, int) const {}
+};
+
+// SDDMM in the same-head lane layout (gat_sh.cuh): a lane's VPL vectors lie in one head and come in neighbouring
+// pairs, so the column operand is gathered with 256-bit loads, the dot product of a head needs log2(lanes per head)
+// shuffles instead of log2(vectors per head) per vector, and every lane computes one head's product per edge.
+// For rows of more than 32 vectors whose heads hold at least VPL vectors, 32-byte aligned operands.
+template <int VPL>
+struct SddmmOpSH {
+  static constexpr int MIN_BLOCKS = VPL <= 2 ? 5 : (VPL == 4 ? 4 : 3);
+  static constexpr bool HAS_PARTIALS = false;
+  i64 n_rows, nnz;
+  const void* indptr;
+  int idx_bits;
+  int H, hf4, f4_shift;
+  float* ws;
+  i64 slot_stride;
+  int skip_empty;
+  const int* col_ind;
+  const float4* a;
+  const float4* b;
+  float* out;
+
+  struct State {
+    HeadLanes<VPL> lm;
+    float4 a[VPL];
+  };
+  __device__ __forceinline__ void init(State& st, i64 r, int lane) const {
+    st.lm.init(lane, H, f4_shift);
+    load_row<false>(st.a, a + r * hf4, st.lm, st.lm.act, 0ull);
+  }
+  __host__ __device__ __forceinline__ int ring_bytes() const { return 0; }
+  __device__ __forceinline__ void range(State& st, i64, i64 e0, i64 e1, int lane, float4*) const {
+    constexpr int U = VPL <= 2 ? 4 : 2;
+    for (i64 base = e0; base < e1; base += 32) {
+      const int cnt = (int)((e1 - base) < 32 ? (e1 - base) : 32);
+      const int my_c = lane < cnt ? __ldg(col_ind + base + lane) : 0;
+      for (int k = 0; k < cnt; k += U) {
+        float4 x[U][VPL];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int c = __shfl_sync(DGNN_FULL, my_c, (k + u) & 31);
+          load_row<false>(x[u], b + (i64)c * hf4, st.lm, k + u < cnt && st.lm.act, 0ull);
+        }
+        float d[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float2 t = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) dot4_acc(t, st.a[v], x[u][v]);
+          d[u] = t.x + t.y;
+        }
+        lanes_reduce<U>(d, st.lm.lph_shift);   // all lanes take part
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (k + u < cnt && st.lm.lead) out[(base + k + u) * H + st.lm.hd] = d[u];
       }
     }
   }
@@ -339,15 +405,23 @@ __global__ void k_gaussian_bp_final(i64 blocks, int kd, const float* part, float
 
 inline i64 gbp_blocks(i64 nnz) { return (nnz + GBP_EDGES_PER_BLOCK - 1) / GBP_EDGES_PER_BLOCK; }
 
-template <int VPL, int LPR>
-int launch_sddmm(const FastShape& fs, i64 n_rows, i64 nnz, int h, const void* row_ptr, int idx_bits,
-                 const int* col_ind, const float* a, const float* b, float* out, void* ws, cudaStream_t s) {
-  SddmmOp<VPL, LPR> op;
+template <class Op>
+int launch_sddmm_op(const FastShape& fs, i64 n_rows, i64 nnz, int h, const void* row_ptr, int idx_bits,
+                    const int* col_ind, const float* a, const float* b, float* out, void* ws, cudaStream_t s) {
+  Op op;
   op.ws = nullptr; op.slot_stride = 0; op.skip_empty = 1;
   op.n_rows = n_rows; op.nnz = nnz; op.indptr = row_ptr; op.idx_bits = idx_bits;
   op.H = h; op.hf4 = fs.hf4; op.f4_shift = fs.f4_shift; op.col_ind = col_ind;
   op.a = reinterpret_cast<const float4*>(a); op.b = reinterpret_cast<const float4*>(b); op.out = out;
   return dgnn_launch_trio(op, reinterpret_cast<unsigned long long*>(ws), s);
+}
+
+template <int VPL, int LPR, class... A>
+int launch_sddmm(const FastShape& fs, A... args) {
+  if constexpr (VPL > 1 && DGNN_LD256) {
+    if (fs.same_head) return launch_sddmm_op<SddmmOpSH<VPL>>(fs, args...);
+  }
+  return launch_sddmm_op<SddmmOp<VPL, LPR>>(fs, args...);
 }
 
 template <int VPL, int LPR>
@@ -379,7 +453,9 @@ int dgnn_mhsddmm(int64_t n_rows, int64_t nnz, int h, int f, const void* row_ptr,
   if (n_rows == 0 || nnz == 0) return DGNN_OK;
   if (!row_ptr || !col_ind || !a || !b || !out) return DGNN_ERR_NULL;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const FastShape fs = fast_shape(h, f);
+  FastShape fs = fast_shape(h, f);
+  fs.same_head = fs.ok && fs.vpl > 1 && (1 << fs.f4_shift) >= fs.vpl &&
+                 ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 31) == 0;
   if (fs.ok && aligned16(a) && aligned16(b)) {
     if (!workspace || workspace_bytes < DGNN_WS_HEADER) return DGNN_ERR_WORKSPACE;
 #define SD_ARGS fs, n_rows, nnz, h, row_ptr, idx_bits, col_ind, a, b, out, workspace, s
