@@ -181,7 +181,9 @@ int dgnn_gat_backward_cols(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, i
  * grad_feat / grad_attn_col are written by the last call, grad_attn_row (of the block's
  * rows, unless NULL) by every call.  first = last = 1 is dgnn_gat_backward_cols.  stage_mask / stage: as for
  * dgnn_gat_forward_staged, one byte per column.  hot_rows: as hot_cols there, one bit per destination row (from
- * dgnn_hot_rows on the CSR row pointer): the grad_out / pack rows that stay in the L2. */
+ * dgnn_hot_rows on the CSR row pointer): the grad_out / pack rows that stay in the L2.  As in the forward, the lane
+ * layout (and with it the carried state) depends on whether in_feat and grad_out are 32-byte aligned: every stage of
+ * one sweep must pass tensors of the same alignment class. */
 size_t dgnn_gat_backward_state_bytes(int64_t n_cols, int h, int f);
 int dgnn_gat_backward_cols_staged(int64_t n_rows, int64_t n_cols, int64_t nnz, int h, int f,
                                   const void* row_ptr, const void* col_ptr, int idx_bits,
